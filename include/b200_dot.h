@@ -1,0 +1,160 @@
+/*
+ * b200_dot.h — C-ABI of the `b200_dot` backend extension: the launch interface of the
+ * hand-written sm_100a kernels that execute one `tt.dot` tile-GEMM K-loop
+ * (main body + LoopSplit-peeled remainder, fp32 accumulate, fused scale/cast epilogue).
+ *
+ * What it replaces in the reference (triton-lang/triton-ext):
+ *   - backend/CMakeLists.txt (0 bytes): the reference's `backend/` extension slot is empty; this
+ *     library is what fills it.
+ *   - The contraction itself is the `tl.dot` call sites of
+ *     pass/LoopSplit/06-fused-attention.py:63,85,115,135 (fp32 accumulator created at :222) and the
+ *     scale/cast epilogue idioms of :66,78,237,240 — in the reference they are lowered by upstream
+ *     Triton's NVIDIA backend (GPU) or by Triton's interpreter (CPU, `create_dot`).
+ *   - The main/tail split of the K loop is the loop pair produced by
+ *     pass/LoopSplit/LoopSplit.cpp:179-193; here it is executed inside one kernel.
+ *
+ * Plain C, plain pointers and sizes; no torch or MLIR types cross this boundary.
+ * Every entry point returns a tx_dot_status; tx_dot_last_error() gives the text for the calling thread.
+ * There is no CPU fallback: without a CUDA device every compute entry point returns
+ * TXD_ERR_NO_DEVICE.
+ */
+#ifndef B200_DOT_H
+#define B200_DOT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define TXD_API
+#else
+#define TXD_API __attribute__((visibility("default")))
+#endif
+
+typedef enum tx_dot_status {
+  TXD_OK = 0,
+  TXD_ERR_INVALID = 1,        /* bad argument (null pointer, non-positive extent, misaligned pointer) */
+  TXD_ERR_UNSUPPORTED = 2,    /* legal tt.dot, but outside what the kernels cover (see message) */
+  TXD_ERR_CUDA = 3,           /* a CUDA runtime / driver call failed */
+  TXD_ERR_DEVICE_TIMEOUT = 4, /* a bounded device-side wait ran out; output is undefined */
+  TXD_ERR_NO_DEVICE = 5       /* no CUDA device / driver available */
+} tx_dot_status;
+
+/* Element types. Operands of one tt.dot share a type (Triton's semantic.dot rule). */
+typedef enum tx_dot_dtype {
+  TXD_F16 = 0,
+  TXD_BF16 = 1,
+  TXD_F8E4M3 = 2,
+  TXD_F32 = 3, /* output only */
+  TXD_F8E5M2 = 4
+} tx_dot_dtype;
+
+typedef enum tx_dot_layout {
+  TXD_ROW_MAJOR = 0, /* A[m,k] at a[m*lda+k];  B[k,n] at b[k*ldb+n] */
+  TXD_COL_MAJOR = 1  /* A[m,k] at a[k*lda+m];  B[k,n] at b[n*ldb+k] */
+} tx_dot_layout;
+
+typedef enum tx_dot_schedule {
+  TXD_SCHED_AUTO = 0,
+  TXD_SCHED_DATA_PARALLEL = 1, /* persistent CTAs, whole output tiles */
+  TXD_SCHED_STREAM_K = 2       /* persistent CTAs, equal shares of the (tile, k-block) space; partial
+                                  tiles are combined through plan-owned scratch memory */
+} tx_dot_schedule;
+
+/* C[m,n] = cast( alpha * row_scale[m] * col_scale[n] * sum_k A[m,k]*B[k,n] ), fp32 accumulate.
+ * C is always row-major with leading dimension ldc. */
+typedef struct tx_dot_problem {
+  int32_t m, n, k;
+  int32_t ab_dtype;      /* tx_dot_dtype of A and B */
+  int32_t out_dtype;     /* tx_dot_dtype of C: F16, BF16 or F32 */
+  int32_t a_layout;      /* tx_dot_layout */
+  int32_t b_layout;      /* tx_dot_layout */
+  int32_t has_row_scale; /* run() takes a float[m] multiplied into row m  */
+  int32_t has_col_scale; /* run() takes a float[n] multiplied into column n */
+  int64_t lda, ldb, ldc; /* leading dimensions in elements */
+  float alpha;           /* scalar scale of the accumulator (1.0f for a plain dot) */
+} tx_dot_problem;
+
+/* Kernel configuration. Zero in a field = let the arithmetic-intensity analysis choose. */
+typedef struct tx_dot_config {
+  int32_t block_n;       /* MMA N extent per tile: 16, 32, 64, 128 or 256 */
+  int32_t stages;        /* depth of the TMA shared-memory ring (2..12) */
+  int32_t swap_ab;       /* 1 = compute C^T = B^T A^T (skinny m), 2 = never swap, 0 = auto */
+  int32_t schedule;      /* tx_dot_schedule */
+  int32_t group_m;       /* tile-raster group height (tiles) for L2 reuse */
+  int32_t max_ctas;      /* cap on the persistent grid (0 = number of SMs) */
+  int32_t k_split_point; /* LoopSplit mid point of the K loop in elements; 0 = floor(K/BK)*BK,
+                            negative = split at 0 (the whole loop runs as the masked remainder).
+                            Must be a multiple of BLOCK_K and <= K. Iterations below it run
+                            unpredicated; the rest run as the masked remainder. */
+  int32_t reserved;
+} tx_dot_config;
+
+/* What a plan decided; filled by tx_dot_plan_query. */
+typedef struct tx_dot_plan_info {
+  int32_t block_m, block_n, block_k;
+  int32_t stages;
+  int32_t swap_ab;
+  int32_t schedule;
+  int32_t group_m;
+  int32_t grid;            /* CTAs launched */
+  int32_t k_main_iters;    /* unpredicated K iterations: [0, k_split_point) */
+  int32_t k_tail_iters;    /* masked remainder iterations: [k_split_point, K) */
+  int32_t k_tail_mmas;     /* tcgen05.mma instructions issued by the last remainder iteration */
+  int32_t smem_bytes;      /* dynamic shared memory per CTA */
+  int32_t tmem_columns;    /* TMEM columns allocated per CTA */
+  int32_t reserved;
+  int64_t scratch_bytes;   /* plan-owned global scratch (stream-K partial tiles + counters) */
+  double flops;            /* 2*m*n*k */
+  double algorithmic_bytes;/* read A once + read B once + write C once (+ scales) */
+} tx_dot_plan_info;
+
+typedef struct tx_dot_plan tx_dot_plan; /* opaque */
+
+/* Number of CUDA devices visible, 0 if none (never fails). */
+TXD_API int tx_dot_device_count(void);
+
+/* Text of the last error raised on the calling thread ("" if none). Borrowed pointer. */
+TXD_API const char *tx_dot_last_error(void);
+
+/* Validate the problem, run the tile-selection analysis for unset config fields, and allocate
+ * plan-owned scratch on the current device. `cfg` may be NULL. Needs a CUDA device. */
+TXD_API int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg,
+                               tx_dot_plan **out_plan);
+
+/* Same analysis without touching a device: fills `info` for (problem, cfg) assuming `sm_count` SMs.
+ * Usable on a machine with no GPU. */
+TXD_API int tx_dot_plan_preview(const tx_dot_problem *problem, const tx_dot_config *cfg,
+                                int32_t sm_count, tx_dot_plan_info *info);
+
+TXD_API int tx_dot_plan_query(const tx_dot_plan *plan, tx_dot_plan_info *info);
+
+/* Launch on `stream` (a cudaStream_t; NULL = default stream). All pointers are device pointers,
+ * 16-byte aligned. row_scale / col_scale must be non-NULL exactly when the plan asked for them.
+ * Asynchronous: returns after the launch. Device-side waits are bounded; a wait that runs out is
+ * reported by tx_dot_plan_check(). */
+TXD_API int tx_dot_run(tx_dot_plan *plan, const void *a, const void *b, void *c,
+                       const float *row_scale, const float *col_scale, void *stream);
+
+/* Synchronise `stream` and report TXD_ERR_DEVICE_TIMEOUT if any launch of this plan since the last
+ * check gave up on a wait. */
+TXD_API int tx_dot_plan_check(tx_dot_plan *plan, void *stream);
+
+/* The same contraction from HOST buffers: copies A, B (and scales) to plan-owned device buffers,
+ * launches, copies C back and synchronises. This is the call a host-side user of the extension
+ * makes; it is what the end-to-end figure of the benchmark times. Pinned host memory is used as-is. */
+TXD_API int tx_dot_run_host(tx_dot_plan *plan, const void *a_host, const void *b_host, void *c_host,
+                            const float *row_scale_host, const float *col_scale_host);
+
+TXD_API int tx_dot_plan_destroy(tx_dot_plan *plan);
+
+/* Kernels this library has launched in this process since load (for launch accounting). */
+TXD_API uint64_t tx_dot_kernel_launches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_DOT_H */

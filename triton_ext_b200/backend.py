@@ -1,0 +1,266 @@
+"""ctypes binding of the `b200_dot` backend extension (include/b200_dot.h).
+
+This is the host-side mirror of what a `tl.dot` call means in the reference's only kernels
+(pass/LoopSplit/06-fused-attention.py:63,85 — `tl.dot(a, b)` / `tl.dot(a, b, acc)` with an fp32
+accumulator, followed by the scale and cast idioms of :66,78,237,240): one call computes
+``cast(alpha * row_scale[:, None] * col_scale[None, :] * (A @ B))`` with fp32 accumulation.
+
+torch is used for device memory and streams only. There is no fallback: if the shared library is
+missing or no B200 is present the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+_LIB_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
+_LIB_PATH = os.path.join(_LIB_DIR, "libb200_dot.so")
+
+TXD_OK = 0
+TXD_ERR_INVALID = 1
+TXD_ERR_UNSUPPORTED = 2
+TXD_ERR_CUDA = 3
+TXD_ERR_DEVICE_TIMEOUT = 4
+TXD_ERR_NO_DEVICE = 5
+
+TXD_F16, TXD_BF16, TXD_F8E4M3, TXD_F32, TXD_F8E5M2 = 0, 1, 2, 3, 4
+TXD_ROW_MAJOR, TXD_COL_MAJOR = 0, 1
+TXD_SCHED_AUTO, TXD_SCHED_DATA_PARALLEL, TXD_SCHED_STREAM_K = 0, 1, 2
+
+_DTYPES = {
+    torch.float16: TXD_F16,
+    torch.bfloat16: TXD_BF16,
+    torch.float8_e4m3fn: TXD_F8E4M3,
+    torch.float32: TXD_F32,
+    torch.float8_e5m2: TXD_F8E5M2,
+}
+
+
+class DotError(RuntimeError):
+    """A b200_dot entry point returned a non-zero tx_dot_status."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"b200_dot status {status}: {message}")
+        self.status = status
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [
+        ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
+        ("ab_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+        ("a_layout", ctypes.c_int32), ("b_layout", ctypes.c_int32),
+        ("has_row_scale", ctypes.c_int32), ("has_col_scale", ctypes.c_int32),
+        ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
+        ("alpha", ctypes.c_float),
+    ]
+
+
+class Config(ctypes.Structure):
+    _fields_ = [
+        ("block_n", ctypes.c_int32), ("stages", ctypes.c_int32), ("swap_ab", ctypes.c_int32),
+        ("schedule", ctypes.c_int32), ("group_m", ctypes.c_int32), ("max_ctas", ctypes.c_int32),
+        ("k_split_point", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
+class PlanInfo(ctypes.Structure):
+    _fields_ = [
+        ("block_m", ctypes.c_int32), ("block_n", ctypes.c_int32), ("block_k", ctypes.c_int32),
+        ("stages", ctypes.c_int32), ("swap_ab", ctypes.c_int32), ("schedule", ctypes.c_int32),
+        ("group_m", ctypes.c_int32), ("grid", ctypes.c_int32),
+        ("k_main_iters", ctypes.c_int32), ("k_tail_iters", ctypes.c_int32),
+        ("k_tail_mmas", ctypes.c_int32), ("smem_bytes", ctypes.c_int32),
+        ("tmem_columns", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("scratch_bytes", ctypes.c_int64), ("flops", ctypes.c_double),
+        ("algorithmic_bytes", ctypes.c_double),
+    ]
+
+    def as_dict(self) -> dict:
+        return {name: getattr(self, name) for name, _ in self._fields_ if name != "reserved"}
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """dlopen libb200_dot.so from the package's lib/ directory (built by __graft_entry__.build())."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build the CUDA extension first "
+            "(python -c 'import __graft_entry__ as g; g.build()'); there is no CPU fallback")
+    lib = ctypes.CDLL(_LIB_PATH)
+    vp, i32, f32p = ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p
+    lib.tx_dot_device_count.restype = ctypes.c_int
+    lib.tx_dot_last_error.restype = ctypes.c_char_p
+    lib.tx_dot_kernel_launches.restype = ctypes.c_uint64
+    lib.tx_dot_plan_create.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config), ctypes.POINTER(vp)]
+    lib.tx_dot_plan_preview.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config), i32, ctypes.POINTER(PlanInfo)]
+    lib.tx_dot_plan_query.argtypes = [vp, ctypes.POINTER(PlanInfo)]
+    lib.tx_dot_run.argtypes = [vp, vp, vp, vp, f32p, f32p, vp]
+    lib.tx_dot_plan_check.argtypes = [vp, vp]
+    lib.tx_dot_run_host.argtypes = [vp, vp, vp, vp, f32p, f32p]
+    lib.tx_dot_plan_destroy.argtypes = [vp]
+    for name in ("tx_dot_plan_create", "tx_dot_plan_preview", "tx_dot_plan_query", "tx_dot_run",
+                 "tx_dot_plan_check", "tx_dot_run_host", "tx_dot_plan_destroy"):
+        getattr(lib, name).restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+def _check(rc: int) -> None:
+    if rc != TXD_OK:
+        raise DotError(rc, load_library().tx_dot_last_error().decode())
+
+
+def kernel_launches() -> int:
+    return int(load_library().tx_dot_kernel_launches())
+
+
+def _layout_and_ld(t: torch.Tensor, name: str) -> tuple[int, int]:
+    """(layout, leading dimension) of a 2-D tensor addressed as [rows, cols]."""
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D")
+    rows, cols = t.shape
+    s0, s1 = t.stride()
+    if s1 == 1 or cols == 1:
+        return TXD_ROW_MAJOR, max(s0 if rows > 1 else cols, cols, 1)
+    if s0 == 1 or rows == 1:
+        return TXD_COL_MAJOR, max(s1 if cols > 1 else rows, rows, 1)
+    raise ValueError(f"{name} must have a unit stride in one dimension (strides {t.stride()})")
+
+
+def make_problem(m: int, n: int, k: int, ab_dtype: torch.dtype, out_dtype: torch.dtype, *,
+                 a_layout: int = TXD_ROW_MAJOR, b_layout: int = TXD_ROW_MAJOR,
+                 lda: Optional[int] = None, ldb: Optional[int] = None, ldc: Optional[int] = None,
+                 row_scale: bool = False, col_scale: bool = False, alpha: float = 1.0) -> Problem:
+    pr = Problem()
+    pr.m, pr.n, pr.k = m, n, k
+    pr.ab_dtype, pr.out_dtype = _DTYPES[ab_dtype], _DTYPES[out_dtype]
+    pr.a_layout, pr.b_layout = a_layout, b_layout
+    pr.lda = lda if lda is not None else (k if a_layout == TXD_ROW_MAJOR else m)
+    pr.ldb = ldb if ldb is not None else (n if b_layout == TXD_ROW_MAJOR else k)
+    pr.ldc = ldc if ldc is not None else n
+    pr.has_row_scale, pr.has_col_scale = int(row_scale), int(col_scale)
+    pr.alpha = alpha
+    return pr
+
+
+def make_config(**kw) -> Config:
+    cfg = Config()
+    for key, val in kw.items():
+        if not hasattr(cfg, key):
+            raise TypeError(f"unknown tx_dot_config field {key!r}")
+        setattr(cfg, key, int(val))
+    return cfg
+
+
+def preview(problem: Problem, config: Optional[Config] = None, sm_count: int = 148) -> dict:
+    """Tile-selection result for a problem without touching a GPU."""
+    info = PlanInfo()
+    _check(load_library().tx_dot_plan_preview(ctypes.byref(problem), ctypes.byref(config) if config else None,
+                                              sm_count, ctypes.byref(info)))
+    return info.as_dict()
+
+
+class DotPlan:
+    """Owns one tx_dot_plan. Create once per (shape, dtype, layout); run many times."""
+
+    def __init__(self, problem: Problem, config: Optional[Config] = None):
+        lib = load_library()
+        self._lib = lib
+        self.problem = problem
+        handle = ctypes.c_void_p()
+        _check(lib.tx_dot_plan_create(ctypes.byref(problem), ctypes.byref(config) if config else None,
+                                      ctypes.byref(handle)))
+        self._h = handle
+        info = PlanInfo()
+        _check(lib.tx_dot_plan_query(self._h, ctypes.byref(info)))
+        self.info = info.as_dict()
+
+    def run(self, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
+            row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None,
+            stream: Optional[torch.cuda.Stream] = None) -> None:
+        s = stream if stream is not None else torch.cuda.current_stream(c.device)
+        _check(self._lib.tx_dot_run(
+            self._h, a.data_ptr(), b.data_ptr(), c.data_ptr(),
+            row_scale.data_ptr() if row_scale is not None else None,
+            col_scale.data_ptr() if col_scale is not None else None,
+            ctypes.c_void_p(s.cuda_stream)))
+
+    def check(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        s = stream if stream is not None else torch.cuda.current_stream()
+        _check(self._lib.tx_dot_plan_check(self._h, ctypes.c_void_p(s.cuda_stream)))
+
+    def run_host(self, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
+                 row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None) -> None:
+        """Host buffers in, host buffer out (copies inside); synchronous."""
+        for t in (a, b, c, row_scale, col_scale):
+            if t is not None and t.is_cuda:
+                raise ValueError("run_host takes CPU tensors")
+        _check(self._lib.tx_dot_run_host(
+            self._h, a.data_ptr(), b.data_ptr(), c.data_ptr(),
+            row_scale.data_ptr() if row_scale is not None else None,
+            col_scale.data_ptr() if col_scale is not None else None))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.tx_dot_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_plan_cache: dict = {}
+
+
+def dot(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+        out_dtype: Optional[torch.dtype] = None, row_scale: Optional[torch.Tensor] = None,
+        col_scale: Optional[torch.Tensor] = None, alpha: float = 1.0,
+        config: Optional[Config] = None, check: bool = False) -> torch.Tensor:
+    """C = cast(alpha * row_scale[:,None] * col_scale[None,:] * (A @ B)), fp32 accumulate, on the GPU.
+
+    `a` is [M, K], `b` is [K, N]; either may be a transposed view (unit stride in one dimension).
+    Default output dtype: the operand dtype for f16/bf16, bf16 for fp8 operands.
+    """
+    if not (a.is_cuda and b.is_cuda):
+        raise ValueError("dot() takes CUDA tensors; there is no CPU path")
+    if a.dtype != b.dtype:
+        raise TypeError(f"tt.dot operands must share a dtype, got {a.dtype} and {b.dtype}")
+    m, k = a.shape
+    k2, n = b.shape
+    if k != k2:
+        raise ValueError(f"shape mismatch: A is {tuple(a.shape)}, B is {tuple(b.shape)}")
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else (a.dtype if a.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16)
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if out.stride(1) != 1 and n > 1:
+        raise ValueError("out must be row-major")
+    a_layout, lda = _layout_and_ld(a, "a")
+    b_layout, ldb = _layout_and_ld(b, "b")
+    ldc = max(out.stride(0), n) if m > 1 else n
+    key = (m, n, k, a.dtype, out_dtype, a_layout, b_layout, lda, ldb, ldc, row_scale is not None,
+           col_scale is not None, float(alpha), bytes(config) if config is not None else None, a.device.index)
+    plan = _plan_cache.get(key)
+    if plan is None:
+        with torch.cuda.device(a.device):
+            pr = make_problem(m, n, k, a.dtype, out_dtype, a_layout=a_layout, b_layout=b_layout, lda=lda, ldb=ldb,
+                              ldc=ldc, row_scale=row_scale is not None, col_scale=col_scale is not None, alpha=alpha)
+            plan = DotPlan(pr, config)
+        _plan_cache[key] = plan
+    with torch.cuda.device(a.device):
+        plan.run(a, b, out, row_scale, col_scale)
+        if check:
+            plan.check()
+    return out

@@ -1,0 +1,458 @@
+// Host side of the `b200_dot` backend extension: plan creation (tile selection, TMA descriptors,
+// tcgen05 descriptors, scratch) and launch of the sm_100a kernel, behind the C-ABI of b200_dot.h.
+//
+// There is no CPU path in this file: without a CUDA device every compute entry point fails with
+// TXD_ERR_NO_DEVICE.
+#include "b200_dot.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "dot_tile_model.h"
+#include "dot_umma_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define TXD_CUDA(expr)                                                                     \
+  do {                                                                                     \
+    cudaError_t e_ = (expr);                                                               \
+    if (e_ != cudaSuccess)                                                                 \
+      return fail(TXD_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_));           \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+__global__ void dot_zero_fill_kernel(void *out, long long ldo, int rows, int cols, int elem_bytes) {
+  // K == 0: the accumulator of an empty K loop is zero, and so is every scaled/cast result.
+  const long long n = static_cast<long long>(rows) * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols, c = i - r * cols;
+    unsigned char *dst = static_cast<unsigned char *>(out) + (r * ldo + c) * elem_bytes;
+    for (int b = 0; b < elem_bytes; ++b) dst[b] = 0;
+  }
+}
+
+struct MapKey {
+  const void *ptr = nullptr;
+  CUtensorMap map;
+};
+
+}  // namespace
+
+struct tx_dot_plan {
+  tx_dot_problem problem;
+  txd::TileChoice tc;
+  txd::DotParams base;  // everything except pointers and tensor maps
+  int device = 0;
+  int sm_count = 0;
+  void *scratch = nullptr;      // partials, then counters
+  uint32_t *status = nullptr;   // device status word
+  MapKey p_cache, q_cache;
+  // host-buffer path
+  cudaStream_t host_stream = nullptr;
+  void *dev_a = nullptr, *dev_b = nullptr, *dev_c = nullptr;
+  float *dev_rs = nullptr, *dev_cs = nullptr;
+  size_t a_bytes = 0, b_bytes = 0, c_bytes = 0;
+};
+
+namespace {
+
+int validate(const tx_dot_problem &pr) {
+  if (pr.m < 0 || pr.n < 0 || pr.k < 0) return fail(TXD_ERR_INVALID, "negative extent m=%d n=%d k=%d", pr.m, pr.n, pr.k);
+  const int es = txd::elem_bytes(pr.ab_dtype);
+  if (pr.ab_dtype == TXD_F32 || (es != 1 && es != 2))
+    return fail(TXD_ERR_UNSUPPORTED, "operand dtype %d: tt.dot operands must be f16, bf16, f8e4m3 or f8e5m2", pr.ab_dtype);
+  if (pr.out_dtype != TXD_F16 && pr.out_dtype != TXD_BF16 && pr.out_dtype != TXD_F32)
+    return fail(TXD_ERR_UNSUPPORTED, "output dtype %d: must be f16, bf16 or f32", pr.out_dtype);
+  if ((pr.a_layout != TXD_ROW_MAJOR && pr.a_layout != TXD_COL_MAJOR) ||
+      (pr.b_layout != TXD_ROW_MAJOR && pr.b_layout != TXD_COL_MAJOR))
+    return fail(TXD_ERR_INVALID, "layout must be TXD_ROW_MAJOR or TXD_COL_MAJOR");
+  const long long a_min = pr.a_layout == TXD_ROW_MAJOR ? pr.k : pr.m;
+  const long long b_min = pr.b_layout == TXD_ROW_MAJOR ? pr.n : pr.k;
+  if (pr.lda < a_min || pr.ldb < b_min || pr.ldc < pr.n)
+    return fail(TXD_ERR_INVALID, "leading dimension smaller than the row length (lda=%lld ldb=%lld ldc=%lld)",
+                (long long)pr.lda, (long long)pr.ldb, (long long)pr.ldc);
+  // TMA: every global stride is a multiple of 16 bytes.
+  if ((pr.lda * es) % 16 != 0 || (pr.ldb * es) % 16 != 0)
+    return fail(TXD_ERR_UNSUPPORTED,
+                "lda and ldb must be multiples of %d elements (TMA needs 16-byte row strides); pad the operands",
+                16 / es);
+  return TXD_OK;
+}
+
+void fill_info(const tx_dot_problem &pr, const txd::TileChoice &tc, tx_dot_plan_info *info) {
+  memset(info, 0, sizeof *info);
+  info->block_m = tc.block_m;
+  info->block_n = tc.block_n;
+  info->block_k = tc.block_k;
+  info->stages = tc.stages;
+  info->swap_ab = tc.swap_ab;
+  info->schedule = tc.schedule;
+  info->group_m = tc.group_m;
+  info->grid = tc.grid;
+  info->k_main_iters = tc.k_main_blocks;
+  info->k_tail_iters = tc.k_blocks - tc.k_main_blocks;
+  info->k_tail_mmas = tc.tail_mmas;
+  info->smem_bytes = tc.smem_bytes;
+  info->tmem_columns = tc.tmem_cols;
+  info->scratch_bytes = tc.scratch_bytes;
+  info->flops = 2.0 * pr.m * pr.n * pr.k;
+  info->algorithmic_bytes = txd::algorithmic_bytes(pr);
+}
+
+uint32_t make_idesc(int ab_dtype, bool p_mn, bool q_mn, int block_n) {
+  uint32_t fmt = 0;
+  if (ab_dtype == TXD_BF16) fmt = 1;        // kind::f16: 0 = f16, 1 = bf16
+  if (ab_dtype == TXD_F8E4M3) fmt = 0;      // kind::f8f6f4: 0 = e4m3, 1 = e5m2
+  if (ab_dtype == TXD_F8E5M2) fmt = 1;
+  uint32_t d = 0;
+  d |= 1u << 4;                              // accumulator format: f32
+  d |= fmt << 7;                             // A format
+  d |= fmt << 10;                            // B format
+  d |= (p_mn ? 1u : 0u) << 15;               // A is MN-major
+  d |= (q_mn ? 1u : 0u) << 16;               // B is MN-major
+  d |= static_cast<uint32_t>(block_n >> 3) << 17;
+  d |= static_cast<uint32_t>(txd::kBlockM >> 4) << 24;
+  return d;
+}
+
+// Shared-memory matrix descriptor pieces for a SWIZZLE_128B operand stage.
+void make_smem_desc(bool mn_major, int bk_elems, int umma_k, uint32_t *hi, uint32_t *lbo, uint32_t *kstep) {
+  // 8 rows (K-major) or 8 K-slices (MN-major) of 128 bytes form one 1024-byte swizzle atom.
+  const uint32_t sbo_bytes = 1024;
+  // MN-major: consecutive 128-byte-wide boxes along the row index are bk_elems*128 bytes apart.
+  const uint32_t lbo_bytes = mn_major ? static_cast<uint32_t>(bk_elems) * 128u : 16u;
+  *hi = ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) /* descriptor version for sm_100 */ |
+        (2u << 29) /* SWIZZLE_128B */;
+  *lbo = ((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  // Start-address step per MMA: 32 bytes along K (K-major) or umma_k 128-byte slices (MN-major).
+  *kstep = mn_major ? static_cast<uint32_t>(umma_k) * 128u / 16u : 2u;
+}
+
+int encode_operand_map(CUtensorMap *map, const void *ptr, int dtype, bool mn_major, long long rows,
+                       long long k, long long ld, int tile_rows, int bk_elems) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  const int es = txd::elem_bytes(dtype);
+  CUtensorMapDataType dt = es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : (dtype == TXD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  cuuint64_t dims[2], strides[1];
+  cuuint32_t box[2], estr[2] = {1, 1};
+  if (!mn_major) {
+    dims[0] = static_cast<cuuint64_t>(k);       // contiguous: K
+    dims[1] = static_cast<cuuint64_t>(rows);
+    box[0] = static_cast<cuuint32_t>(bk_elems);
+    box[1] = static_cast<cuuint32_t>(tile_rows);
+  } else {
+    dims[0] = static_cast<cuuint64_t>(rows);    // contiguous: the row (M or N) index
+    dims[1] = static_cast<cuuint64_t>(k);
+    box[0] = static_cast<cuuint32_t>(128 / es);
+    box[1] = static_cast<cuuint32_t>(bk_elems);
+  }
+  strides[0] = static_cast<cuuint64_t>(ld) * es;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(TXD_ERR_INVALID, "operand pointer %p is not 16-byte aligned", ptr);
+  CUresult r = enc(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, stride %llu, box %u x %u)",
+                (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)strides[0], box[0], box[1]);
+  return TXD_OK;
+}
+
+int build_plan_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg, int sm_count, txd::TileChoice &tc) {
+  txd::MachineModel mm;
+  mm.sm_count = sm_count;
+  const char *why = "";
+  if (txd::select_tiles(pr, cfg, mm, tc, &why) != 0) return fail(TXD_ERR_INVALID, "tile selection: %s", why);
+  return TXD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tx_dot_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+const char *tx_dot_last_error(void) { return g_last_error.c_str(); }
+
+uint64_t tx_dot_kernel_launches(void) { return g_launches.load(); }
+
+int tx_dot_plan_preview(const tx_dot_problem *problem, const tx_dot_config *cfg, int32_t sm_count,
+                        tx_dot_plan_info *info) {
+  if (!problem || !info) return fail(TXD_ERR_INVALID, "null argument");
+  int rc = validate(*problem);
+  if (rc) return rc;
+  if (sm_count <= 0) sm_count = 148;
+  txd::TileChoice tc;
+  if (problem->m == 0 || problem->n == 0 || problem->k == 0) {
+    memset(info, 0, sizeof *info);
+    return TXD_OK;
+  }
+  rc = build_plan_tiles(*problem, cfg, sm_count, tc);
+  if (rc) return rc;
+  fill_info(*problem, tc, info);
+  return TXD_OK;
+}
+
+int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, tx_dot_plan **out_plan) {
+  if (!problem || !out_plan) return fail(TXD_ERR_INVALID, "null argument");
+  *out_plan = nullptr;
+  int rc = validate(*problem);
+  if (rc) return rc;
+  if (tx_dot_device_count() <= 0) return fail(TXD_ERR_NO_DEVICE, "no CUDA device: the b200_dot backend has no CPU path");
+  int dev = 0;
+  TXD_CUDA(cudaGetDevice(&dev));
+  cudaDeviceProp prop;
+  TXD_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10)
+    return fail(TXD_ERR_UNSUPPORTED, "device %d is sm_%d%d; these kernels are built for sm_100a only", dev, prop.major, prop.minor);
+
+  tx_dot_plan *pl = new (std::nothrow) tx_dot_plan();
+  if (!pl) return fail(TXD_ERR_INVALID, "out of host memory");
+  pl->problem = *problem;
+  pl->device = dev;
+  pl->sm_count = prop.multiProcessorCount;
+  const tx_dot_problem &pr = pl->problem;
+  TXD_CUDA(cudaMalloc(&pl->status, sizeof(uint32_t)));
+  TXD_CUDA(cudaMemset(pl->status, 0, sizeof(uint32_t)));
+  if (pr.m == 0 || pr.n == 0 || pr.k == 0) {  // nothing for the tensor pipe to do
+    *out_plan = pl;
+    return TXD_OK;
+  }
+  rc = build_plan_tiles(pr, cfg, pl->sm_count, pl->tc);
+  if (rc) {
+    tx_dot_plan_destroy(pl);
+    return rc;
+  }
+  const txd::TileChoice &tc = pl->tc;
+  const int es = txd::elem_bytes(pr.ab_dtype);
+  const bool swap = tc.swap_ab != 0;
+  // Roles: P feeds the 128 TMEM lanes, Q the block_n TMEM columns.
+  const bool p_mn = swap ? (pr.b_layout == TXD_ROW_MAJOR) : (pr.a_layout == TXD_COL_MAJOR);
+  const bool q_mn = swap ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
+
+  txd::DotParams &bp = pl->base;
+  memset(&bp, 0, sizeof bp);
+  bp.ldo = pr.ldc;
+  bp.wait_limit_ns = 2000000000ull;  // 2 s per wait; a healthy kernel waits microseconds
+  if (const char *e = getenv("TXD_WAIT_LIMIT_MS")) {
+    const long v = atol(e);
+    if (v > 0) bp.wait_limit_ns = static_cast<unsigned long long>(v) * 1000000ull;
+  }
+  bp.alpha = pr.alpha;
+  bp.p_extent = tc.p_extent;
+  bp.q_extent = tc.q_extent;
+  bp.k_extent = pr.k;
+  bp.trans_out = swap ? 1 : 0;
+  bp.out_dtype = pr.out_dtype;
+  bp.block_n = tc.block_n;
+  bp.bk_elems = tc.block_k;
+  bp.stages = tc.stages;
+  bp.k_blocks = tc.k_blocks;
+  bp.k_main_blocks = tc.k_main_blocks;
+  bp.tail_mmas = tc.tail_mmas;
+  bp.tiles_p = tc.tiles_p;
+  bp.tiles_q = tc.tiles_q;
+  bp.group_p = tc.group_m;
+  bp.stream_k = tc.schedule == TXD_SCHED_STREAM_K ? 1 : 0;
+  bp.kind_f8 = es == 1 ? 1 : 0;
+  bp.idesc = make_idesc(pr.ab_dtype, p_mn, q_mn, tc.block_n);
+  const int umma_k = 32 / es;
+  make_smem_desc(p_mn, tc.block_k, umma_k, &bp.p_desc_hi, &bp.p_desc_lbo, &bp.p_kstep);
+  make_smem_desc(q_mn, tc.block_k, umma_k, &bp.q_desc_hi, &bp.q_desc_lbo, &bp.q_kstep);
+  bp.p_mn_major = p_mn;
+  bp.q_mn_major = q_mn;
+  bp.chunk_elems = 128 / es;
+  bp.p_stage_bytes = tc.p_stage_bytes;
+  bp.q_stage_bytes = tc.q_stage_bytes;
+  bp.tmem_cols = tc.tmem_cols;
+  bp.status = pl->status;
+
+  if (tc.scratch_bytes > 0) {
+    TXD_CUDA(cudaMalloc(&pl->scratch, static_cast<size_t>(tc.scratch_bytes)));
+    TXD_CUDA(cudaMemset(pl->scratch, 0, static_cast<size_t>(tc.scratch_bytes)));
+    bp.partials = static_cast<float *>(pl->scratch);
+    bp.tile_counters = reinterpret_cast<uint32_t *>(static_cast<char *>(pl->scratch) +
+                                                    static_cast<size_t>(tc.grid) * 2 * tc.block_n * 128 * 4);
+  }
+  cudaError_t e = cudaFuncSetAttribute(txd::dot_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess) {
+    tx_dot_plan_destroy(pl);
+    return fail(TXD_ERR_CUDA, "cannot reserve %d bytes of dynamic shared memory: %s", tc.smem_bytes, cudaGetErrorString(e));
+  }
+  *out_plan = pl;
+  return TXD_OK;
+}
+
+int tx_dot_plan_query(const tx_dot_plan *plan, tx_dot_plan_info *info) {
+  if (!plan || !info) return fail(TXD_ERR_INVALID, "null argument");
+  fill_info(plan->problem, plan->tc, info);
+  return TXD_OK;
+}
+
+int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const float *row_scale,
+               const float *col_scale, void *stream_v) {
+  if (!pl) return fail(TXD_ERR_INVALID, "null plan");
+  const tx_dot_problem &pr = pl->problem;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (pr.m == 0 || pr.n == 0) return TXD_OK;
+  if (!c) return fail(TXD_ERR_INVALID, "null output pointer");
+  if (pr.k == 0) {
+    dot_zero_fill_kernel<<<pl->sm_count, 256, 0, stream>>>(c, pr.ldc, pr.m, pr.n, txd::elem_bytes(pr.out_dtype));
+    TXD_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return TXD_OK;
+  }
+  if (!a || !b) return fail(TXD_ERR_INVALID, "null operand pointer");
+  if ((pr.has_row_scale != 0) != (row_scale != nullptr) || (pr.has_col_scale != 0) != (col_scale != nullptr))
+    return fail(TXD_ERR_INVALID, "scale pointers must be given exactly when the plan was created with them");
+  const txd::TileChoice &tc = pl->tc;
+  const bool swap = tc.swap_ab != 0;
+  const void *p_ptr = swap ? b : a;
+  const void *q_ptr = swap ? a : b;
+  const long long p_ld = swap ? pr.ldb : pr.lda;
+  const long long q_ld = swap ? pr.lda : pr.ldb;
+  if (pl->p_cache.ptr != p_ptr) {
+    int rc = encode_operand_map(&pl->p_cache.map, p_ptr, pr.ab_dtype, pl->base.p_mn_major != 0, tc.p_extent, pr.k, p_ld,
+                                txd::kBlockM, tc.block_k);
+    if (rc) return rc;
+    pl->p_cache.ptr = p_ptr;
+  }
+  if (pl->q_cache.ptr != q_ptr) {
+    int rc = encode_operand_map(&pl->q_cache.map, q_ptr, pr.ab_dtype, pl->base.q_mn_major != 0, tc.q_extent, pr.k, q_ld,
+                                tc.block_n, tc.block_k);
+    if (rc) return rc;
+    pl->q_cache.ptr = q_ptr;
+  }
+  txd::DotParams prm = pl->base;
+  prm.tmap_p = pl->p_cache.map;
+  prm.tmap_q = pl->q_cache.map;
+  prm.out = c;
+  // Scales follow their matrix: after the role swap, rows of C are the Q index.
+  prm.scale_row = swap ? col_scale : row_scale;
+  prm.scale_col = swap ? row_scale : col_scale;
+  txd::dot_umma_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
+  TXD_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  return TXD_OK;
+}
+
+int tx_dot_plan_check(tx_dot_plan *pl, void *stream_v) {
+  if (!pl) return fail(TXD_ERR_INVALID, "null plan");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  TXD_CUDA(cudaStreamSynchronize(stream));
+  uint32_t st = 0;
+  TXD_CUDA(cudaMemcpy(&st, pl->status, sizeof st, cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(pl->status, 0, sizeof st);
+    if (pl->scratch) cudaMemset(pl->scratch, 0, static_cast<size_t>(pl->tc.scratch_bytes));
+    static const char *kWho[] = {"", "TMA producer (stage never freed)", "MMA issuer (stage never filled)",
+                                 "MMA issuer (accumulator never drained)", "epilogue (accumulator never completed)",
+                                 "teardown (copies or MMAs still in flight)"};
+    return fail(TXD_ERR_DEVICE_TIMEOUT, "device-side wait ran out in the %s; output is undefined", kWho[st < 6 ? st : 0]);
+  }
+  return TXD_OK;
+}
+
+int tx_dot_run_host(tx_dot_plan *pl, const void *a_host, const void *b_host, void *c_host,
+                    const float *row_scale_host, const float *col_scale_host) {
+  if (!pl) return fail(TXD_ERR_INVALID, "null plan");
+  const tx_dot_problem &pr = pl->problem;
+  if (pr.m == 0 || pr.n == 0) return TXD_OK;
+  if (!c_host || (pr.k > 0 && (!a_host || !b_host))) return fail(TXD_ERR_INVALID, "null host pointer");
+  const size_t es = txd::elem_bytes(pr.ab_dtype), os = txd::elem_bytes(pr.out_dtype);
+  const size_t a_rows = pr.a_layout == TXD_ROW_MAJOR ? pr.m : pr.k;
+  const size_t b_rows = pr.b_layout == TXD_ROW_MAJOR ? pr.k : pr.n;
+  if (!pl->host_stream) {
+    TXD_CUDA(cudaStreamCreateWithFlags(&pl->host_stream, cudaStreamNonBlocking));
+    pl->a_bytes = a_rows * pr.lda * es;
+    pl->b_bytes = b_rows * pr.ldb * es;
+    pl->c_bytes = static_cast<size_t>(pr.m) * pr.ldc * os;
+    if (pl->a_bytes) TXD_CUDA(cudaMalloc(&pl->dev_a, pl->a_bytes));
+    if (pl->b_bytes) TXD_CUDA(cudaMalloc(&pl->dev_b, pl->b_bytes));
+    TXD_CUDA(cudaMalloc(&pl->dev_c, pl->c_bytes));
+    if (pr.has_row_scale) TXD_CUDA(cudaMalloc(&pl->dev_rs, sizeof(float) * pr.m));
+    if (pr.has_col_scale) TXD_CUDA(cudaMalloc(&pl->dev_cs, sizeof(float) * pr.n));
+  }
+  cudaStream_t s = pl->host_stream;
+  if (pr.k > 0) {
+    TXD_CUDA(cudaMemcpyAsync(pl->dev_a, a_host, pl->a_bytes, cudaMemcpyHostToDevice, s));
+    TXD_CUDA(cudaMemcpyAsync(pl->dev_b, b_host, pl->b_bytes, cudaMemcpyHostToDevice, s));
+  }
+  if (pr.has_row_scale) {
+    if (!row_scale_host) return fail(TXD_ERR_INVALID, "row scale expected");
+    TXD_CUDA(cudaMemcpyAsync(pl->dev_rs, row_scale_host, sizeof(float) * pr.m, cudaMemcpyHostToDevice, s));
+  }
+  if (pr.has_col_scale) {
+    if (!col_scale_host) return fail(TXD_ERR_INVALID, "column scale expected");
+    TXD_CUDA(cudaMemcpyAsync(pl->dev_cs, col_scale_host, sizeof(float) * pr.n, cudaMemcpyHostToDevice, s));
+  }
+  int rc = tx_dot_run(pl, pl->dev_a, pl->dev_b, pl->dev_c, pl->dev_rs, pl->dev_cs, s);
+  if (rc) return rc;
+  TXD_CUDA(cudaMemcpyAsync(c_host, pl->dev_c, pl->c_bytes, cudaMemcpyDeviceToHost, s));
+  return tx_dot_plan_check(pl, s);
+}
+
+int tx_dot_plan_destroy(tx_dot_plan *pl) {
+  if (!pl) return TXD_OK;
+  if (pl->scratch) cudaFree(pl->scratch);
+  if (pl->status) cudaFree(pl->status);
+  if (pl->dev_a) cudaFree(pl->dev_a);
+  if (pl->dev_b) cudaFree(pl->dev_b);
+  if (pl->dev_c) cudaFree(pl->dev_c);
+  if (pl->dev_rs) cudaFree(pl->dev_rs);
+  if (pl->dev_cs) cudaFree(pl->dev_cs);
+  if (pl->host_stream) cudaStreamDestroy(pl->host_stream);
+  delete pl;
+  return TXD_OK;
+}
+
+}  // extern "C"

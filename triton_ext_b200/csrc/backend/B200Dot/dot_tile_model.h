@@ -1,0 +1,227 @@
+// Arithmetic-intensity model that picks tile shape, pipeline depth, operand roles and schedule for one
+// tt.dot K-loop on a B200. Pure host C++ (no CUDA): shared by the `dot_tile_select` pass extension and
+// by the `b200_dot` backend's plan creation, so both always agree.
+//
+// The reference has no counterpart: its only analysis is LoopSplit's compare scan
+// (pass/LoopSplit/LoopSplit.cpp:107-123). The quantities modelled here are the ones that decide a
+// tcgen05 kernel's speed: tensor-pipe cycles per K block, shared-memory feed bytes per K block, wave
+// quantisation of the persistent grid, and HBM bytes.
+#pragma once
+
+#include <algorithm>
+#include <cstdint>
+
+#include "b200_dot.h"
+
+namespace txd {
+
+struct MachineModel {
+  int sm_count = 148;
+  double sm_clock_ghz = 1.9;            // tensor work runs power-capped; only ratios matter here
+  double mma_flops_per_clk_16bit = 8192;  // dense bf16/fp16 FLOP per SM per clock
+  double mma_flops_per_clk_8bit = 16384;
+  double smem_bytes_per_clk = 128;      // shared-memory read bandwidth per SM
+  double hbm_bytes_per_s = 6.4596e12;   // measured copy bandwidth of this pool's B200
+  double hbm_bytes_per_s_per_cta = 50e9; // what one persistent CTA's TMA ring sustains
+  int smem_budget = 227 * 1024 - 2048;  // dynamic shared memory per CTA minus control block + slack
+};
+
+inline int elem_bytes(int dtype) {
+  switch (dtype) {
+    case TXD_F16:
+    case TXD_BF16:
+      return 2;
+    case TXD_F8E4M3:
+    case TXD_F8E5M2:
+      return 1;
+    case TXD_F32:
+      return 4;
+    default:
+      return 0;
+  }
+}
+
+struct TileChoice {
+  int block_m = 128, block_n = 0, block_k = 0;
+  int stages = 0;
+  int swap_ab = 0;       // 0/1 (resolved)
+  int schedule = 0;      // TXD_SCHED_DATA_PARALLEL or TXD_SCHED_STREAM_K (resolved)
+  int group_m = 0;
+  int grid = 0;
+  int k_blocks = 0, k_main_blocks = 0, tail_mmas = 0;
+  int p_extent = 0, q_extent = 0;   // MMA-M side and MMA-N side extents after role assignment
+  int tiles_p = 0, tiles_q = 0;
+  int p_stage_bytes = 0, q_stage_bytes = 0;
+  int smem_bytes = 0, tmem_cols = 0;
+  int64_t scratch_bytes = 0;
+  double arithmetic_intensity = 0;  // FLOP per algorithmic byte
+  double ridge_intensity = 0;       // machine balance: FLOP per byte at which HBM and tensor time meet
+  double est_seconds = 0;
+  bool hbm_bound = false;
+};
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+inline int cdiv(int x, int m) { return (x + m - 1) / m; }
+
+inline double algorithmic_bytes(const tx_dot_problem &pr) {
+  const double es = elem_bytes(pr.ab_dtype), os = elem_bytes(pr.out_dtype);
+  double b = (double)pr.m * pr.k * es + (double)pr.k * pr.n * es + (double)pr.m * pr.n * os;
+  if (pr.has_row_scale) b += 4.0 * pr.m;
+  if (pr.has_col_scale) b += 4.0 * pr.n;
+  return b;
+}
+
+// Modelled time of one (role assignment, block_n, schedule) candidate.
+inline double model_seconds(const MachineModel &mm, int es, int p_extent, int q_extent, int k,
+                            int block_n, bool q_mn_major, int schedule, int grid, double algo_bytes) {
+  const int bk = 128 / es;
+  const int k_blocks = cdiv(k, bk);
+  const int tiles = cdiv(p_extent, 128) * cdiv(q_extent, block_n);
+  const double flops_per_clk = es == 1 ? mm.mma_flops_per_clk_8bit : mm.mma_flops_per_clk_16bit;
+  const double mma_clk = 2.0 * 128 * block_n * bk / flops_per_clk;
+  const int q_rows = q_mn_major ? round_up(block_n, bk) : block_n;  // MN-major boxes are 128 B wide
+  // Each stage byte is read once by the tensor pipe while TMA writes the next stages into the same
+  // banks; charge the write at a quarter of a read.
+  const double feed_clk = 1.25 * (128.0 * 128 + q_rows * 128.0) / mm.smem_bytes_per_clk;
+  const double blk_clk = std::max(mma_clk, feed_clk);
+  const long long total = (long long)tiles * k_blocks;
+  double blocks_per_cta;  // the busiest CTA's share
+  if (schedule == TXD_SCHED_STREAM_K) {
+    blocks_per_cta = (double)((total + grid - 1) / grid);
+  } else {
+    blocks_per_cta = (double)cdiv(tiles, grid) * k_blocks;
+  }
+  const double balance = ((double)total / grid) / blocks_per_cta;  // 1 = every CTA equally loaded
+  double busy_clk = blocks_per_cta * blk_clk;
+  if (schedule == TXD_SCHED_STREAM_K) {
+    // Up to two partial tiles per CTA go through scratch: fp32 write + read, ~64 B/clk through L2.
+    busy_clk += 2.0 * (128.0 * block_n * 4 * 2) / 64.0;
+  }
+  const double t_tensor = busy_clk / (mm.sm_clock_ghz * 1e9);
+  // A CTA keeps only its own ring of loads in flight, so few CTAs cannot pull the whole HBM rate,
+  // and an unbalanced grid leaves HBM idle while the last CTAs finish.
+  const double t_hbm =
+      algo_bytes / std::min(mm.hbm_bytes_per_s, grid * mm.hbm_bytes_per_s_per_cta) / balance;
+  return std::max(t_tensor, t_hbm) + 3e-6;  // + launch and pipeline fill
+}
+
+// Fill every unset field of `cfg`. Returns 0, or a negative value with *why set.
+inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, const MachineModel &mm,
+                        TileChoice &out, const char **why) {
+  static const char *kNoWhy = "";
+  if (why) *why = kNoWhy;
+  tx_dot_config cfg = {};
+  if (cfg_in) cfg = *cfg_in;
+  const int es = elem_bytes(pr.ab_dtype);
+  if (es != 1 && es != 2) {
+    if (why) *why = "operand dtype must be f16, bf16, f8e4m3 or f8e5m2";
+    return -1;
+  }
+  const int bk = 128 / es;
+  const double algo = algorithmic_bytes(pr);
+  const double flops = 2.0 * pr.m * pr.n * pr.k;
+  const double flops_per_clk = es == 1 ? mm.mma_flops_per_clk_8bit : mm.mma_flops_per_clk_16bit;
+  out.arithmetic_intensity = flops / algo;
+  out.ridge_intensity = flops_per_clk * mm.sm_count * mm.sm_clock_ghz * 1e9 / mm.hbm_bytes_per_s;
+  out.hbm_bound = out.arithmetic_intensity < out.ridge_intensity;
+  const int max_grid = cfg.max_ctas > 0 ? std::min(cfg.max_ctas, mm.sm_count) : mm.sm_count;
+
+  double best = 1e30;
+  bool found = false;
+  static const int kBlockNs[] = {256, 128, 64, 32, 16};
+  for (int swap = 0; swap <= 1; ++swap) {
+    if (cfg.swap_ab == 1 && !swap) continue;
+    if (cfg.swap_ab == 2 && swap) continue;
+    // Swapping only pays when m is the short side; do not consider it otherwise.
+    if (cfg.swap_ab == 0 && swap && !(pr.m < 128 && pr.n > pr.m)) continue;
+    const int p_extent = swap ? pr.n : pr.m;
+    const int q_extent = swap ? pr.m : pr.n;
+    // Q is MN-major when its rows (the Q index) are contiguous in memory.
+    const bool q_mn = swap ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
+    for (int bn : kBlockNs) {
+      if (cfg.block_n && bn != cfg.block_n) continue;
+      // Do not pad the Q side by more than one tile's worth beyond need.
+      if (!cfg.block_n && bn > 16 && bn / 2 >= q_extent) continue;
+      const int tiles = cdiv(p_extent, 128) * cdiv(q_extent, bn);
+      const int k_blocks = cdiv(pr.k, bk);
+      for (int sched = TXD_SCHED_DATA_PARALLEL; sched <= TXD_SCHED_STREAM_K; ++sched) {
+        if (cfg.schedule && sched != cfg.schedule) continue;
+        long long units = (long long)tiles * (sched == TXD_SCHED_STREAM_K ? k_blocks : 1);
+        if (units < 1) units = 1;
+        const int grid = (int)std::min<long long>(max_grid, units);
+        double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, q_mn, sched, grid, algo);
+        // Prefer the simpler schedule / bigger tile on near-ties.
+        if (sched == TXD_SCHED_STREAM_K) t *= 1.03;
+        if (t < best) {
+          best = t;
+          found = true;
+          out.swap_ab = swap;
+          out.block_n = bn;
+          out.schedule = sched;
+          out.grid = grid;
+        }
+      }
+    }
+  }
+  if (!found) {
+    if (why) *why = "no tile configuration satisfies the given constraints";
+    return -1;
+  }
+  out.est_seconds = best;
+  out.block_k = bk;
+  out.p_extent = out.swap_ab ? pr.n : pr.m;
+  out.q_extent = out.swap_ab ? pr.m : pr.n;
+  out.tiles_p = cdiv(out.p_extent, 128);
+  out.tiles_q = cdiv(out.q_extent, out.block_n);
+  out.k_blocks = cdiv(pr.k, bk);
+  // LoopSplit mid point: first K index of the masked remainder.
+  int mid = cfg.k_split_point > 0 ? cfg.k_split_point : (cfg.k_split_point < 0 ? 0 : (pr.k / bk) * bk);
+  if (mid % bk != 0 || mid > pr.k || mid < 0) {
+    if (why) *why = "k_split_point must be a multiple of BLOCK_K in [0, K]";
+    return -1;
+  }
+  out.k_main_blocks = mid / bk;
+  const int rem = pr.k - (out.k_blocks - 1) * bk;  // columns in the last block: 1..bk
+  const int umma_k = 32 / es;
+  out.tail_mmas = pr.k > 0 ? cdiv(rem, umma_k) : 0;
+  const bool p_mn = out.swap_ab ? (pr.b_layout == TXD_ROW_MAJOR) : (pr.a_layout == TXD_COL_MAJOR);
+  const bool q_mn = out.swap_ab ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
+  (void)p_mn;
+  out.p_stage_bytes = 128 * 128;
+  out.q_stage_bytes = (q_mn ? round_up(out.block_n, bk) : out.block_n) * 128;
+  // The Q stage must keep the next P stage 1024-byte aligned.
+  out.q_stage_bytes = round_up(out.q_stage_bytes, 1024);
+  const int stage_bytes = out.p_stage_bytes + out.q_stage_bytes;
+  int stages = cfg.stages ? cfg.stages : std::min(12, mm.smem_budget / stage_bytes);
+  if (stages < 2 || stages > 12 || stages * stage_bytes > mm.smem_budget) {
+    if (why) *why = "stages out of range for this tile (2..12, ring must fit shared memory)";
+    return -1;
+  }
+  out.stages = stages;
+  out.smem_bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 512 /*control block*/;
+  int cols = 32;
+  while (cols < 2 * out.block_n) cols *= 2;
+  out.tmem_cols = cols;
+  if (cfg.group_m > 0) {
+    out.group_m = cfg.group_m;
+  } else {
+    // Shape one wave of tiles as close to square (in elements) as the grid allows.
+    int g = 1;
+    double best_g = 1e30;
+    for (int cand = 1; cand <= 32; cand *= 2) {
+      const double rows = cand * 128.0, cols_e = (double)out.grid / cand * out.block_n;
+      const double cost = rows + cols_e;
+      if (cost < best_g) {
+        best_g = cost;
+        g = cand;
+      }
+    }
+    out.group_m = std::max(1, std::min(g, out.tiles_p));
+  }
+  out.scratch_bytes = 0;
+  if (out.schedule == TXD_SCHED_STREAM_K)
+    out.scratch_bytes = (int64_t)out.grid * 2 * out.block_n * 128 * 4 + (int64_t)out.tiles_p * out.tiles_q * 4;
+  return 0;
+}
+
+}  // namespace txd
