@@ -88,9 +88,11 @@ typedef struct tx_dot_config {
   int32_t max_ctas;      /* cap on the persistent grid (0 = number of SMs) */
   int32_t k_split_point; /* LoopSplit mid point of the K loop in elements; 0 = floor(K/BK)*BK,
                             negative = split at 0 (the whole loop runs as the masked remainder).
-                            Must be a multiple of BLOCK_K and <= K. Iterations below it run
-                            unpredicated; the rest run as the masked remainder. */
-  int32_t reserved;
+                            Must not exceed floor(K/BK)*BK; a value inside a physical K block is
+                            moved down to the block start. Iterations below it run unpredicated;
+                            the rest run as the masked remainder. */
+  int32_t cta_pair;      /* 1 = two-CTA clusters (tcgen05 cta_group::2, 256 x block_n tiles),
+                            2 = single CTAs (128 x block_n tiles), 0 = auto */
 } tx_dot_config;
 
 /* What a plan decided; filled by tx_dot_plan_query. */
@@ -106,7 +108,7 @@ typedef struct tx_dot_plan_info {
   int32_t k_tail_mmas;     /* tcgen05.mma instructions issued by the last remainder iteration */
   int32_t smem_bytes;      /* dynamic shared memory per CTA */
   int32_t tmem_columns;    /* TMEM columns allocated per CTA */
-  int32_t reserved;
+  int32_t cta_pair;        /* 1 when the two-CTA kernel was chosen (block_m is then 256) */
   int64_t scratch_bytes;   /* plan-owned global scratch (stream-K partial tiles + counters) */
   double flops;            /* 2*m*n*k */
   double algorithmic_bytes;/* read A once + read B once + write C once (+ scales) */

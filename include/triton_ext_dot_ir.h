@@ -106,6 +106,10 @@ TXIR_API int32_t txir_pass_manager_run(TritonExtPassManagerRef pm, txir_module *
 TXIR_API int32_t txir_registered_pass_count(void);
 TXIR_API int32_t txir_registered_pass_lookup(const char *argument);
 
+/* Implemented by the backend extension library (libb200_dot.so): build a launchable plan from a dot
+ * that the `b200_dot` pass has lowered. Returns a tx_dot_status. */
+TXIR_API int32_t txir_module_create_plan(const txir_module *m, int32_t dot_index, tx_dot_plan **out_plan);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,124 @@
+"""The pass-plugin C-ABI: symbols, registration at dlopen, enumerate / register / add semantics.
+
+Expected behaviour is the reference's infra/pass/TritonExtPassInfra.cpp:7-52, except where
+include/triton_ext_plugin.h documents a deliberate difference (enumeration fills every slot)."""
+import ctypes
+import os
+import re
+import subprocess
+
+from triton_ext_b200 import plugin as P
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+INCLUDE = os.path.join(ROOT, "include")
+
+
+def _exported(lib_path):
+    out = subprocess.run(["nm", "-D", "--defined-only", lib_path], capture_output=True, text=True, check=True).stdout
+    return {line.split()[-1] for line in out.splitlines() if line.strip()}
+
+
+def _declared(header, prefix_regex):
+    text = open(os.path.join(INCLUDE, header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return set(re.findall(prefix_regex, text))
+
+
+def test_infra_exports_the_four_plugin_symbols(built_libs):
+    syms = _exported(P.infra_path())
+    for s in ("tritonAddPluginPass", "tritonRegisterPluginPass", "tritonEnumeratePluginPasses", "TritonExtLoadPass"):
+        assert s in syms
+
+
+def test_every_declared_symbol_is_exported(built_libs):
+    infra_syms = _exported(P.infra_path())
+    dot_syms = _exported(P.plugin_path("b200_dot"))
+    for name in _declared("triton_ext_dot_ir.h", r"\b(txir_\w+)\s*\("):
+        assert name in infra_syms or name in dot_syms, name
+    for name in _declared("b200_dot.h", r"\b(tx_dot_\w+)\s*\("):
+        assert name in dot_syms, name
+
+
+def test_extensions_register_at_dlopen_in_load_order(built_libs):
+    P.load_default_plugins()
+    names = P.enumerate_passes()
+    assert names[:3] == ["loop_split", "dot_tile_select", "b200_dot"]
+    # every slot is filled (the reference leaves all names in slot 0, TritonExtPassInfra.cpp:47-50)
+    assert len(set(names)) == len(names)
+
+
+def test_enumerate_protocol(built_libs):
+    P.load_default_plugins()
+    lib = P.infra()
+    assert lib.tritonEnumeratePluginPasses(None, None) == P.TP_GENERIC_FAILURE  # null count -> failure
+    n = ctypes.c_uint32(0)
+    assert lib.tritonEnumeratePluginPasses(ctypes.byref(n), None) == P.TP_SUCCESS  # count only
+    assert n.value >= 3
+
+
+def test_unknown_and_null_names_fail(built_libs):
+    P.load_default_plugins()
+    lib = P.infra()
+    pm = P.PassManager()
+    assert pm.add("no_such_pass") == P.TP_GENERIC_FAILURE
+    assert P.register_pass("no_such_pass") == P.TP_GENERIC_FAILURE
+    assert lib.tritonRegisterPluginPass(None) == P.TP_GENERIC_FAILURE
+    assert lib.tritonAddPluginPass(pm._h, None) == P.TP_GENERIC_FAILURE
+    assert lib.tritonAddPluginPass(None, b"loop_split") == P.TP_GENERIC_FAILURE
+    assert pm.arguments() == []
+
+
+def test_add_appends_in_order_and_register_is_idempotent(built_libs):
+    P.load_default_plugins()
+    pm = P.PassManager()
+    assert pm.add("loop_split") == P.TP_SUCCESS
+    assert pm.add("b200_dot") == P.TP_SUCCESS
+    assert pm.add("loop_split") == P.TP_SUCCESS
+    assert pm.arguments() == ["triton-loop-split", "triton-b200-dot", "triton-loop-split"]
+    assert P.register_pass("loop_split") == P.TP_SUCCESS
+    count = P.infra().txir_registered_pass_count()
+    assert P.register_pass("loop_split") == P.TP_SUCCESS
+    assert P.infra().txir_registered_pass_count() == count
+    assert P.registered_pass_lookup("triton-loop-split") >= 0
+    assert P.registered_pass_lookup("triton-nope") == -1
+
+
+def test_load_pass_from_a_foreign_extension(built_libs, tmp_path):
+    """A third-party extension written against the public headers only (C callbacks) can register."""
+    src = tmp_path / "ext.c"
+    src.write_text(r'''
+#include "triton_ext_plugin.h"
+static int registered = 0, added = 0;
+static void reg(void) { registered++; }
+static void add(TritonExtPassManagerRef pm) { (void)pm; added++; }
+__attribute__((constructor)) static void init(void) { TritonExtLoadPass("foreign_ext", reg, add); }
+__attribute__((visibility("default"))) int foreign_counts(void) { return registered * 100 + added; }
+''')
+    so = tmp_path / "libforeign_ext.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-I", INCLUDE, str(src), "-o", str(so),
+                    "-L", os.path.dirname(P.infra_path()), "-lTritonExtPassInfra",
+                    f"-Wl,-rpath,{os.path.dirname(P.infra_path())}"], check=True)
+    P.load_plugins_from_env(str(so))
+    assert "foreign_ext" in P.enumerate_passes()
+    pm = P.PassManager()
+    assert pm.add("foreign_ext") == P.TP_SUCCESS
+    assert P.register_pass("foreign_ext") == P.TP_SUCCESS
+    lib = ctypes.CDLL(str(so))
+    assert lib.foreign_counts() == 101
+
+
+def test_threaded_lookups(built_libs):
+    import threading
+    P.load_default_plugins()
+    errs = []
+
+    def work():
+        for _ in range(200):
+            pm = P.PassManager()
+            if pm.add("loop_split") != P.TP_SUCCESS or "loop_split" not in P.enumerate_passes():
+                errs.append(1)
+
+    ts = [threading.Thread(target=work) for _ in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not errs

@@ -63,7 +63,7 @@ class Config(ctypes.Structure):
     _fields_ = [
         ("block_n", ctypes.c_int32), ("stages", ctypes.c_int32), ("swap_ab", ctypes.c_int32),
         ("schedule", ctypes.c_int32), ("group_m", ctypes.c_int32), ("max_ctas", ctypes.c_int32),
-        ("k_split_point", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("k_split_point", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
     ]
 
 
@@ -74,7 +74,7 @@ class PlanInfo(ctypes.Structure):
         ("group_m", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("k_main_iters", ctypes.c_int32), ("k_tail_iters", ctypes.c_int32),
         ("k_tail_mmas", ctypes.c_int32), ("smem_bytes", ctypes.c_int32),
-        ("tmem_columns", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("tmem_columns", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
         ("scratch_bytes", ctypes.c_int64), ("flops", ctypes.c_double),
         ("algorithmic_bytes", ctypes.c_double),
     ]

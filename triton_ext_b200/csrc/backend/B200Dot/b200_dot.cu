@@ -86,7 +86,7 @@ struct tx_dot_plan {
   int sm_count = 0;
   void *scratch = nullptr;      // partials, then counters
   uint32_t *status = nullptr;   // device status word
-  MapKey p_cache, q_cache;
+  MapKey p_cache, q_cache, out_cache;
   // host-buffer path
   cudaStream_t host_stream = nullptr;
   void *dev_a = nullptr, *dev_b = nullptr, *dev_c = nullptr;
@@ -119,27 +119,7 @@ int validate(const tx_dot_problem &pr) {
   return TXD_OK;
 }
 
-void fill_info(const tx_dot_problem &pr, const txd::TileChoice &tc, tx_dot_plan_info *info) {
-  memset(info, 0, sizeof *info);
-  info->block_m = tc.block_m;
-  info->block_n = tc.block_n;
-  info->block_k = tc.block_k;
-  info->stages = tc.stages;
-  info->swap_ab = tc.swap_ab;
-  info->schedule = tc.schedule;
-  info->group_m = tc.group_m;
-  info->grid = tc.grid;
-  info->k_main_iters = tc.k_main_blocks;
-  info->k_tail_iters = tc.k_blocks - tc.k_main_blocks;
-  info->k_tail_mmas = tc.tail_mmas;
-  info->smem_bytes = tc.smem_bytes;
-  info->tmem_columns = tc.tmem_cols;
-  info->scratch_bytes = tc.scratch_bytes;
-  info->flops = 2.0 * pr.m * pr.n * pr.k;
-  info->algorithmic_bytes = txd::algorithmic_bytes(pr);
-}
-
-uint32_t make_idesc(int ab_dtype, bool p_mn, bool q_mn, int block_n) {
+uint32_t make_idesc(int ab_dtype, bool p_mn, bool q_mn, int block_m, int block_n) {
   uint32_t fmt = 0;
   if (ab_dtype == TXD_BF16) fmt = 1;        // kind::f16: 0 = f16, 1 = bf16
   if (ab_dtype == TXD_F8E4M3) fmt = 0;      // kind::f8f6f4: 0 = e4m3, 1 = e5m2
@@ -151,7 +131,7 @@ uint32_t make_idesc(int ab_dtype, bool p_mn, bool q_mn, int block_n) {
   d |= (p_mn ? 1u : 0u) << 15;               // A is MN-major
   d |= (q_mn ? 1u : 0u) << 16;               // B is MN-major
   d |= static_cast<uint32_t>(block_n >> 3) << 17;
-  d |= static_cast<uint32_t>(txd::kBlockM >> 4) << 24;
+  d |= static_cast<uint32_t>(block_m >> 4) << 24;  // 128, or 256 across a CTA pair
   return d;
 }
 
@@ -200,6 +180,24 @@ int encode_operand_map(CUtensorMap *map, const void *ptr, int dtype, bool mn_maj
   return TXD_OK;
 }
 
+// Tensor map for the epilogue's TMA store: C is row-major [m, n]; one box is 32 rows x 128 bytes.
+int encode_store_map(CUtensorMap *map, void *ptr, int out_dtype, long long m, long long n, long long ldc) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  const int os = txd::elem_bytes(out_dtype);
+  CUtensorMapDataType dt = out_dtype == TXD_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                 : (out_dtype == TXD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * os};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / os), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled (store map) failed with CUresult %d", (int)r);
+  return TXD_OK;
+}
+
 int build_plan_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg, int sm_count, txd::TileChoice &tc) {
   txd::MachineModel mm;
   mm.sm_count = sm_count;
@@ -238,7 +236,7 @@ int tx_dot_plan_preview(const tx_dot_problem *problem, const tx_dot_config *cfg,
   }
   rc = build_plan_tiles(*problem, cfg, sm_count, tc);
   if (rc) return rc;
-  fill_info(*problem, tc, info);
+  txd::fill_plan_info(*problem, tc, info);
   return TXD_OK;
 }
 
@@ -261,8 +259,8 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
   pl->device = dev;
   pl->sm_count = prop.multiProcessorCount;
   const tx_dot_problem &pr = pl->problem;
-  TXD_CUDA(cudaMalloc(&pl->status, sizeof(uint32_t)));
-  TXD_CUDA(cudaMemset(pl->status, 0, sizeof(uint32_t)));
+  TXD_CUDA(cudaMalloc(&pl->status, 256));
+  TXD_CUDA(cudaMemset(pl->status, 0, 256));
   if (pr.m == 0 || pr.n == 0 || pr.k == 0) {  // nothing for the tensor pipe to do
     *out_plan = pl;
     return TXD_OK;
@@ -304,7 +302,8 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
   bp.group_p = tc.group_m;
   bp.stream_k = tc.schedule == TXD_SCHED_STREAM_K ? 1 : 0;
   bp.kind_f8 = es == 1 ? 1 : 0;
-  bp.idesc = make_idesc(pr.ab_dtype, p_mn, q_mn, tc.block_n);
+  bp.idesc = make_idesc(pr.ab_dtype, p_mn, q_mn, tc.block_m, tc.block_n);
+  bp.tma_store = tc.tma_store;
   const int umma_k = 32 / es;
   make_smem_desc(p_mn, tc.block_k, umma_k, &bp.p_desc_hi, &bp.p_desc_lbo, &bp.p_kstep);
   make_smem_desc(q_mn, tc.block_k, umma_k, &bp.q_desc_hi, &bp.q_desc_lbo, &bp.q_kstep);
@@ -315,6 +314,7 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
   bp.q_stage_bytes = tc.q_stage_bytes;
   bp.tmem_cols = tc.tmem_cols;
   bp.status = pl->status;
+  if (const char *e = getenv("TXD_DEBUG_FLAGS")) bp.debug_flags = atoi(e);
 
   if (tc.scratch_bytes > 0) {
     TXD_CUDA(cudaMalloc(&pl->scratch, static_cast<size_t>(tc.scratch_bytes)));
@@ -324,6 +324,8 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
                                                     static_cast<size_t>(tc.grid) * 2 * tc.block_n * 128 * 4);
   }
   cudaError_t e = cudaFuncSetAttribute(txd::dot_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(txd::dot_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) {
     tx_dot_plan_destroy(pl);
     return fail(TXD_ERR_CUDA, "cannot reserve %d bytes of dynamic shared memory: %s", tc.smem_bytes, cudaGetErrorString(e));
@@ -334,7 +336,7 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
 
 int tx_dot_plan_query(const tx_dot_plan *plan, tx_dot_plan_info *info) {
   if (!plan || !info) return fail(TXD_ERR_INVALID, "null argument");
-  fill_info(plan->problem, plan->tc, info);
+  txd::fill_plan_info(plan->problem, plan->tc, info);
   return TXD_OK;
 }
 
@@ -368,9 +370,16 @@ int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
   }
   if (pl->q_cache.ptr != q_ptr) {
     int rc = encode_operand_map(&pl->q_cache.map, q_ptr, pr.ab_dtype, pl->base.q_mn_major != 0, tc.q_extent, pr.k, q_ld,
-                                tc.block_n, tc.block_k);
+                                tc.cta_pair ? tc.block_n / 2 : tc.block_n, tc.block_k);
     if (rc) return rc;
     pl->q_cache.ptr = q_ptr;
+  }
+  // TMA store needs a 16-byte aligned C; otherwise this launch stores straight from registers.
+  const bool tma_store = tc.tma_store && (reinterpret_cast<uintptr_t>(c) & 15) == 0;
+  if (tma_store && pl->out_cache.ptr != c) {
+    int rc = encode_store_map(&pl->out_cache.map, c, pr.out_dtype, pr.m, pr.n, pr.ldc);
+    if (rc) return rc;
+    pl->out_cache.ptr = c;
   }
   txd::DotParams prm = pl->base;
   prm.tmap_p = pl->p_cache.map;
@@ -379,7 +388,25 @@ int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
   // Scales follow their matrix: after the role swap, rows of C are the Q index.
   prm.scale_row = swap ? col_scale : row_scale;
   prm.scale_col = swap ? row_scale : col_scale;
-  txd::dot_umma_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
+  prm.tma_store = tma_store ? 1 : 0;
+  if (tma_store) prm.tmap_out = pl->out_cache.map;
+  if (tc.cta_pair) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(tc.grid);
+    lc.blockDim = dim3(txd::kNumThreads);
+    lc.dynamicSmemBytes = tc.smem_bytes;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    TXD_CUDA(cudaLaunchKernelEx(&lc, txd::dot_umma_pair_kernel, prm));
+  } else {
+    txd::dot_umma_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
+  }
   TXD_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return TXD_OK;

@@ -10,6 +10,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstring>
 
 #include "b200_dot.h"
 
@@ -21,6 +22,8 @@ struct MachineModel {
   double mma_flops_per_clk_16bit = 8192;  // dense bf16/fp16 FLOP per SM per clock
   double mma_flops_per_clk_8bit = 16384;
   double smem_bytes_per_clk = 128;      // shared-memory read bandwidth per SM
+  double ingest_bytes_per_clk = 60;     // what TMA can deliver into one SM's shared memory (measured:
+                                        // a loads-only run of the ring moved 56 B/clk/SM)
   double hbm_bytes_per_s = 6.4596e12;   // measured copy bandwidth of this pool's B200
   double hbm_bytes_per_s_per_cta = 50e9; // what one persistent CTA's TMA ring sustains
   int smem_budget = 227 * 1024 - 2048;  // dynamic shared memory per CTA minus control block + slack
@@ -45,6 +48,8 @@ struct TileChoice {
   int block_m = 128, block_n = 0, block_k = 0;
   int stages = 0;
   int swap_ab = 0;       // 0/1 (resolved)
+  int cta_pair = 0;      // 0/1 (resolved): two-CTA clusters, 256-row tiles
+  int tma_store = 0;     // epilogue goes through shared memory + TMA store
   int schedule = 0;      // TXD_SCHED_DATA_PARALLEL or TXD_SCHED_STREAM_K (resolved)
   int group_m = 0;
   int grid = 0;
@@ -71,37 +76,46 @@ inline double algorithmic_bytes(const tx_dot_problem &pr) {
   return b;
 }
 
-// Modelled time of one (role assignment, block_n, schedule) candidate.
+// Modelled time of one (role assignment, block_n, pairing, schedule) candidate.
 inline double model_seconds(const MachineModel &mm, int es, int p_extent, int q_extent, int k,
-                            int block_n, bool q_mn_major, int schedule, int grid, double algo_bytes) {
+                            int block_n, bool q_mn_major, bool pair, int schedule, int workers,
+                            double algo_bytes) {
   const int bk = 128 / es;
   const int k_blocks = cdiv(k, bk);
-  const int tiles = cdiv(p_extent, 128) * cdiv(q_extent, block_n);
+  const int tile_rows = pair ? 256 : 128;
+  const int tiles = cdiv(p_extent, tile_rows) * cdiv(q_extent, block_n);
   const double flops_per_clk = es == 1 ? mm.mma_flops_per_clk_8bit : mm.mma_flops_per_clk_16bit;
+  // Per SM and K block: a 128 x block_n x bk MMA either way (a pair splits a 256-row tile).
   const double mma_clk = 2.0 * 128 * block_n * bk / flops_per_clk;
-  const int q_rows = q_mn_major ? round_up(block_n, bk) : block_n;  // MN-major boxes are 128 B wide
-  // Each stage byte is read once by the tensor pipe while TMA writes the next stages into the same
-  // banks; charge the write at a quarter of a read.
-  const double feed_clk = 1.25 * (128.0 * 128 + q_rows * 128.0) / mm.smem_bytes_per_clk;
-  const double blk_clk = std::max(mma_clk, feed_clk);
+  const int q_rows_cta = pair ? block_n / 2 : block_n;
+  const int q_rows = q_mn_major ? round_up(q_rows_cta, bk) : q_rows_cta;  // MN-major boxes are 128 B wide
+  const double stage_bytes = 128.0 * 128 + q_rows * 128.0;
+  // The tensor pipe reads every stage byte once (a pair reads the peer's Q half as well) ...
+  const double read_clk = (128.0 * 128 + (pair ? 2 : 1) * q_rows * 128.0) / mm.smem_bytes_per_clk;
+  // ... and TMA has to deliver the CTA's own stage bytes.
+  const double ingest_clk = stage_bytes / mm.ingest_bytes_per_clk;
+  const double blk_clk = std::max(mma_clk, std::max(read_clk, ingest_clk));
   const long long total = (long long)tiles * k_blocks;
-  double blocks_per_cta;  // the busiest CTA's share
+  double blocks_per_worker;  // the busiest worker's share
   if (schedule == TXD_SCHED_STREAM_K) {
-    blocks_per_cta = (double)((total + grid - 1) / grid);
+    blocks_per_worker = (double)((total + workers - 1) / workers);
   } else {
-    blocks_per_cta = (double)cdiv(tiles, grid) * k_blocks;
+    blocks_per_worker = (double)cdiv(tiles, workers) * k_blocks;
   }
-  const double balance = ((double)total / grid) / blocks_per_cta;  // 1 = every CTA equally loaded
-  double busy_clk = blocks_per_cta * blk_clk;
+  const double balance = ((double)total / workers) / blocks_per_worker;  // 1 = equally loaded
+  double busy_clk = blocks_per_worker * blk_clk;
   if (schedule == TXD_SCHED_STREAM_K) {
     // Up to two partial tiles per CTA go through scratch: fp32 write + read, ~64 B/clk through L2.
     busy_clk += 2.0 * (128.0 * block_n * 4 * 2) / 64.0;
   }
+  // The last tile's epilogue is not hidden behind a main loop.
+  busy_clk += 128.0 * block_n * 4 / 64.0;
   const double t_tensor = busy_clk / (mm.sm_clock_ghz * 1e9);
   // A CTA keeps only its own ring of loads in flight, so few CTAs cannot pull the whole HBM rate,
   // and an unbalanced grid leaves HBM idle while the last CTAs finish.
+  const int ctas = pair ? 2 * workers : workers;
   const double t_hbm =
-      algo_bytes / std::min(mm.hbm_bytes_per_s, grid * mm.hbm_bytes_per_s_per_cta) / balance;
+      algo_bytes / std::min(mm.hbm_bytes_per_s, ctas * mm.hbm_bytes_per_s_per_cta) / balance;
   return std::max(t_tensor, t_hbm) + 3e-6;  // + launch and pipeline fill
 }
 
@@ -142,23 +156,37 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
       if (cfg.block_n && bn != cfg.block_n) continue;
       // Do not pad the Q side by more than one tile's worth beyond need.
       if (!cfg.block_n && bn > 16 && bn / 2 >= q_extent) continue;
-      const int tiles = cdiv(p_extent, 128) * cdiv(q_extent, bn);
-      const int k_blocks = cdiv(pr.k, bk);
-      for (int sched = TXD_SCHED_DATA_PARALLEL; sched <= TXD_SCHED_STREAM_K; ++sched) {
-        if (cfg.schedule && sched != cfg.schedule) continue;
-        long long units = (long long)tiles * (sched == TXD_SCHED_STREAM_K ? k_blocks : 1);
-        if (units < 1) units = 1;
-        const int grid = (int)std::min<long long>(max_grid, units);
-        double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, q_mn, sched, grid, algo);
-        // Prefer the simpler schedule / bigger tile on near-ties.
-        if (sched == TXD_SCHED_STREAM_K) t *= 1.03;
-        if (t < best) {
-          best = t;
-          found = true;
-          out.swap_ab = swap;
-          out.block_n = bn;
-          out.schedule = sched;
-          out.grid = grid;
+      for (int pair = 0; pair <= 1; ++pair) {
+        if (cfg.cta_pair == 1 && !pair) continue;
+        if (cfg.cta_pair == 2 && pair) continue;
+        if (pair) {
+          // Each CTA of a pair holds half of the Q tile, in whole 128-byte-wide boxes when Q is
+          // MN-major; pairs are for big problems in the natural orientation only.
+          if (swap || bn < 128 || (q_mn && (bn / 2) % bk != 0)) continue;
+          if (cfg.cta_pair == 0 && p_extent < 512) continue;
+        }
+        const int tiles = cdiv(p_extent, pair ? 256 : 128) * cdiv(q_extent, bn);
+        const int k_blocks = cdiv(pr.k, bk);
+        for (int sched = TXD_SCHED_DATA_PARALLEL; sched <= TXD_SCHED_STREAM_K; ++sched) {
+          if (cfg.schedule && sched != cfg.schedule) continue;
+          if (pair && sched == TXD_SCHED_STREAM_K) continue;  // stream-K runs on single CTAs only
+          long long units = (long long)tiles * (sched == TXD_SCHED_STREAM_K ? k_blocks : 1);
+          if (units < 1) units = 1;
+          const int max_workers = pair ? max_grid / 2 : max_grid;
+          if (max_workers < 1) continue;
+          const int workers = (int)std::min<long long>(max_workers, units);
+          double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, q_mn, pair != 0, sched, workers, algo);
+          // Prefer the simpler schedule on near-ties.
+          if (sched == TXD_SCHED_STREAM_K) t *= 1.03;
+          if (t < best) {
+            best = t;
+            found = true;
+            out.swap_ab = swap;
+            out.block_n = bn;
+            out.cta_pair = pair;
+            out.schedule = sched;
+            out.grid = pair ? 2 * workers : workers;
+          }
         }
       }
     }
@@ -171,15 +199,17 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
   out.block_k = bk;
   out.p_extent = out.swap_ab ? pr.n : pr.m;
   out.q_extent = out.swap_ab ? pr.m : pr.n;
-  out.tiles_p = cdiv(out.p_extent, 128);
+  out.block_m = out.cta_pair ? 256 : 128;
+  out.tiles_p = cdiv(out.p_extent, out.block_m);
   out.tiles_q = cdiv(out.q_extent, out.block_n);
   out.k_blocks = cdiv(pr.k, bk);
   // LoopSplit mid point: first K index of the masked remainder.
   int mid = cfg.k_split_point > 0 ? cfg.k_split_point : (cfg.k_split_point < 0 ? 0 : (pr.k / bk) * bk);
-  if (mid % bk != 0 || mid > pr.k || mid < 0) {
-    if (why) *why = "k_split_point must be a multiple of BLOCK_K in [0, K]";
+  if (mid > (pr.k / bk) * bk || mid < 0) {
+    if (why) *why = "k_split_point lies past the last full K block: a partial block would run unmasked";
     return -1;
   }
+  mid = (mid / bk) * bk;  // a split inside a physical block moves down: the remainder only adds masking
   out.k_main_blocks = mid / bk;
   const int rem = pr.k - (out.k_blocks - 1) * bk;  // columns in the last block: 1..bk
   const int umma_k = 32 / es;
@@ -188,19 +218,25 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
   const bool q_mn = out.swap_ab ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
   (void)p_mn;
   out.p_stage_bytes = 128 * 128;
-  out.q_stage_bytes = (q_mn ? round_up(out.block_n, bk) : out.block_n) * 128;
+  const int q_rows_cta = out.cta_pair ? out.block_n / 2 : out.block_n;
+  out.q_stage_bytes = (q_mn ? round_up(q_rows_cta, bk) : q_rows_cta) * 128;
   // The Q stage must keep the next P stage 1024-byte aligned.
   out.q_stage_bytes = round_up(out.q_stage_bytes, 1024);
   const int stage_bytes = out.p_stage_bytes + out.q_stage_bytes;
-  int stages = cfg.stages ? cfg.stages : std::min(12, mm.smem_budget / stage_bytes);
-  if (stages < 2 || stages > 12 || stages * stage_bytes > mm.smem_budget) {
+  // C goes out through a shared-memory slab + TMA store when its rows are 16-byte aligned.
+  const int os = elem_bytes(pr.out_dtype);
+  out.tma_store = (!out.swap_ab && out.block_n >= 64 && (pr.ldc * os) % 16 == 0) ? 1 : 0;  // whole 128-byte slabs
+  const int staging = out.tma_store ? 4 * 2 * 32 * 128 : 0;
+  int stages = cfg.stages ? cfg.stages : std::min(12, (mm.smem_budget - staging) / stage_bytes);
+  if (stages < 2 || stages > 12 || stages * stage_bytes + staging > mm.smem_budget) {
     if (why) *why = "stages out of range for this tile (2..12, ring must fit shared memory)";
     return -1;
   }
   out.stages = stages;
-  out.smem_bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 512 /*control block*/;
+  out.smem_bytes = stages * stage_bytes + staging + 1024 /*alignment slack*/ + 512 /*control block*/;
   int cols = 32;
   while (cols < 2 * out.block_n) cols *= 2;
+  if (out.cta_pair) cols = 512;  // both CTAs of a pair must get the same (whole) allocation
   out.tmem_cols = cols;
   if (cfg.group_m > 0) {
     out.group_m = cfg.group_m;
@@ -209,7 +245,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
     int g = 1;
     double best_g = 1e30;
     for (int cand = 1; cand <= 32; cand *= 2) {
-      const double rows = cand * 128.0, cols_e = (double)out.grid / cand * out.block_n;
+      const double rows = cand * (double)out.block_m, cols_e = (double)(out.cta_pair ? out.grid / 2 : out.grid) / cand * out.block_n;
       const double cost = rows + cols_e;
       if (cost < best_g) {
         best_g = cost;
@@ -223,5 +259,27 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
     out.scratch_bytes = (int64_t)out.grid * 2 * out.block_n * 128 * 4 + (int64_t)out.tiles_p * out.tiles_q * 4;
   return 0;
 }
+
+inline void fill_plan_info(const tx_dot_problem &pr, const TileChoice &tc, tx_dot_plan_info *info) {
+  memset(info, 0, sizeof *info);
+  info->block_m = tc.block_m;
+  info->block_n = tc.block_n;
+  info->block_k = tc.block_k;
+  info->stages = tc.stages;
+  info->swap_ab = tc.swap_ab;
+  info->schedule = tc.schedule;
+  info->group_m = tc.group_m;
+  info->grid = tc.grid;
+  info->k_main_iters = tc.k_main_blocks;
+  info->k_tail_iters = tc.k_blocks - tc.k_main_blocks;
+  info->k_tail_mmas = tc.tail_mmas;
+  info->smem_bytes = tc.smem_bytes;
+  info->tmem_columns = tc.tmem_cols;
+  info->cta_pair = tc.cta_pair;
+  info->scratch_bytes = tc.scratch_bytes;
+  info->flops = 2.0 * pr.m * pr.n * pr.k;
+  info->algorithmic_bytes = algorithmic_bytes(pr);
+}
+
 
 }  // namespace txd

@@ -10,8 +10,19 @@
 // remainder loop over [k_main_blocks, k_blocks) in which the operand tiles are zero-filled past K
 // and only the tcgen05.mma instructions that cover real data are issued.
 //
-// Operand roles: "P" is the MMA A operand (128 rows per tile, TMEM lanes), "Q" the MMA B operand
+// Operand roles: "P" is the MMA A operand (128 rows per CTA, TMEM lanes), "Q" the MMA B operand
 // (block_n rows per tile, TMEM columns). The host maps tt.dot's A/B onto P/Q (swapped for skinny m).
+//
+// Two instantiations of one template:
+//   single : one CTA per 128 x block_n tile (tcgen05 cta_group::1); also runs the stream-K schedule.
+//   pair   : a cluster of two CTAs per 256 x block_n tile (cta_group::2). Each CTA loads its own 128
+//            rows of P and its own half of Q; the leader CTA issues MMAs that read both CTAs' shared
+//            memory and write both CTAs' TMEM. A CTA then ingests 2/3 of the bytes per FLOP of the
+//            single variant, which is what the SM's shared-memory fill rate asks for.
+//            No TMA load here uses multicast.
+//
+// Epilogue stores go through a swizzled shared-memory slab and a TMA tensor store (full 128-byte
+// lines) when C allows it, else straight from registers.
 //
 // Every wait on an mbarrier is bounded in time. A wait that runs out raises an abort flag in shared
 // memory and a status word in global memory; all roles then leave their loops, outstanding TMA
@@ -31,6 +42,8 @@ constexpr int kMmasPerBlock = 4;      // 128 B / 32 B per tcgen05.mma
 constexpr int kMaxStages = 12;
 constexpr int kNumThreads = 192;
 constexpr int kEpilogueThreads = 128;
+constexpr int kStoreSlabBytes = 32 * 128;  // one epilogue warp's staging slab: 32 rows x 128 bytes
+constexpr int kStoreStagingBytes = 4 * 2 * kStoreSlabBytes;  // 4 warps, double-buffered
 
 enum DeviceStatus : uint32_t {
   kDevOk = 0,
@@ -44,6 +57,7 @@ enum DeviceStatus : uint32_t {
 struct alignas(64) DotParams {
   CUtensorMap tmap_p;
   CUtensorMap tmap_q;
+  CUtensorMap tmap_out;    // valid when tma_store != 0
   void *out;
   const float *scale_row;  // indexed by the P (lane) index, or null
   const float *scale_col;  // indexed by the Q (column) index, or null
@@ -75,6 +89,8 @@ struct alignas(64) DotParams {
   int32_t chunk_elems;               // 128 B / element size: MN-major box width
   int32_t p_stage_bytes, q_stage_bytes;
   int32_t tmem_cols;
+  int32_t tma_store;                 // 1 = epilogue stores through shared memory + TMA
+  int32_t debug_flags;               // bring-up only: 1 = reuse stale stages, 2 = skip MMAs, 4 = skip stores
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -104,6 +120,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       "{\n"
       ".reg .pred p;\n"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking probe of a barrier phase: never suspends the thread, so a waiter that spins on it
+// reacts within a few cycles of the phase completing.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -205,6 +236,92 @@ __device__ __forceinline__ void epilogue_bar_sync() {
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
+// One lane of a converged warp (the rest of the warp executes the same control flow, so addresses and
+// descriptors stay warp-uniform and can live in uniform registers).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+// ---- cluster / pair variants -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion may be counted on an mbarrier of either CTA of the pair (no multicast:
+// the data lands in the issuing CTA's own shared memory only).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *m, int x, int y,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// ---- TMA tensor store ---------------------------------------------------------------------------
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // ----------------------------------------------------------------------------------------------
 // Bounded waits
 // ----------------------------------------------------------------------------------------------
@@ -214,13 +331,18 @@ struct AbortCtl {
   unsigned long long limit_ns;
 };
 
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const AbortCtl &ac,
-                                            uint32_t code) {
+// The global timer is slow to read (it lives outside the SM), so the common case never touches it:
+// a wait first polls the barrier a few thousand times, and only a wait that is still pending after
+// that starts the clock. The time limit therefore counts from the end of the polling phase.
+constexpr uint32_t kPollsBeforeTimer = 4096;
+
+__device__ __noinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, const AbortCtl &ac,
+                                             uint32_t code) {
   const unsigned long long t0 = global_timer_ns();
   uint32_t it = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++it & 63u) == 0) {
+    if ((++it & 255u) == 0) {
       if (*ac.flag) return false;
       if (global_timer_ns() - t0 > ac.limit_ns) {
         *ac.flag = 1;
@@ -232,12 +354,15 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl &ac,
                                           uint32_t code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, ac, code);
+#pragma unroll 1
+  for (uint32_t it = 0; it < kPollsBeforeTimer; ++it)
+    if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait_timed(bar, parity, ac, code);
 }
 
 // ----------------------------------------------------------------------------------------------
 // Work iteration: every role walks the same sequence of segments (tile, [kb0, kb1)).
+// A "worker" is a CTA (single) or a CTA pair (pair).
 // ----------------------------------------------------------------------------------------------
 struct Segment {
   int tile;
@@ -245,22 +370,20 @@ struct Segment {
 };
 
 struct WorkIter {
-  // data-parallel
-  int next_tile, tile_stride, tiles;
-  // stream-K
-  long long unit, unit_end;
+  int next_tile, tile_stride, tiles;  // whole tiles, round-robin
+  long long unit, unit_end;           // stream-K share
   int k_blocks;
   bool stream_k;
 
-  __device__ __forceinline__ WorkIter(const DotParams &p) {
+  __device__ __forceinline__ WorkIter(const DotParams &p, int worker, int workers) {
     tiles = p.tiles_p * p.tiles_q;
     k_blocks = p.k_blocks;
     stream_k = p.stream_k != 0;
-    next_tile = blockIdx.x;
-    tile_stride = gridDim.x;
+    next_tile = worker;
+    tile_stride = workers;
     const long long total = static_cast<long long>(tiles) * k_blocks;
-    unit = total * blockIdx.x / gridDim.x;
-    unit_end = total * (blockIdx.x + 1) / gridDim.x;
+    unit = total * worker / workers;
+    unit_end = total * (worker + 1) / workers;
   }
   __device__ __forceinline__ bool next(Segment &s) {
     if (!stream_k) {
@@ -282,12 +405,11 @@ struct WorkIter {
   }
 };
 
-// First CTA whose stream-K share contains `unit`.
-__device__ __forceinline__ int stream_k_owner(long long unit, long long total, int grid) {
-  // share c = [total*c/grid, total*(c+1)/grid)
-  int c = static_cast<int>((unit * grid) / total);
-  while (c + 1 < grid && total * (c + 1) / grid <= unit) ++c;
-  while (c > 0 && total * c / grid > unit) --c;
+// The worker whose stream-K share [total*c/n, total*(c+1)/n) contains `unit`.
+__device__ __forceinline__ int stream_k_owner(long long unit, long long total, int workers) {
+  int c = static_cast<int>((unit * workers) / total);
+  while (c + 1 < workers && total * (c + 1) / workers <= unit) ++c;
+  while (c > 0 && total * c / workers > unit) --c;
   return c;
 }
 
@@ -302,7 +424,7 @@ __device__ __forceinline__ void tile_coords(const DotParams &p, int tile, int &t
 }
 
 // ----------------------------------------------------------------------------------------------
-// Epilogue store of one 32-column (or 16-column) chunk held by one thread
+// Epilogue helpers
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack2(float a, float b, int out_dtype) {
   if (out_dtype == 1) {
@@ -313,18 +435,27 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int out_dtype) {
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// acc * alpha * row_scale[p] * col_scale[q] for one thread's chunk of kCols consecutive columns.
 template <int kCols>
-__device__ __forceinline__ void store_chunk(const DotParams &p, float (&f)[32], int prow, int qcol0) {
-  // prow: global P index of this thread's accumulator row; qcol0: global Q index of f[0]
+__device__ __forceinline__ void scale_chunk(const DotParams &p, float (&f)[32], int prow, int qcol0) {
   const bool row_ok = prow < p.p_extent;
   const float rs = (p.scale_row && row_ok) ? __ldg(p.scale_row + prow) * p.alpha : p.alpha;
+  if (p.scale_col) {
 #pragma unroll
-  for (int j = 0; j < kCols; ++j) {
-    float cs = 1.0f;
-    if (p.scale_col && (qcol0 + j) < p.q_extent) cs = __ldg(p.scale_col + qcol0 + j);
-    f[j] = f[j] * rs * cs;
+    for (int j = 0; j < kCols; ++j) {
+      const float cs = (qcol0 + j) < p.q_extent ? __ldg(p.scale_col + qcol0 + j) : 1.0f;
+      f[j] = f[j] * rs * cs;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) f[j] *= rs;
   }
-  if (!row_ok) return;
+}
+
+// Store straight from registers (any alignment, either orientation).
+template <int kCols>
+__device__ __forceinline__ void store_chunk_direct(const DotParams &p, float (&f)[32], int prow, int qcol0) {
+  if (prow >= p.p_extent || (p.debug_flags & 4)) return;
   if (p.trans_out) {
     // out[q*ldo + p]: lanes of a warp hold consecutive p -> coalesced per column
     if (p.out_dtype == 3) {
@@ -384,6 +515,30 @@ __device__ __forceinline__ void store_chunk(const DotParams &p, float (&f)[32], 
   }
 }
 
+// Write 32 consecutive columns of this thread's row into a SWIZZLE_128B staging slab.
+// `byte0` is the byte offset of f[0] inside the 128-byte slab row (a multiple of 16).
+__device__ __forceinline__ void stage_chunk(uint32_t slab, int row_in_slab, int byte0, const float (&f)[32],
+                                            int out_dtype) {
+  const uint32_t row_addr = slab + static_cast<uint32_t>(row_in_slab) * 128u;
+  const uint32_t sw = static_cast<uint32_t>(row_in_slab & 7);
+  if (out_dtype == 3) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint32_t chunk = (static_cast<uint32_t>(byte0 >> 4) + c) ^ sw;
+      st_shared_v4(row_addr + chunk * 16u, __float_as_uint(f[4 * c]), __float_as_uint(f[4 * c + 1]),
+                   __float_as_uint(f[4 * c + 2]), __float_as_uint(f[4 * c + 3]));
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t chunk = (static_cast<uint32_t>(byte0 >> 4) + c) ^ sw;
+      st_shared_v4(row_addr + chunk * 16u, pack2(f[8 * c], f[8 * c + 1], out_dtype),
+                   pack2(f[8 * c + 2], f[8 * c + 3], out_dtype), pack2(f[8 * c + 4], f[8 * c + 5], out_dtype),
+                   pack2(f[8 * c + 6], f[8 * c + 7], out_dtype));
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------------------------
 // The kernel
 // ----------------------------------------------------------------------------------------------
@@ -399,22 +554,27 @@ struct SharedCtl {
   uint32_t epi_ok;
 };
 
-template <int kChunk>  // TMEM columns per tcgen05.ld: 32, or 16 when block_n == 16
-__device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl,
-                                              const AbortCtl &ac, int warp, int lane) {
+template <int kChunk, bool kPair>  // kChunk: TMEM columns per tcgen05.ld (32, or 16 when block_n == 16)
+__device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl, const AbortCtl &ac,
+                                              uint32_t staging, int warp, int lane, int worker, int workers,
+                                              uint32_t cta_rank) {
   const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
   const int row_in_tile = quarter * 32 + lane;  // accumulator row held by this thread
   const int epi_tid = (warp - 2) * 32 + lane;
   const uint32_t tmem_base = ctl->tmem_base;
   const long long total_units = static_cast<long long>(p.tiles_p) * p.tiles_q * p.k_blocks;
-  WorkIter it(p);
+  const int rows_per_tile = kPair ? 2 * kBlockM : kBlockM;
+  const uint32_t my_slabs = staging + static_cast<uint32_t>(quarter) * 2u * kStoreSlabBytes;
+  const int slab_cols = p.out_dtype == 3 ? 32 : 64;  // 128 bytes of output per slab row
+  uint32_t stores = 0;                               // TMA stores issued by this warp (slab parity)
+  WorkIter it(p, worker, workers);
   Segment s;
   uint32_t seg_i = 0;
-  int cta_first_tile = -1;
+  int first_tile = -1;
   while (it.next(s)) {
     const uint32_t acc = seg_i & 1u;
     const uint32_t acc_phase = (seg_i >> 1) & 1u;
-    if (cta_first_tile < 0) cta_first_tile = s.tile;
+    if (first_tile < 0) first_tile = s.tile;
     // One thread watches the barrier and publishes the outcome, so that all 128 epilogue threads
     // take the same branch (they meet again at named barrier 1 below).
     if (epi_tid == 0)
@@ -422,15 +582,53 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
     epilogue_bar_sync();
     const bool seg_ok = ctl->epi_ok != 0;
     epilogue_bar_sync();
-    if (!seg_ok) return;
+    if (!seg_ok) break;
     tc_fence_after();
     int tp, tq;
     tile_coords(p, s.tile, tp, tq);
-    const int prow = tp * kBlockM + row_in_tile;
+    const int prow0 = tp * rows_per_tile + static_cast<int>(cta_rank) * kBlockM;  // first row of this CTA
+    const int prow = prow0 + row_in_tile;
+    const int qcol_tile = tq * p.block_n;
     const uint32_t taddr =
         tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * static_cast<uint32_t>(p.block_n);
+    const uint32_t empty_bar = smem_u32(&ctl->tmem_empty_bar[acc]);
+    auto release_accumulator = [&]() {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (kPair) mbar_arrive_cluster(map_to_cta(empty_bar, 0));
+        else mbar_arrive(empty_bar);
+      }
+    };
     const bool whole = (s.kb1 - s.kb0) == p.k_blocks;
-    if (whole) {
+    if (p.debug_flags & 32) {
+      release_accumulator();
+    } else if (whole && p.tma_store && kChunk == 32) {
+      // TMEM -> registers -> swizzled slab -> TMA store; each warp owns 32 rows and two slabs.
+      for (int c0 = 0; c0 < p.block_n; c0 += slab_cols) {
+        const uint32_t slab = my_slabs + (stores & 1u) * kStoreSlabBytes;
+        if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this slab has drained
+        __syncwarp();
+        for (int h = 0; h < slab_cols; h += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c0 + h, v);
+          tmem_ld_wait();
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          scale_chunk<32>(p, f, prow, qcol_tile + c0 + h);
+          if (!(p.debug_flags & 8)) stage_chunk(slab, lane, h * (p.out_dtype == 3 ? 4 : 2), f, p.out_dtype);
+        }
+        if (c0 + slab_cols >= p.block_n) release_accumulator();
+        if (!(p.debug_flags & 16)) fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && !(p.debug_flags & 4)) {
+          tma_store_2d(&p.tmap_out, slab, qcol_tile + c0, prow0 + quarter * 32);
+          bulk_commit_group();
+        }
+        ++stores;
+      }
+    } else if (whole) {
       for (int c0 = 0; c0 < p.block_n; c0 += kChunk) {
         uint32_t v[32];
         if (kChunk == 32) tmem_ld_32x32(taddr + c0, v); else tmem_ld_32x16(taddr + c0, v);
@@ -438,14 +636,14 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
         float f[32];
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) f[j] = __uint_as_float(v[j]);
-        store_chunk<kChunk>(p, f, prow, tq * p.block_n + c0);
+        scale_chunk<kChunk>(p, f, prow, qcol_tile + c0);
+        store_chunk_direct<kChunk>(p, f, prow, qcol_tile + c0);
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->tmem_empty_bar[acc]));
+      release_accumulator();
     } else {
-      // Partial tile: park the fp32 partial in scratch, column-major inside the tile so that the
-      // 32 lanes of a warp write 128 consecutive bytes.
-      const int slot = blockIdx.x * 2 + (s.tile == cta_first_tile ? 0 : 1);
+      // Partial tile (stream-K, single variant only): park the fp32 partial in scratch, column-major
+      // inside the tile so that the 32 lanes of a warp write 128 consecutive bytes.
+      const int slot = worker * 2 + (s.tile == first_tile ? 0 : 1);
       float *mine = p.partials + static_cast<long long>(slot) * p.block_n * kBlockM;
       for (int c0 = 0; c0 < p.block_n; c0 += kChunk) {
         uint32_t v[32];
@@ -455,12 +653,11 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
         for (int j = 0; j < kChunk; ++j)
           __stcg(mine + static_cast<long long>(c0 + j) * kBlockM + row_in_tile, __uint_as_float(v[j]));
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->tmem_empty_bar[acc]));
-      // Contributors of this tile are the CTAs whose shares intersect its k-block range.
+      release_accumulator();
+      // Contributors of this tile are the workers whose shares intersect its k-block range.
       const long long u0 = static_cast<long long>(s.tile) * p.k_blocks;
-      const int c_first = stream_k_owner(u0, total_units, gridDim.x);
-      const int c_last = stream_k_owner(u0 + p.k_blocks - 1, total_units, gridDim.x);
+      const int c_first = stream_k_owner(u0, total_units, workers);
+      const int c_last = stream_k_owner(u0 + p.k_blocks - 1, total_units, workers);
       __threadfence();
       epilogue_bar_sync();
       if (epi_tid == 0) {
@@ -480,7 +677,7 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
           for (int j = 0; j < kChunk; ++j) f[j] = 0.0f;
           // Sum in ascending k order: deterministic regardless of arrival order.
           for (int c = c_first; c <= c_last; ++c) {
-            const long long cb = total_units * c / gridDim.x;
+            const long long cb = total_units * c / workers;
             const int c_first_tile = static_cast<int>(cb / p.k_blocks);
             const int cslot = c * 2 + (s.tile == c_first_tile ? 0 : 1);
             const float *src = p.partials + static_cast<long long>(cslot) * p.block_n * kBlockM;
@@ -488,26 +685,40 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
             for (int j = 0; j < kChunk; ++j)
               f[j] += __ldcg(src + static_cast<long long>(c0 + j) * kBlockM + row_in_tile);
           }
-          store_chunk<kChunk>(p, f, prow, tq * p.block_n + c0);
+          scale_chunk<kChunk>(p, f, prow, qcol_tile + c0);
+          store_chunk_direct<kChunk>(p, f, prow, qcol_tile + c0);
         }
       }
     }
     ++seg_i;
   }
+  // Shared memory must stay valid until every TMA store has read it.
+  if (lane == 0) bulk_wait_group_all();
 }
 
-__global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_constant__ DotParams p) {
+template <bool kPair>
+__device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   extern __shared__ uint8_t smem_raw[];
   // Stage buffers need 1024-byte alignment (SWIZZLE_128B atoms); the launch asks for 1 KiB of slack.
+  // The pad is the same in every CTA of the grid, so both CTAs of a pair use the same offsets.
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t *smem = smem_raw + pad;
   const uint32_t stage_bytes = static_cast<uint32_t>(p.p_stage_bytes + p.q_stage_bytes);
-  SharedCtl *ctl = reinterpret_cast<SharedCtl *>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  const uint32_t ring_bytes = static_cast<uint32_t>(p.stages) * stage_bytes;
+  const uint32_t staging_bytes = p.tma_store ? static_cast<uint32_t>(kStoreStagingBytes) : 0u;
+  SharedCtl *ctl = reinterpret_cast<SharedCtl *>(smem + ring_bytes + staging_bytes);
   const uint32_t stage_base = smem_u32(smem);
+  const uint32_t staging = stage_base + ring_bytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int rows_per_tile = kPair ? 2 * kBlockM : kBlockM;
+  const int q_rows_per_cta = kPair ? p.block_n / 2 : p.block_n;  // Q rows this CTA loads per tile
 
   AbortCtl ac;
   ac.flag = &ctl->abort_flag;
@@ -521,7 +732,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_c
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&ctl->tmem_empty_bar[a]), kEpilogueThreads);
+      mbar_init(smem_u32(&ctl->tmem_empty_bar[a]), kPair ? 8 : 4);  // one arrival per epilogue warp
     }
     mbar_init(smem_u32(&ctl->drain_bar), 1);
     ctl->abort_flag = 0;
@@ -529,6 +740,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_c
     fence_mbar_init();
     tma_prefetch_desc(&p.tmap_p);
     tma_prefetch_desc(&p.tmap_q);
+    if (p.tma_store) tma_prefetch_desc(&p.tmap_out);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctl->tmem_base), static_cast<uint32_t>(p.tmem_cols));
@@ -536,46 +748,63 @@ __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_c
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      WorkIter it(p);
+    // The whole warp walks the loop; one elected lane arms the barrier and issues the copies.
+    {
+      WorkIter it(p, worker, workers);
       Segment s;
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;
       bool ok = true;
+      const bool issuer = elect_one();
       while (ok && it.next(s)) {
         int tp, tq;
         tile_coords(p, s.tile, tp, tq);
-        const int p0 = tp * kBlockM;
-        const int q0 = tq * p.block_n;
+        const int p0 = tp * rows_per_tile + static_cast<int>(cta_rank) * kBlockM;
+        const int q0 = tq * p.block_n + static_cast<int>(cta_rank) * q_rows_per_cta;
         for (int kb = s.kb0; kb < s.kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer))) {
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&ctl->full_bar[stage]);
-          mbar_arrive_expect_tx(full, stage_bytes);
+          const uint32_t full_local = smem_u32(&ctl->full_bar[stage]);
+          // Pair: every byte of both CTAs is counted on the leader's barrier.
+          const uint32_t full = kPair ? map_to_cta(full_local, 0) : full_local;
+          if ((p.debug_flags & 1) && issued >= static_cast<uint32_t>(p.stages)) {
+            if (leader && issuer) mbar_arrive(full_local);
+            ++issued;
+            if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+          if (issuer) {
+          if (leader) mbar_arrive_expect_tx(full_local, kPair ? 2u * stage_bytes : stage_bytes);
           const uint32_t p_dst = stage_base + stage * stage_bytes;
           const uint32_t q_dst = p_dst + static_cast<uint32_t>(p.p_stage_bytes);
           const int k0 = kb * p.bk_elems;
+          const uint32_t box_bytes = static_cast<uint32_t>(p.bk_elems) * kStageRowBytes;
+          auto load = [&](uint32_t dst, const CUtensorMap *m, int x, int y) {
+            if (kPair) tma_load_2d_pair(dst, m, x, y, full);
+            else tma_load_2d(dst, m, x, y, full);
+          };
           if (!p.p_mn_major) {
-            tma_load_2d(p_dst, &p.tmap_p, k0, p0, full);
+            load(p_dst, &p.tmap_p, k0, p0);
           } else {
-            const uint32_t box_bytes = static_cast<uint32_t>(p.bk_elems) * kStageRowBytes;
             for (int c = 0; c * p.chunk_elems < kBlockM; ++c)
-              tma_load_2d(p_dst + c * box_bytes, &p.tmap_p, p0 + c * p.chunk_elems, k0, full);
+              load(p_dst + c * box_bytes, &p.tmap_p, p0 + c * p.chunk_elems, k0);
           }
           if (!p.q_mn_major) {
-            tma_load_2d(q_dst, &p.tmap_q, k0, q0, full);
+            load(q_dst, &p.tmap_q, k0, q0);
           } else {
-            const uint32_t box_bytes = static_cast<uint32_t>(p.bk_elems) * kStageRowBytes;
-            for (int c = 0; c * p.chunk_elems < p.block_n; ++c)
-              tma_load_2d(q_dst + c * box_bytes, &p.tmap_q, q0 + c * p.chunk_elems, k0, full);
+            for (int c = 0; c * p.chunk_elems < q_rows_per_cta; ++c)
+              load(q_dst + c * box_bytes, &p.tmap_q, q0 + c * p.chunk_elems, k0);
           }
+          }
+          __syncwarp();
           ++issued;
           if (++stage == static_cast<uint32_t>(p.stages)) {
             stage = 0;
@@ -583,12 +812,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_c
           }
         }
       }
-      if (!ok || *ac.flag) {
+      if ((!ok || *ac.flag) && issuer) {
         // Abort path: wait (bounded) until every copy this thread started has landed, so that no
-        // TMA write is in flight when the CTA's shared memory is released.
+        // TMA write is in flight when the CTA's shared memory is released. (Single variant and the
+        // pair's leader; the follower's copies are counted on the leader's barriers.)
         const uint32_t n = issued < static_cast<uint32_t>(p.stages) ? issued : static_cast<uint32_t>(p.stages);
         uint32_t st = stage, ph = phase;
-        for (uint32_t i = 0; i < n; ++i) {
+        for (uint32_t i = 0; i < n && leader; ++i) {
           if (st == 0) {
             st = static_cast<uint32_t>(p.stages);
             ph ^= 1u;
@@ -605,68 +835,100 @@ __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_c
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      WorkIter it(p);
+    // ------------------------------ MMA issuer (leader CTA only in a pair) ------------------------------
+    // The whole warp walks the loop; one elected lane issues tcgen05 instructions.
+    if (leader) {
+      WorkIter it(p, worker, workers);
       Segment s;
       uint32_t stage = 0, phase = 0, seg_i = 0;
       bool ok = true;
+      const bool issuer = elect_one();
+      auto commit_to = [&](uint32_t local_bar) {
+        if (kPair) {
+          // Same barrier in both CTAs: the follower's producer / epilogue wait on their own copy.
+          tc_commit_pair(map_to_cta(local_bar, 0));
+          tc_commit_pair(map_to_cta(local_bar, 1));
+        } else {
+          tc_commit(local_bar);
+        }
+      };
+      auto mma = [&](uint32_t d_tmem, uint64_t pd, uint64_t qd, uint32_t accumulate) {
+        if (kPair) {
+          if (p.kind_f8) umma_f8_pair(d_tmem, pd, qd, p.idesc, accumulate);
+          else umma_f16_pair(d_tmem, pd, qd, p.idesc, accumulate);
+        } else {
+          if (p.kind_f8) umma_f8(d_tmem, pd, qd, p.idesc, accumulate);
+          else umma_f16(d_tmem, pd, qd, p.idesc, accumulate);
+        }
+      };
       while (ok && it.next(s)) {
         const uint32_t acc = seg_i & 1u;
         const uint32_t acc_phase = (seg_i >> 1) & 1u;
-        if (!mbar_wait(smem_u32(&ctl->tmem_empty_bar[acc]), acc_phase ^ 1u, ac, kDevTimeoutMmaTmem)) {
-          ok = false;
-          break;
-        }
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(smem_u32(&ctl->tmem_empty_bar[acc]), acc_phase ^ 1u, ac, kDevTimeoutMmaTmem));
+        if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * static_cast<uint32_t>(p.block_n);
         uint32_t accumulate = 0;
-        // One K block: wait for its stage, issue `n_mma` MMAs, hand the stage back.
-        auto k_block = [&](int n_mma) -> bool {
-          if (!mbar_wait(smem_u32(&ctl->full_bar[stage]), phase, ac, kDevTimeoutMmaFull)) return false;
+        // Software-pipelined K loop. tcgen05.commit holds the issuing thread until the MMAs before it
+        // have been handed to the tensor pipe, so everything that can be done ahead of it is: the wait
+        // for the NEXT stage sits between this block's MMAs and this block's commit and runs while the
+        // MMAs execute. After the commit the next block's MMAs go out at once.
+        auto wait_full = [&](uint32_t st, uint32_t ph) -> bool {
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->full_bar[st]), ph, ac, kDevTimeoutMmaFull))) return false;
           tc_fence_after();
-          const uint32_t p_addr = stage_base + stage * stage_bytes;
+          return true;
+        };
+        auto issue_block = [&](uint32_t st, int n_mma) {
+          const uint32_t p_addr = stage_base + st * stage_bytes;
           const uint32_t q_addr = p_addr + static_cast<uint32_t>(p.p_stage_bytes);
           const uint64_t pdesc = (static_cast<uint64_t>(p.p_desc_hi) << 32) |
                                  static_cast<uint64_t>(p.p_desc_lbo | ((p_addr & 0x3FFFFu) >> 4));
           const uint64_t qdesc = (static_cast<uint64_t>(p.q_desc_hi) << 32) |
                                  static_cast<uint64_t>(p.q_desc_lbo | ((q_addr & 0x3FFFFu) >> 4));
-          if (p.kind_f8) {
+          if (p.debug_flags & 2) n_mma = (accumulate == 0) ? 1 : 0;
+          if (issuer) {
+            if (n_mma == kMmasPerBlock) {
+#pragma unroll
+              for (int j = 0; j < kMmasPerBlock; ++j)
+                mma(d_tmem, pdesc + static_cast<uint64_t>(j * p.p_kstep), qdesc + static_cast<uint64_t>(j * p.q_kstep),
+                    (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
+            } else {
 #pragma unroll 1
-            for (int j = 0; j < n_mma; ++j) {
-              umma_f8(d_tmem, pdesc + static_cast<uint64_t>(j * p.p_kstep),
-                      qdesc + static_cast<uint64_t>(j * p.q_kstep), p.idesc, accumulate);
-              accumulate = 1;
-            }
-          } else {
-#pragma unroll 1
-            for (int j = 0; j < n_mma; ++j) {
-              umma_f16(d_tmem, pdesc + static_cast<uint64_t>(j * p.p_kstep),
-                       qdesc + static_cast<uint64_t>(j * p.q_kstep), p.idesc, accumulate);
-              accumulate = 1;
+              for (int j = 0; j < n_mma; ++j)
+                mma(d_tmem, pdesc + static_cast<uint64_t>(j * p.p_kstep), qdesc + static_cast<uint64_t>(j * p.q_kstep),
+                    (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
             }
           }
-          tc_commit(smem_u32(&ctl->empty_bar[stage]));  // frees the stage when these MMAs retire
-          if (++stage == static_cast<uint32_t>(p.stages)) {
-            stage = 0;
-            phase ^= 1u;
-          }
-          return true;
+          if (n_mma > 0) accumulate = 1;
         };
-        // LoopSplit main loop [lo, mid): every block is full, no predication of any kind.
+        // LoopSplit: blocks below `mid` belong to the main loop [lo, mid) — full, unpredicated; blocks
+        // from `mid` on are the remainder loop [mid, hi), whose stages TMA zero-filled past K and whose
+        // last block issues only the MMAs that cover real columns.
         const int mid = s.kb1 < p.k_main_blocks ? s.kb1 : p.k_main_blocks;
-        int kb = s.kb0;
-        for (; ok && kb < mid; ++kb) ok = k_block(kMmasPerBlock);
-        // LoopSplit remainder loop [mid, hi): TMA zero-filled the stage past K; the last block
-        // issues only the MMAs that cover real columns.
-        for (; ok && kb < s.kb1; ++kb)
-          ok = k_block(kb == p.k_blocks - 1 ? p.tail_mmas : kMmasPerBlock);
-        if (ok) tc_commit(smem_u32(&ctl->tmem_full_bar[acc]));
+        ok = wait_full(stage, phase);
+        for (int kb = s.kb0; ok && kb < s.kb1; ++kb) {
+          const bool in_main = kb < mid;
+          issue_block(stage, (in_main || kb != p.k_blocks - 1) ? kMmasPerBlock : p.tail_mmas);
+          uint32_t next_stage = stage + 1, next_phase = phase;
+          if (next_stage == static_cast<uint32_t>(p.stages)) {
+            next_stage = 0;
+            next_phase ^= 1u;
+          }
+          if (kb + 1 < s.kb1) ok = wait_full(next_stage, next_phase);
+          if (issuer) commit_to(smem_u32(&ctl->empty_bar[stage]));  // frees the stage when its MMAs retire
+          __syncwarp();
+          stage = next_stage;
+          phase = next_phase;
+        }
+        if (ok && issuer) commit_to(smem_u32(&ctl->tmem_full_bar[acc]));
+        __syncwarp();
         ++seg_i;
       }
-      if (!ok || *ac.flag) {
+      if ((!ok || *ac.flag) && issuer) {
         // Abort path: make sure no MMA is still reading shared memory / writing TMEM.
-        tc_commit(smem_u32(&ctl->drain_bar));
+        if (kPair) tc_commit_pair(map_to_cta(smem_u32(&ctl->drain_bar), 0));
+        else tc_commit(smem_u32(&ctl->drain_bar));
         const unsigned long long t0 = global_timer_ns();
         while (!mbar_try_wait(smem_u32(&ctl->drain_bar), 0)) {
           if (global_timer_ns() - t0 > ac.limit_ns) {
@@ -675,21 +937,33 @@ __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_c
           }
         }
       }
+      __syncwarp();
     }
   } else {
     // ------------------------------ epilogue ------------------------------
     if (p.block_n >= 32)
-      epilogue_role<32>(p, ctl, ac, warp, lane);
+      epilogue_role<32, kPair>(p, ctl, ac, staging, warp, lane, worker, workers, cta_rank);
     else
-      epilogue_role<16>(p, ctl, ac, warp, lane);
+      epilogue_role<16, kPair>(p, ctl, ac, staging, warp, lane, worker, workers, cta_rank);
   }
 
   tc_fence_before();
   __syncthreads();
+  // Pair: neither CTA may leave while the other can still signal its barriers, read its shared
+  // memory (MMA) or write its TMEM.
+  if (kPair) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
+}
+
+__global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_constant__ DotParams p) {
+  dot_umma_body<false>(p);
+}
+
+__global__ void __launch_bounds__(kNumThreads, 1) dot_umma_pair_kernel(const __grid_constant__ DotParams p) {
+  dot_umma_body<true>(p);
 }
 
 }  // namespace txd
