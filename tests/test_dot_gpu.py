@@ -1,0 +1,260 @@
+"""Parity of the CUDA kernels with the oracle, through the C-ABI (ctypes -> libb200_dot.so).
+
+Tolerances are north_star's: rtol = atol = 1e-2 for f16/bf16, 3e-2 for scaled fp8. The interpreter
+oracle truncates fp32->bf16 where the kernels round to nearest even, so bf16 outputs are never compared
+bit for bit with the oracle; bit-exact checks are made only between runs of the kernels themselves.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.cases import (CFG1, CFG2, CFG3, CFG4, CFG5, GOLDEN_CASES, Case, make_inputs, reference_fp64, tolerance_ok)
+from tests.test_oracle import DTYPE_CODE, c_oracle, golden_tensor
+
+pytestmark = pytest.mark.gpu
+
+bf16, f16, f8, f32 = torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float32
+
+
+@pytest.fixture(scope="module")
+def B(built_libs, cuda_device):
+    from triton_ext_b200 import backend
+    assert backend.load_library().tx_dot_device_count() >= 1
+    return backend
+
+
+@pytest.fixture(scope="module")
+def dot_lib(built_libs):
+    lib = ctypes.CDLL(built_libs["oracles"]["libdot_oracle.so"])
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+    lib.dot_oracle_tiles.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i64, i64,
+                                     ctypes.c_float, i32, i32, i32, i32, vp, i32]
+    lib.dot_oracle_tiles.restype = ctypes.c_int
+    return lib
+
+
+def gpu_dot(B, case, a, b, rs, cs, config=None):
+    dev = torch.device("cuda:0")
+    ad, bd = a.to(dev), b.to(dev)          # .to() keeps strides, so transposed layouts survive
+    out = B.dot(ad, bd, out_dtype=case.out_dtype, row_scale=rs.to(dev) if rs is not None else None,
+                col_scale=cs.to(dev) if cs is not None else None, alpha=case.alpha, config=config, check=True)
+    return out.cpu()
+
+
+def bits(t):
+    return t.contiguous().view(torch.int32 if t.dtype == torch.float32 else torch.int16)
+
+
+# ---- 1. every golden case: kernels vs committed oracle output vs exact arithmetic ---------------------------
+@pytest.mark.parametrize("case", GOLDEN_CASES, ids=lambda c: c.name)
+def test_golden_cases(B, case):
+    launches = B.kernel_launches()
+    a, b, rs, cs = make_inputs(case)
+    got = gpu_dot(B, case, a, b, rs, cs)
+    assert B.kernel_launches() > launches, "no kernel of this library was launched"
+    want = golden_tensor(case.name, case.out_dtype)
+    ok, err = tolerance_ok(got, want, case.rtol, case.atol)
+    assert ok, f"vs oracle fixture: max err {err}"
+    ok, err = tolerance_ok(got, reference_fp64(case, a, b, rs, cs), case.rtol, case.atol)
+    assert ok, f"vs fp64: max err {err}"
+
+
+# ---- 2. shape sweep against the C oracle (edges: 1, sub-tile, tile +- 1, ragged K) ---------------------------
+SWEEP = [(1, 8, 8), (7, 16, 24), (8, 8, 8), (63, 64, 72), (64, 64, 64), (65, 72, 136), (127, 128, 120),
+         (128, 128, 128), (129, 136, 200), (255, 264, 72), (256, 512, 320), (300, 520, 1000), (513, 40, 264)]
+
+
+@pytest.mark.parametrize("m,n,k", SWEEP)
+@pytest.mark.parametrize("dt", [bf16, f16, f8])
+def test_shape_sweep(B, dot_lib, m, n, k, dt):
+    if dt == f8 and (k % 16 or n % 16):
+        pytest.skip("fp8 rows must be 16-byte aligned for TMA")
+    case = Case(f"sweep_{m}x{n}x{k}", m, n, k, dt, bf16 if dt == f8 else dt, seed=100 + m + n + k,
+                scales=(dt == f8), block=(64, 64, 64), rtol=3e-2 if dt == f8 else 1e-2, atol=3e-2 if dt == f8 else 1e-2)
+    a, b, rs, cs = make_inputs(case)
+    got = gpu_dot(B, case, a, b, rs, cs)
+    want = c_oracle(dot_lib, case, a, b, rs, cs, bf16_truncate=False)
+    ok, err = tolerance_ok(got, want, case.rtol, case.atol)
+    assert ok, f"max err {err}"
+
+
+# ---- 3. every kernel configuration on one problem ------------------------------------------------------------
+CONFIGS = [
+    dict(block_n=256, cta_pair=1), dict(block_n=128, cta_pair=1), dict(block_n=256, cta_pair=1, stages=3, group_m=1),
+    dict(block_n=256, cta_pair=2, schedule=1), dict(block_n=128, cta_pair=2, schedule=1), dict(block_n=64, cta_pair=2, schedule=1),
+    dict(block_n=32, cta_pair=2, schedule=1), dict(block_n=16, cta_pair=2, schedule=1),
+    dict(block_n=256, cta_pair=2, schedule=2), dict(block_n=64, cta_pair=2, schedule=2, max_ctas=37),
+    dict(swap_ab=1, block_n=128, cta_pair=2, schedule=1), dict(swap_ab=1, block_n=16, cta_pair=2, schedule=2),
+    dict(block_n=128, cta_pair=2, schedule=1, stages=2), dict(block_n=256, cta_pair=1, max_ctas=6),
+]
+
+
+@pytest.mark.parametrize("kw", CONFIGS, ids=lambda kw: ",".join(f"{k}={v}" for k, v in kw.items()))
+@pytest.mark.parametrize("layout", ["row,row", "row,col", "col,row", "col,col"])
+def test_config_sweep(B, dot_lib, kw, layout):
+    la, lb = layout.split(",")
+    case = Case("cfgsweep", 520, 776, 1096, bf16, bf16, seed=21, a_t=(la == "col"), b_t=(lb == "col"), block=(64, 64, 64))
+    a, b, rs, cs = make_inputs(case)
+    got = gpu_dot(B, case, a, b, rs, cs, config=B.make_config(**kw))
+    want = c_oracle(dot_lib, case, a, b, rs, cs, bf16_truncate=False)
+    ok, err = tolerance_ok(got, want, case.rtol, case.atol)
+    assert ok, f"max err {err}"
+
+
+# ---- 4. BASELINE configurations at full size --------------------------------------------------------------------
+def check_full_size(B, dot_lib, case, n_c_tiles, n_interp_tiles, config=None):
+    from oracle.interp_dot import interp_dot, sample_tiles, tile_mask
+    a, b, rs, cs = make_inputs(case)
+    got = gpu_dot(B, case, a, b, rs, cs, config=config)
+    bm, bn, bk = case.block
+    ids = sample_tiles(case.m, case.n, bm, bn, n_c_tiles, seed=case.seed)
+    want = c_oracle(dot_lib, case, a, b, rs, cs, bf16_truncate=False, tile_ids=ids)
+    mask = tile_mask(case.m, case.n, bm, bn, ids)
+    ok, err = tolerance_ok(got[mask], want[mask], case.rtol, case.atol)
+    assert ok, f"vs C oracle on {len(ids)} tiles: max err {err}"
+    ids2 = ids[:n_interp_tiles]
+    y = interp_dot(a, b, out_dtype=case.out_dtype, block_m=bm, block_n=bn, block_k=bk, row_scale=rs, col_scale=cs,
+                   alpha=case.alpha, tile_ids=ids2)
+    mask2 = tile_mask(case.m, case.n, bm, bn, ids2)
+    ok, err = tolerance_ok(got[mask2], y[mask2], case.rtol, case.atol)
+    assert ok, f"vs interpreter oracle on {len(ids2)} tiles: max err {err}"
+    return a, b, rs, cs, got
+
+
+def test_cfg1_fp16_512(B, dot_lib):
+    a, b, rs, cs, got = check_full_size(B, dot_lib, CFG1, 64, 8)
+    want = golden_tensor(CFG1.name, f16)          # fp16 casts round the same way on both sides:
+    assert float((bits(got) != bits(want)).float().mean()) < 0.02  # only fp32 summation order differs
+
+
+def test_cfg2_loop_split_tail(B, dot_lib):
+    cfg = B.make_config(k_split_point=4096)       # BLOCK_K = 128: main [0, 4096), 64-wide remainder
+    a, b, rs, cs, got = check_full_size(B, dot_lib, CFG2, 12, 2, config=cfg)
+    dev = torch.device("cuda:0")
+    ad, bd = a.to(dev), b.to(dev)
+    # the split point never changes a bit of the result
+    for split in (0, -1, 2048, 4160 // 64 * 64):
+        other = B.dot(ad, bd, out_dtype=bf16, config=B.make_config(k_split_point=split), check=True).cpu()
+        assert torch.equal(bits(other), bits(got)), f"k_split_point={split}"
+    # linearity in a power-of-two alpha is exact
+    twice = B.dot(ad, bd, out_dtype=bf16, alpha=2.0, check=True).cpu()
+    assert torch.equal(bits(twice), bits((got.float() * 2).to(bf16)))
+    # (A B)^T = B^T A^T: swapping the operand roles accumulates in the same k order
+    swapped = B.dot(bd.t(), ad.t(), out_dtype=bf16, check=True).cpu()
+    assert torch.equal(bits(swapped.t().contiguous()), bits(got))
+    # pair / single / stream-K agree within tolerance (stream-K sums partial tiles in a different order)
+    for kw in (dict(cta_pair=2, schedule=1), dict(cta_pair=2, schedule=2)):
+        other = B.dot(ad, bd, out_dtype=bf16, config=B.make_config(**kw), check=True).cpu()
+        ok, err = tolerance_ok(other, got, 1e-2, 1e-2)
+        assert ok, (kw, err)
+
+
+def test_cfg3_decode_skinny(B, dot_lib):
+    a, b, rs, cs, got = check_full_size(B, dot_lib, CFG3, 112, 4)
+    dev = torch.device("cuda:0")
+    again = B.dot(a.to(dev), b.to(dev), out_dtype=bf16, check=True).cpu()
+    assert torch.equal(bits(again), bits(got)), "stream-K fix-up must be deterministic"
+
+
+def test_cfg4_fp8_scaled(B, dot_lib):
+    check_full_size(B, dot_lib, CFG4, 6, 1)
+
+
+def test_cfg5_big_bf16_and_n_shards(B, dot_lib):
+    from triton_ext_b200.parallel import split_range
+    a, b, rs, cs, got = check_full_size(B, dot_lib, CFG5, 4, 1)
+    dev = torch.device("cuda:0")
+    ad, bd = a.to(dev), b.to(dev)
+    # an N-shard computed alone is bit-identical to the same columns of the unsharded result
+    for world, rank in ((2, 1), (8, 5)):
+        n0, n1 = split_range(CFG5.n, world, rank, align=256)
+        panel = B.dot(ad, bd[:, n0:n1], out_dtype=bf16, check=True).cpu()
+        assert torch.equal(bits(panel), bits(got[:, n0:n1].contiguous()))
+
+
+# ---- 5. the host-buffer entry point ------------------------------------------------------------------------------
+def test_run_host_matches_device_path(B):
+    case = Case("host", 384, 520, 264, bf16, bf16, seed=31, scales=True)
+    a, b, rs, cs = make_inputs(case)
+    want = gpu_dot(B, case, a, b, rs, cs)
+    plan = B.DotPlan(B.make_problem(case.m, case.n, case.k, bf16, bf16, row_scale=True, col_scale=True))
+    out = torch.empty(case.m, case.n, dtype=bf16).pin_memory()
+    for _ in range(2):
+        out.zero_()
+        plan.run_host(a.contiguous().pin_memory(), b.contiguous().pin_memory(), out, rs, cs)
+        assert torch.equal(bits(out), bits(want))
+    plan.close()
+
+
+def test_empty_and_zero_k(B):
+    dev = torch.device("cuda:0")
+    out = B.dot(torch.zeros(0, 64, dtype=bf16, device=dev), torch.zeros(64, 32, dtype=bf16, device=dev), check=True)
+    assert out.shape == (0, 32)
+    out = torch.full((16, 24), 7.0, dtype=bf16, device=dev)
+    B.dot(torch.zeros(16, 0, dtype=bf16, device=dev), torch.zeros(0, 24, dtype=bf16, device=dev), out=out, check=True)
+    assert bool((out == 0).all())
+
+
+def test_padded_leading_dimensions(B, dot_lib):
+    dev = torch.device("cuda:0")
+    case = Case("ld", 200, 136, 72, bf16, bf16, seed=41, block=(64, 64, 64))
+    a, b, rs, cs = make_inputs(case)
+    abig = torch.zeros(200, 96, dtype=bf16, device=dev)
+    bbig = torch.zeros(72, 160, dtype=bf16, device=dev)
+    cbig = torch.full((200, 144), 3.0, dtype=bf16, device=dev)
+    abig[:, :72] = a.to(dev)
+    bbig[:, :136] = b.to(dev)
+    B.dot(abig[:, :72], bbig[:, :136], out=cbig[:, :136], check=True)
+    want = c_oracle(dot_lib, case, a, b, None, None, bf16_truncate=False)
+    ok, err = tolerance_ok(cbig[:, :136].cpu(), want, 1e-2, 1e-2)
+    assert ok, err
+    assert bool((cbig[:, 136:] == 3.0).all()), "columns outside C were written"
+
+
+# ---- 6. the pass pipeline drives the kernels ---------------------------------------------------------------------
+def test_pipeline_to_plan(B, dot_lib):
+    from triton_ext_b200 import plugin as P
+    case = Case("pipe", 512, 512, 1096, bf16, bf16, seed=51, block=(64, 64, 128))
+    a, b, rs, cs = make_inputs(case)
+    pr = B.make_problem(case.m, case.n, case.k, bf16, bf16)
+    cfg, info, module = P.lower_dot(pr, 128)
+    assert cfg.k_split_point == 1024 and info["k_main_iters"] == 16 and info["k_tail_iters"] == 2
+    lib = B.load_library()
+    lib.txir_module_create_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]
+    h = ctypes.c_void_p()
+    assert lib.txir_module_create_plan(module._h, 0, ctypes.byref(h)) == B.TXD_OK
+    dev = torch.device("cuda:0")
+    ad, bd = a.to(dev), b.to(dev)
+    out = torch.empty(case.m, case.n, dtype=bf16, device=dev)
+    s = torch.cuda.current_stream()
+    assert lib.tx_dot_run(h, ad.data_ptr(), bd.data_ptr(), out.data_ptr(), None, None, ctypes.c_void_p(s.cuda_stream)) == B.TXD_OK
+    assert lib.tx_dot_plan_check(h, ctypes.c_void_p(s.cuda_stream)) == B.TXD_OK
+    lib.tx_dot_plan_destroy(h)
+    want = c_oracle(dot_lib, case, a, b, None, None, bf16_truncate=False)
+    ok, err = tolerance_ok(out.cpu(), want, 1e-2, 1e-2)
+    assert ok, err
+
+
+# ---- 7. a wait that runs out is reported, and the context stays usable ----------------------------------------
+def test_bounded_wait_reports_timeout(B, monkeypatch):
+    dev = torch.device("cuda:0")
+    a = torch.randn(256, 512, device=dev).to(bf16)
+    b = torch.randn(512, 256, device=dev).to(bf16)
+    out = torch.empty(256, 256, dtype=bf16, device=dev)
+    monkeypatch.setenv("TXD_INJECT_STALL", "1")    # the producer stops after its first K block
+    monkeypatch.setenv("TXD_WAIT_LIMIT_MS", "50")
+    plan = B.DotPlan(B.make_problem(256, 256, 512, bf16, bf16), B.make_config(cta_pair=2, schedule=1))
+    monkeypatch.delenv("TXD_INJECT_STALL")
+    monkeypatch.delenv("TXD_WAIT_LIMIT_MS")
+    plan.run(a, b, out)
+    with pytest.raises(B.DotError) as e:
+        plan.check()
+    assert e.value.status == B.TXD_ERR_DEVICE_TIMEOUT
+    plan.close()
+    # same context, healthy plan: still works
+    good = B.dot(a, b, out_dtype=bf16, check=True)
+    ref = a.float() @ b.float()
+    assert bool(((good.float() - ref).abs() <= 1e-2 + 1e-2 * ref.abs()).all())

@@ -1,0 +1,84 @@
+"""The arithmetic-intensity analysis (no GPU): what it picks for the BASELINE configurations, that
+explicit settings are respected, and the C-ABI's argument checking."""
+import ctypes
+
+import pytest
+import torch
+
+from triton_ext_b200 import backend as B
+
+bf16, f16, f8, f32 = torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float32
+
+
+def test_library_loads_without_a_gpu(built_libs):
+    lib = B.load_library()
+    assert lib.tx_dot_device_count() >= 0
+    assert B.kernel_launches() >= 0
+
+
+def test_compute_bound_shapes_get_cta_pairs_and_big_tiles(built_libs):
+    for m, n, k, dt in [(4096, 4096, 4160, bf16), (8192, 8192, 8192, f8), (16384, 28672, 8192, bf16), (16384, 3584, 8192, bf16)]:
+        info = B.preview(B.make_problem(m, n, k, dt, bf16))
+        assert info["cta_pair"] == 1 and info["block_m"] == 256 and info["block_n"] == 256, (m, n, k, info)
+        assert info["grid"] == 148 and info["swap_ab"] == 0
+        assert info["smem_bytes"] <= 227 * 1024 and info["tmem_columns"] == 512
+        assert info["block_k"] * (1 if dt == f8 else 2) == 128
+
+
+def test_decode_shape_is_swapped_and_streamed(built_libs):
+    info = B.preview(B.make_problem(16, 14336, 4096, bf16, bf16))
+    assert info["swap_ab"] == 1 and info["block_n"] == 16 and info["cta_pair"] == 0
+    assert info["schedule"] == B.TXD_SCHED_STREAM_K and info["scratch_bytes"] > 0
+    assert info["algorithmic_bytes"] == 16 * 4096 * 2 + 4096 * 14336 * 2 + 16 * 14336 * 2
+
+
+def test_split_point_fields(built_libs):
+    info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16))
+    assert (info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (65, 0, 4)
+    info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16), B.make_config(k_split_point=4096))
+    assert (info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (64, 1, 4)
+    info = B.preview(B.make_problem(256, 256, 200, bf16, bf16))
+    assert (info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (3, 1, 1)  # 200 = 3*64 + 8
+    info = B.preview(B.make_problem(256, 256, 200, bf16, bf16), B.make_config(k_split_point=-1))
+    assert (info["k_main_iters"], info["k_tail_iters"]) == (0, 4)
+    with pytest.raises(B.DotError) as e:
+        B.preview(B.make_problem(256, 256, 200, bf16, bf16), B.make_config(k_split_point=256))
+    assert e.value.status == B.TXD_ERR_INVALID
+
+
+def test_explicit_config_is_kept(built_libs):
+    info = B.preview(B.make_problem(1024, 1024, 1024, bf16, bf16),
+                     B.make_config(block_n=64, stages=3, cta_pair=2, schedule=2, group_m=2, max_ctas=40))
+    assert (info["block_n"], info["stages"], info["cta_pair"], info["schedule"], info["group_m"]) == (64, 3, 0, 2, 2)
+    assert info["grid"] <= 40
+    with pytest.raises(B.DotError):
+        B.preview(B.make_problem(1024, 1024, 1024, bf16, bf16), B.make_config(block_n=256, stages=12))  # ring too big
+
+
+def test_argument_checks(built_libs):
+    bad = [
+        (B.make_problem(-1, 8, 8, bf16, bf16), B.TXD_ERR_INVALID),
+        (B.make_problem(64, 64, 64, f32, f32), B.TXD_ERR_UNSUPPORTED),       # fp32 operands are not tt.dot tensor-core types
+        (B.make_problem(64, 64, 64, bf16, f8), B.TXD_ERR_UNSUPPORTED),       # fp8 output
+        (B.make_problem(64, 64, 60, bf16, bf16), B.TXD_ERR_UNSUPPORTED),     # lda = 60: rows not 16-byte aligned
+        (B.make_problem(64, 60, 64, bf16, bf16), B.TXD_ERR_UNSUPPORTED),     # ldb = 60
+        (B.make_problem(64, 64, 64, bf16, bf16, lda=32), B.TXD_ERR_INVALID),  # lda < k
+    ]
+    for pr, status in bad:
+        with pytest.raises(B.DotError) as e:
+            B.preview(pr)
+        assert e.value.status == status, B.load_library().tx_dot_last_error()
+    info = B.PlanInfo()
+    assert B.load_library().tx_dot_plan_preview(None, None, 148, ctypes.byref(info)) == B.TXD_ERR_INVALID
+    # empty problems are legal and need no kernel
+    assert B.preview(B.make_problem(0, 64, 64, bf16, bf16))["grid"] == 0
+
+
+def test_no_gpu_means_no_compute(built_libs):
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(B.DotError) as e:
+        B.DotPlan(B.make_problem(128, 128, 128, bf16, bf16))
+    assert e.value.status == B.TXD_ERR_NO_DEVICE
+    with pytest.raises(ValueError):
+        B.dot(torch.zeros(8, 8, dtype=bf16), torch.zeros(8, 8, dtype=bf16))

@@ -111,8 +111,9 @@ int validate(const tx_dot_problem &pr) {
   if (pr.lda < a_min || pr.ldb < b_min || pr.ldc < pr.n)
     return fail(TXD_ERR_INVALID, "leading dimension smaller than the row length (lda=%lld ldb=%lld ldc=%lld)",
                 (long long)pr.lda, (long long)pr.ldb, (long long)pr.ldc);
-  // TMA: every global stride is a multiple of 16 bytes.
-  if ((pr.lda * es) % 16 != 0 || (pr.ldb * es) % 16 != 0)
+  // TMA: every global stride is a multiple of 16 bytes (no operand is read when an extent is zero).
+  const bool empty = pr.m == 0 || pr.n == 0 || pr.k == 0;
+  if (!empty && ((pr.lda * es) % 16 != 0 || (pr.ldb * es) % 16 != 0))
     return fail(TXD_ERR_UNSUPPORTED,
                 "lda and ldb must be multiples of %d elements (TMA needs 16-byte row strides); pad the operands",
                 16 / es);
@@ -314,7 +315,10 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
   bp.q_stage_bytes = tc.q_stage_bytes;
   bp.tmem_cols = tc.tmem_cols;
   bp.status = pl->status;
-  if (const char *e = getenv("TXD_DEBUG_FLAGS")) bp.debug_flags = atoi(e);
+  if (const char *e = getenv("TXD_DEBUG_FLAGS")) bp.debug_flags = atoi(e) & 7;   // measurement switches
+  if (const char *e = getenv("TXD_INJECT_STALL")) {                                   // host-side fault injection
+    if (atoi(e) != 0) bp.debug_flags |= 128;
+  }
 
   if (tc.scratch_bytes > 0) {
     TXD_CUDA(cudaMalloc(&pl->scratch, static_cast<size_t>(tc.scratch_bytes)));

@@ -176,8 +176,12 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
           if (max_workers < 1) continue;
           const int workers = (int)std::min<long long>(max_workers, units);
           double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, q_mn, pair != 0, sched, workers, algo);
-          // Prefer the simpler schedule on near-ties.
+          // Prefer the simpler schedule on near-ties, and the role assignment that pads less: zero
+          // rows still cost shared-memory fill and tensor cycles even when HBM time hides them.
           if (sched == TXD_SCHED_STREAM_K) t *= 1.03;
+          const double tile_rows = pair ? 256.0 : 128.0;
+          const double padded = (double)cdiv(p_extent, (int)tile_rows) * tile_rows * cdiv(q_extent, bn) * bn;
+          t *= 1.0 + 0.25 * (1.0 - (double)p_extent * q_extent / padded);
           if (t < best) {
             best = t;
             found = true;

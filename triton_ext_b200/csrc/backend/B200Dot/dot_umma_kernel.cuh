@@ -90,7 +90,11 @@ struct alignas(64) DotParams {
   int32_t p_stage_bytes, q_stage_bytes;
   int32_t tmem_cols;
   int32_t tma_store;                 // 1 = epilogue stores through shared memory + TMA
-  int32_t debug_flags;               // bring-up only: 1 = reuse stale stages, 2 = skip MMAs, 4 = skip stores
+  int32_t debug_flags;               // measurement / test switches, 0 in production (results are wrong
+                                     // when set): 1 = do not refill stages (tensor-pipe-only timing),
+                                     // 2 = one MMA per tile (load-only timing), 4 = skip C stores,
+                                     // 128 = producer stops after its first K block (exercises the
+                                     // bounded waits)
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -601,9 +605,7 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
       }
     };
     const bool whole = (s.kb1 - s.kb0) == p.k_blocks;
-    if (p.debug_flags & 32) {
-      release_accumulator();
-    } else if (whole && p.tma_store && kChunk == 32) {
+    if (whole && p.tma_store && kChunk == 32) {
       // TMEM -> registers -> swizzled slab -> TMA store; each warp owns 32 rows and two slabs.
       for (int c0 = 0; c0 < p.block_n; c0 += slab_cols) {
         const uint32_t slab = my_slabs + (stores & 1u) * kStoreSlabBytes;
@@ -617,10 +619,10 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
           scale_chunk<32>(p, f, prow, qcol_tile + c0 + h);
-          if (!(p.debug_flags & 8)) stage_chunk(slab, lane, h * (p.out_dtype == 3 ? 4 : 2), f, p.out_dtype);
+          stage_chunk(slab, lane, h * (p.out_dtype == 3 ? 4 : 2), f, p.out_dtype);
         }
         if (c0 + slab_cols >= p.block_n) release_accumulator();
-        if (!(p.debug_flags & 16)) fence_proxy_async();
+        fence_proxy_async();
         __syncwarp();
         if (lane == 0 && !(p.debug_flags & 4)) {
           tma_store_2d(&p.tmap_out, slab, qcol_tile + c0, prow0 + quarter * 32);
@@ -769,6 +771,10 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         const int q0 = tq * p.block_n + static_cast<int>(cta_rank) * q_rows_per_cta;
         for (int kb = s.kb0; kb < s.kb1; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer))) {
+            ok = false;
+            break;
+          }
+          if ((p.debug_flags & 128) && issued >= 1) {  // injected stall: nothing arrives any more
             ok = false;
             break;
           }

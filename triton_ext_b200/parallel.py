@@ -1,0 +1,111 @@
+"""Multi-GPU partitioning of one tt.dot GEMM: one process per GPU, `torch.distributed` for plumbing.
+
+Two partitions, as the path's two natural cuts:
+
+  N-sharded (column-parallel)  rank r owns B[:, n0:n1] and produces C[:, n0:n1]; A is replicated.
+                               Independent output panels: no data-path collective at all.
+  K-sharded                    rank r owns A[:, k0:k1] and B[k0:k1, :], produces a full-size fp32
+                               partial of C, and one NCCL reduce-scatter (sum) over NVLink leaves
+                               rank r with rows [m0:m1) of C, which it casts to the output type.
+
+The reference has no multi-GPU code; these follow the partitioning its tt.dot tiles allow
+(independent output tiles; K blocks summed into one accumulator,
+pass/LoopSplit/06-fused-attention.py:85).
+
+`local_dot` is the per-rank GEMM. It defaults to the CUDA kernels (triton_ext_b200.backend.dot);
+the CPU tests of the partition logic pass the oracle instead. Nothing here falls back by itself.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def split_range(extent: int, parts: int, index: int, align: int = 1) -> tuple[int, int]:
+    """[lo, hi) of part `index` when `extent` is cut into `parts` pieces whose boundaries are multiples
+    of `align` (the last piece takes the remainder). Pieces differ by at most one aligned unit."""
+    if parts <= 0 or not (0 <= index < parts):
+        raise ValueError("bad partition index")
+    units = (extent + align - 1) // align
+    base, extra = divmod(units, parts)
+    lo_u = index * base + min(index, extra)
+    hi_u = lo_u + base + (1 if index < extra else 0)
+    return min(lo_u * align, extent), min(hi_u * align, extent)
+
+
+def _default_local_dot():
+    from . import backend
+    return backend.dot
+
+
+def n_sharded_dot(a: torch.Tensor, b_shard: torch.Tensor, *, out_dtype: torch.dtype,
+                  row_scale: Optional[torch.Tensor] = None, col_scale_shard: Optional[torch.Tensor] = None,
+                  alpha: float = 1.0, local_dot: Optional[Callable] = None, **kw) -> torch.Tensor:
+    """This rank's panel C[:, n0:n1] = A @ B[:, n0:n1]. No communication."""
+    fn = local_dot or _default_local_dot()
+    return fn(a, b_shard, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale_shard, alpha=alpha, **kw)
+
+
+def k_sharded_dot(a_shard: torch.Tensor, b_shard: torch.Tensor, *, out_dtype: torch.dtype,
+                  row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None,
+                  alpha: float = 1.0, group=None, local_dot: Optional[Callable] = None,
+                  partial_dtype: torch.dtype = torch.float32, chunks: int = 1,
+                  partial: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+    """Rows [m0:m1) of C = sum over ranks of A[:, k_r] @ B[k_r, :], with the scale/cast epilogue applied
+    after the reduction.
+
+    The local GEMM writes an unscaled partial in `partial_dtype` (fp32 keeps the accumulator's
+    precision across ranks; bf16 halves the NVLink bytes at a documented cost in accuracy). The partial
+    is reduce-scattered along M: rank r receives the sum of rows split_range(M, world, r).
+    With chunks > 1 the M range of every rank is cut into `chunks` panels and the reduce-scatter of
+    panel i is issued while the GEMM of panel i+1 runs (two streams on a GPU).
+    M must be divisible by world * chunks.
+    """
+    fn = local_dot or _default_local_dot()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    m, n = a_shard.shape[0], b_shard.shape[1]
+    if m % (world * chunks) != 0:
+        raise ValueError(f"M={m} must be divisible by world*chunks={world * chunks}")
+    rows = m // world
+    out_part = torch.empty((rows, n), dtype=partial_dtype, device=a_shard.device)
+    if chunks == 1:
+        if partial is None:
+            partial = torch.empty((m, n), dtype=partial_dtype, device=a_shard.device)
+        fn(a_shard, b_shard, out=partial, out_dtype=partial_dtype, **kw)
+        dist.reduce_scatter_tensor(out_part, partial, op=dist.ReduceOp.SUM, group=group)
+    else:
+        # Panel p holds, for every destination rank d, rows [d*rows + p*pr, d*rows + (p+1)*pr).
+        pr = rows // chunks
+        on_gpu = a_shard.is_cuda
+        comm_stream = torch.cuda.Stream(device=a_shard.device) if on_gpu else None
+        works = []
+        for pidx in range(chunks):
+            idx = torch.cat([torch.arange(d * rows + pidx * pr, d * rows + (pidx + 1) * pr, device=a_shard.device)
+                             for d in range(world)])
+            a_panel = a_shard.index_select(0, idx)
+            panel = fn(a_panel, b_shard, out_dtype=partial_dtype, **kw)
+            dst = out_part[pidx * pr:(pidx + 1) * pr]
+            if on_gpu:
+                ev = torch.cuda.Event()
+                ev.record()
+                with torch.cuda.stream(comm_stream):
+                    comm_stream.wait_event(ev)
+                    dist.reduce_scatter_tensor(dst, panel, op=dist.ReduceOp.SUM, group=group)
+                panel.record_stream(comm_stream)
+            else:
+                dist.reduce_scatter_tensor(dst, panel, op=dist.ReduceOp.SUM, group=group)
+        if on_gpu:
+            torch.cuda.current_stream(a_shard.device).wait_stream(comm_stream)
+    # Epilogue after the reduction: alpha, row scale (this rank's rows), column scale, cast.
+    m0, _ = rank * rows, (rank + 1) * rows
+    acc = out_part.float()
+    if alpha != 1.0:
+        acc = acc * alpha
+    if row_scale is not None:
+        acc = acc * row_scale[m0:m0 + rows, None]
+    if col_scale is not None:
+        acc = acc * col_scale[None, :]
+    return acc.to(out_dtype)
