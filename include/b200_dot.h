@@ -153,6 +153,32 @@ TXD_API int tx_dot_run_host(tx_dot_plan *plan, const void *a_host, const void *b
 
 TXD_API int tx_dot_plan_destroy(tx_dot_plan *plan);
 
+/*
+ * No counterpart in the reference (it has no kernels and no allocator policy): a launch for callers
+ * that may not allocate — hosts whose memory pool belongs to another library, threads that must not
+ * take the driver's allocator lock, plug-in sandboxes that forbid cudaMalloc. It runs the stream-K
+ * schedule on single CTAs with the partial-tile scratch, tile counters and status word held in one
+ * fixed array inside the library image, and calls no allocating routine of CUDA or of any library.
+ *
+ *   - `problem` and `cfg` as for tx_dot_plan_create (cfg may be NULL; schedule and cta_pair are
+ *     overridden). The configuration's scratch must fit: at most tx_dot_static_scratch_capacity()
+ *     bytes of partial tiles (grid * 2 * block_n * 128 * 4) and 16384 output tiles; otherwise
+ *     TXD_ERR_UNSUPPORTED with both sizes in the message. Lower block_n or max_ctas to fit.
+ *   - All calls on a GPU share the array: launches that overlap in time race and give garbage, so
+ *     serialise them (one stream, or events). Each call clears the counters it needs on `stream`.
+ *   - The first call on a device resolves the array's device address and raises the kernel's
+ *     shared-memory limit; make it before starting any stream capture.
+ *   - Every GPU that loads the library holds the array (about 4.1 MiB) until the process exits.
+ * tx_dot_static_scratch_check synchronises `stream` and reports a wait that ran out since the last
+ * check. Error text: tx_dot_static_scratch_last_error().
+ */
+TXD_API int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config *cfg,
+                                      const void *a, const void *b, void *c, const float *row_scale,
+                                      const float *col_scale, void *stream);
+TXD_API int tx_dot_static_scratch_check(void *stream);
+TXD_API int64_t tx_dot_static_scratch_capacity(void);
+TXD_API const char *tx_dot_static_scratch_last_error(void);
+
 /* Kernels this library has launched in this process since load (for launch accounting). */
 TXD_API uint64_t tx_dot_kernel_launches(void);
 

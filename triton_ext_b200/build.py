@@ -31,7 +31,7 @@ INCLUDE = os.path.join(ROOT, "include")
 EXTENSIONS = [
     ("pass/LoopSplit", "LoopBisectPass", ["LoopSplitPass.cpp"], False),
     ("pass/DotTileSelect", "DotTileSelectPass", ["DotTileSelectPass.cpp"], False),
-    ("backend/B200Dot", "B200DotLoweringPass", ["b200_dot.cu", "B200DotLowering.cpp"], True),
+    ("backend/B200Dot", "B200DotLoweringPass", ["b200_dot.cu", "b200_dot_static.cu", "B200DotLowering.cpp"], True),
 ]
 
 CXXFLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]

@@ -340,7 +340,7 @@ struct AbortCtl {
 // that starts the clock. The time limit therefore counts from the end of the polling phase.
 constexpr uint32_t kPollsBeforeTimer = 4096;
 
-__device__ __noinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, const AbortCtl &ac,
+static __device__ __noinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, const AbortCtl &ac,
                                              uint32_t code) {
   const unsigned long long t0 = global_timer_ns();
   uint32_t it = 0;
@@ -964,6 +964,9 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   }
 }
 
+// A translation unit that instantiates dot_umma_body under its own kernel name defines
+// TXD_NO_KERNEL_ENTRY_POINTS so that these two are emitted once per library.
+#ifndef TXD_NO_KERNEL_ENTRY_POINTS
 __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_constant__ DotParams p) {
   dot_umma_body<false>(p);
 }
@@ -971,5 +974,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_c
 __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_pair_kernel(const __grid_constant__ DotParams p) {
   dot_umma_body<true>(p);
 }
+#endif  // TXD_NO_KERNEL_ENTRY_POINTS
 
 }  // namespace txd
