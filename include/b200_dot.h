@@ -60,8 +60,10 @@ typedef enum tx_dot_layout {
 typedef enum tx_dot_schedule {
   TXD_SCHED_AUTO = 0,
   TXD_SCHED_DATA_PARALLEL = 1, /* persistent CTAs, whole output tiles */
-  TXD_SCHED_STREAM_K = 2       /* persistent CTAs, equal shares of the (tile, k-block) space; partial
+  TXD_SCHED_STREAM_K = 2,      /* persistent CTAs, equal shares of the (tile, k-block) space; partial
                                   tiles are combined through plan-owned scratch memory */
+  TXD_SCHED_HYBRID = 3         /* whole tiles for every full wave of the grid, then the tiles of the last,
+                                  partial wave cut into equal (tile, k-block) shares as in stream-K */
 } tx_dot_schedule;
 
 /* C[m,n] = cast( alpha * row_scale[m] * col_scale[n] * sum_k A[m,k]*B[k,n] ), fp32 accumulate.
@@ -93,6 +95,8 @@ typedef struct tx_dot_config {
                             the rest run as the masked remainder. */
   int32_t cta_pair;      /* 1 = two-CTA clusters (tcgen05 cta_group::2, 256 x block_n tiles),
                             2 = single CTAs (128 x block_n tiles), 0 = auto */
+  int32_t atoms;         /* 128-byte K atoms per pipeline stage: 1 or 2 (block_k = atoms * 128 B) */
+  int32_t reserved;
 } tx_dot_config;
 
 /* What a plan decided; filled by tx_dot_plan_query. */

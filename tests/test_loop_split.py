@@ -177,7 +177,7 @@ def test_dot_k_loop_split_point(built_libs):
     assert [(l["lo"], l["hi"], l["step"]) for l in loops] == [(0, 4096, 128), (4096, 4160, 128)]
     assert loops[0]["fold"] == P.TXIR_FOLDED_TRUE and loops[1]["fold"] == P.TXIR_FOLDED_FALSE
     assert cfg.k_split_point == 4096
-    assert info["k_main_iters"] == 64 and info["k_tail_iters"] == 1 and info["k_tail_mmas"] == 4
+    assert info["k_main_iters"] * info["block_k"] == 4096 and info["k_tail_iters"] == 1 and info["k_tail_mmas"] == 4
     # K a multiple of BLOCK_K: no remainder loop work
     cfg, info, m = P.lower_dot(B.make_problem(512, 512, 512, torch.float16, torch.float16), 32)
     assert cfg.k_split_point == 512 and info["k_tail_iters"] == 0

@@ -22,7 +22,7 @@ def test_compute_bound_shapes_get_cta_pairs_and_big_tiles(built_libs):
         assert info["cta_pair"] == 1 and info["block_m"] == 256 and info["block_n"] == 256, (m, n, k, info)
         assert info["grid"] == 148 and info["swap_ab"] == 0
         assert info["smem_bytes"] <= 227 * 1024 and info["tmem_columns"] == 512
-        assert info["block_k"] * (1 if dt == f8 else 2) == 128
+        assert info["block_k"] * (1 if dt == f8 else 2) in (128, 256)  # one or two 128-byte K atoms per stage
 
 
 def test_decode_shape_is_swapped_and_streamed(built_libs):
@@ -33,10 +33,13 @@ def test_decode_shape_is_swapped_and_streamed(built_libs):
 
 
 def test_split_point_fields(built_libs):
-    info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16))
+    info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16), B.make_config(atoms=1))
     assert (info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (65, 0, 4)
-    info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16), B.make_config(k_split_point=4096))
+    info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16), B.make_config(atoms=1, k_split_point=4096))
     assert (info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (64, 1, 4)
+    # two atoms per stage: the physical K block is BLOCK_K = 128, main 32 blocks + a 64-wide remainder
+    info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16), B.make_config(atoms=2))
+    assert (info["block_k"], info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (128, 32, 1, 4)
     info = B.preview(B.make_problem(256, 256, 200, bf16, bf16))
     assert (info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (3, 1, 1)  # 200 = 3*64 + 8
     info = B.preview(B.make_problem(256, 256, 200, bf16, bf16), B.make_config(k_split_point=-1))

@@ -29,7 +29,7 @@ TXD_ERR_NO_DEVICE = 5
 
 TXD_F16, TXD_BF16, TXD_F8E4M3, TXD_F32, TXD_F8E5M2 = 0, 1, 2, 3, 4
 TXD_ROW_MAJOR, TXD_COL_MAJOR = 0, 1
-TXD_SCHED_AUTO, TXD_SCHED_DATA_PARALLEL, TXD_SCHED_STREAM_K = 0, 1, 2
+TXD_SCHED_AUTO, TXD_SCHED_DATA_PARALLEL, TXD_SCHED_STREAM_K, TXD_SCHED_HYBRID = 0, 1, 2, 3
 
 _DTYPES = {
     torch.float16: TXD_F16,
@@ -64,6 +64,7 @@ class Config(ctypes.Structure):
         ("block_n", ctypes.c_int32), ("stages", ctypes.c_int32), ("swap_ab", ctypes.c_int32),
         ("schedule", ctypes.c_int32), ("group_m", ctypes.c_int32), ("max_ctas", ctypes.c_int32),
         ("k_split_point", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
+        ("atoms", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 

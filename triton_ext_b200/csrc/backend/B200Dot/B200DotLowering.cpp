@@ -56,6 +56,7 @@ struct B200DotLoweringPass : public mlir::Pass {
       d.config.schedule = info.schedule;
       d.config.group_m = info.group_m;
       d.config.cta_pair = info.cta_pair ? 1 : 2;
+      d.config.atoms = info.block_k / bk;
       d.preview = info;
       d.lowered = true;
     }

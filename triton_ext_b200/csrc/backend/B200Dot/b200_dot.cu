@@ -162,7 +162,7 @@ int encode_operand_map(CUtensorMap *map, const void *ptr, int dtype, bool mn_maj
   if (!mn_major) {
     dims[0] = static_cast<cuuint64_t>(k);       // contiguous: K
     dims[1] = static_cast<cuuint64_t>(rows);
-    box[0] = static_cast<cuuint32_t>(bk_elems);
+    box[0] = static_cast<cuuint32_t>(128 / es);  // one 128-byte K atom; a stage takes `atoms` such boxes
     box[1] = static_cast<cuuint32_t>(tile_rows);
   } else {
     dims[0] = static_cast<cuuint64_t>(rows);    // contiguous: the row (M or N) index
@@ -301,10 +301,12 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
   bp.tiles_p = tc.tiles_p;
   bp.tiles_q = tc.tiles_q;
   bp.group_p = tc.group_m;
-  bp.stream_k = tc.schedule == TXD_SCHED_STREAM_K ? 1 : 0;
+  bp.stream_k = tc.schedule != TXD_SCHED_DATA_PARALLEL ? 1 : 0;
+  bp.sk_first_tile = tc.sk_first_tile;
   bp.kind_f8 = es == 1 ? 1 : 0;
   bp.idesc = make_idesc(pr.ab_dtype, p_mn, q_mn, tc.block_m, tc.block_n);
   bp.tma_store = tc.tma_store;
+  bp.atoms = tc.atoms;
   const int umma_k = 32 / es;
   make_smem_desc(p_mn, tc.block_k, umma_k, &bp.p_desc_hi, &bp.p_desc_lbo, &bp.p_kstep);
   make_smem_desc(q_mn, tc.block_k, umma_k, &bp.q_desc_hi, &bp.q_desc_lbo, &bp.q_kstep);

@@ -133,7 +133,7 @@ int encode_operand(CUtensorMap *map, const void *ptr, int dtype, bool mn_major, 
                                          : (dtype == TXD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_major ? rows : k), static_cast<cuuint64_t>(mn_major ? k : rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(mn_major ? 128 / es : bk), static_cast<cuuint32_t>(mn_major ? bk : tile_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(mn_major ? bk : tile_rows)};
   cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -208,6 +208,7 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   if (cfg_in) cfg = *cfg_in;
   cfg.schedule = TXD_SCHED_STREAM_K;
   cfg.cta_pair = 2;
+  cfg.atoms = 1;
   txd::MachineModel mm;
   mm.sm_count = setup->sm_count;
   txd::TileChoice tc;
@@ -284,6 +285,7 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   prm.q_stage_bytes = tc.q_stage_bytes;
   prm.tmem_cols = tc.tmem_cols;
   prm.tma_store = tma_store ? 1 : 0;
+  prm.atoms = 1;
 
   // The counters of the tiles this call touches must be zero when its kernel starts; an earlier call
   // that gave up on a wait may have left some non-zero.

@@ -25,6 +25,7 @@ struct MachineModel {
   double ingest_bytes_per_clk = 60;     // what TMA can deliver into one SM's shared memory (measured:
                                         // a loads-only run of the ring moved 56 B/clk/SM)
   double hbm_bytes_per_s = 6.4596e12;   // measured copy bandwidth of this pool's B200
+  double block_overhead_clk = 0;        // per K block handshake cost not hidden behind the MMAs (measured: none)
   double hbm_bytes_per_s_per_cta = 50e9; // what one persistent CTA's TMA ring sustains
   int smem_budget = 227 * 1024 - 2048;  // dynamic shared memory per CTA minus control block + slack
 };
@@ -49,8 +50,10 @@ struct TileChoice {
   int stages = 0;
   int swap_ab = 0;       // 0/1 (resolved)
   int cta_pair = 0;      // 0/1 (resolved): two-CTA clusters, 256-row tiles
+  int atoms = 1;         // 128-byte K atoms per stage (block_k = atoms * 128 / element size)
   int tma_store = 0;     // epilogue goes through shared memory + TMA store
-  int schedule = 0;      // TXD_SCHED_DATA_PARALLEL or TXD_SCHED_STREAM_K (resolved)
+  int schedule = 0;      // TXD_SCHED_DATA_PARALLEL, TXD_SCHED_STREAM_K or TXD_SCHED_HYBRID (resolved)
+  int sk_first_tile = 0; // first tile of the stream-K region (0 for pure stream-K)
   int group_m = 0;
   int grid = 0;
   int k_blocks = 0, k_main_blocks = 0, tail_mmas = 0;
@@ -78,9 +81,10 @@ inline double algorithmic_bytes(const tx_dot_problem &pr) {
 
 // Modelled time of one (role assignment, block_n, pairing, schedule) candidate.
 inline double model_seconds(const MachineModel &mm, int es, int p_extent, int q_extent, int k,
-                            int block_n, bool q_mn_major, bool pair, int schedule, int workers,
+                            int block_n, bool q_mn_major, bool pair, int atoms, int schedule, int workers,
                             double algo_bytes) {
-  const int bk = 128 / es;
+  const int bk_atom = 128 / es;
+  const int bk = atoms * bk_atom;
   const int k_blocks = cdiv(k, bk);
   const int tile_rows = pair ? 256 : 128;
   const int tiles = cdiv(p_extent, tile_rows) * cdiv(q_extent, block_n);
@@ -88,23 +92,27 @@ inline double model_seconds(const MachineModel &mm, int es, int p_extent, int q_
   // Per SM and K block: a 128 x block_n x bk MMA either way (a pair splits a 256-row tile).
   const double mma_clk = 2.0 * 128 * block_n * bk / flops_per_clk;
   const int q_rows_cta = pair ? block_n / 2 : block_n;
-  const int q_rows = q_mn_major ? round_up(q_rows_cta, bk) : q_rows_cta;  // MN-major boxes are 128 B wide
-  const double stage_bytes = 128.0 * 128 + q_rows * 128.0;
+  const int q_rows = q_mn_major ? round_up(q_rows_cta, bk_atom) : q_rows_cta;  // MN-major boxes are 128 B wide
+  const double stage_bytes = atoms * (128.0 * 128 + q_rows * 128.0);
   // The tensor pipe reads every stage byte once (a pair reads the peer's Q half as well) ...
-  const double read_clk = (128.0 * 128 + (pair ? 2 : 1) * q_rows * 128.0) / mm.smem_bytes_per_clk;
+  const double read_clk = atoms * (128.0 * 128 + (pair ? 2 : 1) * q_rows * 128.0) / mm.smem_bytes_per_clk;
   // ... and TMA has to deliver the CTA's own stage bytes.
   const double ingest_clk = stage_bytes / mm.ingest_bytes_per_clk;
-  const double blk_clk = std::max(mma_clk, std::max(read_clk, ingest_clk));
+  const double blk_clk = std::max(mma_clk, std::max(read_clk, ingest_clk)) + mm.block_overhead_clk;
   const long long total = (long long)tiles * k_blocks;
   double blocks_per_worker;  // the busiest worker's share
   if (schedule == TXD_SCHED_STREAM_K) {
     blocks_per_worker = (double)((total + workers - 1) / workers);
+  } else if (schedule == TXD_SCHED_HYBRID) {
+    const long long dp_tiles = (long long)(tiles / workers) * workers;
+    blocks_per_worker = (double)(dp_tiles / workers) * k_blocks +
+                        (double)(((long long)(tiles - dp_tiles) * k_blocks + workers - 1) / workers);
   } else {
     blocks_per_worker = (double)cdiv(tiles, workers) * k_blocks;
   }
   const double balance = ((double)total / workers) / blocks_per_worker;  // 1 = equally loaded
   double busy_clk = blocks_per_worker * blk_clk;
-  if (schedule == TXD_SCHED_STREAM_K) {
+  if (schedule != TXD_SCHED_DATA_PARALLEL) {
     // Up to two partial tiles per CTA go through scratch: fp32 write + read, ~64 B/clk through L2.
     busy_clk += 2.0 * (128.0 * block_n * 4 * 2) / 64.0;
   }
@@ -165,20 +173,38 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
           if (swap || bn < 128 || (q_mn && (bn / 2) % bk != 0)) continue;
           if (cfg.cta_pair == 0 && p_extent < 512) continue;
         }
+        for (int atoms = 1; atoms <= 2; ++atoms) {
+        if (cfg.atoms && atoms != cfg.atoms) continue;
+        {
+          // Two atoms per stage halve the per-block handshakes but also the ring depth: keep >= 3 stages.
+          const int q_rows_cta = pair ? bn / 2 : bn;
+          const int stage = atoms * (128 * 128 + round_up((q_mn ? round_up(q_rows_cta, bk) : q_rows_cta) * 128, 1024));
+          const int staging = (!swap && bn >= 64) ? 4 * 2 * 32 * 128 : 0;
+          if (atoms == 2 && (mm.smem_budget - staging) / stage < 3) continue;
+          if (atoms == 2 && pr.k < 4 * atoms * bk) continue;
+        }
         const int tiles = cdiv(p_extent, pair ? 256 : 128) * cdiv(q_extent, bn);
-        const int k_blocks = cdiv(pr.k, bk);
-        for (int sched = TXD_SCHED_DATA_PARALLEL; sched <= TXD_SCHED_STREAM_K; ++sched) {
+        const int k_blocks = cdiv(pr.k, bk * atoms);
+        for (int sched = TXD_SCHED_DATA_PARALLEL; sched <= TXD_SCHED_HYBRID; ++sched) {
           if (cfg.schedule && sched != cfg.schedule) continue;
-          if (pair && sched == TXD_SCHED_STREAM_K) continue;  // stream-K runs on single CTAs only
           long long units = (long long)tiles * (sched == TXD_SCHED_STREAM_K ? k_blocks : 1);
           if (units < 1) units = 1;
           const int max_workers = pair ? max_grid / 2 : max_grid;
           if (max_workers < 1) continue;
           const int workers = (int)std::min<long long>(max_workers, units);
-          double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, q_mn, pair != 0, sched, workers, algo);
+          if (sched == TXD_SCHED_HYBRID) {
+            // Needs at least one full wave, a partial last wave, and a K block for every worker in it.
+            const int tail = tiles % workers;
+            if (tiles < workers || tail == 0 || (long long)tail * k_blocks < workers) continue;
+          }
+          double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, q_mn, pair != 0, atoms, sched, workers, algo);
           // Prefer the simpler schedule on near-ties, and the role assignment that pads less: zero
           // rows still cost shared-memory fill and tensor cycles even when HBM time hides them.
-          if (sched == TXD_SCHED_STREAM_K) t *= 1.03;
+          // Pure stream-K also spreads concurrently running tiles over the whole matrix (worse L2 reuse).
+          if (sched == TXD_SCHED_STREAM_K) t *= 1.10;
+          // Measured on 4096x4096x4160 (3.46 waves): the partial-tile fix-up of the last wave costs more than
+          // the idle SMs it saves, so whole tiles win unless the partial wave is nearly empty.
+          if (sched == TXD_SCHED_HYBRID) t *= 1.20;
           const double tile_rows = pair ? 256.0 : 128.0;
           const double padded = (double)cdiv(p_extent, (int)tile_rows) * tile_rows * cdiv(q_extent, bn) * bn;
           t *= 1.0 + 0.25 * (1.0 - (double)p_extent * q_extent / padded);
@@ -188,9 +214,11 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
             out.swap_ab = swap;
             out.block_n = bn;
             out.cta_pair = pair;
+            out.atoms = atoms;
             out.schedule = sched;
             out.grid = pair ? 2 * workers : workers;
           }
+        }
         }
       }
     }
@@ -200,32 +228,32 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
     return -1;
   }
   out.est_seconds = best;
-  out.block_k = bk;
+  const int bks = bk * out.atoms;  // K elements per stage (the kernels' physical K block)
+  out.block_k = bks;
   out.p_extent = out.swap_ab ? pr.n : pr.m;
   out.q_extent = out.swap_ab ? pr.m : pr.n;
   out.block_m = out.cta_pair ? 256 : 128;
   out.tiles_p = cdiv(out.p_extent, out.block_m);
   out.tiles_q = cdiv(out.q_extent, out.block_n);
-  out.k_blocks = cdiv(pr.k, bk);
+  out.k_blocks = cdiv(pr.k, bks);
   // LoopSplit mid point: first K index of the masked remainder.
-  int mid = cfg.k_split_point > 0 ? cfg.k_split_point : (cfg.k_split_point < 0 ? 0 : (pr.k / bk) * bk);
+  int mid = cfg.k_split_point > 0 ? cfg.k_split_point : (cfg.k_split_point < 0 ? 0 : (pr.k / bks) * bks);
   if (mid > (pr.k / bk) * bk || mid < 0) {
     if (why) *why = "k_split_point lies past the last full K block: a partial block would run unmasked";
     return -1;
   }
-  mid = (mid / bk) * bk;  // a split inside a physical block moves down: the remainder only adds masking
-  out.k_main_blocks = mid / bk;
-  const int rem = pr.k - (out.k_blocks - 1) * bk;  // columns in the last block: 1..bk
+  mid = (mid / bks) * bks;  // a split inside a physical block moves down: the remainder only adds masking
+  out.k_main_blocks = mid / bks;
+  const int rem = pr.k - (out.k_blocks - 1) * bks;  // columns in the last block: 1..bks
   const int umma_k = 32 / es;
   out.tail_mmas = pr.k > 0 ? cdiv(rem, umma_k) : 0;
   const bool p_mn = out.swap_ab ? (pr.b_layout == TXD_ROW_MAJOR) : (pr.a_layout == TXD_COL_MAJOR);
   const bool q_mn = out.swap_ab ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
   (void)p_mn;
-  out.p_stage_bytes = 128 * 128;
+  out.p_stage_bytes = out.atoms * 128 * 128;
   const int q_rows_cta = out.cta_pair ? out.block_n / 2 : out.block_n;
-  out.q_stage_bytes = (q_mn ? round_up(q_rows_cta, bk) : q_rows_cta) * 128;
   // The Q stage must keep the next P stage 1024-byte aligned.
-  out.q_stage_bytes = round_up(out.q_stage_bytes, 1024);
+  out.q_stage_bytes = out.atoms * round_up((q_mn ? round_up(q_rows_cta, bk) : q_rows_cta) * 128, 1024);
   const int stage_bytes = out.p_stage_bytes + out.q_stage_bytes;
   // C goes out through a shared-memory slab + TMA store when its rows are 16-byte aligned.
   const int os = elem_bytes(pr.out_dtype);
@@ -259,8 +287,15 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
     out.group_m = std::max(1, std::min(g, out.tiles_p));
   }
   out.scratch_bytes = 0;
-  if (out.schedule == TXD_SCHED_STREAM_K)
-    out.scratch_bytes = (int64_t)out.grid * 2 * out.block_n * 128 * 4 + (int64_t)out.tiles_p * out.tiles_q * 4;
+  out.sk_first_tile = 0;
+  if (out.schedule != TXD_SCHED_DATA_PARALLEL) {
+    // Two partial-tile slots (128 rows x block_n fp32) per CTA, one counter per (tile, CTA of the pair).
+    const int ranks = out.cta_pair ? 2 : 1;
+    const int workers = out.grid / ranks;
+    const int tiles = out.tiles_p * out.tiles_q;
+    if (out.schedule == TXD_SCHED_HYBRID) out.sk_first_tile = (tiles / workers) * workers;
+    out.scratch_bytes = (int64_t)out.grid * 2 * out.block_n * 128 * 4 + (int64_t)tiles * ranks * 4;
+  }
   return 0;
 }
 

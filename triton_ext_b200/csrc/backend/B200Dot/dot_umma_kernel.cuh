@@ -1,9 +1,12 @@
 // The tt.dot K-loop as one persistent, warp-specialised sm_100a kernel.
 //
-//   warp 0 (one lane)  : TMA producer — fills a ring of shared-memory stages, one K block per stage
+//   warp 0 (one lane)  : TMA producer of the P operand — fills a ring of shared-memory stages, one K block
+//                        per stage, and arms the stage's "full" barrier with the byte count of both operands
+//   warp 2 (one lane)  : TMA producer of the Q operand (issuing a TMA copy occupies the issuing thread for
+//                        over a hundred nanoseconds; two issuing warps halve the time to fill a stage)
 //   warp 1 (one lane)  : tcgen05.mma issuer — accumulates in TMEM (fp32), two accumulators so the
 //                        epilogue of segment i overlaps the main loop of segment i+1
-//   warps 2..5         : epilogue — tcgen05.ld TMEM -> registers, fused scale + cast, global store
+//   warps 3..6         : epilogue — tcgen05.ld TMEM -> registers, fused scale + cast, global store
 //
 // The K loop is executed the way the LoopSplit pass leaves it (reference:
 // pass/LoopSplit/LoopSplit.cpp:179-193): an unpredicated main loop over [0, k_main_blocks) and a
@@ -37,10 +40,11 @@
 namespace txd {
 
 constexpr int kBlockM = 128;          // MMA M = TMEM lanes
-constexpr int kStageRowBytes = 128;   // one K block = 128 bytes of K per row (one SWIZZLE_128B atom)
-constexpr int kMmasPerBlock = 4;      // 128 B / 32 B per tcgen05.mma
+constexpr int kStageRowBytes = 128;   // one K atom = 128 bytes of K per row (one SWIZZLE_128B span);
+                                      // a stage (K block) holds 1 or 2 atoms
+constexpr int kMmasPerAtom = 4;       // 128 B / 32 B per tcgen05.mma
 constexpr int kMaxStages = 12;
-constexpr int kNumThreads = 192;
+constexpr int kNumThreads = 224;
 constexpr int kEpilogueThreads = 128;
 constexpr int kStoreSlabBytes = 32 * 128;  // one epilogue warp's staging slab: 32 rows x 128 bytes
 constexpr int kStoreStagingBytes = 4 * 2 * kStoreSlabBytes;  // 4 warps, double-buffered
@@ -71,14 +75,16 @@ struct alignas(64) DotParams {
   int32_t trans_out;       // 0: out[p*ldo+q]   1: out[q*ldo+p]
   int32_t out_dtype;       // 0 f16, 1 bf16, 3 f32
   int32_t block_n;
-  int32_t bk_elems;        // K elements per stage: 64 (16-bit) or 128 (8-bit)
+  int32_t bk_elems;        // K elements per stage (K block): atoms * chunk_elems
   int32_t stages;
   int32_t k_blocks;        // ceil(K / bk_elems)
   int32_t k_main_blocks;   // LoopSplit mid point / bk_elems
-  int32_t tail_mmas;       // MMAs issued by the last remainder block (1..4)
+  int32_t tail_mmas;       // MMAs issued by the last remainder block (1 .. 4 * atoms)
   int32_t tiles_p, tiles_q;
   int32_t group_p;         // raster group height in tiles
-  int32_t stream_k;        // 0 = whole tiles round-robin, 1 = equal (tile,k-block) shares
+  int32_t stream_k;        // 0 = whole tiles round-robin only; 1 = tiles from sk_first_tile on are cut into
+                           // equal (tile, k-block) shares, one per worker (0: all tiles = pure stream-K)
+  int32_t sk_first_tile;   // first tile of the stream-K region; tiles below it run whole, round-robin
   int32_t kind_f8;         // 0: kind::f16, 1: kind::f8f6f4
   uint32_t idesc;          // tcgen05 instruction descriptor
   // shared-memory matrix descriptors: upper 32 bits, and start-address step (16-byte units) per MMA
@@ -90,6 +96,7 @@ struct alignas(64) DotParams {
   int32_t p_stage_bytes, q_stage_bytes;
   int32_t tmem_cols;
   int32_t tma_store;                 // 1 = epilogue stores through shared memory + TMA
+  int32_t atoms;                     // 128-byte K atoms per stage: 1 or 2 (0 reads as 1)
   int32_t debug_flags;               // measurement / test switches, 0 in production (results are wrong
                                      // when set): 1 = do not refill stages (tensor-pipe-only timing),
                                      // 2 = one MMA per tile (load-only timing), 4 = skip C stores,
@@ -364,6 +371,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
   return mbar_wait_timed(bar, parity, ac, code);
 }
 
+// A converged warp waits on a barrier. Every lane polls: leaving the polling to one lane makes the
+// warp diverge around the loop, and a diverged role warp was measured to run its whole loop about
+// twice as slowly (the K-loop handshake then starves the tensor pipe).
+__device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl &ac, uint32_t code,
+                                               int /*lane*/) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, ac, code));
+}
+
 // ----------------------------------------------------------------------------------------------
 // Work iteration: every role walks the same sequence of segments (tile, [kb0, kb1)).
 // A "worker" is a CTA (single) or a CTA pair (pair).
@@ -374,24 +389,23 @@ struct Segment {
 };
 
 struct WorkIter {
-  int next_tile, tile_stride, tiles;  // whole tiles, round-robin
-  long long unit, unit_end;           // stream-K share
-  int k_blocks;
-  bool stream_k;
+  int next_tile, tile_stride, dp_end;  // whole tiles, round-robin, below dp_end
+  long long unit, unit_end;            // this worker's share of the stream-K region's (tile, k-block) units
+  int k_blocks, sk_tile0;
 
   __device__ __forceinline__ WorkIter(const DotParams &p, int worker, int workers) {
-    tiles = p.tiles_p * p.tiles_q;
+    const int tiles = p.tiles_p * p.tiles_q;
     k_blocks = p.k_blocks;
-    stream_k = p.stream_k != 0;
+    sk_tile0 = p.stream_k ? p.sk_first_tile : tiles;
+    dp_end = sk_tile0;
     next_tile = worker;
     tile_stride = workers;
-    const long long total = static_cast<long long>(tiles) * k_blocks;
+    const long long total = static_cast<long long>(tiles - sk_tile0) * k_blocks;
     unit = total * worker / workers;
     unit_end = total * (worker + 1) / workers;
   }
   __device__ __forceinline__ bool next(Segment &s) {
-    if (!stream_k) {
-      if (next_tile >= tiles) return false;
+    if (next_tile < dp_end) {
       s.tile = next_tile;
       s.kb0 = 0;
       s.kb1 = k_blocks;
@@ -399,9 +413,10 @@ struct WorkIter {
       return true;
     }
     if (unit >= unit_end) return false;
-    s.tile = static_cast<int>(unit / k_blocks);
-    s.kb0 = static_cast<int>(unit - static_cast<long long>(s.tile) * k_blocks);
-    const long long tile_end = static_cast<long long>(s.tile + 1) * k_blocks;
+    const int t = static_cast<int>(unit / k_blocks);
+    s.tile = sk_tile0 + t;
+    s.kb0 = static_cast<int>(unit - static_cast<long long>(t) * k_blocks);
+    const long long tile_end = static_cast<long long>(t + 1) * k_blocks;
     const long long e = tile_end < unit_end ? tile_end : unit_end;
     s.kb1 = s.kb0 + static_cast<int>(e - unit);
     unit = e;
@@ -564,9 +579,11 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
                                               uint32_t cta_rank) {
   const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
   const int row_in_tile = quarter * 32 + lane;  // accumulator row held by this thread
-  const int epi_tid = (warp - 2) * 32 + lane;
+  const int epi_tid = (warp - 3) * 32 + lane;
   const uint32_t tmem_base = ctl->tmem_base;
-  const long long total_units = static_cast<long long>(p.tiles_p) * p.tiles_q * p.k_blocks;
+  const int sk_tile0 = p.stream_k ? p.sk_first_tile : p.tiles_p * p.tiles_q;
+  const long long total_units = static_cast<long long>(p.tiles_p * p.tiles_q - sk_tile0) * p.k_blocks;
+  const int ranks = kPair ? 2 : 1;  // each CTA of a pair parks and combines its own 128 rows
   const int rows_per_tile = kPair ? 2 * kBlockM : kBlockM;
   const uint32_t my_slabs = staging + static_cast<uint32_t>(quarter) * 2u * kStoreSlabBytes;
   const int slab_cols = p.out_dtype == 3 ? 32 : 64;  // 128 bytes of output per slab row
@@ -574,11 +591,9 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
   WorkIter it(p, worker, workers);
   Segment s;
   uint32_t seg_i = 0;
-  int first_tile = -1;
   while (it.next(s)) {
     const uint32_t acc = seg_i & 1u;
     const uint32_t acc_phase = (seg_i >> 1) & 1u;
-    if (first_tile < 0) first_tile = s.tile;
     // One thread watches the barrier and publishes the outcome, so that all 128 epilogue threads
     // take the same branch (they meet again at named barrier 1 below).
     if (epi_tid == 0)
@@ -643,9 +658,11 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
       }
       release_accumulator();
     } else {
-      // Partial tile (stream-K, single variant only): park the fp32 partial in scratch, column-major
+      // Partial tile (stream-K region): park the fp32 partial in scratch, column-major
       // inside the tile so that the 32 lanes of a warp write 128 consecutive bytes.
-      const int slot = worker * 2 + (s.tile == first_tile ? 0 : 1);
+      // A share touches at most two partial tiles: the one it starts in (slot 0) and the one it ends in.
+      const int my_first_tile = sk_tile0 + static_cast<int>((total_units * worker / workers) / p.k_blocks);
+      const int slot = (worker * 2 + (s.tile == my_first_tile ? 0 : 1)) * ranks + static_cast<int>(cta_rank);
       float *mine = p.partials + static_cast<long long>(slot) * p.block_n * kBlockM;
       for (int c0 = 0; c0 < p.block_n; c0 += kChunk) {
         uint32_t v[32];
@@ -657,15 +674,16 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
       }
       release_accumulator();
       // Contributors of this tile are the workers whose shares intersect its k-block range.
-      const long long u0 = static_cast<long long>(s.tile) * p.k_blocks;
+      const long long u0 = static_cast<long long>(s.tile - sk_tile0) * p.k_blocks;
       const int c_first = stream_k_owner(u0, total_units, workers);
       const int c_last = stream_k_owner(u0 + p.k_blocks - 1, total_units, workers);
       __threadfence();
       epilogue_bar_sync();
       if (epi_tid == 0) {
-        const uint32_t old = atomicAdd(p.tile_counters + s.tile, 1u);
+        uint32_t *counter = p.tile_counters + s.tile * ranks + static_cast<int>(cta_rank);
+        const uint32_t old = atomicAdd(counter, 1u);
         const uint32_t last = (old == static_cast<uint32_t>(c_last - c_first)) ? 1u : 0u;
-        if (last) p.tile_counters[s.tile] = 0;  // ready for the next launch
+        if (last) *counter = 0;  // ready for the next launch
         ctl->fixup_last = last;
       }
       epilogue_bar_sync();
@@ -680,8 +698,8 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
           // Sum in ascending k order: deterministic regardless of arrival order.
           for (int c = c_first; c <= c_last; ++c) {
             const long long cb = total_units * c / workers;
-            const int c_first_tile = static_cast<int>(cb / p.k_blocks);
-            const int cslot = c * 2 + (s.tile == c_first_tile ? 0 : 1);
+            const int c_first_tile = sk_tile0 + static_cast<int>(cb / p.k_blocks);
+            const int cslot = (c * 2 + (s.tile == c_first_tile ? 0 : 1)) * ranks + static_cast<int>(cta_rank);
             const float *src = p.partials + static_cast<long long>(cslot) * p.block_n * kBlockM;
 #pragma unroll
             for (int j = 0; j < kChunk; ++j)
@@ -721,6 +739,8 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   const int rows_per_tile = kPair ? 2 * kBlockM : kBlockM;
   const int q_rows_per_cta = kPair ? p.block_n / 2 : p.block_n;  // Q rows this CTA loads per tile
+  const int atoms = p.atoms > 1 ? p.atoms : 1;
+  const int mmas_per_block = kMmasPerAtom * atoms;
 
   AbortCtl ac;
   ac.flag = &ctl->abort_flag;
@@ -754,9 +774,9 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    // The whole warp walks the loop; one elected lane arms the barrier and issues the copies.
+  // ------------------------------ TMA producer (one warp per operand) ------------------------------
+  // The whole warp walks the loop; one elected lane arms the barrier (P side) and issues the copies.
+  auto producer_role = [&](const bool load_p, const bool load_q) {
     {
       WorkIter it(p, worker, workers);
       Segment s;
@@ -770,7 +790,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         const int p0 = tp * rows_per_tile + static_cast<int>(cta_rank) * kBlockM;
         const int q0 = tq * p.block_n + static_cast<int>(cta_rank) * q_rows_per_cta;
         for (int kb = s.kb0; kb < s.kb1; ++kb) {
-          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer))) {
+          if (!warp_mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer, lane)) {
             ok = false;
             break;
           }
@@ -782,29 +802,35 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           // Pair: every byte of both CTAs is counted on the leader's barrier.
           const uint32_t full = kPair ? map_to_cta(full_local, 0) : full_local;
           if ((p.debug_flags & 1) && issued >= static_cast<uint32_t>(p.stages)) {
-            if (leader && issuer) mbar_arrive(full_local);
+            if (leader && issuer && load_p) mbar_arrive(full_local);
             ++issued;
             if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1u; }
             continue;
           }
           if (issuer) {
-          if (leader) mbar_arrive_expect_tx(full_local, kPair ? 2u * stage_bytes : stage_bytes);
+          if (leader && load_p) mbar_arrive_expect_tx(full_local, kPair ? 2u * stage_bytes : stage_bytes);
           const uint32_t p_dst = stage_base + stage * stage_bytes;
           const uint32_t q_dst = p_dst + static_cast<uint32_t>(p.p_stage_bytes);
           const int k0 = kb * p.bk_elems;
+          // MN-major: one box per 128-byte-wide row chunk, bk_elems K slices tall.
+          // K-major: one box per K atom (its rows x 128 bytes), atoms side by side in the stage.
           const uint32_t box_bytes = static_cast<uint32_t>(p.bk_elems) * kStageRowBytes;
+          const uint32_t p_atom_bytes = static_cast<uint32_t>(kBlockM) * kStageRowBytes;
+          const uint32_t q_atom_bytes = static_cast<uint32_t>(q_rows_per_cta) * kStageRowBytes;
           auto load = [&](uint32_t dst, const CUtensorMap *m, int x, int y) {
             if (kPair) tma_load_2d_pair(dst, m, x, y, full);
             else tma_load_2d(dst, m, x, y, full);
           };
-          if (!p.p_mn_major) {
-            load(p_dst, &p.tmap_p, k0, p0);
+          if (!load_p) {
+          } else if (!p.p_mn_major) {
+            for (int at = 0; at < atoms; ++at) load(p_dst + at * p_atom_bytes, &p.tmap_p, k0 + at * p.chunk_elems, p0);
           } else {
             for (int c = 0; c * p.chunk_elems < kBlockM; ++c)
               load(p_dst + c * box_bytes, &p.tmap_p, p0 + c * p.chunk_elems, k0);
           }
-          if (!p.q_mn_major) {
-            load(q_dst, &p.tmap_q, k0, q0);
+          if (!load_q) {
+          } else if (!p.q_mn_major) {
+            for (int at = 0; at < atoms; ++at) load(q_dst + at * q_atom_bytes, &p.tmap_q, k0 + at * p.chunk_elems, q0);
           } else {
             for (int c = 0; c * p.chunk_elems < q_rows_per_cta; ++c)
               load(q_dst + c * box_bytes, &p.tmap_q, q0 + c * p.chunk_elems, k0);
@@ -818,7 +844,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           }
         }
       }
-      if ((!ok || *ac.flag) && issuer) {
+      if ((!ok || *ac.flag) && issuer && load_p) {
         // Abort path: wait (bounded) until every copy this thread started has landed, so that no
         // TMA write is in flight when the CTA's shared memory is released. (Single variant and the
         // pair's leader; the follower's copies are counted on the leader's barriers.)
@@ -840,6 +866,11 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         }
       }
     }
+  };
+  if (warp == 0) {
+    producer_role(true, false);
+  } else if (warp == 2) {
+    producer_role(false, true);
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only in a pair) ------------------------------
     // The whole warp walks the loop; one elected lane issues tcgen05 instructions.
@@ -858,6 +889,15 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           tc_commit(local_bar);
         }
       };
+      // Descriptor pieces that do not change during the kernel.
+      auto desc64 = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | static_cast<uint64_t>(lo); };
+      const uint32_t p_lo_base = p.p_desc_lbo | ((stage_base & 0x3FFFFu) >> 4);
+      const uint32_t q_lo_base = p.q_desc_lbo | (((stage_base + static_cast<uint32_t>(p.p_stage_bytes)) & 0x3FFFFu) >> 4);
+      const uint32_t stage16 = stage_bytes >> 4;
+      // Start-address step (16-byte units) from one K atom of a stage to the next: K-major atoms lie side
+      // by side (rows x 128 bytes each); MN-major stages are linear in K.
+      const uint32_t p_atom_step = p.p_mn_major ? 4u * p.p_kstep : static_cast<uint32_t>(kBlockM) * kStageRowBytes / 16u;
+      const uint32_t q_atom_step = p.q_mn_major ? 4u * p.q_kstep : static_cast<uint32_t>(q_rows_per_cta) * kStageRowBytes / 16u;
       auto mma = [&](uint32_t d_tmem, uint64_t pd, uint64_t qd, uint32_t accumulate) {
         if (kPair) {
           if (p.kind_f8) umma_f8_pair(d_tmem, pd, qd, p.idesc, accumulate);
@@ -870,8 +910,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
       while (ok && it.next(s)) {
         const uint32_t acc = seg_i & 1u;
         const uint32_t acc_phase = (seg_i >> 1) & 1u;
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(smem_u32(&ctl->tmem_empty_bar[acc]), acc_phase ^ 1u, ac, kDevTimeoutMmaTmem));
+        ok = warp_mbar_wait(smem_u32(&ctl->tmem_empty_bar[acc]), acc_phase ^ 1u, ac, kDevTimeoutMmaTmem, lane);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * static_cast<uint32_t>(p.block_n);
@@ -881,28 +920,30 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         // for the NEXT stage sits between this block's MMAs and this block's commit and runs while the
         // MMAs execute. After the commit the next block's MMAs go out at once.
         auto wait_full = [&](uint32_t st, uint32_t ph) -> bool {
-          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->full_bar[st]), ph, ac, kDevTimeoutMmaFull))) return false;
+          if (!warp_mbar_wait(smem_u32(&ctl->full_bar[st]), ph, ac, kDevTimeoutMmaFull, lane)) return false;
           tc_fence_after();
           return true;
         };
         auto issue_block = [&](uint32_t st, int n_mma) {
-          const uint32_t p_addr = stage_base + st * stage_bytes;
-          const uint32_t q_addr = p_addr + static_cast<uint32_t>(p.p_stage_bytes);
-          const uint64_t pdesc = (static_cast<uint64_t>(p.p_desc_hi) << 32) |
-                                 static_cast<uint64_t>(p.p_desc_lbo | ((p_addr & 0x3FFFFu) >> 4));
-          const uint64_t qdesc = (static_cast<uint64_t>(p.q_desc_hi) << 32) |
-                                 static_cast<uint64_t>(p.q_desc_lbo | ((q_addr & 0x3FFFFu) >> 4));
+          // Low descriptor words (start address in 16-byte units | leading-dimension field); shared
+          // memory ends below 256 KiB, so adding offsets never carries out of the 14-bit address field.
+          const uint32_t plo = p_lo_base + st * stage16;
+          const uint32_t qlo = q_lo_base + st * stage16;
           if (p.debug_flags & 2) n_mma = (accumulate == 0) ? 1 : 0;
           if (issuer) {
-            if (n_mma == kMmasPerBlock) {
+            if (n_mma == mmas_per_block) {
+              for (int at = 0; at < atoms; ++at) {
+                const uint32_t pa = plo + at * p_atom_step, qa = qlo + at * q_atom_step;
 #pragma unroll
-              for (int j = 0; j < kMmasPerBlock; ++j)
-                mma(d_tmem, pdesc + static_cast<uint64_t>(j * p.p_kstep), qdesc + static_cast<uint64_t>(j * p.q_kstep),
-                    (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
+                for (int j = 0; j < kMmasPerAtom; ++j)
+                  mma(d_tmem, desc64(p.p_desc_hi, pa + j * p.p_kstep), desc64(p.q_desc_hi, qa + j * p.q_kstep),
+                      (accumulate | static_cast<uint32_t>(at | j)) != 0 ? 1u : 0u);
+              }
             } else {
 #pragma unroll 1
               for (int j = 0; j < n_mma; ++j)
-                mma(d_tmem, pdesc + static_cast<uint64_t>(j * p.p_kstep), qdesc + static_cast<uint64_t>(j * p.q_kstep),
+                mma(d_tmem, desc64(p.p_desc_hi, plo + (j >> 2) * p_atom_step + (j & 3) * p.p_kstep),
+                    desc64(p.q_desc_hi, qlo + (j >> 2) * q_atom_step + (j & 3) * p.q_kstep),
                     (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
             }
           }
@@ -915,7 +956,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         ok = wait_full(stage, phase);
         for (int kb = s.kb0; ok && kb < s.kb1; ++kb) {
           const bool in_main = kb < mid;
-          issue_block(stage, (in_main || kb != p.k_blocks - 1) ? kMmasPerBlock : p.tail_mmas);
+          issue_block(stage, (in_main || kb != p.k_blocks - 1) ? mmas_per_block : p.tail_mmas);
           uint32_t next_stage = stage + 1, next_phase = phase;
           if (next_stage == static_cast<uint32_t>(p.stages)) {
             next_stage = 0;

@@ -39,6 +39,7 @@ struct DotTileSelectPass : public mlir::Pass {
       d.config.schedule = tc.schedule;
       d.config.group_m = tc.group_m;
       d.config.cta_pair = tc.cta_pair ? 1 : 2;
+      d.config.atoms = tc.atoms;
       txd::fill_plan_info(d.problem, tc, &d.preview);
     }
   }
