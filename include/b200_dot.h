@@ -95,7 +95,7 @@ typedef struct tx_dot_config {
                             the rest run as the masked remainder. */
   int32_t cta_pair;      /* 1 = two-CTA clusters (tcgen05 cta_group::2, 256 x block_n tiles),
                             2 = single CTAs (128 x block_n tiles), 0 = auto */
-  int32_t atoms;         /* 128-byte K atoms per pipeline stage: 1 or 2 (block_k = atoms * 128 B) */
+  int32_t atoms;         /* 128-byte K atoms per pipeline stage: 1, 2 or 4 (block_k = atoms * 128 B) */
   int32_t reserved;
 } tx_dot_config;
 

@@ -208,7 +208,6 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   if (cfg_in) cfg = *cfg_in;
   cfg.schedule = TXD_SCHED_STREAM_K;
   cfg.cta_pair = 2;
-  cfg.atoms = 1;
   txd::MachineModel mm;
   mm.sm_count = setup->sm_count;
   txd::TileChoice tc;
@@ -285,7 +284,7 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   prm.q_stage_bytes = tc.q_stage_bytes;
   prm.tmem_cols = tc.tmem_cols;
   prm.tma_store = tma_store ? 1 : 0;
-  prm.atoms = 1;
+  prm.atoms = tc.atoms;
 
   // The counters of the tiles this call touches must be zero when its kernel starts; an earlier call
   // that gave up on a wait may have left some non-zero.

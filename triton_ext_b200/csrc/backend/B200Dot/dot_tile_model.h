@@ -26,7 +26,9 @@ struct MachineModel {
                                         // a loads-only run of the ring moved 56 B/clk/SM)
   double hbm_bytes_per_s = 6.4596e12;   // measured copy bandwidth of this pool's B200
   double block_overhead_clk = 0;        // per K block handshake cost not hidden behind the MMAs (measured: none)
-  double hbm_bytes_per_s_per_cta = 50e9; // what one persistent CTA's TMA ring sustains
+  double hbm_bytes_per_s_per_cta = 60e9; // what one persistent CTA's TMA ring sustains from HBM
+  double tma_issue_ns = 90;             // time one TMA copy occupies the thread that issues it
+  double stage_issue_ns = 60;           // per-stage cost of a producer warp besides the copies
   int smem_budget = 227 * 1024 - 2048;  // dynamic shared memory per CTA minus control block + slack
 };
 
@@ -81,8 +83,8 @@ inline double algorithmic_bytes(const tx_dot_problem &pr) {
 
 // Modelled time of one (role assignment, block_n, pairing, schedule) candidate.
 inline double model_seconds(const MachineModel &mm, int es, int p_extent, int q_extent, int k,
-                            int block_n, bool q_mn_major, bool pair, int atoms, int schedule, int workers,
-                            double algo_bytes) {
+                            int block_n, bool p_mn_major, bool q_mn_major, bool pair, int atoms, int schedule,
+                            int workers, double algo_bytes) {
   const int bk_atom = 128 / es;
   const int bk = atoms * bk_atom;
   const int k_blocks = cdiv(k, bk);
@@ -124,7 +126,12 @@ inline double model_seconds(const MachineModel &mm, int es, int p_extent, int q_
   const int ctas = pair ? 2 * workers : workers;
   const double t_hbm =
       algo_bytes / std::min(mm.hbm_bytes_per_s, ctas * mm.hbm_bytes_per_s_per_cta) / balance;
-  return std::max(t_tensor, t_hbm) + 3e-6;  // + launch and pipeline fill
+  // One warp per operand issues the stage's TMA copies: K-major operands take one copy per atom,
+  // MN-major operands one per 128-byte-wide chunk of rows.
+  const int p_copies = p_mn_major ? 128 / bk_atom : atoms;
+  const int q_copies = q_mn_major ? cdiv(q_rows_cta, bk_atom) : atoms;
+  const double t_issue = blocks_per_worker * (mm.stage_issue_ns + mm.tma_issue_ns * std::max(p_copies, q_copies)) * 1e-9;
+  return std::max(std::max(t_tensor, t_hbm), t_issue) + 3e-6;  // + launch and pipeline fill
 }
 
 // Fill every unset field of `cfg`. Returns 0, or a negative value with *why set.
@@ -160,6 +167,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
     const int q_extent = swap ? pr.m : pr.n;
     // Q is MN-major when its rows (the Q index) are contiguous in memory.
     const bool q_mn = swap ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
+    const bool p_mn_c = swap ? (pr.b_layout == TXD_ROW_MAJOR) : (pr.a_layout == TXD_COL_MAJOR);
     for (int bn : kBlockNs) {
       if (cfg.block_n && bn != cfg.block_n) continue;
       // Do not pad the Q side by more than one tile's worth beyond need.
@@ -173,15 +181,17 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
           if (swap || bn < 128 || (q_mn && (bn / 2) % bk != 0)) continue;
           if (cfg.cta_pair == 0 && p_extent < 512) continue;
         }
-        for (int atoms = 1; atoms <= 2; ++atoms) {
+        for (int atoms = 1; atoms <= 4; atoms *= 2) {
         if (cfg.atoms && atoms != cfg.atoms) continue;
+        // An MN-major operand is loaded as boxes atoms*bk K-slices tall; a TMA box dimension is at most 256.
+        if ((p_mn_c || q_mn) && atoms * bk > 256) continue;
         {
           // Two atoms per stage halve the per-block handshakes but also the ring depth: keep >= 3 stages.
           const int q_rows_cta = pair ? bn / 2 : bn;
           const int stage = atoms * (128 * 128 + round_up((q_mn ? round_up(q_rows_cta, bk) : q_rows_cta) * 128, 1024));
           const int staging = (!swap && bn >= 64) ? 4 * 2 * 32 * 128 : 0;
-          if (atoms == 2 && (mm.smem_budget - staging) / stage < 3) continue;
-          if (atoms == 2 && pr.k < 4 * atoms * bk) continue;
+          if (atoms >= 2 && (mm.smem_budget - staging) / stage < 3) continue;
+          if (atoms >= 2 && pr.k < 4 * atoms * bk) continue;
         }
         const int tiles = cdiv(p_extent, pair ? 256 : 128) * cdiv(q_extent, bn);
         const int k_blocks = cdiv(pr.k, bk * atoms);
@@ -197,11 +207,17 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
             const int tail = tiles % workers;
             if (tiles < workers || tail == 0 || (long long)tail * k_blocks < workers) continue;
           }
-          double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, q_mn, pair != 0, atoms, sched, workers, algo);
+          double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, p_mn_c, q_mn, pair != 0, atoms, sched, workers, algo);
           // Prefer the simpler schedule on near-ties, and the role assignment that pads less: zero
           // rows still cost shared-memory fill and tensor cycles even when HBM time hides them.
           // Pure stream-K also spreads concurrently running tiles over the whole matrix (worse L2 reuse).
-          if (sched == TXD_SCHED_STREAM_K) t *= 1.10;
+          // K-block depth: tensor-bound problems ran fastest with one atom per stage (deepest ring);
+          // HBM-bound ones with deep blocks (fewer TMA copies and handshakes per byte). Both measured.
+          {
+            int lg = atoms == 4 ? 2 : (atoms == 2 ? 1 : 0);
+            t *= out.hbm_bound ? 1.0 - (lg >= 1 ? 0.02 : 0.0) + (lg == 2 ? 0.005 : 0.0) : 1.0 + 0.02 * lg;
+          }
+          if (sched == TXD_SCHED_STREAM_K) t = t * 1.10 + 6e-6;  // + fix-up of the partial tiles (measured on 16x14336x4096)
           // Measured on 4096x4096x4160 (3.46 waves): the partial-tile fix-up of the last wave costs more than
           // the idle SMs it saves, so whole tiles win unless the partial wave is nearly empty.
           if (sched == TXD_SCHED_HYBRID) t *= 1.20;

@@ -96,7 +96,7 @@ struct alignas(64) DotParams {
   int32_t p_stage_bytes, q_stage_bytes;
   int32_t tmem_cols;
   int32_t tma_store;                 // 1 = epilogue stores through shared memory + TMA
-  int32_t atoms;                     // 128-byte K atoms per stage: 1 or 2 (0 reads as 1)
+  int32_t atoms;                     // 128-byte K atoms per stage: 1, 2 or 4 (0 reads as 1)
   int32_t debug_flags;               // measurement / test switches, 0 in production (results are wrong
                                      // when set): 1 = do not refill stages (tensor-pipe-only timing),
                                      // 2 = one MMA per tile (load-only timing), 4 = skip C stores,
@@ -371,12 +371,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
   return mbar_wait_timed(bar, parity, ac, code);
 }
 
-// A converged warp waits on a barrier. Every lane polls: leaving the polling to one lane makes the
-// warp diverge around the loop, and a diverged role warp was measured to run its whole loop about
-// twice as slowly (the K-loop handshake then starves the tensor pipe).
+// A converged warp waits on a barrier. The loop is warp-uniform (a role warp that diverges around its
+// wait loop was measured to run about twice as slowly), but only lane 0 touches the barrier, with
+// mbarrier.try_wait, which parks the thread in hardware until the phase completes or a short time-out:
+// this kernel runs at the board's power limit, and 32 lanes spinning on shared memory in three warps
+// per CTA cost clock frequency.
 __device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl &ac, uint32_t code,
-                                               int /*lane*/) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, ac, code));
+                                               int lane) {
+#pragma unroll 1
+  for (uint32_t it = 0; it < kPollsBeforeTimer; ++it) {
+    uint32_t ok = 0;
+    if (lane == 0) ok = mbar_try_wait(bar, parity) ? 1u : 0u;
+    if (__shfl_sync(0xffffffffu, ok, 0)) return true;
+  }
+  uint32_t ok = 0;
+  if (lane == 0) ok = mbar_wait_timed(bar, parity, ac, code) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -784,13 +794,15 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
       uint32_t issued = 0;
       bool ok = true;
       const bool issuer = elect_one();
+      bool have_slot = false;
       while (ok && it.next(s)) {
         int tp, tq;
         tile_coords(p, s.tile, tp, tq);
         const int p0 = tp * rows_per_tile + static_cast<int>(cta_rank) * kBlockM;
         const int q0 = tq * p.block_n + static_cast<int>(cta_rank) * q_rows_per_cta;
         for (int kb = s.kb0; kb < s.kb1; ++kb) {
-          if (!warp_mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer, lane)) {
+          // `have_slot`: the probe issued at the end of the previous block already saw this stage free.
+          if (!have_slot && !warp_mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer, lane)) {
             ok = false;
             break;
           }
@@ -805,6 +817,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
             if (leader && issuer && load_p) mbar_arrive(full_local);
             ++issued;
             if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1u; }
+            have_slot = false;
             continue;
           }
           if (issuer) {
@@ -842,6 +855,8 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
             stage = 0;
             phase ^= 1u;
           }
+          // Probe the next stage's "empty" barrier now; the answer is used at the top of the next block.
+          have_slot = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u));
         }
       }
       if ((!ok || *ac.flag) && issuer && load_p) {
@@ -894,16 +909,21 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
       const uint32_t p_lo_base = p.p_desc_lbo | ((stage_base & 0x3FFFFu) >> 4);
       const uint32_t q_lo_base = p.q_desc_lbo | (((stage_base + static_cast<uint32_t>(p.p_stage_bytes)) & 0x3FFFFu) >> 4);
       const uint32_t stage16 = stage_bytes >> 4;
+      const uint32_t full0 = smem_u32(&ctl->full_bar[0]), empty0 = smem_u32(&ctl->empty_bar[0]);
+      const uint32_t n_stages = static_cast<uint32_t>(p.stages);
+      const uint32_t p_hi = p.p_desc_hi, q_hi = p.q_desc_hi, p_kstep = p.p_kstep, q_kstep = p.q_kstep;
+      const bool slow_mode = (p.debug_flags & 2) != 0;
       // Start-address step (16-byte units) from one K atom of a stage to the next: K-major atoms lie side
       // by side (rows x 128 bytes each); MN-major stages are linear in K.
       const uint32_t p_atom_step = p.p_mn_major ? 4u * p.p_kstep : static_cast<uint32_t>(kBlockM) * kStageRowBytes / 16u;
       const uint32_t q_atom_step = p.q_mn_major ? 4u * p.q_kstep : static_cast<uint32_t>(q_rows_per_cta) * kStageRowBytes / 16u;
+      const bool f8 = p.kind_f8 != 0;
       auto mma = [&](uint32_t d_tmem, uint64_t pd, uint64_t qd, uint32_t accumulate) {
         if (kPair) {
-          if (p.kind_f8) umma_f8_pair(d_tmem, pd, qd, p.idesc, accumulate);
+          if (f8) umma_f8_pair(d_tmem, pd, qd, p.idesc, accumulate);
           else umma_f16_pair(d_tmem, pd, qd, p.idesc, accumulate);
         } else {
-          if (p.kind_f8) umma_f8(d_tmem, pd, qd, p.idesc, accumulate);
+          if (f8) umma_f8(d_tmem, pd, qd, p.idesc, accumulate);
           else umma_f16(d_tmem, pd, qd, p.idesc, accumulate);
         }
       };
@@ -915,15 +935,18 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * static_cast<uint32_t>(p.block_n);
         uint32_t accumulate = 0;
-        // Software-pipelined K loop. tcgen05.commit holds the issuing thread until the MMAs before it
-        // have been handed to the tensor pipe, so everything that can be done ahead of it is: the wait
-        // for the NEXT stage sits between this block's MMAs and this block's commit and runs while the
-        // MMAs execute. After the commit the next block's MMAs go out at once.
+        // The tensor pipe does not run ahead of the issuing thread: every cycle this thread spends on
+        // anything but MMA issue between two MMAs of consecutive K blocks was measured to be a pipe bubble
+        // of the same length, and each tcgen05.commit costs a further ~140 cycles of drain. So the probe
+        // of the NEXT stage's barrier and the warp vote on it are interleaved with this block's MMAs
+        // (whose issue is back-pressured by the pipe anyway), and only the commit, the loop counters and
+        // one branch separate the last MMA of a block from the first MMA of the next.
         auto wait_full = [&](uint32_t st, uint32_t ph) -> bool {
-          if (!warp_mbar_wait(smem_u32(&ctl->full_bar[st]), ph, ac, kDevTimeoutMmaFull, lane)) return false;
+          if (!warp_mbar_wait(full0 + st * 8u, ph, ac, kDevTimeoutMmaFull, lane)) return false;
           tc_fence_after();
           return true;
         };
+        // Generic block: any MMA count (the remainder's last block, measurement modes); no probe.
         auto issue_block = [&](uint32_t st, int n_mma) {
           // Low descriptor words (start address in 16-byte units | leading-dimension field); shared
           // memory ends below 256 KiB, so adding offsets never carries out of the 14-bit address field.
@@ -931,23 +954,38 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           const uint32_t qlo = q_lo_base + st * stage16;
           if (p.debug_flags & 2) n_mma = (accumulate == 0) ? 1 : 0;
           if (issuer) {
-            if (n_mma == mmas_per_block) {
-              for (int at = 0; at < atoms; ++at) {
-                const uint32_t pa = plo + at * p_atom_step, qa = qlo + at * q_atom_step;
-#pragma unroll
-                for (int j = 0; j < kMmasPerAtom; ++j)
-                  mma(d_tmem, desc64(p.p_desc_hi, pa + j * p.p_kstep), desc64(p.q_desc_hi, qa + j * p.q_kstep),
-                      (accumulate | static_cast<uint32_t>(at | j)) != 0 ? 1u : 0u);
-              }
-            } else {
 #pragma unroll 1
-              for (int j = 0; j < n_mma; ++j)
-                mma(d_tmem, desc64(p.p_desc_hi, plo + (j >> 2) * p_atom_step + (j & 3) * p.p_kstep),
-                    desc64(p.q_desc_hi, qlo + (j >> 2) * q_atom_step + (j & 3) * p.q_kstep),
-                    (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
-            }
+            for (int j = 0; j < n_mma; ++j)
+              mma(d_tmem, desc64(p.p_desc_hi, plo + (j >> 2) * p_atom_step + (j & 3) * p.p_kstep),
+                  desc64(p.q_desc_hi, qlo + (j >> 2) * q_atom_step + (j & 3) * p.q_kstep),
+                  (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
+            commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
           }
           if (n_mma > 0) accumulate = 1;
+        };
+        // Full block on the fast path. Returns the warp-uniform probe result for stage `nst`.
+        auto full_block = [&](uint32_t st, uint32_t nst, uint32_t nph, bool more) -> bool {
+          const uint32_t plo = p_lo_base + st * stage16;
+          const uint32_t qlo = q_lo_base + st * stage16;
+          if (issuer) mma(d_tmem, desc64(p_hi, plo), desc64(q_hi, qlo), accumulate);
+          const bool peek = more ? mbar_test_wait(full0 + nst * 8u, nph) : true;
+          if (issuer) {
+            mma(d_tmem, desc64(p_hi, plo + p_kstep), desc64(q_hi, qlo + q_kstep), 1u);
+            mma(d_tmem, desc64(p_hi, plo + 2u * p_kstep), desc64(q_hi, qlo + 2u * q_kstep), 1u);
+          }
+          const bool peek_all = __all_sync(0xffffffffu, peek);
+          if (issuer) {
+            mma(d_tmem, desc64(p_hi, plo + 3u * p_kstep), desc64(q_hi, qlo + 3u * q_kstep), 1u);
+            for (int at = 1; at < atoms; ++at) {
+              const uint32_t pa = plo + at * p_atom_step, qa = qlo + at * q_atom_step;
+#pragma unroll
+              for (int j = 0; j < kMmasPerAtom; ++j)
+                mma(d_tmem, desc64(p_hi, pa + j * p_kstep), desc64(q_hi, qa + j * q_kstep), 1u);
+            }
+            commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
+          }
+          accumulate = 1;
+          return peek_all;
         };
         // LoopSplit: blocks below `mid` belong to the main loop [lo, mid) — full, unpredicated; blocks
         // from `mid` on are the remainder loop [mid, hi), whose stages TMA zero-filled past K and whose
@@ -955,16 +993,21 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         const int mid = s.kb1 < p.k_main_blocks ? s.kb1 : p.k_main_blocks;
         ok = wait_full(stage, phase);
         for (int kb = s.kb0; ok && kb < s.kb1; ++kb) {
-          const bool in_main = kb < mid;
-          issue_block(stage, (in_main || kb != p.k_blocks - 1) ? mmas_per_block : p.tail_mmas);
           uint32_t next_stage = stage + 1, next_phase = phase;
-          if (next_stage == static_cast<uint32_t>(p.stages)) {
+          if (next_stage == n_stages) {
             next_stage = 0;
             next_phase ^= 1u;
           }
-          if (kb + 1 < s.kb1) ok = wait_full(next_stage, next_phase);
-          if (issuer) commit_to(smem_u32(&ctl->empty_bar[stage]));  // frees the stage when its MMAs retire
-          __syncwarp();
+          const bool more = kb + 1 < s.kb1;
+          const bool full = (kb < mid || kb != p.k_blocks - 1 || p.tail_mmas == mmas_per_block) && !slow_mode;
+          bool next_ready = false;
+          if (full) {
+            next_ready = full_block(stage, next_stage, next_phase, more);
+          } else {
+            issue_block(stage, kb == p.k_blocks - 1 ? p.tail_mmas : mmas_per_block);
+            __syncwarp();
+          }
+          if (more && !next_ready) ok = wait_full(next_stage, next_phase);
           stage = next_stage;
           phase = next_phase;
         }
