@@ -33,7 +33,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures
 # (profiles/*.md name the command); None where no capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": None, "cfg3": None, "cfg4": None, "cfg5_nshard": None, "cfg5_kshard": None}
+NCU_TRAFFIC_BYTES = {"cfg2": 110.2e6, "cfg3": 122.2e6, "cfg4": 462.9e6, "cfg5_nshard": None, "cfg5_kshard": None}
 
 
 def measured_peaks() -> dict:
