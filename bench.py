@@ -12,6 +12,8 @@ through the C-ABI (tx_dot_run). Workloads (BASELINE.json `configs`):
     cfg4         fp8 e4m3 8192^3 with per-row / per-column fp32 scales -> bf16.
     cfg5_nshard  bf16 16384x28672x8192, columns of B and C split over the ranks: strong scaling.
     cfg5_kshard  same GEMM, K split over the ranks, fp32 partials, NCCL reduce-scatter.
+    cfg5_kshard_fused[_bf16]  K split over the ranks, the GEMM epilogue stores partial tiles into the owning
+                 rank's memory over NVLink (fp32 or bf16 partials), then one local slot reduction.
 
 One JSON line is printed by rank 0. `--impl reference` times the reference's CPU path for the same
 workload (the same tt.dot run by Triton's interpreter on the host cores) on a bounded tile sample.
@@ -53,6 +55,8 @@ WORKLOADS = {
     "cfg4": dict(m=8192, n=8192, k=8192, dtype="fp8", seed=3, dist="normal", scales=True, k_split=0, block=(128, 128, 128)),
     "cfg5_nshard": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
     "cfg5_kshard": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
+    "cfg5_kshard_fused": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
+    "cfg5_kshard_fused_bf16": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
 }
 
 
@@ -127,7 +131,7 @@ def shard_shape(name: str, w: dict, rank: int, world: int) -> dict:
     if name == "cfg5_nshard":
         n0, n1 = split_range(n, world, rank, align=256)
         return dict(m=m, n=n1 - n0, k=k, scaling="strong", job_flops=2.0 * m * n * k, parallelism=f"n-sharded x{world}")
-    if name == "cfg5_kshard":
+    if name.startswith("cfg5_kshard"):
         k0, k1 = split_range(k, world, rank, align=128)
         return dict(m=m, n=n, k=k1 - k0, scaling="strong", job_flops=2.0 * m * n * k, parallelism=f"k-sharded x{world} + reduce-scatter")
     # every rank runs one full-size problem: its own column panel of an N-times-wider GEMM
@@ -266,7 +270,8 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
     m, n, k = shp["m"], shp["n"], shp["k"]
     in_dt = torch_dtype(w["dtype"])
     out_dt = torch.bfloat16
-    kshard = name == "cfg5_kshard" and world > 1
+    fused = name.startswith("cfg5_kshard_fused") and world > 1
+    kshard = name.startswith("cfg5_kshard") and world > 1 and not fused
     a_h, b_h, rs_h, cs_h = make_host_inputs(w, shp, rank)
     a_h, b_h = a_h.pin_memory(), b_h.pin_memory()
     step_out_dt = torch.float32 if kshard else out_dt
@@ -281,6 +286,10 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
     rs_d = rs_h.to(dev) if rs_h is not None else None
     cs_d = cs_h.to(dev) if cs_h is not None else None
 
+    fused_op = None
+    if fused:
+        pdt = torch.bfloat16 if name.endswith("_bf16") else torch.float32
+        fused_op = par.FusedKShardedDot(m, n, k, in_dt, out_dt, partial_dtype=pdt, device=dev)
     cfg = B.make_config(k_split_point=w["k_split"]) if w["k_split"] else None
     pr = B.make_problem(m, n, k, in_dt, step_out_dt, row_scale=rs_h is not None and not kshard,
                         col_scale=cs_h is not None and not kshard)
@@ -302,6 +311,10 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
             part = gemm(i)
             dist.reduce_scatter_tensor(scat, part, op=dist.ReduceOp.SUM)
             final.copy_(scat)  # cast epilogue after the reduction
+    elif fused:
+        def step(i):
+            a_d, b_d, _ = sets[i % n_sets]
+            return fused_op(a_d, b_d)
     else:
         step = gemm
 
@@ -339,13 +352,13 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
 
     # ---- end to end through the host-buffer entry point (H2D + kernel + D2H every step) -------------------
     e2e_steps = max(1, min(args.steps, 10))
-    if kshard:
+    if kshard or fused:
         def e2e_step(i):
             a_d, b_d, c_d = sets[0]
             a_d.copy_(a_h, non_blocking=True)
             b_d.copy_(b_h, non_blocking=True)
-            step(0)
-            return final.cpu()
+            r = step(0)
+            return (r if fused else final).cpu()
         h2d, d2h = (m * k + k * n) * es, (m // world) * n * 2
     else:
         def e2e_step(i):
@@ -381,7 +394,7 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_BYTES.get(name),
                 "peak_source": f"bf16_tflops (burst) of {peaks['_source']}" + (" x2 for fp8 (no measured fp8 figure)" if w["dtype"] == "fp8" else "")}
-        if kshard:
+        if kshard or fused:
             roof["note"] = "step time includes the reduce-scatter; achieved is per-GPU GEMM FLOPs over the whole step"
 
     line = {

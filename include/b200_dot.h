@@ -155,6 +155,25 @@ TXD_API int tx_dot_plan_check(tx_dot_plan *plan, void *stream);
 TXD_API int tx_dot_run_host(tx_dot_plan *plan, const void *a_host, const void *b_host, void *c_host,
                             const float *row_scale_host, const float *col_scale_host);
 
+/*
+ * K-sharded GEMM fused with its partial-sum exchange (one process per GPU, `world` ranks over NVLink).
+ * Rank r holds A[:, k_r] and B[k_r, :] and creates a plan for the m x n x |k_r| problem with out_dtype F32
+ * or BF16, no scales, alpha 1, whole-tile schedule. Instead of writing C, the kernel's epilogue stores each
+ * tile straight into the memory of the rank that owns the tile's rows: slot_bases[o] is the device address
+ * (peer-mapped where o != rank) of rank o's slot buffer, laid out [world][m / world][n] in out_dtype, and this
+ * rank writes slot `rank` of every buffer. The stores are ordinary TMA tensor stores; no multicast is used.
+ * Needs m % world == 0 and (m / world) % block_m == 0, world <= 8.
+ * After every rank's launch has completed (a stream-ordered barrier between the ranks is the caller's job),
+ * tx_dot_reduce_slots sums the `world` slots of the local buffer in slot order (deterministic), applies
+ * alpha / row_scale / col_scale and casts:  out[r, c] = cast(alpha * rs[r] * cs[c] * sum_s slots[s][r][c]).
+ * The reference has no multi-GPU code; this is the fused form of "GEMM, then reduce-scatter".
+ */
+TXD_API int tx_dot_run_to_slots(tx_dot_plan *plan, const void *a, const void *b, void *const *slot_bases,
+                                int32_t world, int32_t rank, void *stream);
+TXD_API int tx_dot_reduce_slots(const void *slots, int32_t world, int32_t rows, int32_t n, int32_t slot_dtype,
+                                void *out, int32_t out_dtype, int64_t ldc, const float *row_scale,
+                                const float *col_scale, float alpha, void *stream);
+
 TXD_API int tx_dot_plan_destroy(tx_dot_plan *plan);
 
 /*

@@ -260,3 +260,48 @@ def test_bounded_wait_reports_timeout(B, monkeypatch):
     good = B.dot(a, b, out_dtype=bf16, check=True)
     ref = a.float() @ b.float()
     assert bool(((good.float() - ref).abs() <= 1e-2 + 1e-2 * ref.abs()).all())
+
+
+# ---- 8. K-sharded GEMM with the exchange in its epilogue, emulated on one GPU ----------------------------------
+@pytest.mark.parametrize("partial_dtype", [f32, bf16])
+def test_slot_stores_and_reduction_single_gpu(B, dot_lib, partial_dtype):
+    """Two "ranks" share one GPU: each runs its K shard and stores tiles into its slot of the owner's buffer
+    (both buffers are local here, on a real job they are peer-mapped); the slot reduction then gives each
+    owner its rows of C. The kernels run one after the other, never waiting on one another."""
+    dev = torch.device("cuda:0")
+    world = 2
+    case = Case("kshard", 512, 384, 1152, bf16, bf16, seed=61, scales=True, block=(64, 64, 64))
+    a, b, rs, cs = make_inputs(case)
+    ad, bd, rsd, csd = a.to(dev), b.to(dev), rs.to(dev), cs.to(dev)
+    rows = case.m // world
+    slots = [torch.zeros(world, rows, case.n, dtype=partial_dtype, device=dev) for _ in range(world)]
+    ptrs = [t.data_ptr() for t in slots]
+    kshard = case.k // world
+    for rank in range(world):
+        plan = B.DotPlan(B.make_problem(case.m, case.n, kshard, bf16, partial_dtype, lda=case.k),  # A shard is a column slice
+                         B.make_config(schedule=B.TXD_SCHED_DATA_PARALLEL, swap_ab=2, cta_pair=1, block_n=128))
+        a_sh = ad[:, rank * kshard:(rank + 1) * kshard]
+        b_sh = bd[rank * kshard:(rank + 1) * kshard, :]
+        plan.run_to_slots(a_sh, b_sh, ptrs, rank)
+        plan.check()
+        plan.close()
+    want = c_oracle(dot_lib, case, a, b, rs, cs, bf16_truncate=False)
+    for owner in range(world):
+        out = torch.empty(rows, case.n, dtype=bf16, device=dev)
+        B.reduce_slots(slots[owner], out, row_scale=rsd[owner * rows:(owner + 1) * rows], col_scale=csd)
+        torch.cuda.synchronize()
+        got = out.cpu().double()
+        w = want[owner * rows:(owner + 1) * rows].double()
+        bound = 1e-2 + 1e-2 * w.abs()
+        if partial_dtype == bf16:
+            # each partial is rounded to bf16 before the sum: allow one bf16 ulp of every partial's magnitude
+            sl = slice(owner * rows, (owner + 1) * rows)
+            mag = sum((a[sl, r * kshard:(r + 1) * kshard].double() @ b[r * kshard:(r + 1) * kshard].double()).abs()
+                      for r in range(world))
+            bound = bound + 2.0 ** -8 * mag * rs[sl].double()[:, None] * cs.double()[None, :]
+        assert bool(((got - w).abs() <= bound).all()), (owner, float((got - w).abs().max()))
+    # argument checks of the slot form
+    plan = B.DotPlan(B.make_problem(case.m, case.n, kshard, bf16, f32, row_scale=True))
+    with pytest.raises(B.DotError):
+        plan.run_to_slots(ad[:, :kshard], bd[:kshard], ptrs, 0)
+    plan.close()

@@ -108,8 +108,11 @@ def load_library() -> ctypes.CDLL:
     lib.tx_dot_plan_check.argtypes = [vp, vp]
     lib.tx_dot_run_host.argtypes = [vp, vp, vp, vp, f32p, f32p]
     lib.tx_dot_plan_destroy.argtypes = [vp]
+    lib.tx_dot_run_to_slots.argtypes = [vp, vp, vp, ctypes.POINTER(vp), i32, i32, vp]
+    lib.tx_dot_reduce_slots.argtypes = [vp, i32, i32, i32, i32, vp, i32, ctypes.c_int64, f32p, f32p, ctypes.c_float, vp]
     for name in ("tx_dot_plan_create", "tx_dot_plan_preview", "tx_dot_plan_query", "tx_dot_run",
-                 "tx_dot_plan_check", "tx_dot_run_host", "tx_dot_plan_destroy"):
+                 "tx_dot_plan_check", "tx_dot_run_host", "tx_dot_plan_destroy", "tx_dot_run_to_slots",
+                 "tx_dot_reduce_slots"):
         getattr(lib, name).restype = ctypes.c_int
     _lib = lib
     return lib
@@ -195,6 +198,16 @@ class DotPlan:
             col_scale.data_ptr() if col_scale is not None else None,
             ctypes.c_void_p(s.cuda_stream)))
 
+    def run_to_slots(self, a: torch.Tensor, b: torch.Tensor, slot_ptrs: list, rank: int,
+                     stream: Optional[torch.cuda.Stream] = None) -> None:
+        """K-sharded form: store every tile into slot `rank` of the buffer of the rank owning its rows.
+        `slot_ptrs[o]` is the device address of rank o's [world, m/world, n] slot buffer (peer-mapped)."""
+        s = stream if stream is not None else torch.cuda.current_stream(a.device)
+        world = len(slot_ptrs)
+        arr = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(p)) for p in slot_ptrs])
+        _check(self._lib.tx_dot_run_to_slots(self._h, a.data_ptr(), b.data_ptr(), arr, world, rank,
+                                             ctypes.c_void_p(s.cuda_stream)))
+
     def check(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream()
         _check(self._lib.tx_dot_plan_check(self._h, ctypes.c_void_p(s.cuda_stream)))
@@ -220,6 +233,21 @@ class DotPlan:
             self.close()
         except Exception:
             pass
+
+
+def reduce_slots(slots: torch.Tensor, out: torch.Tensor, *, row_scale: Optional[torch.Tensor] = None,
+                 col_scale: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                 stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """out[r, c] = cast(alpha * rs[r] * cs[c] * sum_s slots[s, r, c]); slots is [world, rows, n], f32 or bf16."""
+    world, rows, n = slots.shape
+    if not slots.is_contiguous() or out.stride(1) != 1:
+        raise ValueError("slots must be contiguous and out row-major")
+    s = stream if stream is not None else torch.cuda.current_stream(slots.device)
+    _check(load_library().tx_dot_reduce_slots(
+        slots.data_ptr(), world, rows, n, _DTYPES[slots.dtype], out.data_ptr(), _DTYPES[out.dtype], out.stride(0),
+        row_scale.data_ptr() if row_scale is not None else None,
+        col_scale.data_ptr() if col_scale is not None else None, ctypes.c_float(alpha), ctypes.c_void_p(s.cuda_stream)))
+    return out
 
 
 _plan_cache: dict = {}

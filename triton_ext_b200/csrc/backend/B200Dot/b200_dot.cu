@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -346,13 +347,121 @@ int tx_dot_plan_query(const tx_dot_plan *plan, tx_dot_plan_info *info) {
   return TXD_OK;
 }
 
+}  // extern "C"
+
+namespace {
+struct RemoteTarget {
+  void *const *slot_bases = nullptr;
+  int world = 0, rank = 0;
+};
+int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const float *row_scale, const float *col_scale,
+               void *stream_v, const RemoteTarget *remote);
+
+__global__ void reduce_slots_kernel(const void *slots, int world, long long rows, long long n, int slot_f32, void *out,
+                                    int out_dtype, long long ldc, const float *row_scale, const float *col_scale,
+                                    float alpha) {
+  // One thread per 4 consecutive columns; slots are summed in slot order in fp32.
+  const long long groups = (n + 3) / 4;
+  const long long total = rows * groups;
+  const long long slot_elems = rows * n;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / groups, c0 = (i - r * groups) * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool vec = (c0 + 4 <= n) && (n % 4 == 0);
+    for (int s = 0; s < world; ++s) {
+      const long long off = s * slot_elems + r * n + c0;
+      if (slot_f32) {
+        const float *src = static_cast<const float *>(slots) + off;
+        if (vec) {
+          const float4 v = __ldcs(reinterpret_cast<const float4 *>(src));
+          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        } else {
+          for (int j = 0; j < 4 && c0 + j < n; ++j) acc[j] += src[j];
+        }
+      } else {
+        const __nv_bfloat16 *src = static_cast<const __nv_bfloat16 *>(slots) + off;
+        if (vec) {
+          const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(src));
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&v.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&v.y);
+          acc[0] += __low2float(lo); acc[1] += __high2float(lo); acc[2] += __low2float(hi); acc[3] += __high2float(hi);
+        } else {
+          for (int j = 0; j < 4 && c0 + j < n; ++j) acc[j] += __bfloat162float(src[j]);
+        }
+      }
+    }
+    const float rs = (row_scale ? row_scale[r] : 1.0f) * alpha;
+    for (int j = 0; j < 4 && c0 + j < n; ++j) {
+      const float v = acc[j] * rs * (col_scale ? col_scale[c0 + j] : 1.0f);
+      const long long o = r * ldc + c0 + j;
+      if (out_dtype == TXD_F32) static_cast<float *>(out)[o] = v;
+      else if (out_dtype == TXD_BF16) static_cast<__nv_bfloat16 *>(out)[o] = __float2bfloat16_rn(v);
+      else static_cast<__half *>(out)[o] = __float2half_rn(v);
+    }
+  }
+}
+}  // namespace
+
+extern "C" {
+
 int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const float *row_scale,
                const float *col_scale, void *stream_v) {
+  return launch_dot(pl, a, b, c, row_scale, col_scale, stream_v, nullptr);
+}
+
+int tx_dot_run_to_slots(tx_dot_plan *pl, const void *a, const void *b, void *const *slot_bases, int32_t world,
+                        int32_t rank, void *stream_v) {
+  if (!pl || !slot_bases) return fail(TXD_ERR_INVALID, "null argument");
+  const tx_dot_problem &pr = pl->problem;
+  const txd::TileChoice &tc = pl->tc;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(TXD_ERR_INVALID, "world must be 1..8 and rank inside it");
+  if (pr.m == 0 || pr.n == 0 || pr.k == 0) return fail(TXD_ERR_UNSUPPORTED, "empty problems have no slot form");
+  if (pr.has_row_scale || pr.has_col_scale || pr.alpha != 1.0f)
+    return fail(TXD_ERR_INVALID, "partials are exchanged unscaled: create the plan without scales; tx_dot_reduce_slots applies them");
+  if (pr.out_dtype != TXD_F32 && pr.out_dtype != TXD_BF16) return fail(TXD_ERR_UNSUPPORTED, "slots are f32 or bf16");
+  if (!tc.tma_store || tc.swap_ab || tc.schedule != TXD_SCHED_DATA_PARALLEL || pr.ldc != pr.n)
+    return fail(TXD_ERR_UNSUPPORTED, "slot stores need the whole-tile schedule, the TMA-store epilogue and ldc == n "
+                                     "(create the plan with schedule = TXD_SCHED_DATA_PARALLEL, swap_ab = 2)");
+  if (pr.m % world != 0 || (pr.m / world) % tc.block_m != 0)
+    return fail(TXD_ERR_UNSUPPORTED, "m / world = %d must be a multiple of the tile height %d", pr.m / world, tc.block_m);
+  for (int r = 0; r < world; ++r)
+    if (!slot_bases[r] || (reinterpret_cast<uintptr_t>(slot_bases[r]) & 15))
+      return fail(TXD_ERR_INVALID, "slot base %d is null or not 16-byte aligned", r);
+  RemoteTarget rt;
+  rt.slot_bases = slot_bases;
+  rt.world = world;
+  rt.rank = rank;
+  return launch_dot(pl, a, b, nullptr, nullptr, nullptr, stream_v, &rt);
+}
+
+int tx_dot_reduce_slots(const void *slots, int32_t world, int32_t rows, int32_t n, int32_t slot_dtype, void *out,
+                        int32_t out_dtype, int64_t ldc, const float *row_scale, const float *col_scale, float alpha,
+                        void *stream_v) {
+  if (!slots || !out || world < 1 || rows < 0 || n < 0 || ldc < n) return fail(TXD_ERR_INVALID, "bad argument");
+  if (slot_dtype != TXD_F32 && slot_dtype != TXD_BF16) return fail(TXD_ERR_UNSUPPORTED, "slots are f32 or bf16");
+  if (out_dtype != TXD_F32 && out_dtype != TXD_BF16 && out_dtype != TXD_F16) return fail(TXD_ERR_UNSUPPORTED, "output dtype must be f16, bf16 or f32");
+  if (rows == 0 || n == 0) return TXD_OK;
+  const long long total = static_cast<long long>(rows) * ((n + 3) / 4);
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148LL * 16));
+  reduce_slots_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
+      slots, world, rows, n, slot_dtype == TXD_F32 ? 1 : 0, out, out_dtype, ldc, row_scale, col_scale, alpha);
+  TXD_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  return TXD_OK;
+}
+
+}  // extern "C"
+
+namespace {
+int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const float *row_scale, const float *col_scale,
+               void *stream_v, const RemoteTarget *remote) {
   if (!pl) return fail(TXD_ERR_INVALID, "null plan");
   const tx_dot_problem &pr = pl->problem;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (pr.m == 0 || pr.n == 0) return TXD_OK;
-  if (!c) return fail(TXD_ERR_INVALID, "null output pointer");
+  if (!c && !remote) return fail(TXD_ERR_INVALID, "null output pointer");
   if (pr.k == 0) {
     dot_zero_fill_kernel<<<pl->sm_count, 256, 0, stream>>>(c, pr.ldc, pr.m, pr.n, txd::elem_bytes(pr.out_dtype));
     TXD_CUDA(cudaGetLastError());
@@ -381,8 +490,8 @@ int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
     pl->q_cache.ptr = q_ptr;
   }
   // TMA store needs a 16-byte aligned C; otherwise this launch stores straight from registers.
-  const bool tma_store = tc.tma_store && (reinterpret_cast<uintptr_t>(c) & 15) == 0;
-  if (tma_store && pl->out_cache.ptr != c) {
+  const bool tma_store = tc.tma_store && (remote || (reinterpret_cast<uintptr_t>(c) & 15) == 0);
+  if (tma_store && !remote && pl->out_cache.ptr != c) {
     int rc = encode_store_map(&pl->out_cache.map, c, pr.out_dtype, pr.m, pr.n, pr.ldc);
     if (rc) return rc;
     pl->out_cache.ptr = c;
@@ -395,7 +504,17 @@ int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
   prm.scale_row = swap ? col_scale : row_scale;
   prm.scale_col = swap ? row_scale : col_scale;
   prm.tma_store = tma_store ? 1 : 0;
-  if (tma_store) prm.tmap_out = pl->out_cache.map;
+  if (tma_store && !remote) prm.tmap_out = pl->out_cache.map;
+  if (remote) {
+    // One store map per destination rank: its slot buffer seen as a [world * rows_per_rank, n] matrix.
+    prm.remote_world = remote->world;
+    prm.remote_rank = remote->rank;
+    prm.rows_per_rank = pr.m / remote->world;
+    for (int r = 0; r < remote->world; ++r) {
+      int rc = encode_store_map(&prm.tmap_remote[r], remote->slot_bases[r], pr.out_dtype, pr.m, pr.n, pr.n);
+      if (rc) return rc;
+    }
+  }
   if (tc.cta_pair) {
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(tc.grid);
@@ -417,6 +536,9 @@ int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
   g_launches.fetch_add(1);
   return TXD_OK;
 }
+}  // namespace
+
+extern "C" {
 
 int tx_dot_plan_check(tx_dot_plan *pl, void *stream_v) {
   if (!pl) return fail(TXD_ERR_INVALID, "null plan");

@@ -62,6 +62,7 @@ struct alignas(64) DotParams {
   CUtensorMap tmap_p;
   CUtensorMap tmap_q;
   CUtensorMap tmap_out;    // valid when tma_store != 0
+  CUtensorMap tmap_remote[8];  // valid when remote_world > 0: rank r's partial-tile slots (peer memory)
   void *out;
   const float *scale_row;  // indexed by the P (lane) index, or null
   const float *scale_col;  // indexed by the Q (column) index, or null
@@ -97,6 +98,12 @@ struct alignas(64) DotParams {
   int32_t tmem_cols;
   int32_t tma_store;                 // 1 = epilogue stores through shared memory + TMA
   int32_t atoms;                     // 128-byte K atoms per stage: 1, 2 or 4 (0 reads as 1)
+  // K-sharded GEMM fused with its exchange: instead of C, a tile is stored into the slot this rank owns
+  // inside the memory of the rank that owns the tile's rows (plain TMA stores over NVLink, no multicast):
+  // slot buffer of rank o = [remote_world][rows_per_rank][n], this rank writes slot `remote_rank`.
+  int32_t remote_world;              // 0 = store to `out` as usual
+  int32_t remote_rank;
+  int32_t rows_per_rank;             // m / remote_world, a multiple of the tile height
   int32_t debug_flags;               // measurement / test switches, 0 in production (results are wrong
                                      // when set): 1 = do not refill stages (tensor-pipe-only timing),
                                      // 2 = one MMA per tile (load-only timing), 4 = skip C stores,
@@ -650,7 +657,13 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
         fence_proxy_async();
         __syncwarp();
         if (lane == 0 && !(p.debug_flags & 4)) {
-          tma_store_2d(&p.tmap_out, slab, qcol_tile + c0, prow0 + quarter * 32);
+          if (p.remote_world > 0) {
+            const int owner = prow0 / p.rows_per_rank;
+            const int y = (p.remote_rank - owner) * p.rows_per_rank + prow0 + quarter * 32;
+            tma_store_2d(&p.tmap_remote[owner], slab, qcol_tile + c0, y);
+          } else {
+            tma_store_2d(&p.tmap_out, slab, qcol_tile + c0, prow0 + quarter * 32);
+          }
           bulk_commit_group();
         }
         ++stores;
