@@ -510,6 +510,9 @@ int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
     prm.remote_world = remote->world;
     prm.remote_rank = remote->rank;
     prm.rows_per_rank = pr.m / remote->world;
+    // Rank r starts on the tile rows owned by rank r+1 and ends on its own, so that at any moment every owner
+    // receives from about one peer instead of all peers storing to the same owner.
+    prm.tp_rotate = ((remote->rank + 1) % remote->world) * (prm.rows_per_rank / (tc.cta_pair ? 256 : 128));
     for (int r = 0; r < remote->world; ++r) {
       int rc = encode_store_map(&prm.tmap_remote[r], remote->slot_bases[r], pr.out_dtype, pr.m, pr.n, pr.n);
       if (rc) return rc;

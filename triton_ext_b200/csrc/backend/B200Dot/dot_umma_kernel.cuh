@@ -104,6 +104,7 @@ struct alignas(64) DotParams {
   int32_t remote_world;              // 0 = store to `out` as usual
   int32_t remote_rank;
   int32_t rows_per_rank;             // m / remote_world, a multiple of the tile height
+  int32_t tp_rotate;                 // tile rows are visited starting here (mod tiles_p): ranks start on different owners
   int32_t debug_flags;               // measurement / test switches, 0 in production (results are wrong
                                      // when set): 1 = do not refill stages (tensor-pipe-only timing),
                                      // 2 = one MMA per tile (load-only timing), 4 = skip C stores,
@@ -457,6 +458,10 @@ __device__ __forceinline__ void tile_coords(const DotParams &p, int tile, int &t
   const int r = tile - g * per_group;
   tp = first + r % gsize;
   tq = r / gsize;
+  if (p.tp_rotate) {
+    tp += p.tp_rotate;
+    if (tp >= p.tiles_p) tp -= p.tiles_p;
+  }
 }
 
 // ----------------------------------------------------------------------------------------------
