@@ -1,0 +1,58 @@
+/* C-ABI of the fused attention forward kernel for sm_100a (B200).
+ *
+ * Replaces, for callers that bind a library instead of JIT-compiling Triton, the forward launch of the
+ * reference's demo kernel: `_attn_fwd[grid](q, k, v, sm_scale, M, o, strides..., Z, H, N_CTX, HEAD_DIM,
+ * BLOCK_M, BLOCK_N, CAUSAL)` in pass/LoopSplit/06-fused-attention.py:626-637 (kernel :164-240, inner loop
+ * :43-90). Same operands and results: q, k, v, out are contiguous [batch, heads, n_ctx, head_dim] tensors
+ * of one 16-bit type; `m` receives, per query row, running max + log2(sum) in base 2 (:236,:239), which
+ * the reference keeps for its backward pass.
+ *
+ * Plain pointers and sizes only; every function returns a tx_dot_status code (b200_dot.h) and
+ * tx_attn_last_error() holds the text of this thread's last failure. There is no CPU path: without an
+ * sm_100 device every compute entry point returns TXD_ERR_NO_DEVICE.
+ */
+#ifndef B200_ATTENTION_H_
+#define B200_ATTENTION_H_
+
+#include <stdint.h>
+
+#include "b200_dot.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tx_attn_problem {
+  int32_t batch, heads; /* Z, H of the reference launch                                             */
+  int32_t n_ctx;        /* sequence length; any value >= 1 (the reference asks for multiples of BLOCK_M) */
+  int32_t head_dim;     /* 64 or 128 (reference: {16, 32, 64, 128, 256}, :589)                       */
+  int32_t dtype;        /* TXD_F16 or TXD_BF16 for q, k, v and out                                   */
+  int32_t causal;       /* 0 / 1                                                                     */
+  float sm_scale;       /* > 0; scores are scaled by sm_scale * log2(e) and exponentiated in base 2   */
+  int32_t reserved[5];  /* zero                                                                      */
+} tx_attn_problem;
+
+/* Asynchronous launch on `stream` (a cudaStream_t); all pointers are device pointers, 16-byte aligned.
+ * `m` may be NULL when the caller does not need it. */
+TXD_API int tx_attn_fwd(const tx_attn_problem *problem, const void *q, const void *k, const void *v, void *out,
+                        float *m, void *stream);
+
+/* Synchronises `stream` and reports a bounded wait that ran out inside the kernel
+ * (TXD_ERR_DEVICE_TIMEOUT) or a CUDA error. */
+TXD_API int tx_attn_check(void *stream);
+
+/* The same through host buffers: copies q, k, v to the device, runs, copies out (and m) back, synchronises. */
+TXD_API int tx_attn_fwd_host(const tx_attn_problem *problem, const void *q, const void *k, const void *v, void *out,
+                             float *m);
+
+/* FLOPs of one forward call as the reference's benchmark counts them (:795-798): 4 * Z * H * N^2 * D, halved
+ * when causal. */
+TXD_API double tx_attn_flops(const tx_attn_problem *problem);
+
+TXD_API uint64_t tx_attn_kernel_launches(void);
+TXD_API const char *tx_attn_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_ATTENTION_H_ */

@@ -1,0 +1,94 @@
+"""CPU restatement of the reference's fused attention forward. TEST INFRASTRUCTURE, not product code: only
+tests/, __graft_entry__.smoke() and bench.py's CPU legs may import this file.
+
+  attention_blockwise  the algorithm of `_attn_fwd` / `_attn_fwd_inner`
+                       (pass/LoopSplit/06-fused-attention.py:164-240 and :43-90) block by block in numpy fp32:
+                       base-2 online softmax, the `start_n >= causal_start` compare LoopSplit splits on (:64),
+                       the -1.0e6 additive mask (:66), l_i starting at 1.0 (:222), P rounded to the input type
+                       before the second dot (:81-84), M = m_i + log2(l_i) (:236).
+  attention_eager      the formula the reference's own test compares its kernel with (`test_op`, :697-703):
+                       softmax(q k^T * sm_scale with -inf above the diagonal) rounded to the input type, times v.
+
+Pinned by tests/test_attention_oracle.py against outputs of the reference kernel itself (run by Triton's CPU
+interpreter, tests/golden/make_attn_golden.py -> tests/golden/attn_golden.npz).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+def _round_to(x: np.ndarray, dtype: torch.dtype) -> np.ndarray:
+    """fp32 array rounded to `dtype` (nearest even) and widened back to fp32."""
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dtype).float().numpy()
+
+
+def attention_blockwise(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, sm_scale: float,
+                        block_m: int = 128, block_n: int = 128, skip_above_diagonal: bool = False):
+    """Returns (out [Z,H,N,D] in q.dtype, M [Z,H,N] fp32). N must be a multiple of both block sizes, as in
+    the reference. With skip_above_diagonal the KV loop of a causal tile stops after the diagonal block
+    (the blocks it leaves out contribute p == 0 and alpha == 1 exactly)."""
+    z, h, n, d = q.shape
+    assert n % block_m == 0 and n % block_n == 0
+    dt = q.dtype
+    qf, kf, vf = (t.float().numpy() for t in (q, k, v))
+    out = np.empty((z, h, n, d), dtype=np.float32)
+    m_out = np.empty((z, h, n), dtype=np.float32)
+    qk_scale = np.float32(np.float32(sm_scale) * np.float32(1.44269504))
+    for iz in range(z):
+        for ih in range(h):
+            for start_m in range(n // block_m):
+                offs_m = start_m * block_m + np.arange(block_m)
+                qt = qf[iz, ih, offs_m]
+                m_i = np.full(block_m, -np.inf, dtype=np.float32)
+                l_i = np.ones(block_m, dtype=np.float32)
+                acc = np.zeros((block_m, d), dtype=np.float32)
+                causal_start = start_m * block_m if causal else n
+                hi = n
+                if causal and skip_above_diagonal:
+                    hi = min(n, (start_m + 1) * block_m)
+                for start_n in range(0, hi, block_n):
+                    kt = kf[iz, ih, start_n:start_n + block_n]
+                    qk = (qt @ kt.T).astype(np.float32)
+                    if start_n >= causal_start:  # the on-band loop after LoopSplit
+                        mask = offs_m[:, None] >= (start_n + np.arange(block_n))[None, :]
+                        qk = qk * qk_scale + np.where(mask, np.float32(0), np.float32(-1.0e6))
+                        m_ij = np.maximum(m_i, qk.max(axis=1))
+                        qk = qk - m_ij[:, None]
+                    else:                         # the off-band loop
+                        m_ij = np.maximum(m_i, qk.max(axis=1) * qk_scale)
+                        qk = qk * qk_scale - m_ij[:, None]
+                    p = np.exp2(qk.astype(np.float32)).astype(np.float32)
+                    l_ij = p.sum(axis=1, dtype=np.float32)
+                    alpha = np.exp2(m_i - m_ij).astype(np.float32)
+                    l_i = l_i * alpha + l_ij
+                    acc = acc * alpha[:, None]
+                    acc = acc + _round_to(p, dt) @ vf[iz, ih, start_n:start_n + block_n]
+                    m_i = m_ij
+                m_out[iz, ih, offs_m] = m_i + np.log2(l_i)
+                out[iz, ih, offs_m] = acc / l_i[:, None]
+    return torch.from_numpy(out).to(dt), torch.from_numpy(m_out)
+
+
+def attention_eager(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, sm_scale: float,
+                    round_p: bool = True) -> torch.Tensor:
+    """fp32 result of the reference test's formula; works for any N_CTX."""
+    n = q.shape[2]
+    p = torch.matmul(q.float(), k.float().transpose(2, 3)) * sm_scale
+    if causal:
+        tril = torch.tril(torch.ones((n, n), dtype=torch.bool))
+        p = p.masked_fill(~tril, float("-inf"))
+    p = torch.softmax(p, dim=-1)
+    if round_p:
+        p = p.to(q.dtype).float()
+    return torch.matmul(p, v.float())
+
+
+def logsumexp2(q: torch.Tensor, k: torch.Tensor, causal: bool, sm_scale: float) -> torch.Tensor:
+    """What M holds: log2 of the row sums of exp2(scores * sm_scale * log2 e), fp64 arithmetic."""
+    n = q.shape[2]
+    s = torch.matmul(q.double(), k.double().transpose(2, 3)) * (sm_scale * 1.4426950408889634)
+    if causal:
+        tril = torch.tril(torch.ones((n, n), dtype=torch.bool))
+        s = s.masked_fill(~tril, float("-inf"))
+    return (torch.logsumexp(s * 0.6931471805599453, dim=-1) * 1.4426950408889634).float()

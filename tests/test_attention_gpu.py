@@ -1,0 +1,165 @@
+"""Fused attention forward on the GPU, through the C-ABI (triton_ext_b200.attention -> tx_attn_fwd).
+
+Parity bar: the reference's own test compares its kernel with the eager formula at atol 1e-2, rtol 0
+(pass/LoopSplit/06-fused-attention.py:714) on fp16 inputs drawn from normal(0, 0.5) with sm_scale 0.5; the
+same inputs and bound are used here, first against outputs of the reference kernel itself
+(tests/golden/attn_golden.npz), then against the oracle over the shapes the reference tests and
+benchmarks, then through size-independent properties at the benchmark's size."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+f16, bf16 = torch.float16, torch.bfloat16
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attn_golden.npz")
+ATOL = {f16: 1e-2, bf16: 2e-2}   # bf16 keeps 8 bits of P and of the output instead of 11
+
+
+@pytest.fixture(scope="module")
+def A(built_libs, cuda_device):
+    from triton_ext_b200 import attention
+    return attention
+
+
+def draw(z, h, n, d, dtype, seed=20, std=0.5):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.empty((z, h, n, d), dtype=torch.float32).normal_(mean=0.0, std=std, generator=g).to(dtype)
+            for _ in range(3)]
+
+
+def golden_names():
+    npz = np.load(GOLDEN)
+    return sorted({key.split(".")[0] for key in npz.files if "." in key})
+
+
+# ---- 1. the reference kernel's own outputs -----------------------------------------------------------------
+@pytest.mark.parametrize("name", golden_names())
+def test_matches_reference_kernel_outputs(A, name):
+    npz = np.load(GOLDEN)
+    z, h, n, d, causal, _, _ = (int(x) for x in npz[f"{name}.meta"])
+    q, k, v, o = (torch.from_numpy(npz[f"{name}.{key}"].view(np.float16).copy()) for key in ("q", "k", "v", "o"))
+    m_ref = torch.from_numpy(npz[f"{name}.m"].copy())
+    out, m = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), bool(causal), float(npz["sm_scale"]), return_m=True,
+                                 check=True)
+    err = float((out.cpu().float() - o.float()).abs().max())
+    assert err <= 1e-2, err            # the reference's bound; measured error is a few 1e-4
+    assert err <= 2e-3, err            # what two fp16 roundings of outputs of size <= 2 allow
+    assert float((m.cpu() - m_ref).abs().max()) <= 1e-3
+
+
+# ---- 2. against the oracle over shapes, types, masks ---------------------------------------------------------
+SHAPES = [
+    # z, h, n_ctx, head_dim
+    (1, 2, 1024, 64),     # the reference's test_op shape
+    (1, 2, 128, 64),      # one block, second sub-tile idle
+    (2, 3, 384, 128),     # odd number of blocks
+    (1, 1, 1024, 128),
+    (1, 2, 200, 64),      # ragged: not a multiple of the block (outside the reference's domain)
+    (1, 1, 1, 64),        # a single row
+    (2, 2, 333, 128),
+]
+
+
+@pytest.mark.parametrize("dtype", [f16, bf16])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("z,h,n,d", SHAPES)
+def test_against_oracle(A, z, h, n, d, causal, dtype):
+    from oracle import attn_oracle as AO
+    q, k, v = draw(z, h, n, d, dtype)
+    out, m = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal, 0.5, return_m=True, check=True)
+    want = AO.attention_eager(q, k, v, causal, 0.5)
+    err = float((out.cpu().float() - want).abs().max())
+    assert err <= ATOL[dtype], err
+    lse = AO.logsumexp2(q, k, causal, 0.5)
+    assert float((m.cpu() - lse).abs().max()) <= 2e-3
+    if n % 128 == 0 and n <= 384:
+        # the blockwise restatement (pinned to the reference kernel) with this kernel's blocking
+        bw, bm = AO.attention_blockwise(q, k, v, causal, 0.5, 128, 128, skip_above_diagonal=True)
+        assert float((out.cpu().float() - bw.float()).abs().max()) <= ATOL[dtype] / 4
+        assert float((m.cpu() - bm).abs().max()) <= 1e-3
+
+
+def test_benchmark_scale_and_large_scores(A):
+    """sm_scale 1.3 and unit-variance inputs as in the reference's benchmark (:778-787): scores of size ~50."""
+    from oracle import attn_oracle as AO
+    q, k, v = draw(1, 2, 512, 64, f16, seed=5, std=1.0)
+    out = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), True, 1.3, check=True)
+    want = AO.attention_eager(q, k, v, True, 1.3)
+    assert float((out.cpu().float() - want).abs().max()) <= 1e-2
+
+
+# ---- 3. size-independent properties at the benchmark's size --------------------------------------------------
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("causal", [True, False])
+def test_full_size_properties(A, d, causal):
+    z, h, n = 4, 32, 4096     # the reference benchmark's batch and heads (:738), N_CTX = 2^12
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(11)
+    q, k, v = (torch.randn((z, h, n, d), generator=g).to(f16).to(dev) for _ in range(3))
+    out, m = A.attention_forward(q, k, v, causal, 1.3, return_m=True, check=True)
+    # (a) linear in V, and scaling by a power of two is exact: bit-identical results
+    out2 = A.attention_forward(q, k, v * 2, causal, 1.3, check=True)
+    normal = out.abs() >= 2.0 ** -13          # fp16 subnormals have fewer bits: x and 2x round differently there
+    assert torch.equal(out2[normal], (out * 2)[normal])
+    assert float((out2.float() - 2 * out.float())[~normal].abs().max()) <= 2.0 ** -23
+    # (b) rows of softmax sum to one: V == 1 gives 1 up to the rounding of P
+    ones = A.attention_forward(q, k, torch.ones_like(v), causal, 1.3, check=True)
+    assert float((ones.float() - 1).abs().max()) <= 2e-3
+    # (c) causality: keys and values after position r do not reach rows <= r (bit-identical)
+    if causal:
+        k2, v2 = k.clone(), v.clone()
+        k2[:, :, 3000:] = 7.0
+        v2[:, :, 3000:] = -3.0
+        out3 = A.attention_forward(q, k2, v2, True, 1.3, check=True)
+        assert torch.equal(out3[:, :, :3000], out[:, :, :3000])
+    # (d) sampled heads against eager attention in fp32 on the GPU
+    for iz, ih in ((0, 0), (3, 31), (1, 17)):
+        s = (q[iz, ih].float() @ k[iz, ih].float().T) * 1.3
+        if causal:
+            s = s.masked_fill(~torch.tril(torch.ones(n, n, dtype=torch.bool, device=dev)), float("-inf"))
+        want = torch.softmax(s, dim=-1).to(f16).float() @ v[iz, ih].float()
+        assert float((out[iz, ih].float() - want).abs().max()) <= 1e-2
+        lse = torch.logsumexp(s, dim=-1) * 1.4426950408889634
+        assert float((m[iz, ih] - lse).abs().max()) <= 2e-3
+
+
+# ---- 4. host buffers, argument errors, bounded waits ------------------------------------------------------------
+def test_host_buffers(A):
+    from oracle import attn_oracle as AO
+    q, k, v = draw(1, 2, 256, 64, f16)
+    m = torch.empty((1, 2, 256), dtype=torch.float32)
+    out = A.attention_forward_host(q, k, v, True, 0.5, m=m)
+    assert float((out.float() - AO.attention_eager(q, k, v, True, 0.5)).abs().max()) <= 1e-2
+    assert float((m - AO.logsumexp2(q, k, True, 0.5)).abs().max()) <= 2e-3
+
+
+def test_rejected_arguments(A):
+    from triton_ext_b200 import backend as B
+    q = torch.zeros((1, 1, 128, 32), dtype=f16, device="cuda")
+    with pytest.raises(B.DotError) as e:
+        A.attention_forward(q, q, q, True, 0.5)
+    assert e.value.status == B.TXD_ERR_UNSUPPORTED and "head_dim" in str(e.value)
+    q = torch.zeros((1, 1, 128, 64), dtype=f16, device="cuda")
+    with pytest.raises(B.DotError) as e:
+        A.attention_forward(q, q, q, True, -1.0)
+    assert e.value.status == B.TXD_ERR_INVALID
+    with pytest.raises(B.DotError):
+        A.attention_forward(q.float(), q.float(), q.float(), True, 0.5)
+
+
+def test_bounded_wait_reports_timeout(A, monkeypatch):
+    from triton_ext_b200 import backend as B
+    from oracle import attn_oracle as AO
+    q, k, v = draw(1, 1, 256, 64, f16)
+    monkeypatch.setenv("TXD_INJECT_STALL", "1")     # the producer loads Q and never a K or V tile
+    monkeypatch.setenv("TXD_WAIT_LIMIT_MS", "50")
+    with pytest.raises(B.DotError) as e:
+        A.attention_forward(q.cuda(), k.cuda(), v.cuda(), True, 0.5, check=True)
+    assert e.value.status == B.TXD_ERR_DEVICE_TIMEOUT
+    monkeypatch.delenv("TXD_INJECT_STALL")
+    monkeypatch.delenv("TXD_WAIT_LIMIT_MS")
+    out = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), True, 0.5, check=True)   # same context, healthy launch
+    assert float((out.cpu().float() - AO.attention_eager(q, k, v, True, 0.5)).abs().max()) <= 1e-2

@@ -1,0 +1,52 @@
+"""The attention oracle against the reference kernel's own outputs (CPU only).
+
+tests/golden/attn_golden.npz holds what the reference's `_attn_fwd` produced under Triton's CPU interpreter
+(tests/golden/make_attn_golden.py). The blockwise restatement, run with the block sizes each fixture was made
+with, must reproduce those outputs to fp16 rounding; with the 128 x 128 blocks of the CUDA kernel and with the
+above-diagonal blocks skipped it must stay within the tolerance of the reference's own test (atol 1e-2,
+06-fused-attention.py:714)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attn_oracle as AO
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attn_golden.npz")
+
+
+def load_case(npz, name):
+    z, h, n, d, causal, bm, bn = (int(x) for x in npz[f"{name}.meta"])
+    t = {key: torch.from_numpy(npz[f"{name}.{key}"].view(np.float16).copy()) for key in ("q", "k", "v", "o")}
+    return dict(z=z, h=h, n=n, d=d, causal=bool(causal), bm=bm, bn=bn, m=torch.from_numpy(npz[f"{name}.m"].copy()), **t)
+
+
+def case_names():
+    npz = np.load(GOLDEN)
+    return sorted({key.split(".")[0] for key in npz.files if "." in key})
+
+
+@pytest.mark.parametrize("name", case_names())
+def test_blockwise_restatement_reproduces_the_reference_kernel(name):
+    npz = np.load(GOLDEN)
+    c = load_case(npz, name)
+    sm_scale = float(npz["sm_scale"])
+    out, m = AO.attention_blockwise(c["q"], c["k"], c["v"], c["causal"], sm_scale, c["bm"], c["bn"])
+    # same algorithm, same block sizes: differences are the summation order inside a dot / a row sum
+    assert float((out.float() - c["o"].float()).abs().max()) <= 1e-3
+    assert float((m - c["m"]).abs().max()) <= 1e-4
+
+
+@pytest.mark.parametrize("name", case_names())
+def test_kernel_blocking_and_skipped_blocks_stay_within_the_reference_tolerance(name):
+    npz = np.load(GOLDEN)
+    c = load_case(npz, name)
+    sm_scale = float(npz["sm_scale"])
+    out, m = AO.attention_blockwise(c["q"], c["k"], c["v"], c["causal"], sm_scale, 128, 128, skip_above_diagonal=True)
+    assert float((out.float() - c["o"].float()).abs().max()) <= 2e-3
+    assert float((m - c["m"]).abs().max()) <= 1e-4
+    eager = AO.attention_eager(c["q"], c["k"], c["v"], c["causal"], sm_scale)
+    assert float((eager - c["o"].float()).abs().max()) <= 1e-2      # the reference's own test bound
+    lse = AO.logsumexp2(c["q"], c["k"], c["causal"], sm_scale)
+    assert float((lse - c["m"]).abs().max()) <= 1e-3

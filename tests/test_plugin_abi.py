@@ -37,6 +37,10 @@ def test_every_declared_symbol_is_exported(built_libs):
         assert name in infra_syms or name in dot_syms, name
     for name in _declared("b200_dot.h", r"\b(tx_dot_\w+)\s*\("):
         assert name in dot_syms, name
+    attn = _declared("b200_attention.h", r"\b(tx_attn_\w+)\s*\(")
+    assert len(attn) >= 6
+    for name in attn:
+        assert name in dot_syms, name
 
 
 def test_extensions_register_at_dlopen_in_load_order(built_libs):

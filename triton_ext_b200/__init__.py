@@ -6,4 +6,4 @@ Sub-modules:
   conf     - `triton-ext.conf` metadata and TRITON_EXT_NAMES gating
   parallel - N-sharded / K-sharded multi-GPU drivers
 """
-__all__ = ["backend", "plugin", "conf", "parallel"]
+__all__ = ["backend", "attention", "plugin", "conf", "parallel"]

@@ -7,7 +7,8 @@ infra/pass/CMakeLists.txt:3-14):
     lib/libTritonExtPassInfra.so   registry + loop IR + pass manager
     lib/libloop_split.so           pass extension   (pass/LoopSplit)
     lib/libdot_tile_select.so      pass extension   (pass/DotTileSelect)
-    lib/libb200_dot.so             backend extension: sm_100a kernels + launch C-ABI + lowering pass
+    lib/libb200_dot.so             backend extension: sm_100a kernels (tt.dot GEMM, fused attention forward)
+                                   + launch C-ABI + lowering pass
 
 Each extension is named by its `triton-ext.conf` and is skipped when TRITON_EXT_NAMES is set and
 does not list it.
@@ -31,7 +32,8 @@ INCLUDE = os.path.join(ROOT, "include")
 EXTENSIONS = [
     ("pass/LoopSplit", "LoopBisectPass", ["LoopSplitPass.cpp"], False),
     ("pass/DotTileSelect", "DotTileSelectPass", ["DotTileSelectPass.cpp"], False),
-    ("backend/B200Dot", "B200DotLoweringPass", ["b200_dot.cu", "b200_dot_static.cu", "B200DotLowering.cpp"], True),
+    ("backend/B200Dot", "B200DotLoweringPass", ["b200_dot.cu", "b200_dot_static.cu", "B200DotLowering.cpp",
+                                                   "../B200Attention/b200_attention.cu"], True),
 ]
 
 CXXFLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
@@ -81,10 +83,12 @@ def build_all(force: bool = False, verbose: bool = False, ptxas_verbose: bool = 
             continue
         meta = conf.read_conf(d)
         out = os.path.join(LIB, f"lib{meta.name}.so")
-        deps = common_deps + _all_sources(d) + _all_sources(os.path.join(CSRC, "backend", "B200Dot"))
+        deps = (common_deps + _all_sources(d) + _all_sources(os.path.join(CSRC, "backend", "B200Dot")) +
+                _all_sources(os.path.join(CSRC, "backend", "B200Attention")))
         if force or _stale(out, deps):
             defs = [f"-DTRITON_EXT_NAME={meta.name}", f"-DTRITON_EXT_CLASS={cls}"]
-            incs = ["-I", INCLUDE, "-I", os.path.join(CSRC, "infra"), "-I", os.path.join(CSRC, "backend", "B200Dot")]
+            incs = ["-I", INCLUDE, "-I", os.path.join(CSRC, "infra"), "-I", os.path.join(CSRC, "backend", "B200Dot"),
+                    "-I", os.path.join(CSRC, "backend", "B200Attention")]
             link = ["-L", LIB, "-lTritonExtPassInfra"]
             srcs = [os.path.join(d, s) for s in sources]
             if cuda:

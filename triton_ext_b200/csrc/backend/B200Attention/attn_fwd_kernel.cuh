@@ -1,0 +1,463 @@
+// Fused attention forward for sm_100a: the two chained tt.dot of the reference's demo kernel
+// (pass/LoopSplit/06-fused-attention.py:43-90 inner loop, :164-240 outer kernel) with its online softmax,
+// written directly on tcgen05 / TMEM / TMA.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row sub-tiles, each with its own softmax
+// warpgroup, its own S accumulator and its own O accumulator in TMEM. K and V tiles of 128 rows are
+// streamed once per CTA through a shared-memory ring and used by both sub-tiles.
+//
+//   warps 0-3 / 4-7 : softmax warpgroup of sub-tile 0 / 1 (one query row per thread): tcgen05.ld of S,
+//                     running max and sum in base 2, P = exp2(S*scale - m) rounded to the input type and
+//                     written to shared memory as the A operand of the second dot, rescaling of O in TMEM
+//                     (tcgen05.ld / tcgen05.st) when the running max moved, final O / l and TMA store
+//   warp 8          : TMA producer (Q once; K0, K1, V0, K2, V1, ... through the ring)
+//   warp 9          : tcgen05.mma issuer: S_t = Q_t K_j^T, then O_t += P_t V_j one KV block later, so that
+//                     the tensor pipe works on one sub-tile while the other one is in its softmax
+//
+// The KV loop is executed the way LoopSplit leaves it (reference LoopSplit.cpp:179-193 applied to the
+// compare at 06-fused-attention.py:64): an off-band loop over the blocks that need no mask and an
+// on-band loop over the block on the diagonal (and the ragged last block when N_CTX is not a multiple of
+// 128). Blocks above the diagonal, which the reference visits with every element masked (each contributes
+// p == 0 and alpha == 1 exactly), are not visited.
+//
+// Every wait on an mbarrier is bounded in time; a wait that runs out raises the abort flag, all roles
+// leave their loops, copies in flight are drained, TMEM is released and the CTA returns.
+#pragma once
+
+#include "sm100_ptx.cuh"
+
+namespace txa {
+
+using namespace txd;
+
+constexpr int kTileRows = 128;        // query rows per sub-tile == KV rows per block
+constexpr int kAttnThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kMaxKvStages = 6;
+constexpr int kAtomBytes = 128 * 128;  // 128 rows x one 128-byte swizzle span
+constexpr int kPBytes = 2 * kAtomBytes;
+constexpr uint32_t kTmemCols = 512;    // S0 | S1 | O0 | O1, 128 columns each
+
+enum AttnDeviceStatus : uint32_t {
+  kAttnOk = 0,
+  kAttnTimeoutProducer = 1,
+  kAttnTimeoutMmaOperand = 2,
+  kAttnTimeoutMmaP = 3,
+  kAttnTimeoutSoftmaxS = 4,
+  kAttnTimeoutSoftmaxO = 5,
+  kAttnTimeoutDrain = 6
+};
+
+struct AttnParams {
+  CUtensorMap tmap_q, tmap_k, tmap_v;  // 3-D {head_dim, n_ctx, batch*heads}, box {64, 128, 1}, SWIZZLE_128B
+  CUtensorMap tmap_o;                  // same tensor shape, box {64, 32, 1}
+  float *m_out;                        // [batch*heads, n_ctx]: m + log2(l), as the reference stores it
+  uint32_t *status;
+  unsigned long long wait_limit_ns;
+  float qk_scale;                      // sm_scale * log2(e)
+  int32_t n_ctx, head_dim, heads_total, q_tiles;
+  int32_t causal, is_bf16, kv_stages;
+  uint32_t idesc_qk, idesc_pv;
+  int32_t inject_stall;                // host-side fault injection: the producer stops after Q
+};
+
+struct AttnCtl {
+  uint64_t q_full;
+  uint64_t kv_full[kMaxKvStages], kv_empty[kMaxKvStages];
+  uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+__device__ __forceinline__ uint32_t pack_pair(float a, float b, int is_bf16) {
+  if (is_bf16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// Byte offset of the 16-byte chunk `chunk16` (0..7) of row `r` inside one K-major SWIZZLE_128B atom
+// (128 rows x 128 bytes; groups of 8 rows form 1024-byte swizzle blocks).
+__device__ __forceinline__ uint32_t swz_off(int r, int chunk16) {
+  return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((chunk16 ^ (r & 7)) << 4));
+}
+
+// One softmax step of one query row over a 128-column block of S held in registers.
+// kMasked = false: the off-band loop (no element masked); true: the on-band loop.
+template <bool kMasked>
+__device__ __forceinline__ float row_block_max(const uint32_t (&s)[128], int col0, int row, int n_ctx, int causal) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 128; i += 4) {
+    float a = __uint_as_float(s[i]), b = __uint_as_float(s[i + 1]), c = __uint_as_float(s[i + 2]),
+          d = __uint_as_float(s[i + 3]);
+    if (kMasked) {
+      const int lim = causal ? min(row, n_ctx - 1) : n_ctx - 1;  // last allowed column
+      a = col0 + i <= lim ? a : -INFINITY;
+      b = col0 + i + 1 <= lim ? b : -INFINITY;
+      c = col0 + i + 2 <= lim ? c : -INFINITY;
+      d = col0 + i + 3 <= lim ? d : -INFINITY;
+    }
+    m0 = fmaxf(m0, a);
+    m1 = fmaxf(m1, b);
+    m2 = fmaxf(m2, c);
+    m3 = fmaxf(m3, d);
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+template <bool kMasked>
+__device__ __forceinline__ float row_block_exp_store(const uint32_t (&s)[128], float qk_scale, float neg_m, int col0,
+                                                     int row, int n_ctx, int causal, int is_bf16, uint32_t p_tile,
+                                                     int row_in_tile) {
+  float sum0 = 0.f, sum1 = 0.f;
+  const int lim = causal ? min(row, n_ctx - 1) : n_ctx - 1;
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {  // 8 columns = one 16-byte chunk of P
+    float e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float x = fast_exp2(fmaf(__uint_as_float(s[g * 8 + i]), qk_scale, neg_m));
+      if (kMasked) x = col0 + g * 8 + i <= lim ? x : 0.f;
+      e[i] = x;
+    }
+    sum0 += (e[0] + e[1]) + (e[2] + e[3]);
+    sum1 += (e[4] + e[5]) + (e[6] + e[7]);
+    st_shared_v4(p_tile + (g >> 3) * kAtomBytes + swz_off(row_in_tile, g & 7), pack_pair(e[0], e[1], is_bf16),
+                 pack_pair(e[2], e[3], is_bf16), pack_pair(e[4], e[5], is_bf16), pack_pair(e[6], e[7], is_bf16));
+  }
+  return sum0 + sum1;
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t attn_smem_raw[];
+  const uint32_t raw = smem_u32(attn_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const int D = p.head_dim;
+  const uint32_t tile_bytes = static_cast<uint32_t>(kTileRows * D * 2);  // one Q / K / V tile
+  const int d_atoms = D / 64;
+  const uint32_t q_addr0 = base;
+  const uint32_t p_addr0 = base + 2 * tile_bytes;
+  const uint32_t kv_addr0 = p_addr0 + 2 * kPBytes;
+  AttnCtl *ctl = reinterpret_cast<AttnCtl *>(attn_smem_raw + (kv_addr0 - raw) + p.kv_stages * tile_bytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- work: one (head, 256-row query tile); heavy (late) causal tiles are scheduled first ----
+  const int head = static_cast<int>(blockIdx.x) % p.heads_total;
+  const int qt = p.q_tiles - 1 - static_cast<int>(blockIdx.x) / p.heads_total;
+  const int q0 = qt * 2 * kTileRows;
+  const int kv_blocks_all = (p.n_ctx + kTileRows - 1) / kTileRows;
+  const bool ragged = (p.n_ctx % kTileRows) != 0;
+  int n_blk[2], n_full[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qs = q0 + t * kTileRows;
+    int n = 0;
+    if (qs < p.n_ctx) n = p.causal ? min(kv_blocks_all, qs / kTileRows + 1) : kv_blocks_all;
+    n_blk[t] = n;
+    // LoopSplit: [0, n_full) runs unmasked, [n_full, n) masked. The masked block is the one on the diagonal
+    // (causal) or the ragged last one; both can only be the last block of the loop.
+    const bool last_masked = n > 0 && (p.causal || (ragged && n == kv_blocks_all));
+    n_full[t] = last_masked ? n - 1 : n;
+  }
+  const int nmax = max(n_blk[0], n_blk[1]);
+
+  AbortCtl ac;
+  ac.flag = &ctl->abort_flag;
+  ac.status = p.status;
+  ac.limit_ns = p.wait_limit_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctl->q_full), 1);
+    for (int s = 0; s < p.kv_stages; ++s) {
+      mbar_init(smem_u32(&ctl->kv_full[s]), 1);
+      mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&ctl->s_full[t]), 1);
+      mbar_init(smem_u32(&ctl->p_full[t]), kTileRows);  // every softmax thread arrives
+      mbar_init(smem_u32(&ctl->o_done[t]), 1);
+    }
+    mbar_init(smem_u32(&ctl->drain), 1);
+    ctl->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&p.tmap_q);
+    tma_prefetch_desc(&p.tmap_k);
+    tma_prefetch_desc(&p.tmap_v);
+    tma_prefetch_desc(&p.tmap_o);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------ TMA producer ------------------------------
+    const bool issuer = elect_one();
+    uint32_t issued = 0;  // ring items issued
+    bool ok = true;
+    if (nmax > 0) {
+      if (issuer) {
+        const int active = (n_blk[0] > 0 ? 1 : 0) + (n_blk[1] > 0 ? 1 : 0);
+        mbar_arrive_expect_tx(smem_u32(&ctl->q_full), active * tile_bytes);
+        for (int t = 0; t < 2; ++t)
+          if (n_blk[t] > 0)
+            for (int a = 0; a < d_atoms; ++a)
+              tma_load_3d(q_addr0 + t * tile_bytes + a * kAtomBytes, &p.tmap_q, a * 64, q0 + t * kTileRows, head,
+                          smem_u32(&ctl->q_full));
+      }
+      __syncwarp();
+      auto load_tile = [&](const CUtensorMap *map, int kv_block) {
+        const uint32_t slot = issued % static_cast<uint32_t>(p.kv_stages);
+        const uint32_t phase = (issued / static_cast<uint32_t>(p.kv_stages)) & 1u;
+        if (!warp_mbar_wait(smem_u32(&ctl->kv_empty[slot]), phase ^ 1u, ac, kAttnTimeoutProducer, lane)) {
+          ok = false;
+          return;
+        }
+        if (issuer) {
+          const uint32_t bar = smem_u32(&ctl->kv_full[slot]);
+          mbar_arrive_expect_tx(bar, tile_bytes);
+          for (int a = 0; a < d_atoms; ++a)
+            tma_load_3d(kv_addr0 + slot * tile_bytes + a * kAtomBytes, map, a * 64, kv_block * kTileRows, head, bar);
+        }
+        __syncwarp();
+        ++issued;
+      };
+      if (!p.inject_stall) {
+        load_tile(&p.tmap_k, 0);
+        for (int j = 0; ok && j < nmax; ++j) {
+          if (j + 1 < nmax) load_tile(&p.tmap_k, j + 1);
+          if (ok) load_tile(&p.tmap_v, j);
+        }
+      }
+      // Copies still in flight must land before the CTA's shared memory goes away. On the normal path the
+      // MMA warp has waited for every one of them; after an abort, wait for the ones of the last ring pass.
+      if (ctl->abort_flag) {
+        if (lane == 0) {
+          mbar_wait_timed(smem_u32(&ctl->q_full), 0u, ac, kAttnTimeoutDrain);
+          const uint32_t first = issued > static_cast<uint32_t>(p.kv_stages) ? issued - p.kv_stages : 0u;
+          for (uint32_t i = first; i < issued; ++i) {
+            const unsigned long long t0 = global_timer_ns();
+            const uint32_t bar = smem_u32(&ctl->kv_full[i % p.kv_stages]);
+            const uint32_t ph = (i / p.kv_stages) & 1u;
+            while (!mbar_try_wait(bar, ph))
+              if (global_timer_ns() - t0 > ac.limit_ns) break;
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------ tcgen05.mma issuer ------------------------------
+    const bool issuer = elect_one();
+    if (nmax > 0) {
+      auto desc64 = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+      const uint32_t desc_hi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);  // SBO 1024, sm_100, SWIZZLE_128B
+      const uint32_t kmajor_lbo = 1u << 16;                                        // unused for swizzled K-major
+      const uint32_t v_lbo = ((static_cast<uint32_t>(kAtomBytes) >> 4) & 0x3FFFu) << 16;  // between 64-column chunks
+      auto lo_of = [](uint32_t addr) { return (addr & 0x3FFFFu) >> 4; };
+      uint32_t taken = 0;
+      bool ok = true;
+      auto take = [&]() -> uint32_t {  // next ring item, in the producer's order
+        const uint32_t slot = taken % static_cast<uint32_t>(p.kv_stages);
+        const uint32_t phase = (taken / static_cast<uint32_t>(p.kv_stages)) & 1u;
+        if (!warp_mbar_wait(smem_u32(&ctl->kv_full[slot]), phase, ac, kAttnTimeoutMmaOperand, lane)) ok = false;
+        ++taken;
+        return slot;
+      };
+      auto issue_qk = [&](int t, uint32_t k_slot) {  // S_t = Q_t K^T : head_dim / 16 MMAs of 128 x 128 x 16
+        if (issuer) {
+          const uint32_t qa = lo_of(q_addr0 + t * tile_bytes) | kmajor_lbo;
+          const uint32_t ka = lo_of(kv_addr0 + k_slot * tile_bytes) | kmajor_lbo;
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(t) * 128u;
+          for (int i = 0; i < D / 16; ++i) {
+            const uint32_t step = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
+            umma_f16(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), p.idesc_qk, i > 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&ctl->s_full[t]));
+        }
+        __syncwarp();
+      };
+      auto issue_pv = [&](int t, uint32_t v_slot, bool accumulate) {  // O_t += P_t V : 8 MMAs of 128 x head_dim x 16
+        if (issuer) {
+          const uint32_t pa = lo_of(p_addr0 + t * kPBytes) | kmajor_lbo;
+          const uint32_t va = lo_of(kv_addr0 + v_slot * tile_bytes) | v_lbo;
+          const uint32_t d_tmem = tmem_base + 256u + static_cast<uint32_t>(t) * 128u;
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t pstep = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
+            const uint32_t vstep = static_cast<uint32_t>(i) * (16u * 128u >> 4);  // 16 KV rows of 128 bytes
+            umma_f16(d_tmem, desc64(desc_hi, pa + pstep), desc64(desc_hi, va + vstep), p.idesc_pv,
+                     (accumulate || i > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&ctl->o_done[t]));
+        }
+        __syncwarp();
+      };
+      auto release = [&](uint32_t slot) {
+        if (issuer) tc_commit(smem_u32(&ctl->kv_empty[slot]));
+        __syncwarp();
+      };
+
+      ok = warp_mbar_wait(smem_u32(&ctl->q_full), 0u, ac, kAttnTimeoutMmaOperand, lane);
+      uint32_t k_slot = 0;
+      if (ok) k_slot = take();
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < 2; ++t)
+          if (n_blk[t] > 0) issue_qk(t, k_slot);
+        release(k_slot);
+      }
+      for (int j = 0; ok && j < nmax; ++j) {
+        const bool has_next = j + 1 < nmax;
+        uint32_t kn_slot = 0;
+        if (has_next) kn_slot = take();
+        uint32_t v_slot = 0;
+        if (ok) v_slot = take();
+        if (!ok) break;
+        for (int t = 0; t < 2; ++t) {
+          if (j >= n_blk[t]) continue;
+          // P_t(j) is in shared memory, O_t is rescaled, and S_t has been read: both MMAs may go
+          if (!warp_mbar_wait(smem_u32(&ctl->p_full[t]), static_cast<uint32_t>(j) & 1u, ac, kAttnTimeoutMmaP, lane)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (j + 1 < n_blk[t]) issue_qk(t, kn_slot);
+          issue_pv(t, v_slot, j > 0);
+        }
+        if (!ok) break;
+        if (has_next) release(kn_slot);
+        release(v_slot);
+      }
+      // every MMA issued above has completed before TMEM and shared memory are given back
+      if (issuer) tc_commit(smem_u32(&ctl->drain));
+      __syncwarp();
+      if (lane == 0) {
+        const unsigned long long t0 = global_timer_ns();
+        while (!mbar_try_wait(smem_u32(&ctl->drain), 0u)) {
+          if (global_timer_ns() - t0 > ac.limit_ns) {
+            ctl->abort_flag = 1;
+            atomicCAS(ac.status, 0u, static_cast<uint32_t>(kAttnTimeoutDrain));
+            break;
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------ softmax warpgroups ------------------------------
+    const int t = warp >> 2;
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int row = q0 + t * kTileRows + row_in_tile;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_tmem = lane_base + static_cast<uint32_t>(t) * 128u;
+    const uint32_t o_tmem = lane_base + 256u + static_cast<uint32_t>(t) * 128u;
+    const uint32_t p_tile = p_addr0 + t * kPBytes;
+    const int n = n_blk[t];
+    float m_i = -INFINITY, l_i = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      if (!warp_mbar_wait(smem_u32(&ctl->s_full[t]), static_cast<uint32_t>(j) & 1u, ac, kAttnTimeoutSoftmaxS, lane)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t s[128];
+      tmem_ld_32x32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld_32x32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_ld_32x32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+      tmem_ld_32x32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+      tmem_ld_wait();
+      const bool masked = j >= n_full[t];
+      const int col0 = j * kTileRows;
+      const float mx = masked ? row_block_max<true>(s, col0, row, p.n_ctx, p.causal)
+                              : row_block_max<false>(s, col0, row, p.n_ctx, p.causal);
+      float m_new = fmaxf(m_i, mx * p.qk_scale);
+      if (m_new == -INFINITY) m_new = 0.f;  // a row with nothing to attend to yet
+      const float alpha = fast_exp2(m_i - m_new);
+      if (j > 0) {
+        // O_t += P_t(j-1) V has completed: P_t may be overwritten and O_t rescaled
+        if (!warp_mbar_wait(smem_u32(&ctl->o_done[t]), static_cast<uint32_t>(j - 1) & 1u, ac, kAttnTimeoutSoftmaxO,
+                            lane)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_tmem + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(o_tmem + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float sum = masked ? row_block_exp_store<true>(s, p.qk_scale, -m_new, col0, row, p.n_ctx, p.causal,
+                                                           p.is_bf16, p_tile, row_in_tile)
+                               : row_block_exp_store<false>(s, p.qk_scale, -m_new, col0, row, p.n_ctx, p.causal,
+                                                            p.is_bf16, p_tile, row_in_tile);
+      l_i = l_i * alpha + sum;
+      m_i = m_new;
+      fence_proxy_async();  // P is read by the tensor core through the async proxy
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->p_full[t]));
+    }
+    if (ok && n > 0) {
+      // ---- epilogue of the sub-tile: O / l, cast, store; M = m + log2(l) ----
+      ok = warp_mbar_wait(smem_u32(&ctl->o_done[t]), static_cast<uint32_t>(n - 1) & 1u, ac, kAttnTimeoutSoftmaxO, lane);
+      if (ok) {
+        tc_fence_after();
+        const float inv_l = 1.0f / l_i;
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(o_tmem + c * 32, o);
+          tmem_ld_wait();
+          // 32 columns = 64 bytes = chunks (c&1)*4 .. +3 of this row in atom c/2 (P_t's buffer is free now)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              w[i] = pack_pair(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l,
+                               p.is_bf16);
+            st_shared_v4(p_tile + (c >> 1) * kAtomBytes + swz_off(row_in_tile, (c & 1) * 4 + q), w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && q0 + t * kTileRows + quarter * 32 < p.n_ctx) {  // rows past n_ctx are clipped by the copy
+          for (int a = 0; a < d_atoms; ++a)
+            tma_store_3d(&p.tmap_o, p_tile + a * kAtomBytes + quarter * 32 * 128, a * 64, q0 + t * kTileRows + quarter * 32,
+                         head);
+          bulk_commit_group();
+          bulk_wait_group_all();
+        }
+        __syncwarp();
+        if (row < p.n_ctx) p.m_out[static_cast<long long>(head) * p.n_ctx + row] = m_i + log2f(l_i);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace txa

@@ -1,0 +1,258 @@
+// Host side of the fused attention forward: argument checks, TMA descriptors, launch, status.
+// There is no CPU path here: without an sm_100 device every compute entry point fails.
+#include "b200_attention.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+#include <string>
+
+#include "attn_fwd_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_attn_error;
+std::atomic<uint64_t> g_attn_launches{0};
+
+int afail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_attn_error = buf;
+  return code;
+}
+
+#define TXA_CUDA(expr)                                                                      \
+  do {                                                                                      \
+    cudaError_t e_ = (expr);                                                                \
+    if (e_ != cudaSuccess)                                                                  \
+      return afail(TXD_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_));           \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn attn_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [batch*heads, n_ctx, head_dim] viewed as a 3-D tensor; a box is 64 columns (128 bytes) x box_rows rows.
+int encode_head_map(CUtensorMap *map, const void *ptr, bool bf16, long long heads_total, long long n_ctx, int head_dim,
+                    int box_rows) {
+  EncodeTiledFn enc = attn_encode_fn();
+  if (!enc) return afail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(n_ctx),
+                        static_cast<cuuint64_t>(heads_total)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(n_ctx) * head_dim * 2};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                   const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return afail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+  return TXD_OK;
+}
+
+uint32_t attn_idesc(bool bf16, bool b_mn_major, int n) {
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  uint32_t d = 0;
+  d |= 1u << 4;    // fp32 accumulator
+  d |= fmt << 7;   // A type
+  d |= fmt << 10;  // B type
+  d |= (b_mn_major ? 1u : 0u) << 16;
+  d |= static_cast<uint32_t>(n >> 3) << 17;
+  d |= static_cast<uint32_t>(128 >> 4) << 24;
+  return d;
+}
+
+struct DeviceState {
+  uint32_t *status = nullptr;
+  bool attr_set = false;
+  // host-buffer path
+  cudaStream_t stream = nullptr;
+  void *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr;
+  float *m = nullptr;
+  size_t tensor_bytes = 0, m_bytes = 0;
+};
+std::mutex g_state_mutex;
+DeviceState g_state[64];
+
+int device_state(DeviceState **out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return afail(TXD_ERR_NO_DEVICE, "no CUDA device");
+  }
+  std::lock_guard<std::mutex> lock(g_state_mutex);
+  DeviceState &st = g_state[dev];
+  if (!st.status) {
+    cudaDeviceProp prop;
+    TXA_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      return afail(TXD_ERR_NO_DEVICE, "device %d is sm_%d%d; these kernels are built for sm_100a only", dev, prop.major,
+                   prop.minor);
+    TXA_CUDA(cudaMalloc(&st.status, sizeof(uint32_t)));
+    TXA_CUDA(cudaMemset(st.status, 0, sizeof(uint32_t)));
+  }
+  if (!st.attr_set) {
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    st.attr_set = true;
+  }
+  *out = &st;
+  return TXD_OK;
+}
+
+int validate(const tx_attn_problem *pr) {
+  if (!pr) return afail(TXD_ERR_INVALID, "null problem");
+  if (pr->batch < 1 || pr->heads < 1 || pr->n_ctx < 1) return afail(TXD_ERR_INVALID, "batch, heads and n_ctx must be >= 1");
+  if (pr->head_dim != 64 && pr->head_dim != 128)
+    return afail(TXD_ERR_UNSUPPORTED, "head_dim %d: 64 and 128 are built", pr->head_dim);
+  if (pr->dtype != TXD_F16 && pr->dtype != TXD_BF16) return afail(TXD_ERR_UNSUPPORTED, "dtype must be f16 or bf16");
+  if (!(pr->sm_scale > 0.f)) return afail(TXD_ERR_INVALID, "sm_scale must be positive");
+  if (static_cast<long long>(pr->batch) * pr->heads > 0x7fffffffLL / ((pr->n_ctx + 255) / 256))
+    return afail(TXD_ERR_UNSUPPORTED, "too many (head, query tile) pairs for one grid");
+  return TXD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *tx_attn_last_error(void) { return g_attn_error.c_str(); }
+uint64_t tx_attn_kernel_launches(void) { return g_attn_launches.load(); }
+
+double tx_attn_flops(const tx_attn_problem *pr) {
+  if (!pr) return 0.0;
+  double f = 4.0 * pr->batch * pr->heads * static_cast<double>(pr->n_ctx) * pr->n_ctx * pr->head_dim;
+  return pr->causal ? 0.5 * f : f;
+}
+
+int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const void *v, void *out, float *m,
+                void *stream_v) {
+  int rc = validate(pr);
+  if (rc) return rc;
+  if (!q || !k || !v || !out) return afail(TXD_ERR_INVALID, "null tensor pointer");
+  DeviceState *st = nullptr;
+  rc = device_state(&st);
+  if (rc) return rc;
+  const bool bf16 = pr->dtype == TXD_BF16;
+  const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
+  txa::AttnParams prm = {};
+  if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_o, out, bf16, heads_total, pr->n_ctx, pr->head_dim, 32))) return rc;
+  prm.m_out = m;
+  prm.status = st->status;
+  prm.wait_limit_ns = 2000ull * 1000 * 1000;
+  if (const char *e = getenv("TXD_WAIT_LIMIT_MS")) {
+    const long ms = atol(e);
+    if (ms > 0) prm.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000 * 1000;
+  }
+  if (const char *e = getenv("TXD_INJECT_STALL")) prm.inject_stall = atoi(e) != 0;
+  prm.qk_scale = pr->sm_scale * 1.44269504f;  // 1 / ln 2, as the reference writes it
+  prm.n_ctx = pr->n_ctx;
+  prm.head_dim = pr->head_dim;
+  prm.heads_total = static_cast<int32_t>(heads_total);
+  prm.q_tiles = (pr->n_ctx + 255) / 256;
+  prm.causal = pr->causal ? 1 : 0;
+  prm.is_bf16 = bf16 ? 1 : 0;
+  prm.kv_stages = pr->head_dim == 128 ? 3 : 6;
+  prm.idesc_qk = attn_idesc(bf16, false, 128);
+  prm.idesc_pv = attn_idesc(bf16, true, pr->head_dim);
+  if (!m) {
+    // the kernel always writes M; give it a scratch row vector when the caller does not want it
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    const size_t need = static_cast<size_t>(heads_total) * pr->n_ctx * sizeof(float);
+    if (st->m_bytes < need) {
+      if (st->m) cudaFree(st->m);
+      st->m = nullptr;
+      st->m_bytes = 0;
+      TXA_CUDA(cudaMalloc(&st->m, need));
+      st->m_bytes = need;
+    }
+    prm.m_out = st->m;
+  }
+  const size_t tile_bytes = static_cast<size_t>(128) * pr->head_dim * 2;
+  const size_t smem = 2 * tile_bytes + 2 * txa::kPBytes + prm.kv_stages * tile_bytes + sizeof(txa::AttnCtl) + 1024;
+  const unsigned grid = static_cast<unsigned>(heads_total * prm.q_tiles);
+  txa::attn_fwd_kernel<<<grid, txa::kAttnThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(prm);
+  TXA_CUDA(cudaGetLastError());
+  g_attn_launches.fetch_add(1);
+  return TXD_OK;
+}
+
+int tx_attn_check(void *stream_v) {
+  DeviceState *st = nullptr;
+  int rc = device_state(&st);
+  if (rc) return rc;
+  TXA_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_v)));
+  uint32_t status = 0;
+  TXA_CUDA(cudaMemcpy(&status, st->status, sizeof status, cudaMemcpyDeviceToHost));
+  if (status != 0) {
+    cudaMemset(st->status, 0, sizeof status);
+    return afail(TXD_ERR_DEVICE_TIMEOUT, "a bounded wait inside the attention kernel ran out (role code %u)", status);
+  }
+  return TXD_OK;
+}
+
+int tx_attn_fwd_host(const tx_attn_problem *pr, const void *q, const void *k, const void *v, void *out, float *m) {
+  int rc = validate(pr);
+  if (rc) return rc;
+  if (!q || !k || !v || !out) return afail(TXD_ERR_INVALID, "null host pointer");
+  DeviceState *st = nullptr;
+  rc = device_state(&st);
+  if (rc) return rc;
+  const size_t heads_total = static_cast<size_t>(pr->batch) * pr->heads;
+  const size_t bytes = heads_total * pr->n_ctx * pr->head_dim * 2;
+  const size_t m_bytes = heads_total * pr->n_ctx * sizeof(float);
+  {
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    if (!st->stream) TXA_CUDA(cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking));
+    if (st->tensor_bytes < bytes) {
+      void **bufs[4] = {&st->q, &st->k, &st->v, &st->o};
+      for (void **b : bufs) {
+        if (*b) cudaFree(*b);
+        *b = nullptr;
+      }
+      st->tensor_bytes = 0;
+      for (void **b : bufs) TXA_CUDA(cudaMalloc(b, bytes));
+      st->tensor_bytes = bytes;
+    }
+    if (st->m_bytes < m_bytes) {
+      if (st->m) cudaFree(st->m);
+      st->m = nullptr;
+      st->m_bytes = 0;
+      TXA_CUDA(cudaMalloc(&st->m, m_bytes));
+      st->m_bytes = m_bytes;
+    }
+  }
+  cudaStream_t s = st->stream;
+  TXA_CUDA(cudaMemcpyAsync(st->q, q, bytes, cudaMemcpyHostToDevice, s));
+  TXA_CUDA(cudaMemcpyAsync(st->k, k, bytes, cudaMemcpyHostToDevice, s));
+  TXA_CUDA(cudaMemcpyAsync(st->v, v, bytes, cudaMemcpyHostToDevice, s));
+  rc = tx_attn_fwd(pr, st->q, st->k, st->v, st->o, st->m, s);
+  if (rc) return rc;
+  TXA_CUDA(cudaMemcpyAsync(out, st->o, bytes, cudaMemcpyDeviceToHost, s));
+  if (m) TXA_CUDA(cudaMemcpyAsync(m, st->m, m_bytes, cudaMemcpyDeviceToHost, s));
+  return tx_attn_check(s);
+}
+
+}  // extern "C"
