@@ -14,6 +14,10 @@ through the C-ABI (tx_dot_run). Workloads (BASELINE.json `configs`):
     cfg5_kshard  same GEMM, K split over the ranks, fp32 partials, NCCL reduce-scatter.
     cfg5_kshard_fused[_bf16]  K split over the ranks, the GEMM epilogue stores partial tiles into the owning
                  rank's memory over NVLink (fp32 or bf16 partials), then one local slot reduction.
+    attn_d64[_causal], attn_d128[_causal], attn_d64_16k_causal
+                 the next row after the GEMM: fused attention forward (two chained tt.dot + online softmax)
+                 on the reference benchmark's shapes (batch 4, 32 heads, fp16); metric "attention fwd TFLOP/s".
+                 At N GPUs every rank runs its own batch: weak scaling, no collective.
 
 One JSON line is printed by rank 0. `--impl reference` times the reference's CPU path for the same
 workload (the same tt.dot run by Triton's interpreter on the host cores) on a bounded tile sample.
@@ -57,6 +61,12 @@ WORKLOADS = {
     "cfg5_kshard": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
     "cfg5_kshard_fused": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
     "cfg5_kshard_fused_bf16": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
+    # fused attention forward, the reference's benchmark shapes (06-fused-attention.py:737-763): BATCH 4, 32 heads, fp16
+    "attn_d64": dict(attn=True, z=4, h=32, n_ctx=4096, d=64, causal=False, dtype="f16", seed=6),
+    "attn_d64_causal": dict(attn=True, z=4, h=32, n_ctx=4096, d=64, causal=True, dtype="f16", seed=6),
+    "attn_d128": dict(attn=True, z=4, h=32, n_ctx=4096, d=128, causal=False, dtype="f16", seed=6),
+    "attn_d128_causal": dict(attn=True, z=4, h=32, n_ctx=4096, d=128, causal=True, dtype="f16", seed=6),
+    "attn_d64_16k_causal": dict(attn=True, z=4, h=32, n_ctx=16384, d=64, causal=True, dtype="f16", seed=6),
 }
 
 
@@ -421,6 +431,169 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
     return line if rank == 0 else None
 
 
+# ---- fused attention forward (the two chained tt.dot of the reference's demo kernel) ------------------------------
+ATTN_SM_SCALE = 1.3   # the reference benchmark's value (06-fused-attention.py:785)
+
+
+def attn_flops(w: dict, z: int) -> float:
+    f = 4.0 * z * w["h"] * w["n_ctx"] * w["n_ctx"] * w["d"]
+    return 0.5 * f if w["causal"] else f
+
+
+def attn_host_inputs(w: dict, rank: int):
+    import torch
+    g = torch.Generator().manual_seed(w["seed"] + 1000 * rank)
+    return [torch.randn((w["z"], w["h"], w["n_ctx"], w["d"]), generator=g).to(torch.float16) for _ in range(3)]
+
+
+def attn_cpu_sample(w: dict, budget_s: float = 10.0) -> dict:
+    """The oracle's blockwise restatement of the reference kernel on (batch 1, head 1) slices of the workload,
+    one core; the sequence is cut to 1024 rows so that a slice takes seconds."""
+    import torch
+    from oracle import attn_oracle as AO
+    n = min(w["n_ctx"], 1024)
+    g = torch.Generator().manual_seed(w["seed"])
+    q, k, v = (torch.randn((1, 1, n, w["d"]), generator=g).to(torch.float16) for _ in range(3))
+    torch.set_num_threads(1)
+    done, t0 = 0, time.perf_counter()
+    while True:
+        AO.attention_blockwise(q, k, v, w["causal"], ATTN_SM_SCALE, 128, 64)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    secs = time.perf_counter() - t0
+    fl = 4.0 * n * n * w["d"] * (0.5 if w["causal"] else 1.0) * done
+    return {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+            "sample": f"{done} x (1 batch, 1 head, n_ctx {n}, head_dim {w['d']}) of the workload through oracle/attn_oracle.py "
+                      f"(numpy restatement of the reference kernel, BLOCK_M 128, BLOCK_N 64), {secs:.1f} s"}
+
+
+def run_attention_reference_arm(args, name: str, w: dict) -> dict:
+    """CPU arm: the eager formula of the reference's own test (matmul, softmax, matmul) on all host threads, one
+    (batch, head) slice per step."""
+    import torch
+    from oracle import attn_oracle as AO
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    n = min(w["n_ctx"], 2048)
+    g = torch.Generator().manual_seed(w["seed"])
+    q, k, v = (torch.randn((1, 1, n, w["d"]), generator=g).to(torch.float16) for _ in range(3))
+    for _ in range(args.warmup):
+        AO.attention_eager(q, k, v, w["causal"], ATTN_SM_SCALE)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        AO.attention_eager(q, k, v, w["causal"], ATTN_SM_SCALE)
+    secs = (time.perf_counter() - t0) / max(args.steps, 1)
+    fl = 4.0 * n * n * w["d"] * (0.5 if w["causal"] else 1.0)
+    val = fl / secs / 1e12
+    sample = f"one (batch, head) slice per step, n_ctx cut to {n}, eager matmul-softmax-matmul in fp32 on {cores} threads"
+    return {"impl": "reference", "metric": "attention fwd TFLOP/s", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded randn)",
+            "config": {"workload": name, "z": w["z"], "h": w["h"], "n_ctx": w["n_ctx"], "head_dim": w["d"], "causal": w["causal"]},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def run_attention_gpu_arm(args, name: str, w: dict) -> dict | None:
+    """Every rank runs its own batch of `z` sequences (independent (batch, head) pairs: no collective)."""
+    import torch
+    import torch.distributed as dist
+    from triton_ext_b200 import attention as A
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the attention kernel has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    q_h, k_h, v_h = (t.pin_memory() for t in attn_host_inputs(w, rank))
+    o_h = torch.empty_like(q_h).pin_memory()
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    out = torch.empty_like(q)
+    set_bytes = 4 * q.numel() * 2
+    if set_bytes <= L2_BYTES:
+        raise RuntimeError("attention workload smaller than L2: add rotating buffers before timing it")
+
+    def step(i):
+        A.attention_forward(q, k, v, w["causal"], ATTN_SM_SCALE, out=out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    stream = torch.cuda.current_stream(dev)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    launches0 = A.kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    barrier()
+    launches = A.kernel_launches() - launches0
+    clocks = sampler.stop()
+    A.check(dev)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms, float(launches)], device=dev)
+        dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
+        dist.all_reduce(t[1:], op=dist.ReduceOp.SUM)
+        ms, launches = float(t[0].item()), int(t[1].item())
+    ms_per_step = ms / args.steps
+    per_gpu_flops = attn_flops(w, w["z"])
+    value = per_gpu_flops * world / (ms_per_step * 1e-3) / 1e12
+
+    e2e_steps = max(1, min(args.steps, 10))
+    A.attention_forward_host(q_h, k_h, v_h, w["causal"], ATTN_SM_SCALE, out=o_h)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        A.attention_forward_host(q_h, k_h, v_h, w["causal"], ATTN_SM_SCALE, out=o_h)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    peaks = measured_peaks()
+    achieved = per_gpu_flops / (ms_per_step * 1e-3) / 1e12
+    sm_mhz = clocks.get("sm_mhz") or 1965
+    sfu_bound = 4.0 * w["d"] * 16 * 148 * sm_mhz * 1e6 / 1e12   # one exp2 per score, 16 per clock per SM
+    algo_bytes = 4 * q.numel() * 2 + q.numel() // w["d"] * 4
+    line = {
+        "metric": "attention fwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w["dtype"], "data": "synthetic (seeded randn, the reference benchmark's shapes and sm_scale)",
+        "config": {"workload": name, "z": w["z"] * world, "h": w["h"], "n_ctx": w["n_ctx"], "head_dim": w["d"],
+                   "causal": w["causal"], "per_gpu": [w["z"], w["h"], w["n_ctx"], w["d"]],
+                   "parallelism": "batch-sharded, no collective" if world > 1 else "single GPU",
+                   "kernel": "256 query rows per CTA (2 x 128), KV blocks of 128, tcgen05 + TMEM",
+                   "l2": f"one buffer set of {set_bytes / 1e6:.0f} MB > 126 MB L2"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                     "peak_source": f"bf16_tflops (burst) of {peaks['_source']}",
+                     "note": f"exp2 on the SFU (16 per clock per SM) bounds this shape at {sfu_bound:.0f} TFLOP/s; "
+                             f"algorithmic bytes {algo_bytes / 1e6:.0f} MB"},
+        "e2e": {"value": per_gpu_flops * world / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(3 * q.numel() * 2),
+                "d2h_bytes_per_step": int(q.numel() * 2), "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    return line if rank == 0 else None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -438,7 +611,17 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return  # the CPU arm runs once, on rank 0
-        print(json.dumps(run_reference_arm(args, args.workload, w)), flush=True)
+        arm = run_attention_reference_arm if w.get("attn") else run_reference_arm
+        print(json.dumps(arm(args, args.workload, w)), flush=True)
+        return
+
+    if w.get("attn"):
+        line = run_attention_gpu_arm(args, args.workload, w)
+        if line is None:
+            return
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = attn_cpu_sample(w)
+        print(json.dumps(line), flush=True)
         return
 
     line = run_gpu_arm(args, args.workload, w)

@@ -6,13 +6,20 @@
 // warpgroup, its own S accumulator and its own O accumulator in TMEM. K and V tiles of 128 rows are
 // streamed once per CTA through a shared-memory ring and used by both sub-tiles.
 //
-//   warps 0-3 / 4-7 : softmax warpgroup of sub-tile 0 / 1 (one query row per thread): tcgen05.ld of S,
+//   warps 0-3 / 4-7 : softmax warpgroup of sub-tile 0 / 1 (one query row per thread): tcgen05.ld of S into
+//                     registers (S is then handed back at once, so the next Q K^T overlaps this softmax),
 //                     running max and sum in base 2, P = exp2(S*scale - m) rounded to the input type and
 //                     written to shared memory as the A operand of the second dot, rescaling of O in TMEM
-//                     (tcgen05.ld / tcgen05.st) when the running max moved, final O / l and TMA store
+//                     (tcgen05.ld / tcgen05.st) only when the running max moved by more than 2^8, final
+//                     O / l and TMA store
 //   warp 8          : TMA producer (Q once; K0, K1, V0, K2, V1, ... through the ring)
-//   warp 9          : tcgen05.mma issuer: S_t = Q_t K_j^T, then O_t += P_t V_j one KV block later, so that
-//                     the tensor pipe works on one sub-tile while the other one is in its softmax
+//   warp 9          : tcgen05.mma issuer. Per KV block j: S_t(j+1) = Q_t K_{j+1}^T for both sub-tiles as soon
+//                     as their S_t(j) has been read, K_{j+1} released; then O_t += P_t(j) V_j as each P_t(j)
+//                     is complete, V_j released. The tensor pipe works on one sub-tile while the other one
+//                     is in its softmax.
+//
+// Barriers wait by polling mbarrier.test_wait (mbarrier.try_wait was measured to return hundreds of cycles
+// late even for phases completed long before, and every hop of this pipeline is on the critical path).
 //
 // The KV loop is executed the way LoopSplit leaves it (reference LoopSplit.cpp:179-193 applied to the
 // compare at 06-fused-attention.py:64): an off-band loop over the blocks that need no mask and an
@@ -37,6 +44,7 @@ constexpr int kMmaWarp = 9;
 constexpr int kMaxKvStages = 6;
 constexpr int kAtomBytes = 128 * 128;  // 128 rows x one 128-byte swizzle span
 constexpr int kPBytes = 2 * kAtomBytes;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr uint32_t kTmemCols = 512;    // S0 | S1 | O0 | O1, 128 columns each
 
 enum AttnDeviceStatus : uint32_t {
@@ -66,13 +74,15 @@ struct AttnCtl {
   uint64_t q_full;
   uint64_t kv_full[kMaxKvStages], kv_empty[kMaxKvStages];
   uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t s_free[2];     // S_t has been read into registers: the next Q K^T may overwrite it
   uint64_t drain;
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
 
-__device__ __forceinline__ uint32_t pack_pair(float a, float b, int is_bf16) {
-  if (is_bf16) {
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b) {
+  if (kBf16) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&h);
   }
@@ -87,63 +97,75 @@ __device__ __forceinline__ uint32_t swz_off(int r, int chunk16) {
 }
 
 // One softmax step of one query row over a 128-column block of S held in registers.
-// kMasked = false: the off-band loop (no element masked); true: the on-band loop.
+// kMasked = false: the off-band loop (no element masked); true: the on-band loop, where `lim` is the last
+// column the row may attend to.
 template <bool kMasked>
-__device__ __forceinline__ float row_block_max(const uint32_t (&s)[128], int col0, int row, int n_ctx, int causal) {
+__device__ __forceinline__ float row_block_max(const uint32_t (&s)[128], int col0, int lim) {
   float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < 128; i += 4) {
-    float a = __uint_as_float(s[i]), b = __uint_as_float(s[i + 1]), c = __uint_as_float(s[i + 2]),
-          d = __uint_as_float(s[i + 3]);
-    if (kMasked) {
-      const int lim = causal ? min(row, n_ctx - 1) : n_ctx - 1;  // last allowed column
-      a = col0 + i <= lim ? a : -INFINITY;
-      b = col0 + i + 1 <= lim ? b : -INFINITY;
-      c = col0 + i + 2 <= lim ? c : -INFINITY;
-      d = col0 + i + 3 <= lim ? d : -INFINITY;
+  for (int i = 0; i < 128; i += 8) {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      x[u] = __uint_as_float(s[i + u]);
+      if (kMasked) x[u] = col0 + i + u <= lim ? x[u] : -INFINITY;
     }
-    m0 = fmaxf(m0, a);
-    m1 = fmaxf(m1, b);
-    m2 = fmaxf(m2, c);
-    m3 = fmaxf(m3, d);
+    m0 = fmaxf(m0, fmaxf(x[0], x[1]));
+    m1 = fmaxf(m1, fmaxf(x[2], x[3]));
+    m2 = fmaxf(m2, fmaxf(x[4], x[5]));
+    m3 = fmaxf(m3, fmaxf(x[6], x[7]));
   }
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
+// P = exp2(S * qk_scale - m) for one row: written to shared memory in the input type (swizzled K-major A
+// operand of the second dot); returns the fp32 row sum of the unrounded values, as the reference sums them.
+// The exponentials of group g+1 are issued before group g is summed, packed and stored, so that the SFU
+// pipeline does not drain between groups (a single warp per scheduler has nobody else to hide its latency).
 template <bool kMasked>
-__device__ __forceinline__ float row_block_exp_store(const uint32_t (&s)[128], float qk_scale, float neg_m, int col0,
-                                                     int row, int n_ctx, int causal, int is_bf16, uint32_t p_tile,
-                                                     int row_in_tile) {
-  float sum0 = 0.f, sum1 = 0.f;
-  const int lim = causal ? min(row, n_ctx - 1) : n_ctx - 1;
+__device__ __forceinline__ void exp_group(const uint32_t (&s)[128], int g, float qk_scale, float neg_m, int col0, int lim,
+                                          float (&e)[8]) {
 #pragma unroll
-  for (int g = 0; g < 16; ++g) {  // 8 columns = one 16-byte chunk of P
-    float e[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float x = fast_exp2(fmaf(__uint_as_float(s[g * 8 + i]), qk_scale, neg_m));
-      if (kMasked) x = col0 + g * 8 + i <= lim ? x : 0.f;
-      e[i] = x;
-    }
-    sum0 += (e[0] + e[1]) + (e[2] + e[3]);
-    sum1 += (e[4] + e[5]) + (e[6] + e[7]);
-    st_shared_v4(p_tile + (g >> 3) * kAtomBytes + swz_off(row_in_tile, g & 7), pack_pair(e[0], e[1], is_bf16),
-                 pack_pair(e[2], e[3], is_bf16), pack_pair(e[4], e[5], is_bf16), pack_pair(e[6], e[7], is_bf16));
+  for (int i = 0; i < 8; ++i) {
+    e[i] = fast_exp2(fmaf(__uint_as_float(s[g * 8 + i]), qk_scale, neg_m));
+    if (kMasked) e[i] = col0 + g * 8 + i <= lim ? e[i] : 0.f;
   }
-  return sum0 + sum1;
 }
 
+template <bool kMasked, bool kBf16>
+__device__ __forceinline__ float row_block_exp_store(const uint32_t (&s)[128], float qk_scale, float neg_m, int col0,
+                                                     int lim, uint32_t p_row, int row_xor) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  float cur[8], nxt[8];
+  exp_group<kMasked>(s, 0, qk_scale, neg_m, col0, lim, cur);
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {  // 8 columns = one 16-byte chunk of P
+    if (g + 1 < 16) exp_group<kMasked>(s, g + 1, qk_scale, neg_m, col0, lim, nxt);
+    s0 += cur[0] + cur[1];
+    s1 += cur[2] + cur[3];
+    s2 += cur[4] + cur[5];
+    s3 += cur[6] + cur[7];
+    st_shared_v4(p_row + (g >> 3) * kAtomBytes + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(cur[0], cur[1]),
+                 pack_pair<kBf16>(cur[2], cur[3]), pack_pair<kBf16>(cur[4], cur[5]), pack_pair<kBf16>(cur[6], cur[7]));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+  }
+  return (s0 + s1) + (s2 + s3);
+}
+
+template <bool kBf16, int kD>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t attn_smem_raw[];
   const uint32_t raw = smem_u32(attn_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const int D = p.head_dim;
+  constexpr int D = kD;
   const uint32_t tile_bytes = static_cast<uint32_t>(kTileRows * D * 2);  // one Q / K / V tile
-  const int d_atoms = D / 64;
+  constexpr int d_atoms = D / 64;
+  constexpr uint32_t kStages = kD == 128 ? 3u : 6u;  // ring slots of one K or V tile each
   const uint32_t q_addr0 = base;
   const uint32_t p_addr0 = base + 2 * tile_bytes;
   const uint32_t kv_addr0 = p_addr0 + 2 * kPBytes;
-  AttnCtl *ctl = reinterpret_cast<AttnCtl *>(attn_smem_raw + (kv_addr0 - raw) + p.kv_stages * tile_bytes);
+  AttnCtl *ctl = reinterpret_cast<AttnCtl *>(attn_smem_raw + (kv_addr0 - raw) + kStages * tile_bytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -175,7 +197,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
-    for (int s = 0; s < p.kv_stages; ++s) {
+    for (int s = 0; s < static_cast<int>(kStages); ++s) {
       mbar_init(smem_u32(&ctl->kv_full[s]), 1);
       mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
     }
@@ -183,6 +205,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       mbar_init(smem_u32(&ctl->s_full[t]), 1);
       mbar_init(smem_u32(&ctl->p_full[t]), kTileRows);  // every softmax thread arrives
       mbar_init(smem_u32(&ctl->o_done[t]), 1);
+      mbar_init(smem_u32(&ctl->s_free[t]), kTileRows);
     }
     mbar_init(smem_u32(&ctl->drain), 1);
     ctl->abort_flag = 0;
@@ -201,6 +224,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
+
   if (warp == kProducerWarp) {
     // ------------------------------ TMA producer ------------------------------
     const bool issuer = elect_one();
@@ -218,9 +242,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       }
       __syncwarp();
       auto load_tile = [&](const CUtensorMap *map, int kv_block) {
-        const uint32_t slot = issued % static_cast<uint32_t>(p.kv_stages);
-        const uint32_t phase = (issued / static_cast<uint32_t>(p.kv_stages)) & 1u;
-        if (!warp_mbar_wait(smem_u32(&ctl->kv_empty[slot]), phase ^ 1u, ac, kAttnTimeoutProducer, lane)) {
+        const uint32_t slot = issued % kStages;
+        const uint32_t phase = (issued / kStages) & 1u;
+        if (!warp_mbar_poll(smem_u32(&ctl->kv_empty[slot]), phase ^ 1u, ac, kAttnTimeoutProducer, lane)) {
           ok = false;
           return;
         }
@@ -245,11 +269,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       if (ctl->abort_flag) {
         if (lane == 0) {
           mbar_wait_timed(smem_u32(&ctl->q_full), 0u, ac, kAttnTimeoutDrain);
-          const uint32_t first = issued > static_cast<uint32_t>(p.kv_stages) ? issued - p.kv_stages : 0u;
+          const uint32_t first = issued > kStages ? issued - kStages : 0u;
           for (uint32_t i = first; i < issued; ++i) {
             const unsigned long long t0 = global_timer_ns();
-            const uint32_t bar = smem_u32(&ctl->kv_full[i % p.kv_stages]);
-            const uint32_t ph = (i / p.kv_stages) & 1u;
+            const uint32_t bar = smem_u32(&ctl->kv_full[i % kStages]);
+            const uint32_t ph = (i / kStages) & 1u;
             while (!mbar_try_wait(bar, ph))
               if (global_timer_ns() - t0 > ac.limit_ns) break;
           }
@@ -269,38 +293,39 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       uint32_t taken = 0;
       bool ok = true;
       auto take = [&]() -> uint32_t {  // next ring item, in the producer's order
-        const uint32_t slot = taken % static_cast<uint32_t>(p.kv_stages);
-        const uint32_t phase = (taken / static_cast<uint32_t>(p.kv_stages)) & 1u;
-        if (!warp_mbar_wait(smem_u32(&ctl->kv_full[slot]), phase, ac, kAttnTimeoutMmaOperand, lane)) ok = false;
+        const uint32_t slot = taken % kStages;
+        const uint32_t phase = (taken / kStages) & 1u;
+        if (!warp_mbar_poll(smem_u32(&ctl->kv_full[slot]), phase, ac, kAttnTimeoutMmaOperand, lane)) ok = false;
         ++taken;
         return slot;
       };
+      // The whole warp walks these (addresses and descriptors stay warp-uniform); the elected lane issues.
+      const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
       auto issue_qk = [&](int t, uint32_t k_slot) {  // S_t = Q_t K^T : head_dim / 16 MMAs of 128 x 128 x 16
-        if (issuer) {
-          const uint32_t qa = lo_of(q_addr0 + t * tile_bytes) | kmajor_lbo;
-          const uint32_t ka = lo_of(kv_addr0 + k_slot * tile_bytes) | kmajor_lbo;
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(t) * 128u;
-          for (int i = 0; i < D / 16; ++i) {
-            const uint32_t step = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
-            umma_f16(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), p.idesc_qk, i > 0 ? 1u : 0u);
-          }
-          tc_commit(smem_u32(&ctl->s_full[t]));
+        const uint32_t qa = lo_of(q_addr0 + t * tile_bytes) | kmajor_lbo;
+        const uint32_t ka = lo_of(kv_addr0 + k_slot * tile_bytes) | kmajor_lbo;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(t) * 128u;
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+          const uint32_t step = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
+          if (issuer) umma_f16(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk, i > 0 ? 1u : 0u);
         }
+        if (issuer) tc_commit(smem_u32(&ctl->s_full[t]));
         __syncwarp();
       };
       auto issue_pv = [&](int t, uint32_t v_slot, bool accumulate) {  // O_t += P_t V : 8 MMAs of 128 x head_dim x 16
-        if (issuer) {
-          const uint32_t pa = lo_of(p_addr0 + t * kPBytes) | kmajor_lbo;
-          const uint32_t va = lo_of(kv_addr0 + v_slot * tile_bytes) | v_lbo;
-          const uint32_t d_tmem = tmem_base + 256u + static_cast<uint32_t>(t) * 128u;
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t pstep = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
-            const uint32_t vstep = static_cast<uint32_t>(i) * (16u * 128u >> 4);  // 16 KV rows of 128 bytes
-            umma_f16(d_tmem, desc64(desc_hi, pa + pstep), desc64(desc_hi, va + vstep), p.idesc_pv,
+        const uint32_t pa = lo_of(p_addr0 + t * kPBytes) | kmajor_lbo;
+        const uint32_t va = lo_of(kv_addr0 + v_slot * tile_bytes) | v_lbo;
+        const uint32_t d_tmem = tmem_base + 256u + static_cast<uint32_t>(t) * 128u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t pstep = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
+          const uint32_t vstep = static_cast<uint32_t>(i) * (16u * 128u >> 4);  // 16 KV rows of 128 bytes
+          if (issuer)
+            umma_f16(d_tmem, desc64(desc_hi, pa + pstep), desc64(desc_hi, va + vstep), idesc_pv,
                      (accumulate || i > 0) ? 1u : 0u);
-          }
-          tc_commit(smem_u32(&ctl->o_done[t]));
         }
+        if (issuer) tc_commit(smem_u32(&ctl->o_done[t]));
         __syncwarp();
       };
       auto release = [&](uint32_t slot) {
@@ -308,7 +333,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         __syncwarp();
       };
 
-      ok = warp_mbar_wait(smem_u32(&ctl->q_full), 0u, ac, kAttnTimeoutMmaOperand, lane);
+      ok = warp_mbar_poll(smem_u32(&ctl->q_full), 0u, ac, kAttnTimeoutMmaOperand, lane);
       uint32_t k_slot = 0;
       if (ok) k_slot = take();
       if (ok) {
@@ -318,25 +343,36 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         release(k_slot);
       }
       for (int j = 0; ok && j < nmax; ++j) {
-        const bool has_next = j + 1 < nmax;
-        uint32_t kn_slot = 0;
-        if (has_next) kn_slot = take();
-        uint32_t v_slot = 0;
-        if (ok) v_slot = take();
+        // First half: the next S of both sub-tiles, as soon as their softmax warps hold S(j) in registers.
+        // K_{j+1} goes back to the producer right after, so that V_{j+1} can be fetched a whole block ahead.
+        if (j + 1 < nmax) {
+          const uint32_t kn_slot = take();
+          if (!ok) break;
+          for (int t = 0; t < 2; ++t) {
+            if (j + 1 >= n_blk[t]) continue;
+            if (!warp_mbar_poll(smem_u32(&ctl->s_free[t]), static_cast<uint32_t>(j) & 1u, ac, kAttnTimeoutMmaP, lane)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_qk(t, kn_slot);
+          }
+          if (!ok) break;
+          release(kn_slot);
+        }
+        // Second half: O_t += P_t(j) V_j once P_t(j) is in shared memory and O_t is rescaled.
+        const uint32_t v_slot = take();
         if (!ok) break;
         for (int t = 0; t < 2; ++t) {
           if (j >= n_blk[t]) continue;
-          // P_t(j) is in shared memory, O_t is rescaled, and S_t has been read: both MMAs may go
-          if (!warp_mbar_wait(smem_u32(&ctl->p_full[t]), static_cast<uint32_t>(j) & 1u, ac, kAttnTimeoutMmaP, lane)) {
+          if (!warp_mbar_poll(smem_u32(&ctl->p_full[t]), static_cast<uint32_t>(j) & 1u, ac, kAttnTimeoutMmaP, lane)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          if (j + 1 < n_blk[t]) issue_qk(t, kn_slot);
           issue_pv(t, v_slot, j > 0);
         }
         if (!ok) break;
-        if (has_next) release(kn_slot);
         release(v_slot);
       }
       // every MMA issued above has completed before TMEM and shared memory are given back
@@ -364,11 +400,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     const uint32_t s_tmem = lane_base + static_cast<uint32_t>(t) * 128u;
     const uint32_t o_tmem = lane_base + 256u + static_cast<uint32_t>(t) * 128u;
     const uint32_t p_tile = p_addr0 + t * kPBytes;
+    const uint32_t p_row = p_tile + static_cast<uint32_t>((row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128);
+    const int row_xor = row_in_tile & 7;
+    const int lim = p.causal ? min(row, p.n_ctx - 1) : p.n_ctx - 1;  // last column this row may attend to
     const int n = n_blk[t];
     float m_i = -INFINITY, l_i = 0.f;
     bool ok = true;
     for (int j = 0; j < n; ++j) {
-      if (!warp_mbar_wait(smem_u32(&ctl->s_full[t]), static_cast<uint32_t>(j) & 1u, ac, kAttnTimeoutSoftmaxS, lane)) {
+      if (!warp_mbar_poll(smem_u32(&ctl->s_full[t]), static_cast<uint32_t>(j) & 1u, ac, kAttnTimeoutSoftmaxS, lane)) {
         ok = false;
         break;
       }
@@ -379,22 +418,29 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       tmem_ld_32x32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
       tmem_ld_32x32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
       tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->s_free[t]));
       const bool masked = j >= n_full[t];
       const int col0 = j * kTileRows;
-      const float mx = masked ? row_block_max<true>(s, col0, row, p.n_ctx, p.causal)
-                              : row_block_max<false>(s, col0, row, p.n_ctx, p.causal);
-      float m_new = fmaxf(m_i, mx * p.qk_scale);
+      const float mx = masked ? row_block_max<true>(s, col0, lim) : row_block_max<false>(s, col0, lim);
+      // The running max is only moved when the block's max exceeds it by more than 2^8: until then
+      // exponentials are taken against the older, smaller reference (values up to 256, exact to the same
+      // relative precision), alpha is exactly 1 and O needs no rescaling. O / l and m + log2(l) do not
+      // depend on which reference was used.
+      const float m_cand = fmaxf(m_i, mx * p.qk_scale);
+      float m_new = (m_cand - m_i > kRescaleThreshold) ? m_cand : m_i;
       if (m_new == -INFINITY) m_new = 0.f;  // a row with nothing to attend to yet
       const float alpha = fast_exp2(m_i - m_new);
       if (j > 0) {
         // O_t += P_t(j-1) V has completed: P_t may be overwritten and O_t rescaled
-        if (!warp_mbar_wait(smem_u32(&ctl->o_done[t]), static_cast<uint32_t>(j - 1) & 1u, ac, kAttnTimeoutSoftmaxO,
+        if (!warp_mbar_poll(smem_u32(&ctl->o_done[t]), static_cast<uint32_t>(j - 1) & 1u, ac, kAttnTimeoutSoftmaxO,
                             lane)) {
           ok = false;
           break;
         }
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
             tmem_ld_32x32(o_tmem + c * 32, o);
@@ -406,10 +452,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           tmem_st_wait();
         }
       }
-      const float sum = masked ? row_block_exp_store<true>(s, p.qk_scale, -m_new, col0, row, p.n_ctx, p.causal,
-                                                           p.is_bf16, p_tile, row_in_tile)
-                               : row_block_exp_store<false>(s, p.qk_scale, -m_new, col0, row, p.n_ctx, p.causal,
-                                                            p.is_bf16, p_tile, row_in_tile);
+      const float sum = masked ? row_block_exp_store<true, kBf16>(s, p.qk_scale, -m_new, col0, lim, p_row, row_xor)
+                               : row_block_exp_store<false, kBf16>(s, p.qk_scale, -m_new, col0, lim, p_row, row_xor);
       l_i = l_i * alpha + sum;
       m_i = m_new;
       fence_proxy_async();  // P is read by the tensor core through the async proxy
@@ -418,10 +462,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     }
     if (ok && n > 0) {
       // ---- epilogue of the sub-tile: O / l, cast, store; M = m + log2(l) ----
-      ok = warp_mbar_wait(smem_u32(&ctl->o_done[t]), static_cast<uint32_t>(n - 1) & 1u, ac, kAttnTimeoutSoftmaxO, lane);
+      ok = warp_mbar_poll(smem_u32(&ctl->o_done[t]), static_cast<uint32_t>(n - 1) & 1u, ac, kAttnTimeoutSoftmaxO, lane);
       if (ok) {
         tc_fence_after();
         const float inv_l = 1.0f / l_i;
+#pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
           tmem_ld_32x32(o_tmem + c * 32, o);
@@ -432,8 +477,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              w[i] = pack_pair(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l,
-                               p.is_bf16);
+              w[i] = pack_pair<kBf16>(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l);
             st_shared_v4(p_tile + (c >> 1) * kAtomBytes + swz_off(row_in_tile, (c & 1) * 4 + q), w[0], w[1], w[2], w[3]);
           }
         }

@@ -112,7 +112,10 @@ int device_state(DeviceState **out) {
     TXA_CUDA(cudaMemset(st.status, 0, sizeof(uint32_t)));
   }
   if (!st.attr_set) {
-    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     st.attr_set = true;
   }
   *out = &st;
@@ -174,7 +177,7 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   prm.q_tiles = (pr->n_ctx + 255) / 256;
   prm.causal = pr->causal ? 1 : 0;
   prm.is_bf16 = bf16 ? 1 : 0;
-  prm.kv_stages = pr->head_dim == 128 ? 3 : 6;
+  prm.kv_stages = pr->head_dim == 128 ? 3 : 6;  // what the kernel templates use; shared memory is sized from it
   prm.idesc_qk = attn_idesc(bf16, false, 128);
   prm.idesc_pv = attn_idesc(bf16, true, pr->head_dim);
   if (!m) {
@@ -193,7 +196,11 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   const size_t tile_bytes = static_cast<size_t>(128) * pr->head_dim * 2;
   const size_t smem = 2 * tile_bytes + 2 * txa::kPBytes + prm.kv_stages * tile_bytes + sizeof(txa::AttnCtl) + 1024;
   const unsigned grid = static_cast<unsigned>(heads_total * prm.q_tiles);
-  txa::attn_fwd_kernel<<<grid, txa::kAttnThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(prm);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (bf16 && pr->head_dim == 64) txa::attn_fwd_kernel<true, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else if (bf16) txa::attn_fwd_kernel<true, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else if (pr->head_dim == 64) txa::attn_fwd_kernel<false, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else txa::attn_fwd_kernel<false, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
   TXA_CUDA(cudaGetLastError());
   g_attn_launches.fetch_add(1);
   return TXD_OK;

@@ -330,4 +330,18 @@ __device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, co
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// The same for a warp on a kernel's critical path: mbarrier.try_wait was measured to take a few hundred
+// cycles to return even when the phase had completed long before, mbarrier.test_wait returns within a few
+// cycles. The warp probes with test_wait (all lanes, one shared-memory wavefront, result made uniform by a
+// vote) and only falls back to the timed wait after many failed probes.
+__device__ __forceinline__ bool warp_mbar_poll(uint32_t bar, uint32_t parity, const AbortCtl &ac, uint32_t code,
+                                               int lane) {
+#pragma unroll 1
+  for (uint32_t it = 0; it < 16u * kPollsBeforeTimer; ++it)
+    if (__any_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
+  uint32_t ok = 0;
+  if (lane == 0) ok = mbar_wait_timed(bar, parity, ac, code) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 }  // namespace txd
