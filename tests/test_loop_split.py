@@ -195,3 +195,31 @@ def test_dot_as_written_split_is_rejected_by_the_backend(built_libs):
     pr = B.make_problem(4096, 4096, 4160, torch.bfloat16, torch.bfloat16)
     with pytest.raises(RuntimeError, match="unmasked"):
         P.lower_dot(pr, 128, attrs={"loop_split.mode": "as-written"})
+
+
+@pytest.mark.parametrize("mode", ["intent", "as-written"])
+def test_attention_kv_loop_split_is_what_the_kernel_runs(built_libs, mode):
+    """The reference's use case (06-fused-attention.py:59-64): `for start_n in range(0, hi, BLOCK_N)` with
+    `start_n >= causal_start`, causal_start = start_m * BLOCK_M. sge with a step > 1 and an aligned comparand is
+    the one predicate for which the reference's arithmetic and its intent agree (-step, then +step), so both modes
+    must give the off-band / on-band loops the attention kernel executes per 128-row sub-tile."""
+    from triton_ext_b200 import attention as A
+    block = 128
+    for n_ctx, start_m in [(1024, 0), (1024, 3), (1024, 7), (4096, 17), (384, 2)]:
+        causal_start = start_m * block
+        hi = (start_m + 1) * block          # the kernel does not visit the fully masked blocks above the diagonal
+        loop = P.make_loop(0, hi, block, "sge", causal_start)
+        m, before = run_pass(loop, mode)
+        loops = m.loops()
+        n, unmasked = A.kv_loop_split(n_ctx, causal_start, True, block)
+        assert (n, unmasked) == (start_m + 1, start_m)
+        if start_m == 0:
+            # nothing below the diagonal: the off-band loop is empty
+            live = [l for l in loops if l["hi"] > l["lo"]]
+            assert [(l["lo"], l["hi"]) for l in live] == [(0, block)]
+            assert live[0]["fold"] in (P.TXIR_FOLDED_TRUE, P.TXIR_NOT_FOLDED)
+        else:
+            assert [(l["lo"], l["hi"], l["step"]) for l in loops] == [(0, unmasked * block, block), (unmasked * block, n * block, block)]
+            assert loops[0]["fold"] == P.TXIR_FOLDED_FALSE and loops[1]["fold"] == P.TXIR_FOLDED_TRUE
+        assert m.simulate(0) == before      # same result as the unsplit loop
+

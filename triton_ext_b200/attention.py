@@ -61,6 +61,19 @@ def make_problem(z: int, h: int, n_ctx: int, head_dim: int, dtype: torch.dtype, 
                        causal=1 if causal else 0, sm_scale=float(sm_scale))
 
 
+def kv_loop_split(n_ctx: int, q_start: int, causal: bool, block: int = 128) -> tuple[int, int]:
+    """(blocks visited, blocks of them that run unmasked) for the 128 query rows starting at `q_start`: the
+    arithmetic the kernel uses per sub-tile. It is LoopSplit applied to the reference's KV loop
+    (`for start_n in range(0, hi, BLOCK_N): if start_n >= causal_start`, 06-fused-attention.py:59-64): the
+    off-band loop is [0, unmasked * block), the on-band loop the rest."""
+    if q_start >= n_ctx:
+        return 0, 0
+    all_blocks = -(-n_ctx // block)
+    n = min(all_blocks, q_start // block + 1) if causal else all_blocks
+    last_masked = n > 0 and (causal or (n_ctx % block != 0 and n == all_blocks))
+    return n, n - 1 if last_masked else n
+
+
 def flops(problem: AttnProblem) -> float:
     return float(_lib().tx_attn_flops(ctypes.byref(problem)))
 
