@@ -65,6 +65,7 @@ struct AttnParams {
   unsigned long long wait_limit_ns;
   float qk_scale;                      // sm_scale * log2(e)
   int32_t n_ctx, head_dim, heads_total, q_tiles;
+  int32_t head_group;                  // heads per launch-order group (their K and V share L2)
   int32_t causal, is_bf16, kv_stages;
   uint32_t idesc_qk, idesc_pv;
   int32_t inject_stall;                // host-side fault injection: the producer stops after Q
@@ -170,9 +171,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // ---- work: one (head, 256-row query tile); heavy (late) causal tiles are scheduled first ----
-  const int head = static_cast<int>(blockIdx.x) % p.heads_total;
-  const int qt = p.q_tiles - 1 - static_cast<int>(blockIdx.x) / p.heads_total;
+  // ---- work: one (head, 256-row query tile). Launch order: groups of `head_group` heads whose K and V fit L2
+  // together; inside a group the query tile index is the slow one, late (heavy, when causal) tiles first. The CTAs
+  // that run at the same time then share one group's K and V through L2 (with all heads in one group every wave
+  // of CTAs streamed every head's K and V from HBM again: 2.6 x the algorithmic bytes were measured), and the
+  // last CTAs of the launch are the lightest ones. ----
+  const int per_group = p.head_group * p.q_tiles;
+  const int g = static_cast<int>(blockIdx.x) / per_group;
+  const int r = static_cast<int>(blockIdx.x) - g * per_group;
+  const int heads_here = min(p.head_group, p.heads_total - g * p.head_group);
+  const int head = g * p.head_group + r % heads_here;
+  const int qt = p.q_tiles - 1 - r / heads_here;
   const int q0 = qt * 2 * kTileRows;
   const int kv_blocks_all = (p.n_ctx + kTileRows - 1) / kTileRows;
   const bool ragged = (p.n_ctx % kTileRows) != 0;

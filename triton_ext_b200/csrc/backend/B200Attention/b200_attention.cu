@@ -175,6 +175,16 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   prm.head_dim = pr->head_dim;
   prm.heads_total = static_cast<int32_t>(heads_total);
   prm.q_tiles = (pr->n_ctx + 255) / 256;
+  {
+    // heads whose K and V (2 tensors x n_ctx x head_dim x 2 bytes each) fit in 48 MB of the 126 MB L2 together
+    const long long kv_bytes = 4LL * pr->n_ctx * pr->head_dim;
+    long long grp = (48LL << 20) / (kv_bytes > 0 ? kv_bytes : 1);
+    if (grp < 1) grp = 1;
+    if (grp > heads_total) grp = heads_total;
+    const long long groups = (heads_total + grp - 1) / grp;
+    grp = (heads_total + groups - 1) / groups;  // equal groups: the last one is not a short tail of heavy tiles
+    prm.head_group = static_cast<int32_t>(grp);
+  }
   prm.causal = pr->causal ? 1 : 0;
   prm.is_bf16 = bf16 ? 1 : 0;
   prm.kv_stages = pr->head_dim == 128 ? 3 : 6;  // what the kernel templates use; shared memory is sized from it
