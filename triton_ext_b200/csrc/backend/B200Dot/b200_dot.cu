@@ -93,6 +93,14 @@ struct tx_dot_plan {
   void *dev_a = nullptr, *dev_b = nullptr, *dev_c = nullptr;
   float *dev_rs = nullptr, *dev_cs = nullptr;
   size_t a_bytes = 0, b_bytes = 0, c_bytes = 0;
+  // pipelined host-buffer path: column panels of B and C; copies in, kernels and copies out on three streams
+  tx_dot_config user_cfg = {};
+  bool has_user_cfg = false;
+  cudaStream_t compute_stream = nullptr, d2h_stream = nullptr;
+  tx_dot_plan *panel_plan[2] = {nullptr, nullptr};  // regular panel width, last panel width
+  int panel_cols[2] = {0, 0};
+  cudaEvent_t ev_in[9] = {}, ev_done[8] = {};
+  bool events_made = false;
 };
 
 namespace {
@@ -258,6 +266,10 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
   tx_dot_plan *pl = new (std::nothrow) tx_dot_plan();
   if (!pl) return fail(TXD_ERR_INVALID, "out of host memory");
   pl->problem = *problem;
+  if (cfg) {
+    pl->user_cfg = *cfg;
+    pl->has_user_cfg = true;
+  }
   pl->device = dev;
   pl->sm_count = prop.multiProcessorCount;
   const tx_dot_problem &pr = pl->problem;
@@ -560,6 +572,103 @@ int tx_dot_plan_check(tx_dot_plan *pl, void *stream_v) {
   return TXD_OK;
 }
 
+}  // extern "C"
+
+namespace {
+
+constexpr int kMaxHostPanels = 8;
+
+// How many column panels the host-buffer path cuts B and C into. The copies dominate that path (PCIe), so they
+// are overlapped: panel j+1 travels to the device while panel j is multiplied and panel j-1 travels back.
+int host_panels(const tx_dot_problem &pr) {
+  const long long es = txd::elem_bytes(pr.ab_dtype), os = txd::elem_bytes(pr.out_dtype);
+  const long long bytes = (static_cast<long long>(pr.m) * pr.k + static_cast<long long>(pr.k) * pr.n) * es +
+                          static_cast<long long>(pr.m) * pr.n * os;
+  if (pr.k == 0 || bytes < (32LL << 20) || pr.n < 2 * 512) return 1;
+  int panels = pr.n / 512;  // at least two tile columns per panel
+  if (panels > kMaxHostPanels) panels = kMaxHostPanels;
+  return panels < 2 ? 1 : panels;
+}
+
+int run_host_pipelined(tx_dot_plan *pl, const void *a_host, const void *b_host, void *c_host,
+                       const float *row_scale_host, const float *col_scale_host) {
+  const tx_dot_problem &pr = pl->problem;
+  const size_t es = txd::elem_bytes(pr.ab_dtype), os = txd::elem_bytes(pr.out_dtype);
+  const int panels = host_panels(pr);
+  // panel boundaries on multiples of 256 columns (tile width; keeps every sub-pointer 16-byte aligned)
+  const int cols = ((pr.n / panels + 255) / 256) * 256;
+  if (!pl->compute_stream) {
+    TXD_CUDA(cudaStreamCreateWithFlags(&pl->compute_stream, cudaStreamNonBlocking));
+    TXD_CUDA(cudaStreamCreateWithFlags(&pl->d2h_stream, cudaStreamNonBlocking));
+  }
+  if (!pl->events_made) {
+    for (auto &e : pl->ev_in) TXD_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    for (auto &e : pl->ev_done) TXD_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    pl->events_made = true;
+  }
+  cudaStream_t in = pl->host_stream, run = pl->compute_stream, out = pl->d2h_stream;
+  // A and the scales first, then B panel by panel
+  TXD_CUDA(cudaMemcpyAsync(pl->dev_a, a_host, pl->a_bytes, cudaMemcpyHostToDevice, in));
+  if (pr.has_row_scale) {
+    if (!row_scale_host) return fail(TXD_ERR_INVALID, "row scale expected");
+    TXD_CUDA(cudaMemcpyAsync(pl->dev_rs, row_scale_host, sizeof(float) * pr.m, cudaMemcpyHostToDevice, in));
+  }
+  if (pr.has_col_scale) {
+    if (!col_scale_host) return fail(TXD_ERR_INVALID, "column scale expected");
+    TXD_CUDA(cudaMemcpyAsync(pl->dev_cs, col_scale_host, sizeof(float) * pr.n, cudaMemcpyHostToDevice, in));
+  }
+  int launched = 0;
+  for (int j = 0; j < panels; ++j) {
+    const int n0 = j * cols;
+    if (n0 >= pr.n) break;
+    const int n1 = n0 + cols < pr.n && j + 1 < panels ? n0 + cols : pr.n;
+    const int w = n1 - n0;
+    // B panel: columns [n0, n1) of a row-major [K, N] matrix, or rows [n0, n1) of its column-major storage
+    const size_t b_off = pr.b_layout == TXD_ROW_MAJOR ? static_cast<size_t>(n0) * es : static_cast<size_t>(n0) * pr.ldb * es;
+    const char *b_src = static_cast<const char *>(b_host) + b_off;
+    char *b_dst = static_cast<char *>(pl->dev_b) + b_off;
+    if (pr.b_layout == TXD_ROW_MAJOR)
+      TXD_CUDA(cudaMemcpy2DAsync(b_dst, pr.ldb * es, b_src, pr.ldb * es, static_cast<size_t>(w) * es, pr.k,
+                                 cudaMemcpyHostToDevice, in));
+    else
+      TXD_CUDA(cudaMemcpyAsync(b_dst, b_src, static_cast<size_t>(w) * pr.ldb * es, cudaMemcpyHostToDevice, in));
+    TXD_CUDA(cudaEventRecord(pl->ev_in[j], in));
+    // the panel's own plan (same leading dimensions: it works in place inside the full matrices)
+    const int which = (w == cols) ? 0 : 1;
+    if (!pl->panel_plan[which] || pl->panel_cols[which] != w) {
+      if (pl->panel_plan[which]) tx_dot_plan_destroy(pl->panel_plan[which]);
+      pl->panel_plan[which] = nullptr;
+      tx_dot_problem sub = pr;
+      sub.n = w;
+      int rc = tx_dot_plan_create(&sub, pl->has_user_cfg ? &pl->user_cfg : nullptr, &pl->panel_plan[which]);
+      if (rc) return rc;
+      pl->panel_cols[which] = w;
+    }
+    TXD_CUDA(cudaStreamWaitEvent(run, pl->ev_in[j], 0));
+    int rc = tx_dot_run(pl->panel_plan[which], pl->dev_a, b_dst, static_cast<char *>(pl->dev_c) + static_cast<size_t>(n0) * os,
+                        pl->dev_rs, pl->dev_cs ? pl->dev_cs + n0 : nullptr, run);
+    if (rc) return rc;
+    TXD_CUDA(cudaEventRecord(pl->ev_done[j], run));
+    TXD_CUDA(cudaStreamWaitEvent(out, pl->ev_done[j], 0));
+    TXD_CUDA(cudaMemcpy2DAsync(static_cast<char *>(c_host) + static_cast<size_t>(n0) * os, pr.ldc * os,
+                               static_cast<char *>(pl->dev_c) + static_cast<size_t>(n0) * os, pr.ldc * os,
+                               static_cast<size_t>(w) * os, pr.m, cudaMemcpyDeviceToHost, out));
+    ++launched;
+  }
+  TXD_CUDA(cudaStreamSynchronize(out));
+  for (int which = 0; which < 2; ++which)
+    if (pl->panel_plan[which]) {
+      int rc = tx_dot_plan_check(pl->panel_plan[which], run);
+      if (rc) return rc;
+    }
+  (void)launched;
+  return TXD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
 int tx_dot_run_host(tx_dot_plan *pl, const void *a_host, const void *b_host, void *c_host,
                     const float *row_scale_host, const float *col_scale_host) {
   if (!pl) return fail(TXD_ERR_INVALID, "null plan");
@@ -581,6 +690,7 @@ int tx_dot_run_host(tx_dot_plan *pl, const void *a_host, const void *b_host, voi
     if (pr.has_col_scale) TXD_CUDA(cudaMalloc(&pl->dev_cs, sizeof(float) * pr.n));
   }
   cudaStream_t s = pl->host_stream;
+  if (host_panels(pr) > 1) return run_host_pipelined(pl, a_host, b_host, c_host, row_scale_host, col_scale_host);
   if (pr.k > 0) {
     TXD_CUDA(cudaMemcpyAsync(pl->dev_a, a_host, pl->a_bytes, cudaMemcpyHostToDevice, s));
     TXD_CUDA(cudaMemcpyAsync(pl->dev_b, b_host, pl->b_bytes, cudaMemcpyHostToDevice, s));
@@ -609,6 +719,13 @@ int tx_dot_plan_destroy(tx_dot_plan *pl) {
   if (pl->dev_rs) cudaFree(pl->dev_rs);
   if (pl->dev_cs) cudaFree(pl->dev_cs);
   if (pl->host_stream) cudaStreamDestroy(pl->host_stream);
+  if (pl->compute_stream) cudaStreamDestroy(pl->compute_stream);
+  if (pl->d2h_stream) cudaStreamDestroy(pl->d2h_stream);
+  if (pl->events_made) {
+    for (auto &e : pl->ev_in) cudaEventDestroy(e);
+    for (auto &e : pl->ev_done) cudaEventDestroy(e);
+  }
+  for (tx_dot_plan *sub : pl->panel_plan) tx_dot_plan_destroy(sub);
   delete pl;
   return TXD_OK;
 }
