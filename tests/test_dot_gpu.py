@@ -191,31 +191,34 @@ def test_run_host_matches_device_path(B):
     plan.close()
 
 
-@pytest.mark.parametrize("n,b_col_major", [(4096, False), (3000, False), (4096, True)])
-def test_run_host_pipelined_panels(B, n, b_col_major):
-    """Above 32 MB the host-buffer entry point cuts B and C into column panels and overlaps copy-in, kernel and
-    copy-out on three streams. Same schedule forced on both paths: the panels must reproduce the one-launch result
-    bit for bit (every output element sums the same K blocks in the same order)."""
-    m, k = 2048, 2048
+@pytest.mark.parametrize("m,n,a_col_major,b_col_major", [(2048, 4096, False, False), (3000, 4096, False, True),
+                                                         (2048, 4096, True, False), (2048, 3000, True, False),
+                                                         (2048, 4096, True, True)])
+def test_run_host_pipelined_panels(B, m, n, a_col_major, b_col_major):
+    """Above 32 MB the host-buffer entry point cuts one operand and C into panels (rows of A and C when A is
+    row-major, else columns of B and C) and overlaps copy-in, kernel and copy-out on three streams. Same schedule forced on both paths: the panels must reproduce the one-launch
+    result bit for bit (every output element sums the same K blocks in the same order)."""
+    k = 4096            # every case moves more than 32 MB
     g = torch.Generator().manual_seed(77)
     a = torch.randn(m, k, generator=g).to(bf16)
     b = (torch.randn(k, n, generator=g) * 0.05).to(bf16)
     rs = torch.rand(m, generator=g) + 0.5
     cs = torch.rand(n, generator=g) + 0.5
+    a_store = a.t().contiguous() if a_col_major else a          # [k, m] storage when column-major
     b_store = b.t().contiguous() if b_col_major else b          # [n, k] storage when column-major
-    layout = B.TXD_COL_MAJOR if b_col_major else B.TXD_ROW_MAJOR
     cfg = B.make_config(schedule=B.TXD_SCHED_DATA_PARALLEL)
-    pr = B.make_problem(m, n, k, bf16, bf16, row_scale=True, col_scale=True, b_layout=layout,
-                        ldb=k if b_col_major else n)
+    pr = B.make_problem(m, n, k, bf16, bf16, row_scale=True, col_scale=True,
+                        a_layout=B.TXD_COL_MAJOR if a_col_major else B.TXD_ROW_MAJOR,
+                        b_layout=B.TXD_COL_MAJOR if b_col_major else B.TXD_ROW_MAJOR)
     plan = B.DotPlan(pr, cfg)
     dev = torch.device("cuda:0")
     want = torch.empty(m, n, dtype=bf16, device=dev)
-    plan.run(a.to(dev), b_store.to(dev), want, rs.to(dev), cs.to(dev))
+    plan.run(a_store.to(dev), b_store.to(dev), want, rs.to(dev), cs.to(dev))
     plan.check()
     out = torch.empty(m, n, dtype=bf16).pin_memory()
     for _ in range(2):
         out.zero_()
-        plan.run_host(a.pin_memory(), b_store.pin_memory(), out, rs, cs)
+        plan.run_host(a_store.pin_memory(), b_store.pin_memory(), out, rs, cs)
         assert torch.equal(bits(out), bits(want.cpu()))
     ref = (a.float() @ b.float()) * rs[:, None] * cs[None, :]
     assert bool(((out.float() - ref).abs() <= 1e-2 + 1e-2 * ref.abs()).all())

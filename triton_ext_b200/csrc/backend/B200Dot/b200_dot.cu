@@ -578,14 +578,19 @@ namespace {
 
 constexpr int kMaxHostPanels = 8;
 
-// How many column panels the host-buffer path cuts B and C into. The copies dominate that path (PCIe), so they
-// are overlapped: panel j+1 travels to the device while panel j is multiplied and panel j-1 travels back.
+// The host-buffer path is dominated by its copies (PCIe), so above 32 MB they are overlapped with the kernels:
+// one operand goes to the device whole, the other one and C are cut into panels; panel j+1 travels to the device
+// while panel j is multiplied and panel j-1 travels back. Panels are rows of A and C when A is row-major (both
+// panels are then contiguous in host memory, which the copy engines move fastest), else columns of B and C.
+bool host_panels_by_rows(const tx_dot_problem &pr) { return pr.a_layout == TXD_ROW_MAJOR; }
+
 int host_panels(const tx_dot_problem &pr) {
   const long long es = txd::elem_bytes(pr.ab_dtype), os = txd::elem_bytes(pr.out_dtype);
   const long long bytes = (static_cast<long long>(pr.m) * pr.k + static_cast<long long>(pr.k) * pr.n) * es +
                           static_cast<long long>(pr.m) * pr.n * os;
-  if (pr.k == 0 || bytes < (32LL << 20) || pr.n < 2 * 512) return 1;
-  int panels = pr.n / 512;  // at least two tile columns per panel
+  const int extent = host_panels_by_rows(pr) ? pr.m : pr.n;
+  if (pr.k == 0 || bytes < (32LL << 20) || extent < 2 * 512) return 1;
+  int panels = extent / 512;  // at least two tile rows / columns per panel
   if (panels > kMaxHostPanels) panels = kMaxHostPanels;
   return panels < 2 ? 1 : panels;
 }
@@ -595,8 +600,10 @@ int run_host_pipelined(tx_dot_plan *pl, const void *a_host, const void *b_host, 
   const tx_dot_problem &pr = pl->problem;
   const size_t es = txd::elem_bytes(pr.ab_dtype), os = txd::elem_bytes(pr.out_dtype);
   const int panels = host_panels(pr);
-  // panel boundaries on multiples of 256 columns (tile width; keeps every sub-pointer 16-byte aligned)
-  const int cols = ((pr.n / panels + 255) / 256) * 256;
+  const bool by_rows = host_panels_by_rows(pr);
+  const int extent = by_rows ? pr.m : pr.n;
+  // panel boundaries on multiples of 256 (tile size; keeps every sub-pointer 16-byte aligned)
+  const int step = ((extent / panels + 255) / 256) * 256;
   if (!pl->compute_stream) {
     TXD_CUDA(cudaStreamCreateWithFlags(&pl->compute_stream, cudaStreamNonBlocking));
     TXD_CUDA(cudaStreamCreateWithFlags(&pl->d2h_stream, cudaStreamNonBlocking));
@@ -607,8 +614,9 @@ int run_host_pipelined(tx_dot_plan *pl, const void *a_host, const void *b_host, 
     pl->events_made = true;
   }
   cudaStream_t in = pl->host_stream, run = pl->compute_stream, out = pl->d2h_stream;
-  // A and the scales first, then B panel by panel
-  TXD_CUDA(cudaMemcpyAsync(pl->dev_a, a_host, pl->a_bytes, cudaMemcpyHostToDevice, in));
+  // the whole operand and the scales first
+  if (by_rows) TXD_CUDA(cudaMemcpyAsync(pl->dev_b, b_host, pl->b_bytes, cudaMemcpyHostToDevice, in));
+  else TXD_CUDA(cudaMemcpyAsync(pl->dev_a, a_host, pl->a_bytes, cudaMemcpyHostToDevice, in));
   if (pr.has_row_scale) {
     if (!row_scale_host) return fail(TXD_ERR_INVALID, "row scale expected");
     TXD_CUDA(cudaMemcpyAsync(pl->dev_rs, row_scale_host, sizeof(float) * pr.m, cudaMemcpyHostToDevice, in));
@@ -617,43 +625,59 @@ int run_host_pipelined(tx_dot_plan *pl, const void *a_host, const void *b_host, 
     if (!col_scale_host) return fail(TXD_ERR_INVALID, "column scale expected");
     TXD_CUDA(cudaMemcpyAsync(pl->dev_cs, col_scale_host, sizeof(float) * pr.n, cudaMemcpyHostToDevice, in));
   }
-  int launched = 0;
   for (int j = 0; j < panels; ++j) {
-    const int n0 = j * cols;
-    if (n0 >= pr.n) break;
-    const int n1 = n0 + cols < pr.n && j + 1 < panels ? n0 + cols : pr.n;
-    const int w = n1 - n0;
-    // B panel: columns [n0, n1) of a row-major [K, N] matrix, or rows [n0, n1) of its column-major storage
-    const size_t b_off = pr.b_layout == TXD_ROW_MAJOR ? static_cast<size_t>(n0) * es : static_cast<size_t>(n0) * pr.ldb * es;
-    const char *b_src = static_cast<const char *>(b_host) + b_off;
-    char *b_dst = static_cast<char *>(pl->dev_b) + b_off;
-    if (pr.b_layout == TXD_ROW_MAJOR)
-      TXD_CUDA(cudaMemcpy2DAsync(b_dst, pr.ldb * es, b_src, pr.ldb * es, static_cast<size_t>(w) * es, pr.k,
-                                 cudaMemcpyHostToDevice, in));
-    else
-      TXD_CUDA(cudaMemcpyAsync(b_dst, b_src, static_cast<size_t>(w) * pr.ldb * es, cudaMemcpyHostToDevice, in));
+    const int i0 = j * step;
+    if (i0 >= extent) break;
+    const int i1 = (i0 + step < extent && j + 1 < panels) ? i0 + step : extent;
+    const int w = i1 - i0;
+    const char *a_dev = static_cast<const char *>(pl->dev_a);
+    const char *b_dev = static_cast<const char *>(pl->dev_b);
+    char *c_dev = static_cast<char *>(pl->dev_c);
+    if (by_rows) {
+      // rows [i0, i1) of A (row-major: contiguous) and of C
+      const size_t a_off = static_cast<size_t>(i0) * pr.lda * es;
+      TXD_CUDA(cudaMemcpyAsync(static_cast<char *>(pl->dev_a) + a_off, static_cast<const char *>(a_host) + a_off,
+                               static_cast<size_t>(w) * pr.lda * es, cudaMemcpyHostToDevice, in));
+      a_dev += a_off;
+      c_dev += static_cast<size_t>(i0) * pr.ldc * os;
+    } else {
+      // columns [i0, i1) of B: a strided block of a row-major [K, N] matrix, or rows of its column-major storage
+      const size_t b_off = pr.b_layout == TXD_ROW_MAJOR ? static_cast<size_t>(i0) * es : static_cast<size_t>(i0) * pr.ldb * es;
+      const char *b_src = static_cast<const char *>(b_host) + b_off;
+      char *b_dst = static_cast<char *>(pl->dev_b) + b_off;
+      if (pr.b_layout == TXD_ROW_MAJOR)
+        TXD_CUDA(cudaMemcpy2DAsync(b_dst, pr.ldb * es, b_src, pr.ldb * es, static_cast<size_t>(w) * es, pr.k,
+                                   cudaMemcpyHostToDevice, in));
+      else
+        TXD_CUDA(cudaMemcpyAsync(b_dst, b_src, static_cast<size_t>(w) * pr.ldb * es, cudaMemcpyHostToDevice, in));
+      b_dev += b_off;
+      c_dev += static_cast<size_t>(i0) * os;
+    }
     TXD_CUDA(cudaEventRecord(pl->ev_in[j], in));
     // the panel's own plan (same leading dimensions: it works in place inside the full matrices)
-    const int which = (w == cols) ? 0 : 1;
+    const int which = (w == step) ? 0 : 1;
     if (!pl->panel_plan[which] || pl->panel_cols[which] != w) {
       if (pl->panel_plan[which]) tx_dot_plan_destroy(pl->panel_plan[which]);
       pl->panel_plan[which] = nullptr;
       tx_dot_problem sub = pr;
-      sub.n = w;
+      if (by_rows) sub.m = w; else sub.n = w;
       int rc = tx_dot_plan_create(&sub, pl->has_user_cfg ? &pl->user_cfg : nullptr, &pl->panel_plan[which]);
       if (rc) return rc;
       pl->panel_cols[which] = w;
     }
     TXD_CUDA(cudaStreamWaitEvent(run, pl->ev_in[j], 0));
-    int rc = tx_dot_run(pl->panel_plan[which], pl->dev_a, b_dst, static_cast<char *>(pl->dev_c) + static_cast<size_t>(n0) * os,
-                        pl->dev_rs, pl->dev_cs ? pl->dev_cs + n0 : nullptr, run);
+    const float *rs = pl->dev_rs ? pl->dev_rs + (by_rows ? i0 : 0) : nullptr;
+    const float *cs = pl->dev_cs ? pl->dev_cs + (by_rows ? 0 : i0) : nullptr;
+    int rc = tx_dot_run(pl->panel_plan[which], a_dev, b_dev, c_dev, rs, cs, run);
     if (rc) return rc;
     TXD_CUDA(cudaEventRecord(pl->ev_done[j], run));
     TXD_CUDA(cudaStreamWaitEvent(out, pl->ev_done[j], 0));
-    TXD_CUDA(cudaMemcpy2DAsync(static_cast<char *>(c_host) + static_cast<size_t>(n0) * os, pr.ldc * os,
-                               static_cast<char *>(pl->dev_c) + static_cast<size_t>(n0) * os, pr.ldc * os,
-                               static_cast<size_t>(w) * os, pr.m, cudaMemcpyDeviceToHost, out));
-    ++launched;
+    char *c_dst = static_cast<char *>(c_host) + (c_dev - static_cast<char *>(pl->dev_c));
+    if (by_rows)
+      TXD_CUDA(cudaMemcpyAsync(c_dst, c_dev, static_cast<size_t>(w) * pr.ldc * os, cudaMemcpyDeviceToHost, out));
+    else
+      TXD_CUDA(cudaMemcpy2DAsync(c_dst, pr.ldc * os, c_dev, pr.ldc * os, static_cast<size_t>(w) * os, pr.m,
+                                 cudaMemcpyDeviceToHost, out));
   }
   TXD_CUDA(cudaStreamSynchronize(out));
   for (int which = 0; which < 2; ++which)
@@ -661,7 +685,6 @@ int run_host_pipelined(tx_dot_plan *pl, const void *a_host, const void *b_host, 
       int rc = tx_dot_plan_check(pl->panel_plan[which], run);
       if (rc) return rc;
     }
-  (void)launched;
   return TXD_OK;
 }
 
