@@ -136,6 +136,20 @@ def test_host_buffers(A):
     assert float((m - AO.logsumexp2(q, k, True, 0.5)).abs().max()) <= 2e-3
 
 
+def test_host_buffers_in_groups(A):
+    """Above 32 MB the host entry point moves (batch, head) pairs in groups and overlaps copies with kernels;
+    the result is the device path's, bit for bit."""
+    q, k, v = draw(2, 12, 2048, 128, f16, seed=8)          # 12.6 MB per tensor, 50 MB with the output
+    want, want_m = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), True, 0.5, return_m=True, check=True)
+    m = torch.empty((2, 12, 2048), dtype=torch.float32).pin_memory()
+    out = torch.empty_like(q).pin_memory()
+    for _ in range(2):
+        out.zero_()
+        A.attention_forward_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), True, 0.5, out=out, m=m)
+        assert torch.equal(out, want.cpu())
+        assert torch.equal(m, want_m.cpu())
+
+
 def test_rejected_arguments(A):
     from triton_ext_b200 import backend as B
     q = torch.zeros((1, 1, 128, 32), dtype=f16, device="cuda")

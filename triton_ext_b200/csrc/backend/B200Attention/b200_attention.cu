@@ -86,7 +86,9 @@ struct DeviceState {
   uint32_t *status = nullptr;
   bool attr_set = false;
   // host-buffer path
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr, run_stream = nullptr, out_stream = nullptr;
+  cudaEvent_t ev_in[8] = {}, ev_done[8] = {};
+  bool events_made = false;
   void *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr;
   float *m = nullptr;
   size_t tensor_bytes = 0, m_bytes = 0;
@@ -262,14 +264,58 @@ int tx_attn_fwd_host(const tx_attn_problem *pr, const void *q, const void *k, co
     }
   }
   cudaStream_t s = st->stream;
-  TXA_CUDA(cudaMemcpyAsync(st->q, q, bytes, cudaMemcpyHostToDevice, s));
-  TXA_CUDA(cudaMemcpyAsync(st->k, k, bytes, cudaMemcpyHostToDevice, s));
-  TXA_CUDA(cudaMemcpyAsync(st->v, v, bytes, cudaMemcpyHostToDevice, s));
-  rc = tx_attn_fwd(pr, st->q, st->k, st->v, st->o, st->m, s);
-  if (rc) return rc;
-  TXA_CUDA(cudaMemcpyAsync(out, st->o, bytes, cudaMemcpyDeviceToHost, s));
-  if (m) TXA_CUDA(cudaMemcpyAsync(m, st->m, m_bytes, cudaMemcpyDeviceToHost, s));
-  return tx_attn_check(s);
+  // (batch, head) pairs are independent and contiguous in memory: above 32 MB they travel in up to 8 groups, and
+  // group g+1 is copied in while group g runs and group g-1 is copied out (three streams).
+  const size_t groups = (4 * bytes >= (32u << 20) && heads_total >= 2) ? (heads_total < 8 ? heads_total : 8) : 1;
+  if (groups == 1) {
+    TXA_CUDA(cudaMemcpyAsync(st->q, q, bytes, cudaMemcpyHostToDevice, s));
+    TXA_CUDA(cudaMemcpyAsync(st->k, k, bytes, cudaMemcpyHostToDevice, s));
+    TXA_CUDA(cudaMemcpyAsync(st->v, v, bytes, cudaMemcpyHostToDevice, s));
+    rc = tx_attn_fwd(pr, st->q, st->k, st->v, st->o, st->m, s);
+    if (rc) return rc;
+    TXA_CUDA(cudaMemcpyAsync(out, st->o, bytes, cudaMemcpyDeviceToHost, s));
+    if (m) TXA_CUDA(cudaMemcpyAsync(m, st->m, m_bytes, cudaMemcpyDeviceToHost, s));
+    return tx_attn_check(s);
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    if (!st->run_stream) {
+      TXA_CUDA(cudaStreamCreateWithFlags(&st->run_stream, cudaStreamNonBlocking));
+      TXA_CUDA(cudaStreamCreateWithFlags(&st->out_stream, cudaStreamNonBlocking));
+    }
+    if (!st->events_made) {
+      for (auto &e : st->ev_in) TXA_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      for (auto &e : st->ev_done) TXA_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      st->events_made = true;
+    }
+  }
+  const size_t head_bytes = static_cast<size_t>(pr->n_ctx) * pr->head_dim * 2;
+  const size_t head_m_bytes = static_cast<size_t>(pr->n_ctx) * sizeof(float);
+  for (size_t g = 0; g < groups; ++g) {
+    const size_t h0 = heads_total * g / groups, h1 = heads_total * (g + 1) / groups;
+    const size_t off = h0 * head_bytes, len = (h1 - h0) * head_bytes;
+    auto at = [&](const void *base) { return static_cast<const char *>(base) + off; };
+    auto dev_at = [&](void *base) { return static_cast<char *>(base) + off; };
+    TXA_CUDA(cudaMemcpyAsync(dev_at(st->q), at(q), len, cudaMemcpyHostToDevice, s));
+    TXA_CUDA(cudaMemcpyAsync(dev_at(st->k), at(k), len, cudaMemcpyHostToDevice, s));
+    TXA_CUDA(cudaMemcpyAsync(dev_at(st->v), at(v), len, cudaMemcpyHostToDevice, s));
+    TXA_CUDA(cudaEventRecord(st->ev_in[g], s));
+    TXA_CUDA(cudaStreamWaitEvent(st->run_stream, st->ev_in[g], 0));
+    tx_attn_problem sub = *pr;
+    sub.batch = 1;
+    sub.heads = static_cast<int32_t>(h1 - h0);
+    float *m_dev = st->m + h0 * pr->n_ctx;
+    rc = tx_attn_fwd(&sub, dev_at(st->q), dev_at(st->k), dev_at(st->v), dev_at(st->o), m_dev, st->run_stream);
+    if (rc) return rc;
+    TXA_CUDA(cudaEventRecord(st->ev_done[g], st->run_stream));
+    TXA_CUDA(cudaStreamWaitEvent(st->out_stream, st->ev_done[g], 0));
+    TXA_CUDA(cudaMemcpyAsync(static_cast<char *>(out) + off, dev_at(st->o), len, cudaMemcpyDeviceToHost, st->out_stream));
+    if (m)
+      TXA_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(m) + h0 * head_m_bytes, m_dev, (h1 - h0) * head_m_bytes,
+                               cudaMemcpyDeviceToHost, st->out_stream));
+  }
+  TXA_CUDA(cudaStreamSynchronize(st->out_stream));
+  return tx_attn_check(st->run_stream);
 }
 
 }  // extern "C"
