@@ -92,3 +92,19 @@ def logsumexp2(q: torch.Tensor, k: torch.Tensor, causal: bool, sm_scale: float) 
         tril = torch.tril(torch.ones((n, n), dtype=torch.bool))
         s = s.masked_fill(~tril, float("-inf"))
     return (torch.logsumexp(s * 0.6931471805599453, dim=-1) * 1.4426950408889634).float()
+
+
+def attention_grads_eager(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d_o: torch.Tensor, causal: bool,
+                          sm_scale: float):
+    """(dq, dk, dv) by autograd through the eager formula in fp32, as the reference's test obtains its reference
+    gradients (`ref_out.backward(dout)`, 06-fused-attention.py:704-707), without the rounding of P."""
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    n = q.shape[2]
+    p = torch.matmul(qf, kf.transpose(2, 3)) * sm_scale
+    if causal:
+        tril = torch.tril(torch.ones((n, n), dtype=torch.bool))
+        p = p.masked_fill(~tril, float("-inf"))
+    out = torch.matmul(torch.softmax(p, dim=-1), vf)
+    out.backward(d_o.float())
+    return qf.grad, kf.grad, vf.grad
+

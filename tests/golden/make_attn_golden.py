@@ -30,6 +30,11 @@ CASES = {
     "full_d128": (2, 1, 128, 128, False, 64, 64),
 }
 SM_SCALE = 0.5
+# name: (Z, H, N_CTX, HEAD_DIM, causal); the reference's backward asserts N_CTX % 128 == 0 and is causal-only
+BWD_CASES = {
+    "bwd_causal_d64": (1, 2, 256, 64, True),
+    "bwd_causal_d128": (1, 1, 256, 128, True),
+}
 
 
 def load_reference(root: str):
@@ -67,6 +72,19 @@ def main():
             out[f"{name}.{key}"] = t.numpy().view(np.uint16)  # fp16 bit patterns
         out[f"{name}.m"] = m.numpy()
         out[f"{name}.meta"] = np.array([z, h, n, d, int(causal), bm, bn], dtype=np.int32)
+        print(name, "done", flush=True)
+    # forward + backward through the reference's autograd function (`attention = _attention.apply`, :690). With a
+    # single autotuning configuration the autotuner does not try to time kernels on a device.
+    mod._attn_fwd.configs = mod._attn_fwd.configs[:1]
+    for name, (z, h, n, d, causal) in BWD_CASES.items():
+        torch.manual_seed(20)
+        q, k, v = (torch.empty((z, h, n, d), dtype=torch.float16).normal_(mean=0.0, std=0.5).requires_grad_() for _ in range(3))
+        d_o = torch.randn_like(q)
+        o = mod.attention(q, k, v, causal, SM_SCALE)
+        o.backward(d_o)
+        for key, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", d_o), ("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
+            out[f"{name}.{key}"] = t.detach().numpy().view(np.uint16)
+        out[f"{name}.meta"] = np.array([z, h, n, d, int(causal)], dtype=np.int32)
         print(name, "done", flush=True)
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "attn_golden.npz")
     np.savez_compressed(dst, sm_scale=np.float32(SM_SCALE), **out)

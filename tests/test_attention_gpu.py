@@ -32,7 +32,7 @@ def draw(z, h, n, d, dtype, seed=20, std=0.5):
 
 def golden_names():
     npz = np.load(GOLDEN)
-    return sorted({key.split(".")[0] for key in npz.files if "." in key})
+    return sorted({key.split(".")[0] for key in npz.files if "." in key and not key.startswith("bwd_")})
 
 
 # ---- 1. the reference kernel's own outputs -----------------------------------------------------------------
@@ -177,3 +177,48 @@ def test_bounded_wait_reports_timeout(A, monkeypatch):
     monkeypatch.delenv("TXD_WAIT_LIMIT_MS")
     out = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), True, 0.5, check=True)   # same context, healthy launch
     assert float((out.cpu().float() - AO.attention_eager(q, k, v, True, 0.5)).abs().max()) <= 1e-2
+
+
+# ---- 5. backward -------------------------------------------------------------------------------------------------------
+def bwd_golden_names():
+    npz = np.load(GOLDEN)
+    return sorted({key.split(".")[0] for key in npz.files if key.startswith("bwd_")})
+
+
+@pytest.mark.parametrize("name", bwd_golden_names())
+def test_backward_matches_reference_kernel_outputs(A, name):
+    npz = np.load(GOLDEN)
+    z, h, n, d, causal = (int(x) for x in npz[f"{name}.meta"])
+    t = {key: torch.from_numpy(npz[f"{name}.{key}"].view(np.float16).copy()).cuda()
+         for key in ("q", "k", "v", "do", "dq", "dk", "dv")}
+    sm_scale = float(npz["sm_scale"])
+    o, m = A.attention_forward(t["q"], t["k"], t["v"], bool(causal), sm_scale, return_m=True, check=True)
+    dq, dk, dv = A.attention_backward(t["q"], t["k"], t["v"], o, m, t["do"], bool(causal), sm_scale, check=True)
+    for got, want in ((dq, t["dq"]), (dk, t["dk"]), (dv, t["dv"])):
+        err = float((got.float() - want.float()).abs().max())
+        assert err <= 1e-2, err         # the reference's bound (06-fused-attention.py:715-721)
+        assert err <= 4e-3, err         # fp16 roundings of P, dS and of the results
+
+
+@pytest.mark.parametrize("dtype", [f16, bf16])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("z,h,n,d", [(1, 2, 1024, 64), (2, 2, 384, 128), (1, 2, 200, 64), (1, 1, 128, 128)])
+def test_autograd_function_against_oracle(A, z, h, n, d, causal, dtype):
+    """`attention(q, k, v, causal, sm_scale)` as the reference exposes it (`_attention.apply`): forward and backward
+    through autograd, against fp32 autograd of the eager formula, atol 1e-2 as in the reference's test_op."""
+    from oracle import attn_oracle as AO
+    q, k, v = draw(z, h, n, d, dtype)
+    g = torch.Generator().manual_seed(9)
+    d_o = torch.randn((z, h, n, d), generator=g).to(dtype)
+    qc, kc, vc = (x.cuda().requires_grad_() for x in (q, k, v))
+    out = A.attention(qc, kc, vc, causal, 0.5)
+    out.backward(d_o.cuda())
+    A.check()
+    want_o = AO.attention_eager(q, k, v, causal, 0.5)
+    assert float((out.detach().cpu().float() - want_o).abs().max()) <= ATOL[dtype]
+    dq, dk, dv = AO.attention_grads_eager(q, k, v, d_o, causal, 0.5)
+    tol = 1e-2 if dtype == f16 else 4e-2     # bf16: 8-bit P, dS and results
+    for got, want in ((qc.grad, dq), (kc.grad, dk), (vc.grad, dv)):
+        err = float((got.cpu().float() - want).abs().max())
+        assert err <= tol, err
+

@@ -24,7 +24,7 @@ def load_case(npz, name):
 
 def case_names():
     npz = np.load(GOLDEN)
-    return sorted({key.split(".")[0] for key in npz.files if "." in key})
+    return sorted({key.split(".")[0] for key in npz.files if "." in key and not key.startswith("bwd_")})
 
 
 @pytest.mark.parametrize("name", case_names())
@@ -50,3 +50,21 @@ def test_kernel_blocking_and_skipped_blocks_stay_within_the_reference_tolerance(
     assert float((eager - c["o"].float()).abs().max()) <= 1e-2      # the reference's own test bound
     lse = AO.logsumexp2(c["q"], c["k"], c["causal"], sm_scale)
     assert float((lse - c["m"]).abs().max()) <= 1e-3
+
+
+def bwd_case_names():
+    npz = np.load(GOLDEN)
+    return sorted({key.split(".")[0] for key in npz.files if key.startswith("bwd_")})
+
+
+@pytest.mark.parametrize("name", bwd_case_names())
+def test_eager_gradients_match_the_reference_backward(name):
+    """dq, dk, dv of the reference's own backward kernels (run by the interpreter) against autograd through the eager
+    formula: the bound of the reference's test (atol 1e-2, 06-fused-attention.py:715-721)."""
+    npz = np.load(GOLDEN)
+    z, h, n, d, causal = (int(x) for x in npz[f"{name}.meta"])
+    t = {key: torch.from_numpy(npz[f"{name}.{key}"].view(np.float16).copy()) for key in ("q", "k", "v", "do", "dq", "dk", "dv")}
+    dq, dk, dv = AO.attention_grads_eager(t["q"], t["k"], t["v"], t["do"], bool(causal), float(npz["sm_scale"]))
+    for got, want in ((dq, t["dq"]), (dk, t["dk"]), (dv, t["dv"])):
+        assert float((got - want.float()).abs().max()) <= 1e-2
+

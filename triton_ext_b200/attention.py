@@ -41,6 +41,8 @@ def _lib() -> ctypes.CDLL:
         lib.tx_attn_check.restype = ctypes.c_int
         lib.tx_attn_fwd_host.argtypes = [pp, vp, vp, vp, vp, vp]
         lib.tx_attn_fwd_host.restype = ctypes.c_int
+        lib.tx_attn_bwd.argtypes = [pp] + [vp] * 10
+        lib.tx_attn_bwd.restype = ctypes.c_int
         lib.tx_attn_flops.argtypes = [pp]
         lib.tx_attn_flops.restype = ctypes.c_double
         lib.tx_attn_kernel_launches.restype = ctypes.c_uint64
@@ -135,3 +137,52 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ca
     if rc:
         _raise(lib, rc)
     return out
+
+
+def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, m: torch.Tensor,
+                       d_o: torch.Tensor, causal: bool, sm_scale: float, *, check: bool = False):
+    """(dq, dk, dv) of attention_forward, from its output `o`, its row vector `m` and the output gradient `d_o`
+    (reference `_attention.backward`, 06-fused-attention.py:645-688)."""
+    lib = _lib()
+    tensors = [t.contiguous() for t in (q, k, v, o, d_o)]
+    if not all(t.is_cuda for t in tensors) or not m.is_cuda:
+        raise B.DotError(B.TXD_ERR_NO_DEVICE, "attention_backward takes CUDA tensors")
+    q, k, v, o, d_o = tensors
+    if not (q.shape == k.shape == v.shape == o.shape == d_o.shape) or not (q.dtype == k.dtype == v.dtype == o.dtype == d_o.dtype):
+        raise B.DotError(B.TXD_ERR_INVALID, "q, k, v, o, d_o must share shape and type")
+    z, h, n, d = q.shape
+    m = m.contiguous().float()
+    pr = make_problem(z, h, n, d, q.dtype, causal, sm_scale)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+    with torch.cuda.device(q.device):
+        rc = lib.tx_attn_bwd(ctypes.byref(pr), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(),
+                             m.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), stream)
+        if rc:
+            _raise(lib, rc)
+        if check:
+            rc = lib.tx_attn_check(stream)
+            if rc:
+                _raise(lib, rc)
+    return dq, dk, dv
+
+
+class _Attention(torch.autograd.Function):
+    """The reference's `_attention` autograd function (06-fused-attention.py:581-688) on this library's kernels."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale):
+        o, m = attention_forward(q, k, v, causal, sm_scale, return_m=True)
+        ctx.save_for_backward(q, k, v, o, m)
+        ctx.causal, ctx.sm_scale = causal, sm_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, m = ctx.saved_tensors
+        dq, dk, dv = attention_backward(q, k, v, o, m, d_o, ctx.causal, ctx.sm_scale)
+        return dq, dk, dv, None, None
+
+
+attention = _Attention.apply
+

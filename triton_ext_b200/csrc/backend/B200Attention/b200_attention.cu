@@ -92,6 +92,12 @@ struct DeviceState {
   void *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr;
   float *m = nullptr;
   size_t tensor_bytes = 0, m_bytes = 0;
+  // backward: per-head workspace (scores, probabilities, their gradients) and the GEMM plans of the last shape
+  void *bwd_ws = nullptr;
+  size_t bwd_ws_bytes = 0;
+  tx_dot_plan *bwd_plan[4] = {nullptr, nullptr, nullptr, nullptr};  // QK^T / dO V^T, P^T dO, dS K, dS^T Q
+  int bwd_n = 0, bwd_d = 0, bwd_dtype = -1;
+  float bwd_scale = 0.f;
 };
 std::mutex g_state_mutex;
 DeviceState g_state[64];
@@ -133,6 +139,94 @@ int validate(const tx_attn_problem *pr) {
   if (!(pr->sm_scale > 0.f)) return afail(TXD_ERR_INVALID, "sm_scale must be positive");
   if (static_cast<long long>(pr->batch) * pr->heads > 0x7fffffffLL / ((pr->n_ctx + 255) / 256))
     return afail(TXD_ERR_UNSUPPORTED, "too many (head, query tile) pairs for one grid");
+  return TXD_OK;
+}
+
+
+// ---- backward: the element-wise steps between the GEMMs (reference _attn_bwd_preprocess,
+// pass/LoopSplit/06-fused-attention.py:333-346, and the p / ds lines of _attn_bwd_dkdv :377-393 and _attn_bwd_dq :428-439) ------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// delta[row] = sum_d o[row, d] * do[row, d], one warp per row
+template <typename T>
+__global__ void attn_bwd_delta_kernel(const T *o, const T *d_o, float *delta, long long rows, int d) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float acc = 0.f;
+  for (int c = lane; c < d; c += 32) acc += to_f32(o[row * d + c]) * to_f32(d_o[row * d + c]);
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[row] = acc;
+}
+
+// p[r, c] = exp2(s[r, c] * qk_scale - m[r]) (m already holds the row's log2-sum), zero above the diagonal
+template <typename T>
+__global__ void attn_bwd_p_kernel(const float *s, const float *m, T *p, int n, long long ld, float qk_scale, int causal) {
+  const long long total = static_cast<long long>(n) * n;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / n), c = static_cast<int>(i - static_cast<long long>(r) * n);
+    float v = exp2f(fmaf(s[r * ld + c], qk_scale, -m[r]));
+    if (causal && c > r) v = 0.f;
+    p[r * ld + c] = from_f32<T>(v);
+  }
+}
+
+// ds[r, c] = p[r, c] * (dp[r, c] - delta[r]), written over p
+template <typename T>
+__global__ void attn_bwd_ds_kernel(T *p, const float *dp, const float *delta, int n, long long ld) {
+  const long long total = static_cast<long long>(n) * n;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / n), c = static_cast<int>(i - static_cast<long long>(r) * n);
+    const float v = to_f32(p[r * ld + c]) * (dp[r * ld + c] - delta[r]);
+    p[r * ld + c] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+int attn_bwd_typed(const tx_attn_problem *pr, DeviceState *st, const T *q, const T *k, const T *v, const T *o, const T *d_o,
+                   const float *m, T *dq, T *dk, T *dv, cudaStream_t stream) {
+  const int n = pr->n_ctx, d = pr->head_dim;
+  const long long ld = (n + 7) / 8 * 8;
+  const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
+  char *ws = static_cast<char *>(st->bwd_ws);
+  float *s_buf = reinterpret_cast<float *>(ws);
+  float *dp_buf = s_buf + static_cast<size_t>(n) * ld;
+  T *p_buf = reinterpret_cast<T *>(dp_buf + static_cast<size_t>(n) * ld);
+  float *delta = reinterpret_cast<float *>(p_buf + static_cast<size_t>(n) * ld);
+  const float qk_scale = pr->sm_scale * 1.44269504f;
+  const long long rows = heads_total * n;
+  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
+  TXA_CUDA(cudaGetLastError());
+  const unsigned ew_grid = 148 * 8;
+  for (long long h = 0; h < heads_total; ++h) {
+    const size_t off = static_cast<size_t>(h) * n * d;
+    int rc;
+    // S = Q K^T and dP = dO V^T (fp32)
+    if ((rc = tx_dot_run(st->bwd_plan[0], q + off, k + off, s_buf, nullptr, nullptr, stream))) return rc;
+    if ((rc = tx_dot_run(st->bwd_plan[0], d_o + off, v + off, dp_buf, nullptr, nullptr, stream))) return rc;
+    attn_bwd_p_kernel<T><<<ew_grid, 256, 0, stream>>>(s_buf, m + h * n, p_buf, n, ld, qk_scale, pr->causal);
+    // dV = P^T dO
+    if ((rc = tx_dot_run(st->bwd_plan[1], p_buf, d_o + off, dv + off, nullptr, nullptr, stream))) return rc;
+    attn_bwd_ds_kernel<T><<<ew_grid, 256, 0, stream>>>(p_buf, dp_buf, delta + h * n, n, ld);
+    // dQ = sm_scale dS K, dK = sm_scale dS^T Q
+    if ((rc = tx_dot_run(st->bwd_plan[2], p_buf, k + off, dq + off, nullptr, nullptr, stream))) return rc;
+    if ((rc = tx_dot_run(st->bwd_plan[3], p_buf, q + off, dk + off, nullptr, nullptr, stream))) return rc;
+  }
+  TXA_CUDA(cudaGetLastError());
+  g_attn_launches.fetch_add(static_cast<uint64_t>(1 + 2 * heads_total));
   return TXD_OK;
 }
 
@@ -229,6 +323,8 @@ int tx_attn_check(void *stream_v) {
     cudaMemset(st->status, 0, sizeof status);
     return afail(TXD_ERR_DEVICE_TIMEOUT, "a bounded wait inside the attention kernel ran out (role code %u)", status);
   }
+  for (tx_dot_plan *p : st->bwd_plan)
+    if (p && (rc = tx_dot_plan_check(p, stream_v))) return afail(rc, "backward GEMM: %s", tx_dot_last_error());
   return TXD_OK;
 }
 
@@ -316,6 +412,61 @@ int tx_attn_fwd_host(const tx_attn_problem *pr, const void *q, const void *k, co
   }
   TXA_CUDA(cudaStreamSynchronize(st->out_stream));
   return tx_attn_check(st->run_stream);
+}
+
+int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const void *v, const void *o, const void *d_o,
+                const float *m, void *dq, void *dk, void *dv, void *stream_v) {
+  int rc = validate(pr);
+  if (rc) return rc;
+  if (!q || !k || !v || !o || !d_o || !m || !dq || !dk || !dv) return afail(TXD_ERR_INVALID, "null tensor pointer");
+  DeviceState *st = nullptr;
+  rc = device_state(&st);
+  if (rc) return rc;
+  const int n = pr->n_ctx, d = pr->head_dim;
+  const long long ld = (n + 7) / 8 * 8;
+  {
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    const size_t need = static_cast<size_t>(n) * ld * (4 + 4 + 2) +
+                        static_cast<size_t>(pr->batch) * pr->heads * n * sizeof(float) + 256;
+    if (st->bwd_ws_bytes < need) {
+      if (st->bwd_ws) cudaFree(st->bwd_ws);
+      st->bwd_ws = nullptr;
+      st->bwd_ws_bytes = 0;
+      TXA_CUDA(cudaMalloc(&st->bwd_ws, need));
+      st->bwd_ws_bytes = need;
+    }
+    if (st->bwd_n != n || st->bwd_d != d || st->bwd_dtype != pr->dtype || st->bwd_scale != pr->sm_scale) {
+      for (tx_dot_plan *&p : st->bwd_plan) {
+        if (p) tx_dot_plan_destroy(p);
+        p = nullptr;
+      }
+      tx_dot_problem g = {};
+      // [n, n] = [n, d] x [d, n]: scores and dP, fp32; the second operand is a row-major [n, d] tensor read transposed
+      g.m = n; g.n = n; g.k = d; g.ab_dtype = pr->dtype; g.out_dtype = TXD_F32;
+      g.a_layout = TXD_ROW_MAJOR; g.b_layout = TXD_COL_MAJOR; g.lda = d; g.ldb = d; g.ldc = ld; g.alpha = 1.0f;
+      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[0]))) return afail(rc, "backward plan 0: %s", tx_dot_last_error());
+      // [n, d] = P^T [n, n] x dO [n, d]
+      g.m = n; g.n = d; g.k = n; g.out_dtype = pr->dtype;
+      g.a_layout = TXD_COL_MAJOR; g.b_layout = TXD_ROW_MAJOR; g.lda = ld; g.ldb = d; g.ldc = d; g.alpha = 1.0f;
+      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[1]))) return afail(rc, "backward plan 1: %s", tx_dot_last_error());
+      // dQ = sm_scale dS K
+      g.a_layout = TXD_ROW_MAJOR; g.alpha = pr->sm_scale;
+      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[2]))) return afail(rc, "backward plan 2: %s", tx_dot_last_error());
+      // dK = sm_scale dS^T Q
+      g.a_layout = TXD_COL_MAJOR;
+      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[3]))) return afail(rc, "backward plan 3: %s", tx_dot_last_error());
+      st->bwd_n = n; st->bwd_d = d; st->bwd_dtype = pr->dtype; st->bwd_scale = pr->sm_scale;
+    }
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (pr->dtype == TXD_BF16)
+    return attn_bwd_typed<__nv_bfloat16>(pr, st, static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
+                                         static_cast<const __nv_bfloat16 *>(v), static_cast<const __nv_bfloat16 *>(o),
+                                         static_cast<const __nv_bfloat16 *>(d_o), m, static_cast<__nv_bfloat16 *>(dq),
+                                         static_cast<__nv_bfloat16 *>(dk), static_cast<__nv_bfloat16 *>(dv), stream);
+  return attn_bwd_typed<__half>(pr, st, static_cast<const __half *>(q), static_cast<const __half *>(k),
+                                static_cast<const __half *>(v), static_cast<const __half *>(o), static_cast<const __half *>(d_o), m,
+                                static_cast<__half *>(dq), static_cast<__half *>(dk), static_cast<__half *>(dv), stream);
 }
 
 }  // extern "C"
