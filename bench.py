@@ -67,6 +67,8 @@ WORKLOADS = {
     "attn_d128": dict(attn=True, z=4, h=32, n_ctx=4096, d=128, causal=False, dtype="f16", seed=6),
     "attn_d128_causal": dict(attn=True, z=4, h=32, n_ctx=4096, d=128, causal=True, dtype="f16", seed=6),
     "attn_d64_16k_causal": dict(attn=True, z=4, h=32, n_ctx=16384, d=64, causal=True, dtype="f16", seed=6),
+    # backward of the same (the reference benchmarks it causal only, :742-744); FLOPs = 2.5 x forward (:799-800)
+    "attn_bwd_d64_causal": dict(attn=True, bwd=True, z=4, h=32, n_ctx=4096, d=64, causal=True, dtype="f16", seed=6),
 }
 
 
@@ -437,7 +439,8 @@ ATTN_SM_SCALE = 1.3   # the reference benchmark's value (06-fused-attention.py:7
 
 def attn_flops(w: dict, z: int) -> float:
     f = 4.0 * z * w["h"] * w["n_ctx"] * w["n_ctx"] * w["d"]
-    return 0.5 * f if w["causal"] else f
+    f = 0.5 * f if w["causal"] else f
+    return 2.5 * f if w.get("bwd") else f
 
 
 def attn_host_inputs(w: dict, rank: int):
@@ -456,16 +459,21 @@ def attn_cpu_sample(w: dict, budget_s: float = 10.0) -> dict:
     q, k, v = (torch.randn((1, 1, n, w["d"]), generator=g).to(torch.float16) for _ in range(3))
     torch.set_num_threads(1)
     done, t0 = 0, time.perf_counter()
+    d_o = torch.randn(q.shape, generator=g).to(torch.float16)
     while True:
-        AO.attention_blockwise(q, k, v, w["causal"], ATTN_SM_SCALE, 128, 64)
+        if w.get("bwd"):
+            AO.attention_grads_eager(q, k, v, d_o, w["causal"], ATTN_SM_SCALE)
+        else:
+            AO.attention_blockwise(q, k, v, w["causal"], ATTN_SM_SCALE, 128, 64)
         done += 1
         if time.perf_counter() - t0 > budget_s:
             break
     secs = time.perf_counter() - t0
-    fl = 4.0 * n * n * w["d"] * (0.5 if w["causal"] else 1.0) * done
+    fl = 4.0 * n * n * w["d"] * (0.5 if w["causal"] else 1.0) * (2.5 if w.get("bwd") else 1.0) * done
     return {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
             "sample": f"{done} x (1 batch, 1 head, n_ctx {n}, head_dim {w['d']}) of the workload through oracle/attn_oracle.py "
-                      f"(numpy restatement of the reference kernel, BLOCK_M 128, BLOCK_N 64), {secs:.1f} s"}
+                      + ("(fp32 autograd through the eager formula)" if w.get("bwd") else
+                         "(numpy restatement of the reference kernel, BLOCK_M 128, BLOCK_N 64)") + f", {secs:.1f} s"}
 
 
 def run_attention_reference_arm(args, name: str, w: dict) -> dict:
@@ -478,16 +486,23 @@ def run_attention_reference_arm(args, name: str, w: dict) -> dict:
     n = min(w["n_ctx"], 2048)
     g = torch.Generator().manual_seed(w["seed"])
     q, k, v = (torch.randn((1, 1, n, w["d"]), generator=g).to(torch.float16) for _ in range(3))
+    d_o = torch.randn(q.shape, generator=g).to(torch.float16)
+
+    def one():
+        if w.get("bwd"):
+            AO.attention_grads_eager(q, k, v, d_o, w["causal"], ATTN_SM_SCALE)   # forward + backward; FLOPs count the backward
+        else:
+            AO.attention_eager(q, k, v, w["causal"], ATTN_SM_SCALE)
     for _ in range(args.warmup):
-        AO.attention_eager(q, k, v, w["causal"], ATTN_SM_SCALE)
+        one()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        AO.attention_eager(q, k, v, w["causal"], ATTN_SM_SCALE)
+        one()
     secs = (time.perf_counter() - t0) / max(args.steps, 1)
-    fl = 4.0 * n * n * w["d"] * (0.5 if w["causal"] else 1.0)
+    fl = 4.0 * n * n * w["d"] * (0.5 if w["causal"] else 1.0) * (2.5 if w.get("bwd") else 1.0)
     val = fl / secs / 1e12
     sample = f"one (batch, head) slice per step, n_ctx cut to {n}, eager matmul-softmax-matmul in fp32 on {cores} threads"
-    return {"impl": "reference", "metric": "attention fwd TFLOP/s", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+    return {"impl": "reference", "metric": "attention bwd TFLOP/s" if w.get("bwd") else "attention fwd TFLOP/s", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded randn)",
             "config": {"workload": name, "z": w["z"], "h": w["h"], "n_ctx": w["n_ctx"], "head_dim": w["d"], "causal": w["causal"]},
@@ -518,8 +533,18 @@ def run_attention_gpu_arm(args, name: str, w: dict) -> dict | None:
     if set_bytes <= L2_BYTES:
         raise RuntimeError("attention workload smaller than L2: add rotating buffers before timing it")
 
-    def step(i):
-        A.attention_forward(q, k, v, w["causal"], ATTN_SM_SCALE, out=out)
+    bwd = bool(w.get("bwd"))
+    if bwd:
+        g = torch.Generator().manual_seed(w["seed"] + 7)
+        do_h = torch.randn(q_h.shape, generator=g).to(torch.float16).pin_memory()
+        d_o = do_h.to(dev)
+        o_fwd, m_fwd = A.attention_forward(q, k, v, w["causal"], ATTN_SM_SCALE, return_m=True, check=True)
+
+        def step(i):
+            return A.attention_backward(q, k, v, o_fwd, m_fwd, d_o, w["causal"], ATTN_SM_SCALE)
+    else:
+        def step(i):
+            A.attention_forward(q, k, v, w["causal"], ATTN_SM_SCALE, out=out)
 
     def barrier():
         if world > 1:
@@ -553,11 +578,27 @@ def run_attention_gpu_arm(args, name: str, w: dict) -> dict | None:
     value = per_gpu_flops * world / (ms_per_step * 1e-3) / 1e12
 
     e2e_steps = max(1, min(args.steps, 10))
-    A.attention_forward_host(q_h, k_h, v_h, w["causal"], ATTN_SM_SCALE, out=o_h)
+    if bwd:
+        oh, mh = o_fwd.cpu().pin_memory(), m_fwd.cpu().pin_memory()
+        grads_h = [torch.empty_like(q_h).pin_memory() for _ in range(3)]
+
+        def e2e_step():
+            # inputs of the backward from pinned host memory, the three gradients back to it
+            dev_in = [t.to(dev, non_blocking=True) for t in (q_h, k_h, v_h, oh, do_h)]
+            grads = A.attention_backward(*dev_in[:4], mh.to(dev, non_blocking=True), dev_in[4], w["causal"], ATTN_SM_SCALE)
+            for dst, src in zip(grads_h, grads):
+                dst.copy_(src, non_blocking=True)
+            torch.cuda.synchronize(dev)
+        h2d_bytes, d2h_bytes = 5 * q.numel() * 2 + m_fwd.numel() * 4, 3 * q.numel() * 2
+    else:
+        def e2e_step():
+            A.attention_forward_host(q_h, k_h, v_h, w["causal"], ATTN_SM_SCALE, out=o_h)
+        h2d_bytes, d2h_bytes = 3 * q.numel() * 2, q.numel() * 2
+    e2e_step()
     barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        A.attention_forward_host(q_h, k_h, v_h, w["causal"], ATTN_SM_SCALE, out=o_h)
+        e2e_step()
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
     if world > 1:
@@ -571,21 +612,22 @@ def run_attention_gpu_arm(args, name: str, w: dict) -> dict | None:
     sfu_bound = 4.0 * w["d"] * 16 * 148 * sm_mhz * 1e6 / 1e12   # one exp2 per score, 16 per clock per SM
     algo_bytes = 4 * q.numel() * 2 + q.numel() // w["d"] * 4
     line = {
-        "metric": "attention fwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "metric": "attention bwd TFLOP/s" if bwd else "attention fwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": w["dtype"], "data": "synthetic (seeded randn, the reference benchmark's shapes and sm_scale)",
         "config": {"workload": name, "z": w["z"] * world, "h": w["h"], "n_ctx": w["n_ctx"], "head_dim": w["d"],
                    "causal": w["causal"], "per_gpu": [w["z"], w["h"], w["n_ctx"], w["d"]],
                    "parallelism": "batch-sharded, no collective" if world > 1 else "single GPU",
-                   "kernel": "256 query rows per CTA (2 x 128), KV blocks of 128, tcgen05 + TMEM",
+                   "kernel": ("per head: 5 tt.dot GEMMs + 3 element-wise kernels, 4 heads in flight" if bwd else
+                              "256 query rows per CTA (2 x 128), KV blocks of 128, tcgen05 + TMEM"),
                    "l2": f"one buffer set of {set_bytes / 1e6:.0f} MB > 126 MB L2"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["bf16_tflops"], "traffic": None,
                      "peak_source": f"bf16_tflops (burst) of {peaks['_source']}",
                      "note": f"exp2 on the SFU (16 per clock per SM) bounds this shape at {sfu_bound:.0f} TFLOP/s; "
                              f"algorithmic bytes {algo_bytes / 1e6:.0f} MB"},
-        "e2e": {"value": per_gpu_flops * world / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(3 * q.numel() * 2),
-                "d2h_bytes_per_step": int(q.numel() * 2), "steps": e2e_steps},
+        "e2e": {"value": per_gpu_flops * world / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d_bytes),
+                "d2h_bytes_per_step": int(d2h_bytes), "steps": e2e_steps},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

@@ -82,6 +82,8 @@ uint32_t attn_idesc(bool bf16, bool b_mn_major, int n) {
   return d;
 }
 
+constexpr int kBwdLanes = 4;
+
 struct DeviceState {
   uint32_t *status = nullptr;
   bool attr_set = false;
@@ -93,9 +95,12 @@ struct DeviceState {
   float *m = nullptr;
   size_t tensor_bytes = 0, m_bytes = 0;
   // backward: per-head workspace (scores, probabilities, their gradients) and the GEMM plans of the last shape
+  // (kBwdLanes heads are in flight at a time, each on a stream, a workspace slice and a set of plans of its own)
   void *bwd_ws = nullptr;
   size_t bwd_ws_bytes = 0;
-  tx_dot_plan *bwd_plan[4] = {nullptr, nullptr, nullptr, nullptr};  // QK^T / dO V^T, P^T dO, dS K, dS^T Q
+  tx_dot_plan *bwd_plan[4 * 4] = {};  // per lane: QK^T / dO V^T, P^T dO, dS K, dS^T Q
+  cudaStream_t bwd_stream[4] = {};
+  cudaEvent_t bwd_fork = nullptr, bwd_join[4] = {};
   int bwd_n = 0, bwd_d = 0, bwd_dtype = -1;
   float bwd_scale = 0.f;
 };
@@ -201,29 +206,40 @@ int attn_bwd_typed(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   const int n = pr->n_ctx, d = pr->head_dim;
   const long long ld = (n + 7) / 8 * 8;
   const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
+  const size_t lane_bytes = static_cast<size_t>(n) * ld * (4 + 4 + sizeof(T));
   char *ws = static_cast<char *>(st->bwd_ws);
-  float *s_buf = reinterpret_cast<float *>(ws);
-  float *dp_buf = s_buf + static_cast<size_t>(n) * ld;
-  T *p_buf = reinterpret_cast<T *>(dp_buf + static_cast<size_t>(n) * ld);
-  float *delta = reinterpret_cast<float *>(p_buf + static_cast<size_t>(n) * ld);
+  float *delta = reinterpret_cast<float *>(ws + kBwdLanes * lane_bytes);
   const float qk_scale = pr->sm_scale * 1.44269504f;
   const long long rows = heads_total * n;
   attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
   TXA_CUDA(cudaGetLastError());
-  const unsigned ew_grid = 148 * 8;
+  // heads are independent: kBwdLanes of them are in flight at a time, so that their small kernels fill the GPU
+  TXA_CUDA(cudaEventRecord(st->bwd_fork, stream));
+  for (int l = 0; l < kBwdLanes; ++l) TXA_CUDA(cudaStreamWaitEvent(st->bwd_stream[l], st->bwd_fork, 0));
+  const unsigned ew_grid = 148 * 4;
   for (long long h = 0; h < heads_total; ++h) {
+    const int l = static_cast<int>(h % kBwdLanes);
+    cudaStream_t ls = st->bwd_stream[l];
+    tx_dot_plan **plan = &st->bwd_plan[4 * l];
+    float *s_buf = reinterpret_cast<float *>(ws + l * lane_bytes);
+    float *dp_buf = s_buf + static_cast<size_t>(n) * ld;
+    T *p_buf = reinterpret_cast<T *>(dp_buf + static_cast<size_t>(n) * ld);
     const size_t off = static_cast<size_t>(h) * n * d;
     int rc;
     // S = Q K^T and dP = dO V^T (fp32)
-    if ((rc = tx_dot_run(st->bwd_plan[0], q + off, k + off, s_buf, nullptr, nullptr, stream))) return rc;
-    if ((rc = tx_dot_run(st->bwd_plan[0], d_o + off, v + off, dp_buf, nullptr, nullptr, stream))) return rc;
-    attn_bwd_p_kernel<T><<<ew_grid, 256, 0, stream>>>(s_buf, m + h * n, p_buf, n, ld, qk_scale, pr->causal);
+    if ((rc = tx_dot_run(plan[0], q + off, k + off, s_buf, nullptr, nullptr, ls))) return rc;
+    if ((rc = tx_dot_run(plan[0], d_o + off, v + off, dp_buf, nullptr, nullptr, ls))) return rc;
+    attn_bwd_p_kernel<T><<<ew_grid, 256, 0, ls>>>(s_buf, m + h * n, p_buf, n, ld, qk_scale, pr->causal);
     // dV = P^T dO
-    if ((rc = tx_dot_run(st->bwd_plan[1], p_buf, d_o + off, dv + off, nullptr, nullptr, stream))) return rc;
-    attn_bwd_ds_kernel<T><<<ew_grid, 256, 0, stream>>>(p_buf, dp_buf, delta + h * n, n, ld);
+    if ((rc = tx_dot_run(plan[1], p_buf, d_o + off, dv + off, nullptr, nullptr, ls))) return rc;
+    attn_bwd_ds_kernel<T><<<ew_grid, 256, 0, ls>>>(p_buf, dp_buf, delta + h * n, n, ld);
     // dQ = sm_scale dS K, dK = sm_scale dS^T Q
-    if ((rc = tx_dot_run(st->bwd_plan[2], p_buf, k + off, dq + off, nullptr, nullptr, stream))) return rc;
-    if ((rc = tx_dot_run(st->bwd_plan[3], p_buf, q + off, dk + off, nullptr, nullptr, stream))) return rc;
+    if ((rc = tx_dot_run(plan[2], p_buf, k + off, dq + off, nullptr, nullptr, ls))) return rc;
+    if ((rc = tx_dot_run(plan[3], p_buf, q + off, dk + off, nullptr, nullptr, ls))) return rc;
+  }
+  for (int l = 0; l < kBwdLanes; ++l) {
+    TXA_CUDA(cudaEventRecord(st->bwd_join[l], st->bwd_stream[l]));
+    TXA_CUDA(cudaStreamWaitEvent(stream, st->bwd_join[l], 0));
   }
   TXA_CUDA(cudaGetLastError());
   g_attn_launches.fetch_add(static_cast<uint64_t>(1 + 2 * heads_total));
@@ -426,7 +442,7 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   const long long ld = (n + 7) / 8 * 8;
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);
-    const size_t need = static_cast<size_t>(n) * ld * (4 + 4 + 2) +
+    const size_t need = kBwdLanes * static_cast<size_t>(n) * ld * (4 + 4 + 2) +
                         static_cast<size_t>(pr->batch) * pr->heads * n * sizeof(float) + 256;
     if (st->bwd_ws_bytes < need) {
       if (st->bwd_ws) cudaFree(st->bwd_ws);
@@ -435,26 +451,36 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
       TXA_CUDA(cudaMalloc(&st->bwd_ws, need));
       st->bwd_ws_bytes = need;
     }
+    if (!st->bwd_fork) {
+      TXA_CUDA(cudaEventCreateWithFlags(&st->bwd_fork, cudaEventDisableTiming));
+      for (int l = 0; l < kBwdLanes; ++l) {
+        TXA_CUDA(cudaStreamCreateWithFlags(&st->bwd_stream[l], cudaStreamNonBlocking));
+        TXA_CUDA(cudaEventCreateWithFlags(&st->bwd_join[l], cudaEventDisableTiming));
+      }
+    }
     if (st->bwd_n != n || st->bwd_d != d || st->bwd_dtype != pr->dtype || st->bwd_scale != pr->sm_scale) {
       for (tx_dot_plan *&p : st->bwd_plan) {
         if (p) tx_dot_plan_destroy(p);
         p = nullptr;
       }
-      tx_dot_problem g = {};
-      // [n, n] = [n, d] x [d, n]: scores and dP, fp32; the second operand is a row-major [n, d] tensor read transposed
-      g.m = n; g.n = n; g.k = d; g.ab_dtype = pr->dtype; g.out_dtype = TXD_F32;
-      g.a_layout = TXD_ROW_MAJOR; g.b_layout = TXD_COL_MAJOR; g.lda = d; g.ldb = d; g.ldc = ld; g.alpha = 1.0f;
-      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[0]))) return afail(rc, "backward plan 0: %s", tx_dot_last_error());
-      // [n, d] = P^T [n, n] x dO [n, d]
-      g.m = n; g.n = d; g.k = n; g.out_dtype = pr->dtype;
-      g.a_layout = TXD_COL_MAJOR; g.b_layout = TXD_ROW_MAJOR; g.lda = ld; g.ldb = d; g.ldc = d; g.alpha = 1.0f;
-      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[1]))) return afail(rc, "backward plan 1: %s", tx_dot_last_error());
-      // dQ = sm_scale dS K
-      g.a_layout = TXD_ROW_MAJOR; g.alpha = pr->sm_scale;
-      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[2]))) return afail(rc, "backward plan 2: %s", tx_dot_last_error());
-      // dK = sm_scale dS^T Q
-      g.a_layout = TXD_COL_MAJOR;
-      if ((rc = tx_dot_plan_create(&g, nullptr, &st->bwd_plan[3]))) return afail(rc, "backward plan 3: %s", tx_dot_last_error());
+      for (int l = 0; l < kBwdLanes; ++l) {
+        tx_dot_plan **plan = &st->bwd_plan[4 * l];
+        tx_dot_problem g = {};
+        // [n, n] = [n, d] x [d, n]: scores and dP, fp32; the second operand is a row-major [n, d] tensor read transposed
+        g.m = n; g.n = n; g.k = d; g.ab_dtype = pr->dtype; g.out_dtype = TXD_F32;
+        g.a_layout = TXD_ROW_MAJOR; g.b_layout = TXD_COL_MAJOR; g.lda = d; g.ldb = d; g.ldc = ld; g.alpha = 1.0f;
+        if ((rc = tx_dot_plan_create(&g, nullptr, &plan[0]))) return afail(rc, "backward plan 0: %s", tx_dot_last_error());
+        // [n, d] = P^T [n, n] x dO [n, d]
+        g.m = n; g.n = d; g.k = n; g.out_dtype = pr->dtype;
+        g.a_layout = TXD_COL_MAJOR; g.b_layout = TXD_ROW_MAJOR; g.lda = ld; g.ldb = d; g.ldc = d; g.alpha = 1.0f;
+        if ((rc = tx_dot_plan_create(&g, nullptr, &plan[1]))) return afail(rc, "backward plan 1: %s", tx_dot_last_error());
+        // dQ = sm_scale dS K
+        g.a_layout = TXD_ROW_MAJOR; g.alpha = pr->sm_scale;
+        if ((rc = tx_dot_plan_create(&g, nullptr, &plan[2]))) return afail(rc, "backward plan 2: %s", tx_dot_last_error());
+        // dK = sm_scale dS^T Q
+        g.a_layout = TXD_COL_MAJOR;
+        if ((rc = tx_dot_plan_create(&g, nullptr, &plan[3]))) return afail(rc, "backward plan 3: %s", tx_dot_last_error());
+      }
       st->bwd_n = n; st->bwd_d = d; st->bwd_dtype = pr->dtype; st->bwd_scale = pr->sm_scale;
     }
   }
