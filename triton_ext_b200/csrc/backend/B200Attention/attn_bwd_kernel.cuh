@@ -1,0 +1,397 @@
+// Fused attention backward for sm_100a, head_dim 64: dK, dV and dQ in one kernel, five tt.dot per (KV block,
+// query block) pair with all accumulators in tensor memory. The mathematics is the reference's
+// (pass/LoopSplit/06-fused-attention.py: _attn_bwd_dkdv :351-400, _attn_bwd_dq :404-448):
+//
+//   S^T  = K Q^T                    P^T = exp2(S^T * scale - M[q])      (M = the forward's m + log2 l)
+//   dV  += P^T dO                   dP^T = V dO^T
+//   dS^T = P^T * (dP^T - delta[q])  dK  += dS^T Q                       dQ[q block] += dS K
+//
+// with P^T and dS^T rounded to the input type before their dots, as the reference rounds them (:386,:392,:436).
+//
+// One CTA owns one KV block of 128 rows of one (batch, head) and walks the query blocks that see it (all of
+// them, or those at and below the diagonal when causal: the split LoopSplit makes of the reference's loops, the
+// diagonal block being the masked one). K and V stay in shared memory; Q and dO tiles stream through a ring.
+//
+//   warps 0-3 : one thread per TMEM lane (= KV row for S^T, dP^T, dV, dK; = query row for the dQ partial):
+//               P^T and dS^T into shared memory (the A operands of the next dots), the dQ partial from TMEM
+//               to global memory with vectorised fp32 reductions, dV and dK at the end
+//   warp 4    : TMA producer (K, V once; Q, dO per query block) and the M / delta vectors of the block
+//   warp 5    : tcgen05.mma issuer
+//
+// dS^T lies in shared memory as [KV row][query] (K-major for dK += dS^T Q); dQ += dS K reads the same bytes
+// as an MN-major A operand, so dS is never transposed or stored twice. Every wait is bounded.
+#pragma once
+
+#include "attn_fwd_kernel.cuh"
+
+namespace txa {
+
+constexpr int kBwdThreads = 192;
+constexpr int kBwdProducerWarp = 4;
+constexpr int kBwdMmaWarp = 5;
+constexpr int kBwdStages = 3;
+constexpr int kBwdD = 64;
+constexpr uint32_t kBwdTileBytes = kTileRows * kBwdD * 2;  // one K / V / Q / dO tile: 16 KB, one swizzle atom wide
+
+struct AttnBwdParams {
+  CUtensorMap tmap_q, tmap_k, tmap_v, tmap_do;  // 3-D {64, n_ctx, batch*heads}, box {64, 128, 1}, SWIZZLE_128B
+  const float *m;       // [batch*heads, n_ctx] from the forward
+  const float *delta;   // [batch*heads, n_ctx] rowsum(o * do)
+  float *dq_acc;        // [batch*heads, n_ctx, 64] fp32, zero on entry
+  void *dk, *dv;        // [batch*heads, n_ctx, 64] in the input type
+  uint32_t *status;
+  unsigned long long wait_limit_ns;
+  float qk_scale, sm_scale;
+  int32_t n_ctx, heads_total, kv_blocks;
+  int32_t causal;
+  uint32_t idesc_st;    // 128 x 128, A and B K-major          (S^T, dP^T)
+  uint32_t idesc_acc;   // 128 x 64, A K-major, B MN-major      (dV, dK)
+  uint32_t idesc_dq;    // 128 x 64, A MN-major, B MN-major     (dQ partial)
+  int32_t inject_stall;
+};
+
+struct AttnBwdCtl {
+  uint64_t kv_full;
+  uint64_t full[kBwdStages], empty[kBwdStages];
+  uint64_t s_full, dp_full, pt_full, ds_full, dq_full, dq_free, drain;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+  float m_s[kBwdStages][kTileRows];
+  float delta_s[kBwdStages][kTileRows];
+};
+
+__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
+  extern __shared__ uint8_t attn_bwd_smem_raw[];
+  const uint32_t raw = smem_u32(attn_bwd_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t k_addr = base, v_addr = base + kBwdTileBytes;
+  const uint32_t ring_addr = base + 2 * kBwdTileBytes;             // per stage: Q tile, dO tile
+  const uint32_t pt_addr = ring_addr + kBwdStages * 2 * kBwdTileBytes;  // P^T  [128 KV rows][128 queries], 2 atoms
+  const uint32_t ds_addr = pt_addr + kPBytes;                      // dS^T, same layout
+  AttnBwdCtl *ctl = reinterpret_cast<AttnBwdCtl *>(attn_bwd_smem_raw + (ds_addr + kPBytes - raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- work: (head, KV block); the KV block index is the fast one, early (heavy, when causal) blocks first ----
+  const int head = static_cast<int>(blockIdx.x) / p.kv_blocks;
+  const int j = static_cast<int>(blockIdx.x) % p.kv_blocks;
+  const int kv0 = j * kTileRows;
+  const int q_blocks = (p.n_ctx + kTileRows - 1) / kTileRows;
+  const int i_lo = p.causal ? j : 0;
+  const int n_it = q_blocks - i_lo;
+  const bool kv_ragged = kv0 + kTileRows > p.n_ctx;
+
+  AbortCtl ac;
+  ac.flag = &ctl->abort_flag;
+  ac.status = p.status;
+  ac.limit_ns = p.wait_limit_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctl->kv_full), 1);
+    for (int s = 0; s < kBwdStages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 2);  // the TMA transaction and the M / delta vectors
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->s_full), 1);
+    mbar_init(smem_u32(&ctl->dp_full), 1);
+    mbar_init(smem_u32(&ctl->pt_full), kTileRows);
+    mbar_init(smem_u32(&ctl->ds_full), kTileRows);
+    mbar_init(smem_u32(&ctl->dq_full), 1);
+    mbar_init(smem_u32(&ctl->dq_free), kTileRows);
+    mbar_init(smem_u32(&ctl->drain), 1);
+    ctl->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&p.tmap_q);
+    tma_prefetch_desc(&p.tmap_k);
+    tma_prefetch_desc(&p.tmap_v);
+    tma_prefetch_desc(&p.tmap_do);
+  }
+  if (warp == kBwdMmaWarp) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  // TMEM columns: S^T 0..127 | dP^T 128..255 | dV 256..319 | dK 320..383 | dQ partial 384..447
+  constexpr uint32_t kColSt = 0, kColDp = 128, kColDv = 256, kColDk = 320, kColDq = 384;
+
+  if (warp == kBwdProducerWarp) {
+    // ------------------------------ producer ------------------------------
+    const bool issuer = elect_one();
+    if (issuer) {
+      const uint32_t bar = smem_u32(&ctl->kv_full);
+      mbar_arrive_expect_tx(bar, 2 * kBwdTileBytes);
+      tma_load_3d(k_addr, &p.tmap_k, 0, kv0, head, bar);
+      tma_load_3d(v_addr, &p.tmap_v, 0, kv0, head, bar);
+    }
+    __syncwarp();
+    int issued = 0;
+    bool ok = true;
+    for (int it = 0; ok && it < n_it && !p.inject_stall; ++it) {
+      const int slot = it % kBwdStages;
+      const uint32_t phase = static_cast<uint32_t>(it / kBwdStages) & 1u;
+      if (!warp_mbar_poll(smem_u32(&ctl->empty[slot]), phase ^ 1u, ac, kAttnTimeoutProducer, lane)) {
+        ok = false;
+        break;
+      }
+      const int q0 = (i_lo + it) * kTileRows;
+      const uint32_t bar = smem_u32(&ctl->full[slot]);
+      if (issuer) {
+        mbar_arrive_expect_tx(bar, 2 * kBwdTileBytes);
+        tma_load_3d(ring_addr + slot * 2 * kBwdTileBytes, &p.tmap_q, 0, q0, head, bar);
+        tma_load_3d(ring_addr + slot * 2 * kBwdTileBytes + kBwdTileBytes, &p.tmap_do, 0, q0, head, bar);
+      }
+      // M and delta of the 128 query rows (rows past n_ctx are masked later; give them harmless values)
+      for (int r = lane; r < kTileRows; r += 32) {
+        const int row = q0 + r;
+        const long long g = static_cast<long long>(head) * p.n_ctx + row;
+        ctl->m_s[slot][r] = row < p.n_ctx ? p.m[g] : 0.f;
+        ctl->delta_s[slot][r] = row < p.n_ctx ? p.delta[g] : 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+      __syncwarp();
+      ++issued;
+    }
+    if (ctl->abort_flag) {  // copies in flight must land before shared memory goes away
+      if (lane == 0) {
+        mbar_wait_timed(smem_u32(&ctl->kv_full), 0u, ac, kAttnTimeoutDrain);
+        const int first = issued > kBwdStages ? issued - kBwdStages : 0;
+        for (int it = first; it < issued; ++it) {
+          const unsigned long long t0 = global_timer_ns();
+          const uint32_t bar = smem_u32(&ctl->full[it % kBwdStages]);
+          const uint32_t ph = static_cast<uint32_t>(it / kBwdStages) & 1u;
+          while (!mbar_try_wait(bar, ph))
+            if (global_timer_ns() - t0 > ac.limit_ns) break;
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == kBwdMmaWarp) {
+    // ------------------------------ tcgen05.mma issuer ------------------------------
+    const bool issuer = elect_one();
+    auto desc64 = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+    const uint32_t desc_hi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);  // SBO 1024, sm_100, SWIZZLE_128B
+    const uint32_t lbo_unused = 1u << 16;
+    const uint32_t lbo_atom = ((static_cast<uint32_t>(kAtomBytes) >> 4) & 0x3FFFu) << 16;  // between 64-element chunks
+    auto lo_of = [](uint32_t addr) { return (addr & 0x3FFFFu) >> 4; };
+    // K-major operand, one atom (head_dim 64): 4 MMAs, +32 bytes per MMA
+    // K-major operand, two atoms (128 queries): 8 MMAs, atom step after 4
+    // MN-major operand [K rows][64 or 128 contiguous]: 16 K rows = 2048 bytes per MMA
+    auto kmajor_step = [](int i) { return static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u; };
+    auto mn_step = [](int i) { return static_cast<uint32_t>(i) * (16u * 128u >> 4); };
+    bool ok = warp_mbar_poll(smem_u32(&ctl->kv_full), 0u, ac, kAttnTimeoutMmaOperand, lane);
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int slot = it % kBwdStages;
+      const uint32_t ring_phase = static_cast<uint32_t>(it / kBwdStages) & 1u;
+      const uint32_t ph = static_cast<uint32_t>(it) & 1u;
+      const uint32_t q_addr = ring_addr + slot * 2 * kBwdTileBytes, do_addr = q_addr + kBwdTileBytes;
+      if (!warp_mbar_poll(smem_u32(&ctl->full[slot]), ring_phase, ac, kAttnTimeoutMmaOperand, lane)) break;
+      tc_fence_after();
+      // S^T = K Q^T and dP^T = V dO^T
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (issuer)
+          umma_f16(tmem_base + kColSt, desc64(desc_hi, (lo_of(k_addr) | lbo_unused) + kmajor_step(i)),
+                   desc64(desc_hi, (lo_of(q_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
+      if (issuer) tc_commit(smem_u32(&ctl->s_full));
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (issuer)
+          umma_f16(tmem_base + kColDp, desc64(desc_hi, (lo_of(v_addr) | lbo_unused) + kmajor_step(i)),
+                   desc64(desc_hi, (lo_of(do_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
+      if (issuer) tc_commit(smem_u32(&ctl->dp_full));
+      __syncwarp();
+      // dV += P^T dO
+      if (!warp_mbar_poll(smem_u32(&ctl->pt_full), ph, ac, kAttnTimeoutMmaP, lane)) break;
+      tc_fence_after();
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (issuer)
+          umma_f16(tmem_base + kColDv, desc64(desc_hi, (lo_of(pt_addr) | lbo_unused) + kmajor_step(i)),
+                   desc64(desc_hi, (lo_of(do_addr) | lbo_atom) + mn_step(i)), p.idesc_acc, (it > 0 || i > 0) ? 1u : 0u);
+      __syncwarp();
+      // dK += dS^T Q, dQ partial = dS K
+      if (!warp_mbar_poll(smem_u32(&ctl->ds_full), ph, ac, kAttnTimeoutMmaP, lane)) break;
+      if (it > 0 && !warp_mbar_poll(smem_u32(&ctl->dq_free), ph ^ 1u, ac, kAttnTimeoutMmaP, lane)) break;
+      tc_fence_after();
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (issuer)
+          umma_f16(tmem_base + kColDk, desc64(desc_hi, (lo_of(ds_addr) | lbo_unused) + kmajor_step(i)),
+                   desc64(desc_hi, (lo_of(q_addr) | lbo_atom) + mn_step(i)), p.idesc_acc, (it > 0 || i > 0) ? 1u : 0u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (issuer)
+          umma_f16(tmem_base + kColDq, desc64(desc_hi, (lo_of(ds_addr) | lbo_atom) + mn_step(i)),
+                   desc64(desc_hi, (lo_of(k_addr) | lbo_atom) + mn_step(i)), p.idesc_dq, i > 0 ? 1u : 0u);
+      if (issuer) {
+        tc_commit(smem_u32(&ctl->dq_full));
+        tc_commit(smem_u32(&ctl->empty[slot]));
+      }
+      __syncwarp();
+    }
+    // every MMA issued above has completed before TMEM and shared memory are given back (also after an abort)
+    if (issuer) tc_commit(smem_u32(&ctl->drain));
+    __syncwarp();
+    if (lane == 0) {
+      const unsigned long long t0 = global_timer_ns();
+      while (!mbar_try_wait(smem_u32(&ctl->drain), 0u)) {
+        if (global_timer_ns() - t0 > ac.limit_ns) {
+          ctl->abort_flag = 1;
+          atomicCAS(ac.status, 0u, static_cast<uint32_t>(kAttnTimeoutDrain));
+          break;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ compute warps ------------------------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // TMEM lane
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+    const int row_xor = r & 7;
+    const int kv_row = kv0 + r;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int slot = it % kBwdStages;
+      const uint32_t ring_phase = static_cast<uint32_t>(it / kBwdStages) & 1u;
+      const uint32_t ph = static_cast<uint32_t>(it) & 1u;
+      const int q0 = (i_lo + it) * kTileRows;
+      const bool masked = (p.causal && i_lo + it == j) || kv_ragged || q0 + kTileRows > p.n_ctx;
+      // the block's M and delta are in shared memory once its stage is full
+      if (!warp_mbar_poll(smem_u32(&ctl->full[slot]), ring_phase, ac, kAttnTimeoutSoftmaxS, lane) ||
+          !warp_mbar_poll(smem_u32(&ctl->s_full), ph, ac, kAttnTimeoutSoftmaxS, lane)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t s[128];
+      tmem_ld_32x32(lane_base + kColSt, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld_32x32(lane_base + kColSt + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_ld_32x32(lane_base + kColSt + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+      tmem_ld_32x32(lane_base + kColSt + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+      tmem_ld_wait();
+      const float *m_s = ctl->m_s[slot];
+      const float *delta_s = ctl->delta_s[slot];
+      // P^T[kv row][query] = exp2(S^T * scale - M[query]); kept in fp32 for dS, stored rounded for dV
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = g * 8 + i;
+          float x = fast_exp2(fmaf(__uint_as_float(s[c]), p.qk_scale, -m_s[c]));
+          if (masked) {
+            const int qrow = q0 + c;
+            const bool valid = qrow < p.n_ctx && kv_row < p.n_ctx && (!p.causal || qrow >= kv_row);
+            x = valid ? x : 0.f;
+          }
+          e[i] = x;
+          s[c] = __float_as_uint(x);
+        }
+        st_shared_v4(pt_addr + (g >> 3) * kAtomBytes + row_off + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]),
+                     pack_pair<kBf16>(e[2], e[3]), pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->pt_full));
+      // dS^T = P^T * (dP^T - delta[query])
+      if (!warp_mbar_poll(smem_u32(&ctl->dp_full), ph, ac, kAttnTimeoutSoftmaxS, lane)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t dp[32];
+        tmem_ld_32x32(lane_base + kColDp + c4 * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int gg = 0; gg < 4; ++gg) {
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c4 * 32 + gg * 8 + i;
+            e[i] = __uint_as_float(s[c]) * (__uint_as_float(dp[gg * 8 + i]) - delta_s[c]);
+          }
+          const int g = c4 * 4 + gg;
+          st_shared_v4(ds_addr + (g >> 3) * kAtomBytes + row_off + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]),
+                       pack_pair<kBf16>(e[2], e[3]), pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->ds_full));
+      // the dQ partial of this (query block, KV block) pair: lane = query row
+      if (!warp_mbar_poll(smem_u32(&ctl->dq_full), ph, ac, kAttnTimeoutSoftmaxO, lane)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      {
+        const int qrow = q0 + r;
+        float *dst = p.dq_acc + (static_cast<long long>(head) * p.n_ctx + qrow) * kBwdD;
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t v[32];
+          tmem_ld_32x32(lane_base + kColDq + c2 * 32, v);
+          tmem_ld_wait();
+          if (qrow < p.n_ctx) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              red_add_v4(dst + c2 * 32 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                         __uint_as_float(v[i + 3]));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->dq_free));
+    }
+    if (ok && n_it > 0) {
+      // every MMA has completed (the last dq_full was committed after them): dV and dK of this KV block.
+      // The TMEM loads are warp-wide; rows past n_ctx take part in them and store nothing.
+      const long long g = (static_cast<long long>(head) * p.n_ctx + kv_row) * kBwdD;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const float scale = which == 0 ? 1.0f : p.sm_scale;
+        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<char *>(which == 0 ? p.dv : p.dk) + g * 2);
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t v[32];
+          tmem_ld_32x32(lane_base + (which == 0 ? kColDv : kColDk) + c2 * 32, v);
+          tmem_ld_wait();
+          if (kv_row < p.n_ctx) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              w.x = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 0]) * scale, __uint_as_float(v[q * 8 + 1]) * scale);
+              w.y = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 2]) * scale, __uint_as_float(v[q * 8 + 3]) * scale);
+              w.z = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 4]) * scale, __uint_as_float(v[q * 8 + 5]) * scale);
+              w.w = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 6]) * scale, __uint_as_float(v[q * 8 + 7]) * scale);
+              dst[c2 * 4 + q] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kBwdMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace txa

@@ -12,6 +12,7 @@
 #include <mutex>
 #include <string>
 
+#include "attn_bwd_kernel.cuh"
 #include "attn_fwd_kernel.cuh"
 
 namespace {
@@ -129,6 +130,8 @@ int device_state(DeviceState **out) {
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     st.attr_set = true;
   }
   *out = &st;
@@ -243,6 +246,66 @@ int attn_bwd_typed(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   }
   TXA_CUDA(cudaGetLastError());
   g_attn_launches.fetch_add(static_cast<uint64_t>(1 + 2 * heads_total));
+  return TXD_OK;
+}
+
+
+// dq = cast(sm_scale * dq_acc)
+template <typename T>
+__global__ void attn_bwd_dq_convert_kernel(const float *acc, T *dq, long long count, float sm_scale) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < count;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dq[i] = from_f32<T>(acc[i] * sm_scale);
+}
+
+// head_dim 64: one fused kernel (attn_bwd_kernel.cuh) between the delta pre-pass and the dq conversion
+template <typename T>
+int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const T *k, const T *v, const T *o, const T *d_o,
+                   const float *m, T *dq, T *dk, T *dv, cudaStream_t stream) {
+  const bool bf16 = pr->dtype == TXD_BF16;
+  const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
+  const long long rows = heads_total * pr->n_ctx;
+  float *delta = static_cast<float *>(st->bwd_ws);
+  float *dq_acc = delta + ((rows + 63) / 64) * 64;
+  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, pr->head_dim);
+  TXA_CUDA(cudaGetLastError());
+  TXA_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(rows) * 64 * sizeof(float), stream));
+  txa::AttnBwdParams prm = {};
+  int rc;
+  if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_do, d_o, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
+  prm.m = m;
+  prm.delta = delta;
+  prm.dq_acc = dq_acc;
+  prm.dk = dk;
+  prm.dv = dv;
+  prm.status = st->status;
+  prm.wait_limit_ns = 2000ull * 1000 * 1000;
+  if (const char *e = getenv("TXD_WAIT_LIMIT_MS")) {
+    const long ms = atol(e);
+    if (ms > 0) prm.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000 * 1000;
+  }
+  if (const char *e = getenv("TXD_INJECT_STALL")) prm.inject_stall = atoi(e) != 0;
+  prm.qk_scale = pr->sm_scale * 1.44269504f;
+  prm.sm_scale = pr->sm_scale;
+  prm.n_ctx = pr->n_ctx;
+  prm.heads_total = static_cast<int32_t>(heads_total);
+  prm.kv_blocks = (pr->n_ctx + 127) / 128;
+  prm.causal = pr->causal ? 1 : 0;
+  prm.idesc_st = attn_idesc(bf16, false, 128);
+  prm.idesc_acc = attn_idesc(bf16, true, 64);
+  prm.idesc_dq = attn_idesc(bf16, true, 64) | (1u << 15);  // A operand MN-major as well
+  const size_t smem = 2 * txa::kBwdTileBytes + txa::kBwdStages * 2 * txa::kBwdTileBytes + 2 * txa::kPBytes +
+                      sizeof(txa::AttnBwdCtl) + 1024;
+  const unsigned grid = static_cast<unsigned>(heads_total * prm.kv_blocks);
+  if (bf16) txa::attn_bwd_kernel<true><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
+  else txa::attn_bwd_kernel<false><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
+  TXA_CUDA(cudaGetLastError());
+  attn_bwd_dq_convert_kernel<T><<<148 * 8, 256, 0, stream>>>(dq_acc, dq, rows * 64, pr->sm_scale);
+  TXA_CUDA(cudaGetLastError());
+  g_attn_launches.fetch_add(3);
   return TXD_OK;
 }
 
@@ -440,6 +503,30 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   if (rc) return rc;
   const int n = pr->n_ctx, d = pr->head_dim;
   const long long ld = (n + 7) / 8 * 8;
+  const char *force_unfused = getenv("TXA_BWD_UNFUSED");
+  if (d == 64 && !(force_unfused && atoi(force_unfused) != 0)) {
+    const size_t rows = static_cast<size_t>(pr->batch) * pr->heads * n;
+    const size_t need = ((rows + 63) / 64) * 64 * sizeof(float) + rows * 64 * sizeof(float) + 256;
+    {
+      std::lock_guard<std::mutex> lock(g_state_mutex);
+      if (st->bwd_ws_bytes < need) {
+        if (st->bwd_ws) cudaFree(st->bwd_ws);
+        st->bwd_ws = nullptr;
+        st->bwd_ws_bytes = 0;
+        TXA_CUDA(cudaMalloc(&st->bwd_ws, need));
+        st->bwd_ws_bytes = need;
+      }
+    }
+    cudaStream_t fs = static_cast<cudaStream_t>(stream_v);
+    if (pr->dtype == TXD_BF16)
+      return attn_bwd_fused<__nv_bfloat16>(pr, st, static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
+                                           static_cast<const __nv_bfloat16 *>(v), static_cast<const __nv_bfloat16 *>(o),
+                                           static_cast<const __nv_bfloat16 *>(d_o), m, static_cast<__nv_bfloat16 *>(dq),
+                                           static_cast<__nv_bfloat16 *>(dk), static_cast<__nv_bfloat16 *>(dv), fs);
+    return attn_bwd_fused<__half>(pr, st, static_cast<const __half *>(q), static_cast<const __half *>(k),
+                                  static_cast<const __half *>(v), static_cast<const __half *>(o), static_cast<const __half *>(d_o),
+                                  m, static_cast<__half *>(dq), static_cast<__half *>(dk), static_cast<__half *>(dv), fs);
+  }
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);
     const size_t need = kBwdLanes * static_cast<size_t>(n) * ld * (4 + 4 + 2) +
