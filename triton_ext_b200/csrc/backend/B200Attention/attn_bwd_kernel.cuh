@@ -56,12 +56,40 @@ struct AttnBwdCtl {
   uint64_t s_full, dp_full, pt_full, ds_full, dq_full, dq_free, drain;
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
-  float m_s[kBwdStages][kTileRows];
-  float delta_s[kBwdStages][kTileRows];
+  alignas(16) float m_s[kBwdStages][kTileRows];
+  alignas(16) float delta_s[kBwdStages][kTileRows];
 };
 
 __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// P^T[kv row][query] = exp2(S^T * scale - M[query]) for one KV row: the fp32 values stay in `s` (dS needs them), the
+// rounded ones go to shared memory as the A operand of dV += P^T dO. kMasked: diagonal and ragged blocks.
+template <bool kMasked, bool kBf16>
+__device__ __forceinline__ void bwd_row_p(uint32_t (&s)[128], const float *m_s, float qk_scale, int q0, int kv_row, int n_ctx,
+                                          int causal, uint32_t pt_row, int row_xor) {
+  const float4 *m4 = reinterpret_cast<const float4 *>(m_s);
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {
+    const float4 ma = m4[g * 2], mb = m4[g * 2 + 1];
+    const float mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+    float e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = g * 8 + i;
+      float x = fast_exp2(fmaf(__uint_as_float(s[c]), qk_scale, -mm[i]));
+      if (kMasked) {
+        const int qrow = q0 + c;
+        const bool valid = qrow < n_ctx && kv_row < n_ctx && (!causal || qrow >= kv_row);
+        x = valid ? x : 0.f;
+      }
+      e[i] = x;
+      s[c] = __float_as_uint(x);
+    }
+    st_shared_v4(pt_row + (g >> 3) * kAtomBytes + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]),
+                 pack_pair<kBf16>(e[2], e[3]), pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
+  }
 }
 
 template <bool kBf16>
@@ -283,25 +311,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       tmem_ld_wait();
       const float *m_s = ctl->m_s[slot];
       const float *delta_s = ctl->delta_s[slot];
-      // P^T[kv row][query] = exp2(S^T * scale - M[query]); kept in fp32 for dS, stored rounded for dV
-#pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        float e[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int c = g * 8 + i;
-          float x = fast_exp2(fmaf(__uint_as_float(s[c]), p.qk_scale, -m_s[c]));
-          if (masked) {
-            const int qrow = q0 + c;
-            const bool valid = qrow < p.n_ctx && kv_row < p.n_ctx && (!p.causal || qrow >= kv_row);
-            x = valid ? x : 0.f;
-          }
-          e[i] = x;
-          s[c] = __float_as_uint(x);
-        }
-        st_shared_v4(pt_addr + (g >> 3) * kAtomBytes + row_off + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]),
-                     pack_pair<kBf16>(e[2], e[3]), pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
-      }
+      if (masked) bwd_row_p<true, kBf16>(s, m_s, p.qk_scale, q0, kv_row, p.n_ctx, p.causal, pt_addr + row_off, row_xor);
+      else bwd_row_p<false, kBf16>(s, m_s, p.qk_scale, q0, kv_row, p.n_ctx, p.causal, pt_addr + row_off, row_xor);
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->pt_full));
@@ -318,11 +329,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
         tmem_ld_wait();
 #pragma unroll
         for (int gg = 0; gg < 4; ++gg) {
+          const float4 da = reinterpret_cast<const float4 *>(delta_s)[c4 * 8 + gg * 2];
+          const float4 db = reinterpret_cast<const float4 *>(delta_s)[c4 * 8 + gg * 2 + 1];
+          const float dd[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
           float e[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int c = c4 * 32 + gg * 8 + i;
-            e[i] = __uint_as_float(s[c]) * (__uint_as_float(dp[gg * 8 + i]) - delta_s[c]);
+            e[i] = __uint_as_float(s[c]) * (__uint_as_float(dp[gg * 8 + i]) - dd[i]);
           }
           const int g = c4 * 4 + gg;
           st_shared_v4(ds_addr + (g >> 3) * kAtomBytes + row_off + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]),
