@@ -12,11 +12,14 @@
 // them, or those at and below the diagonal when causal: the split LoopSplit makes of the reference's loops, the
 // diagonal block being the masked one). K and V stay in shared memory; Q and dO tiles stream through a ring.
 //
-//   warps 0-3 : one thread per TMEM lane (= KV row for S^T, dP^T, dV, dK; = query row for the dQ partial):
+//   warps 0-7 : two threads per TMEM lane (= KV row for S^T, dP^T, dV, dK; = query row for the dQ partial), each
+//               with half of the columns:
 //               P^T and dS^T into shared memory (the A operands of the next dots), the dQ partial from TMEM
 //               to global memory with vectorised fp32 reductions, dV and dK at the end
-//   warp 4    : TMA producer (K, V once; Q, dO per query block) and the M / delta vectors of the block
-//   warp 5    : tcgen05.mma issuer
+//   warp 8    : TMA producer (K, V once; Q, dO per query block) and the M / delta vectors of the block
+//   warp 9    : tcgen05.mma issuer. Order per query block i: dV(i), S^T(i+1) as soon as P^T(i) is written;
+//               dK(i), dQ(i), dP^T(i+1) as soon as dS^T(i) is written: the next block's scores are ready when the
+//               compute warps come back for them
 //
 // dS^T lies in shared memory as [KV row][query] (K-major for dK += dS^T Q); dQ += dS K reads the same bytes
 // as an MN-major A operand, so dS is never transposed or stored twice. Every wait is bounded.
@@ -26,9 +29,10 @@
 
 namespace txa {
 
-constexpr int kBwdThreads = 192;
-constexpr int kBwdProducerWarp = 4;
-constexpr int kBwdMmaWarp = 5;
+constexpr int kBwdComputeWarps = 8;   // two threads per TMEM lane, 64 columns each
+constexpr int kBwdProducerWarp = 8;
+constexpr int kBwdMmaWarp = 9;
+constexpr int kBwdThreads = 10 * 32;
 constexpr int kBwdStages = 3;
 constexpr int kBwdD = 64;
 constexpr uint32_t kBwdTileBytes = kTileRows * kBwdD * 2;  // one K / V / Q / dO tile: 16 KB, one swizzle atom wide
@@ -64,14 +68,15 @@ __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// P^T[kv row][query] = exp2(S^T * scale - M[query]) for one KV row: the fp32 values stay in `s` (dS needs them), the
-// rounded ones go to shared memory as the A operand of dV += P^T dO. kMasked: diagonal and ragged blocks.
+// P^T[kv row][query] = exp2(S^T * scale - M[query]) for 64 queries of one KV row: the fp32 values stay in `s` (dS
+// needs them), the rounded ones go to shared memory (one atom of the A operand of dV += P^T dO).
+// kMasked: diagonal and ragged blocks; q0 is the first query of these 64 columns.
 template <bool kMasked, bool kBf16>
-__device__ __forceinline__ void bwd_row_p(uint32_t (&s)[128], const float *m_s, float qk_scale, int q0, int kv_row, int n_ctx,
+__device__ __forceinline__ void bwd_row_p(uint32_t (&s)[64], const float *m_s, float qk_scale, int q0, int kv_row, int n_ctx,
                                           int causal, uint32_t pt_row, int row_xor) {
   const float4 *m4 = reinterpret_cast<const float4 *>(m_s);
 #pragma unroll
-  for (int g = 0; g < 16; ++g) {
+  for (int g = 0; g < 8; ++g) {
     const float4 ma = m4[g * 2], mb = m4[g * 2 + 1];
     const float mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
     float e[8];
@@ -87,8 +92,8 @@ __device__ __forceinline__ void bwd_row_p(uint32_t (&s)[128], const float *m_s, 
       e[i] = x;
       s[c] = __float_as_uint(x);
     }
-    st_shared_v4(pt_row + (g >> 3) * kAtomBytes + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]),
-                 pack_pair<kBf16>(e[2], e[3]), pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
+    st_shared_v4(pt_row + ((g ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]), pack_pair<kBf16>(e[2], e[3]),
+                 pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
   }
 }
 
@@ -128,10 +133,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     }
     mbar_init(smem_u32(&ctl->s_full), 1);
     mbar_init(smem_u32(&ctl->dp_full), 1);
-    mbar_init(smem_u32(&ctl->pt_full), kTileRows);
-    mbar_init(smem_u32(&ctl->ds_full), kTileRows);
+    mbar_init(smem_u32(&ctl->pt_full), 2 * kTileRows);
+    mbar_init(smem_u32(&ctl->ds_full), 2 * kTileRows);
     mbar_init(smem_u32(&ctl->dq_full), 1);
-    mbar_init(smem_u32(&ctl->dq_free), kTileRows);
+    mbar_init(smem_u32(&ctl->dq_free), 2 * kTileRows);
     mbar_init(smem_u32(&ctl->drain), 1);
     ctl->abort_flag = 0;
     fence_mbar_init();
@@ -217,20 +222,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     auto kmajor_step = [](int i) { return static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u; };
     auto mn_step = [](int i) { return static_cast<uint32_t>(i) * (16u * 128u >> 4); };
     bool ok = warp_mbar_poll(smem_u32(&ctl->kv_full), 0u, ac, kAttnTimeoutMmaOperand, lane);
-    for (int it = 0; ok && it < n_it; ++it) {
-      const int slot = it % kBwdStages;
-      const uint32_t ring_phase = static_cast<uint32_t>(it / kBwdStages) & 1u;
-      const uint32_t ph = static_cast<uint32_t>(it) & 1u;
-      const uint32_t q_addr = ring_addr + slot * 2 * kBwdTileBytes, do_addr = q_addr + kBwdTileBytes;
-      if (!warp_mbar_poll(smem_u32(&ctl->full[slot]), ring_phase, ac, kAttnTimeoutMmaOperand, lane)) break;
-      tc_fence_after();
-      // S^T = K Q^T and dP^T = V dO^T
+    auto stage_q = [&](int it) { return ring_addr + static_cast<uint32_t>(it % kBwdStages) * 2 * kBwdTileBytes; };
+    auto wait_stage = [&](int it) {
+      return warp_mbar_poll(smem_u32(&ctl->full[it % kBwdStages]), static_cast<uint32_t>(it / kBwdStages) & 1u, ac,
+                            kAttnTimeoutMmaOperand, lane);
+    };
+    auto issue_st = [&](int it) {  // S^T = K Q^T
+      const uint32_t q_addr = stage_q(it);
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         if (issuer)
           umma_f16(tmem_base + kColSt, desc64(desc_hi, (lo_of(k_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(q_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
       if (issuer) tc_commit(smem_u32(&ctl->s_full));
+      __syncwarp();
+    };
+    auto issue_dp = [&](int it) {  // dP^T = V dO^T
+      const uint32_t do_addr = stage_q(it) + kBwdTileBytes;
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         if (issuer)
@@ -238,7 +246,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
                    desc64(desc_hi, (lo_of(do_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
       if (issuer) tc_commit(smem_u32(&ctl->dp_full));
       __syncwarp();
-      // dV += P^T dO
+    };
+    if (ok && n_it > 0) ok = wait_stage(0);
+    if (ok && n_it > 0) {
+      tc_fence_after();
+      issue_st(0);
+      issue_dp(0);
+    }
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int slot = it % kBwdStages;
+      const uint32_t ph = static_cast<uint32_t>(it) & 1u;
+      const uint32_t q_addr = stage_q(it), do_addr = q_addr + kBwdTileBytes;
+      // dV += P^T dO, then the next block's scores (the compute warps hold S^T(it) in registers by now)
       if (!warp_mbar_poll(smem_u32(&ctl->pt_full), ph, ac, kAttnTimeoutMmaP, lane)) break;
       tc_fence_after();
 #pragma unroll
@@ -247,7 +266,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
           umma_f16(tmem_base + kColDv, desc64(desc_hi, (lo_of(pt_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(do_addr) | lbo_atom) + mn_step(i)), p.idesc_acc, (it > 0 || i > 0) ? 1u : 0u);
       __syncwarp();
-      // dK += dS^T Q, dQ partial = dS K
+      if (it + 1 < n_it) {
+        if (!wait_stage(it + 1)) break;
+        issue_st(it + 1);
+      }
+      // dK += dS^T Q, dQ partial = dS K, then the next block's dP^T
       if (!warp_mbar_poll(smem_u32(&ctl->ds_full), ph, ac, kAttnTimeoutMmaP, lane)) break;
       if (it > 0 && !warp_mbar_poll(smem_u32(&ctl->dq_free), ph ^ 1u, ac, kAttnTimeoutMmaP, lane)) break;
       tc_fence_after();
@@ -266,6 +289,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
         tc_commit(smem_u32(&ctl->empty[slot]));
       }
       __syncwarp();
+      if (it + 1 < n_it) issue_dp(it + 1);
     }
     // every MMA issued above has completed before TMEM and shared memory are given back (also after an abort)
     if (issuer) tc_commit(smem_u32(&ctl->drain));
@@ -284,12 +308,32 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
   } else {
     // ------------------------------ compute warps ------------------------------
     const int quarter = warp & 3;
+    const int half = warp >> 2;         // which 64 of the 128 columns of S^T / dP^T, which 32 of dV / dK / dQ
     const int r = quarter * 32 + lane;  // TMEM lane
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+    const uint32_t row_off = static_cast<uint32_t>(half * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128);
     const int row_xor = r & 7;
     const int kv_row = kv0 + r;
     bool ok = true;
+    // the dQ partial of query block `blk` (lane = query row): this thread's 32 columns, reduced into global memory
+    auto dq_readout = [&](int it_done) -> bool {
+      if (!warp_mbar_poll(smem_u32(&ctl->dq_full), static_cast<uint32_t>(it_done) & 1u, ac, kAttnTimeoutSoftmaxO, lane)) return false;
+      tc_fence_after();
+      const int qrow = (i_lo + it_done) * kTileRows + r;
+      float *dst = p.dq_acc + (static_cast<long long>(head) * p.n_ctx + qrow) * kBwdD + half * 32;
+      uint32_t v[32];
+      tmem_ld_32x32(lane_base + kColDq + half * 32, v);
+      tmem_ld_wait();
+      if (qrow < p.n_ctx) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          red_add_v4(dst + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                     __uint_as_float(v[i + 3]));
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->dq_free));
+      return true;
+    };
     for (int it = 0; it < n_it; ++it) {
       const int slot = it % kBwdStages;
       const uint32_t ring_phase = static_cast<uint32_t>(it / kBwdStages) & 1u;
@@ -303,19 +347,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
         break;
       }
       tc_fence_after();
-      uint32_t s[128];
-      tmem_ld_32x32(lane_base + kColSt, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_ld_32x32(lane_base + kColSt + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      tmem_ld_32x32(lane_base + kColSt + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
-      tmem_ld_32x32(lane_base + kColSt + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+      uint32_t s[64];
+      tmem_ld_32x32(lane_base + kColSt + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld_32x32(lane_base + kColSt + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_ld_wait();
-      const float *m_s = ctl->m_s[slot];
-      const float *delta_s = ctl->delta_s[slot];
-      if (masked) bwd_row_p<true, kBf16>(s, m_s, p.qk_scale, q0, kv_row, p.n_ctx, p.causal, pt_addr + row_off, row_xor);
-      else bwd_row_p<false, kBf16>(s, m_s, p.qk_scale, q0, kv_row, p.n_ctx, p.causal, pt_addr + row_off, row_xor);
+      const float *m_s = ctl->m_s[slot] + half * 64;
+      const float *delta_s = ctl->delta_s[slot] + half * 64;
+      if (masked) bwd_row_p<true, kBf16>(s, m_s, p.qk_scale, q0 + half * 64, kv_row, p.n_ctx, p.causal, pt_addr + row_off, row_xor);
+      else bwd_row_p<false, kBf16>(s, m_s, p.qk_scale, q0 + half * 64, kv_row, p.n_ctx, p.causal, pt_addr + row_off, row_xor);
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->pt_full));
+      // the previous block's dQ partial, while the tensor pipe works on dV and the next scores
+      if (it > 0 && !dq_readout(it - 1)) {
+        ok = false;
+        break;
+      }
       // dS^T = P^T * (dP^T - delta[query])
       if (!warp_mbar_poll(smem_u32(&ctl->dp_full), ph, ac, kAttnTimeoutSoftmaxS, lane)) {
         ok = false;
@@ -323,9 +370,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       }
       tc_fence_after();
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
+      for (int c4 = 0; c4 < 2; ++c4) {
         uint32_t dp[32];
-        tmem_ld_32x32(lane_base + kColDp + c4 * 32, dp);
+        tmem_ld_32x32(lane_base + kColDp + half * 64 + c4 * 32, dp);
         tmem_ld_wait();
 #pragma unroll
         for (int gg = 0; gg < 4; ++gg) {
@@ -339,61 +386,35 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
             e[i] = __uint_as_float(s[c]) * (__uint_as_float(dp[gg * 8 + i]) - dd[i]);
           }
           const int g = c4 * 4 + gg;
-          st_shared_v4(ds_addr + (g >> 3) * kAtomBytes + row_off + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]),
-                       pack_pair<kBf16>(e[2], e[3]), pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
+          st_shared_v4(ds_addr + row_off + ((g ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]), pack_pair<kBf16>(e[2], e[3]),
+                       pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
         }
       }
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->ds_full));
-      // the dQ partial of this (query block, KV block) pair: lane = query row
-      if (!warp_mbar_poll(smem_u32(&ctl->dq_full), ph, ac, kAttnTimeoutSoftmaxO, lane)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      {
-        const int qrow = q0 + r;
-        float *dst = p.dq_acc + (static_cast<long long>(head) * p.n_ctx + qrow) * kBwdD;
-#pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          uint32_t v[32];
-          tmem_ld_32x32(lane_base + kColDq + c2 * 32, v);
-          tmem_ld_wait();
-          if (qrow < p.n_ctx) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              red_add_v4(dst + c2 * 32 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
-                         __uint_as_float(v[i + 3]));
-          }
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->dq_free));
     }
+    if (ok && n_it > 0) ok = dq_readout(n_it - 1);
     if (ok && n_it > 0) {
-      // every MMA has completed (the last dq_full was committed after them): dV and dK of this KV block.
-      // The TMEM loads are warp-wide; rows past n_ctx take part in them and store nothing.
-      const long long g = (static_cast<long long>(head) * p.n_ctx + kv_row) * kBwdD;
+      // every MMA has completed (the last dq_full was committed after them): dV and dK of this KV block, this
+      // thread's 32 columns. The TMEM loads are warp-wide; rows past n_ctx take part in them and store nothing.
+      const long long g = (static_cast<long long>(head) * p.n_ctx + kv_row) * kBwdD + half * 32;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const float scale = which == 0 ? 1.0f : p.sm_scale;
         uint4 *dst = reinterpret_cast<uint4 *>(static_cast<char *>(which == 0 ? p.dv : p.dk) + g * 2);
+        uint32_t v[32];
+        tmem_ld_32x32(lane_base + (which == 0 ? kColDv : kColDk) + half * 32, v);
+        tmem_ld_wait();
+        if (kv_row < p.n_ctx) {
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          uint32_t v[32];
-          tmem_ld_32x32(lane_base + (which == 0 ? kColDv : kColDk) + c2 * 32, v);
-          tmem_ld_wait();
-          if (kv_row < p.n_ctx) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 w;
-              w.x = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 0]) * scale, __uint_as_float(v[q * 8 + 1]) * scale);
-              w.y = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 2]) * scale, __uint_as_float(v[q * 8 + 3]) * scale);
-              w.z = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 4]) * scale, __uint_as_float(v[q * 8 + 5]) * scale);
-              w.w = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 6]) * scale, __uint_as_float(v[q * 8 + 7]) * scale);
-              dst[c2 * 4 + q] = w;
-            }
+          for (int q = 0; q < 4; ++q) {
+            uint4 w;
+            w.x = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 0]) * scale, __uint_as_float(v[q * 8 + 1]) * scale);
+            w.y = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 2]) * scale, __uint_as_float(v[q * 8 + 3]) * scale);
+            w.z = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 4]) * scale, __uint_as_float(v[q * 8 + 5]) * scale);
+            w.w = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 6]) * scale, __uint_as_float(v[q * 8 + 7]) * scale);
+            dst[q] = w;
           }
         }
       }
