@@ -51,8 +51,8 @@ TXD_API int tx_attn_fwd_host(const tx_attn_problem *problem, const void *q, cons
  * are contiguous [batch, heads, n_ctx, head_dim] device tensors of the problem's type, `m` is [batch, heads, n_ctx]
  * fp32. Same mathematics as the reference (P recomputed from the scores and `m`, delta = rowsum(o * d_o),
  * dS = P * (dP - delta), P and dS rounded to the input type before their dots). head_dim 64 runs one fused kernel (all
- * five dots per block pair on tensor memory); head_dim 128 runs, per (batch, head), five tt.dot GEMMs of this library around
- * three element-wise kernels through a workspace of 10 * n_ctx^2 bytes per head in flight. Workspaces are kept per device. Asynchronous on `stream`; tx_attn_check reports its bounded waits too. */
+ * five dots per block pair on tensor memory, dq through fp32 reductions), head_dim 128 two (dk and dv; dq). Workspaces
+ * (row sums, the fp32 dq accumulator) are kept per device. Asynchronous on `stream`; tx_attn_check reports its bounded waits too. */
 TXD_API int tx_attn_bwd(const tx_attn_problem *problem, const void *q, const void *k, const void *v, const void *o,
                         const void *d_o, const float *m, void *dq, void *dk, void *dv, void *stream);
 

@@ -223,13 +223,15 @@ def test_autograd_function_against_oracle(A, z, h, n, d, causal, dtype):
         assert err <= tol, err
 
 
-def test_both_backward_paths_agree_at_head_dim_64(A, monkeypatch):
-    """head_dim 64 runs the fused backward kernel, other sizes the GEMM composition; the composition can be forced
-    for head_dim 64 too, and must give the same gradients up to the rounding of its fp16 intermediates."""
+@pytest.mark.parametrize("d", [64, 128])
+def test_both_backward_paths_agree(A, monkeypatch, d):
+    """The backward runs fused kernels (one at head_dim 64, two at 128); a composition of tt.dot GEMMs and
+    element-wise kernels can be forced instead and must give the same gradients up to the rounding of its
+    fp16 intermediates."""
     from oracle import attn_oracle as AO
-    q, k, v = draw(1, 3, 640, 64, f16, seed=12)
+    q, k, v = draw(1, 3, 640, d, f16, seed=12)
     g = torch.Generator().manual_seed(13)
-    d_o = torch.randn((1, 3, 640, 64), generator=g).to(f16)
+    d_o = torch.randn((1, 3, 640, d), generator=g).to(f16)
     qc, kc, vc, dc = (x.cuda() for x in (q, k, v, d_o))
     o, m = A.attention_forward(qc, kc, vc, True, 0.5, return_m=True, check=True)
     fused = A.attention_backward(qc, kc, vc, o, m, dc, True, 0.5, check=True)

@@ -1,5 +1,6 @@
-// Fused attention backward for sm_100a, head_dim 64: dK, dV and dQ in one kernel, five tt.dot per (KV block,
-// query block) pair with all accumulators in tensor memory. The mathematics is the reference's
+// Fused attention backward for sm_100a. head_dim 64: dK, dV and dQ in one kernel, five tt.dot per (KV block,
+// query block) pair with all accumulators in tensor memory; head_dim 128: the same kernel without the dQ dot, and a
+// second kernel for dQ (tensor memory holds four 128-column accumulators, not five). The mathematics is the reference's
 // (pass/LoopSplit/06-fused-attention.py: _attn_bwd_dkdv :351-400, _attn_bwd_dq :404-448):
 //
 //   S^T  = K Q^T                    P^T = exp2(S^T * scale - M[q])      (M = the forward's m + log2 l)
@@ -33,9 +34,7 @@ constexpr int kBwdComputeWarps = 8;   // two threads per TMEM lane, 64 columns e
 constexpr int kBwdProducerWarp = 8;
 constexpr int kBwdMmaWarp = 9;
 constexpr int kBwdThreads = 10 * 32;
-constexpr int kBwdStages = 3;
-constexpr int kBwdD = 64;
-constexpr uint32_t kBwdTileBytes = kTileRows * kBwdD * 2;  // one K / V / Q / dO tile: 16 KB, one swizzle atom wide
+constexpr int kBwdStages = 3;  // ring slots at head_dim 64; head_dim 128 has shared memory for one
 
 struct AttnBwdParams {
   CUtensorMap tmap_q, tmap_k, tmap_v, tmap_do;  // 3-D {64, n_ctx, batch*heads}, box {64, 128, 1}, SWIZZLE_128B
@@ -97,14 +96,20 @@ __device__ __forceinline__ void bwd_row_p(uint32_t (&s)[64], const float *m_s, f
   }
 }
 
-template <bool kBf16>
+// kD = 64: dK, dV and dQ. kD = 128: dK and dV only (tensor memory has no room for the fifth accumulator); dQ comes from
+// attn_bwd_dq_kernel below, as in the reference's two passes.
+template <bool kBf16, int kD>
 __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
+  constexpr bool kWithDq = kD == 64;
+  constexpr int kStagesT = kD == 64 ? kBwdStages : 1;
+  constexpr int kAtoms = kD / 64;
+  constexpr uint32_t kBwdTileBytes = kTileRows * kD * 2;  // one K / V / Q / dO tile, kAtoms swizzle atoms wide
   extern __shared__ uint8_t attn_bwd_smem_raw[];
   const uint32_t raw = smem_u32(attn_bwd_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   const uint32_t k_addr = base, v_addr = base + kBwdTileBytes;
   const uint32_t ring_addr = base + 2 * kBwdTileBytes;             // per stage: Q tile, dO tile
-  const uint32_t pt_addr = ring_addr + kBwdStages * 2 * kBwdTileBytes;  // P^T  [128 KV rows][128 queries], 2 atoms
+  const uint32_t pt_addr = ring_addr + kStagesT * 2 * kBwdTileBytes;  // P^T  [128 KV rows][128 queries], 2 atoms
   const uint32_t ds_addr = pt_addr + kPBytes;                      // dS^T, same layout
   AttnBwdCtl *ctl = reinterpret_cast<AttnBwdCtl *>(attn_bwd_smem_raw + (ds_addr + kPBytes - raw));
 
@@ -127,7 +132,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ctl->kv_full), 1);
-    for (int s = 0; s < kBwdStages; ++s) {
+    for (int s = 0; s < kStagesT; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 2);  // the TMA transaction and the M / delta vectors
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
@@ -153,8 +158,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
-  // TMEM columns: S^T 0..127 | dP^T 128..255 | dV 256..319 | dK 320..383 | dQ partial 384..447
-  constexpr uint32_t kColSt = 0, kColDp = 128, kColDv = 256, kColDk = 320, kColDq = 384;
+  // TMEM columns: S^T 0..127 | dP^T 128..255 | dV 256.. | dK 256+kD.. | (kD 64) dQ partial 384..447
+  constexpr uint32_t kColSt = 0, kColDp = 128, kColDv = 256, kColDk = 256 + kD, kColDq = 384;
 
   if (warp == kBwdProducerWarp) {
     // ------------------------------ producer ------------------------------
@@ -162,15 +167,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     if (issuer) {
       const uint32_t bar = smem_u32(&ctl->kv_full);
       mbar_arrive_expect_tx(bar, 2 * kBwdTileBytes);
-      tma_load_3d(k_addr, &p.tmap_k, 0, kv0, head, bar);
-      tma_load_3d(v_addr, &p.tmap_v, 0, kv0, head, bar);
+      for (int a = 0; a < kAtoms; ++a) {
+        tma_load_3d(k_addr + a * kAtomBytes, &p.tmap_k, a * 64, kv0, head, bar);
+        tma_load_3d(v_addr + a * kAtomBytes, &p.tmap_v, a * 64, kv0, head, bar);
+      }
     }
     __syncwarp();
     int issued = 0;
     bool ok = true;
     for (int it = 0; ok && it < n_it && !p.inject_stall; ++it) {
-      const int slot = it % kBwdStages;
-      const uint32_t phase = static_cast<uint32_t>(it / kBwdStages) & 1u;
+      const int slot = it % kStagesT;
+      const uint32_t phase = static_cast<uint32_t>(it / kStagesT) & 1u;
       if (!warp_mbar_poll(smem_u32(&ctl->empty[slot]), phase ^ 1u, ac, kAttnTimeoutProducer, lane)) {
         ok = false;
         break;
@@ -179,8 +186,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       const uint32_t bar = smem_u32(&ctl->full[slot]);
       if (issuer) {
         mbar_arrive_expect_tx(bar, 2 * kBwdTileBytes);
-        tma_load_3d(ring_addr + slot * 2 * kBwdTileBytes, &p.tmap_q, 0, q0, head, bar);
-        tma_load_3d(ring_addr + slot * 2 * kBwdTileBytes + kBwdTileBytes, &p.tmap_do, 0, q0, head, bar);
+        for (int a = 0; a < kAtoms; ++a) {
+          tma_load_3d(ring_addr + slot * 2 * kBwdTileBytes + a * kAtomBytes, &p.tmap_q, a * 64, q0, head, bar);
+          tma_load_3d(ring_addr + slot * 2 * kBwdTileBytes + kBwdTileBytes + a * kAtomBytes, &p.tmap_do, a * 64, q0, head, bar);
+        }
       }
       // M and delta of the 128 query rows (rows past n_ctx are masked later; give them harmless values)
       for (int r = lane; r < kTileRows; r += 32) {
@@ -197,11 +206,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     if (ctl->abort_flag) {  // copies in flight must land before shared memory goes away
       if (lane == 0) {
         mbar_wait_timed(smem_u32(&ctl->kv_full), 0u, ac, kAttnTimeoutDrain);
-        const int first = issued > kBwdStages ? issued - kBwdStages : 0;
+        const int first = issued > kStagesT ? issued - kStagesT : 0;
         for (int it = first; it < issued; ++it) {
           const unsigned long long t0 = global_timer_ns();
-          const uint32_t bar = smem_u32(&ctl->full[it % kBwdStages]);
-          const uint32_t ph = static_cast<uint32_t>(it / kBwdStages) & 1u;
+          const uint32_t bar = smem_u32(&ctl->full[it % kStagesT]);
+          const uint32_t ph = static_cast<uint32_t>(it / kStagesT) & 1u;
           while (!mbar_try_wait(bar, ph))
             if (global_timer_ns() - t0 > ac.limit_ns) break;
         }
@@ -222,15 +231,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     auto kmajor_step = [](int i) { return static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u; };
     auto mn_step = [](int i) { return static_cast<uint32_t>(i) * (16u * 128u >> 4); };
     bool ok = warp_mbar_poll(smem_u32(&ctl->kv_full), 0u, ac, kAttnTimeoutMmaOperand, lane);
-    auto stage_q = [&](int it) { return ring_addr + static_cast<uint32_t>(it % kBwdStages) * 2 * kBwdTileBytes; };
+    auto stage_q = [&](int it) { return ring_addr + static_cast<uint32_t>(it % kStagesT) * 2 * kBwdTileBytes; };
     auto wait_stage = [&](int it) {
-      return warp_mbar_poll(smem_u32(&ctl->full[it % kBwdStages]), static_cast<uint32_t>(it / kBwdStages) & 1u, ac,
+      return warp_mbar_poll(smem_u32(&ctl->full[it % kStagesT]), static_cast<uint32_t>(it / kStagesT) & 1u, ac,
                             kAttnTimeoutMmaOperand, lane);
     };
     auto issue_st = [&](int it) {  // S^T = K Q^T
       const uint32_t q_addr = stage_q(it);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < kD / 16; ++i)
         if (issuer)
           umma_f16(tmem_base + kColSt, desc64(desc_hi, (lo_of(k_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(q_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
@@ -240,7 +249,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     auto issue_dp = [&](int it) {  // dP^T = V dO^T
       const uint32_t do_addr = stage_q(it) + kBwdTileBytes;
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < kD / 16; ++i)
         if (issuer)
           umma_f16(tmem_base + kColDp, desc64(desc_hi, (lo_of(v_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(do_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
@@ -254,7 +263,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       issue_dp(0);
     }
     for (int it = 0; ok && it < n_it; ++it) {
-      const int slot = it % kBwdStages;
+      const int slot = it % kStagesT;
       const uint32_t ph = static_cast<uint32_t>(it) & 1u;
       const uint32_t q_addr = stage_q(it), do_addr = q_addr + kBwdTileBytes;
       // dV += P^T dO, then the next block's scores (the compute warps hold S^T(it) in registers by now)
@@ -266,13 +275,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
           umma_f16(tmem_base + kColDv, desc64(desc_hi, (lo_of(pt_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(do_addr) | lbo_atom) + mn_step(i)), p.idesc_acc, (it > 0 || i > 0) ? 1u : 0u);
       __syncwarp();
-      if (it + 1 < n_it) {
+      if (kStagesT > 1 && it + 1 < n_it) {
         if (!wait_stage(it + 1)) break;
         issue_st(it + 1);
       }
       // dK += dS^T Q, dQ partial = dS K, then the next block's dP^T
       if (!warp_mbar_poll(smem_u32(&ctl->ds_full), ph, ac, kAttnTimeoutMmaP, lane)) break;
-      if (it > 0 && !warp_mbar_poll(smem_u32(&ctl->dq_free), ph ^ 1u, ac, kAttnTimeoutMmaP, lane)) break;
+      if (kWithDq && it > 0 && !warp_mbar_poll(smem_u32(&ctl->dq_free), ph ^ 1u, ac, kAttnTimeoutMmaP, lane)) break;
       tc_fence_after();
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -280,7 +289,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
           umma_f16(tmem_base + kColDk, desc64(desc_hi, (lo_of(ds_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(q_addr) | lbo_atom) + mn_step(i)), p.idesc_acc, (it > 0 || i > 0) ? 1u : 0u);
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < (kWithDq ? 8 : 0); ++i)
         if (issuer)
           umma_f16(tmem_base + kColDq, desc64(desc_hi, (lo_of(ds_addr) | lbo_atom) + mn_step(i)),
                    desc64(desc_hi, (lo_of(k_addr) | lbo_atom) + mn_step(i)), p.idesc_dq, i > 0 ? 1u : 0u);
@@ -289,7 +298,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
         tc_commit(smem_u32(&ctl->empty[slot]));
       }
       __syncwarp();
-      if (it + 1 < n_it) issue_dp(it + 1);
+      if (it + 1 < n_it) {
+        if (kStagesT == 1) {  // one ring slot: the next tiles can only arrive once this block's dots are through
+          if (!wait_stage(it + 1)) break;
+          tc_fence_after();
+          issue_st(it + 1);
+        }
+        issue_dp(it + 1);
+      }
     }
     // every MMA issued above has completed before TMEM and shared memory are given back (also after an abort)
     if (issuer) tc_commit(smem_u32(&ctl->drain));
@@ -320,7 +336,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       if (!warp_mbar_poll(smem_u32(&ctl->dq_full), static_cast<uint32_t>(it_done) & 1u, ac, kAttnTimeoutSoftmaxO, lane)) return false;
       tc_fence_after();
       const int qrow = (i_lo + it_done) * kTileRows + r;
-      float *dst = p.dq_acc + (static_cast<long long>(head) * p.n_ctx + qrow) * kBwdD + half * 32;
+      float *dst = p.dq_acc + (static_cast<long long>(head) * p.n_ctx + qrow) * 64 + half * 32;
       uint32_t v[32];
       tmem_ld_32x32(lane_base + kColDq + half * 32, v);
       tmem_ld_wait();
@@ -335,8 +351,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       return true;
     };
     for (int it = 0; it < n_it; ++it) {
-      const int slot = it % kBwdStages;
-      const uint32_t ring_phase = static_cast<uint32_t>(it / kBwdStages) & 1u;
+      const int slot = it % kStagesT;
+      const uint32_t ring_phase = static_cast<uint32_t>(it / kStagesT) & 1u;
       const uint32_t ph = static_cast<uint32_t>(it) & 1u;
       const int q0 = (i_lo + it) * kTileRows;
       const bool masked = (p.causal && i_lo + it == j) || kv_ragged || q0 + kTileRows > p.n_ctx;
@@ -359,7 +375,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->pt_full));
       // the previous block's dQ partial, while the tensor pipe works on dV and the next scores
-      if (it > 0 && !dq_readout(it - 1)) {
+      if (kWithDq && it > 0 && !dq_readout(it - 1)) {
         ok = false;
         break;
       }
@@ -394,27 +410,294 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->ds_full));
     }
-    if (ok && n_it > 0) ok = dq_readout(n_it - 1);
+    if (ok && n_it > 0) {
+      if (kWithDq) ok = dq_readout(n_it - 1);
+      else ok = warp_mbar_poll(smem_u32(&ctl->dq_full), static_cast<uint32_t>(n_it - 1) & 1u, ac, kAttnTimeoutSoftmaxO, lane);
+    }
     if (ok && n_it > 0) {
       // every MMA has completed (the last dq_full was committed after them): dV and dK of this KV block, this
       // thread's 32 columns. The TMEM loads are warp-wide; rows past n_ctx take part in them and store nothing.
-      const long long g = (static_cast<long long>(head) * p.n_ctx + kv_row) * kBwdD + half * 32;
+      tc_fence_after();
+      const long long g = (static_cast<long long>(head) * p.n_ctx + kv_row) * kD + half * (kD / 2);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const float scale = which == 0 ? 1.0f : p.sm_scale;
         uint4 *dst = reinterpret_cast<uint4 *>(static_cast<char *>(which == 0 ? p.dv : p.dk) + g * 2);
-        uint32_t v[32];
-        tmem_ld_32x32(lane_base + (which == 0 ? kColDv : kColDk) + half * 32, v);
+#pragma unroll
+        for (int c = 0; c < kD / 64; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(lane_base + (which == 0 ? kColDv : kColDk) + half * (kD / 2) + c * 32, v);
+          tmem_ld_wait();
+          if (kv_row < p.n_ctx) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              w.x = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 0]) * scale, __uint_as_float(v[q * 8 + 1]) * scale);
+              w.y = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 2]) * scale, __uint_as_float(v[q * 8 + 3]) * scale);
+              w.z = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 4]) * scale, __uint_as_float(v[q * 8 + 5]) * scale);
+              w.w = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 6]) * scale, __uint_as_float(v[q * 8 + 7]) * scale);
+              dst[c * 4 + q] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kBwdMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// dQ for head_dim 128 (reference _attn_bwd_dq, :404-448): one CTA per query block of 128 rows walks the KV blocks it
+// sees. S = Q K^T and dP = dO V^T in tensor memory, dS = P * (dP - delta) with the row's own M and delta, written to
+// shared memory as the A operand of dQ += dS K (K read MN-major from the tile that S used K-major).
+// ---------------------------------------------------------------------------------------------------------------
+struct AttnBwdDqParams {
+  CUtensorMap tmap_q, tmap_k, tmap_v, tmap_do;  // 3-D {128, n_ctx, batch*heads}, box {64, 128, 1}, SWIZZLE_128B
+  const float *m, *delta;
+  void *dq;
+  uint32_t *status;
+  unsigned long long wait_limit_ns;
+  float qk_scale, sm_scale;
+  int32_t n_ctx, heads_total, q_blocks, causal;
+  uint32_t idesc_s;    // 128 x 128, A and B K-major
+  uint32_t idesc_dq;   // 128 x 128, A K-major, B MN-major
+};
+
+struct AttnBwdDqCtl {
+  uint64_t q_full, full[2], empty[2], sdp_full, ds_full, done;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnBwdDqParams p) {
+  constexpr int kD = 128;
+  constexpr int kStg = 2;
+  constexpr uint32_t kTile = kTileRows * kD * 2;  // 32 KB, two atoms
+  extern __shared__ uint8_t attn_bwd_smem_raw[];
+  const uint32_t raw = smem_u32(attn_bwd_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t q_addr = base, do_addr = base + kTile;
+  const uint32_t ring_addr = base + 2 * kTile;        // per stage: K tile, V tile
+  const uint32_t ds_addr = ring_addr + kStg * 2 * kTile;  // dS [128 queries][128 KV], 2 atoms
+  AttnBwdDqCtl *ctl = reinterpret_cast<AttnBwdDqCtl *>(attn_bwd_smem_raw + (ds_addr + kPBytes - raw));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // late (heavy, when causal) query blocks first inside a head
+  const int head = static_cast<int>(blockIdx.x) / p.q_blocks;
+  const int i = p.q_blocks - 1 - static_cast<int>(blockIdx.x) % p.q_blocks;
+  const int q0 = i * kTileRows;
+  const int kv_blocks = (p.n_ctx + kTileRows - 1) / kTileRows;
+  const int n_it = p.causal ? min(kv_blocks, i + 1) : kv_blocks;
+
+  AbortCtl ac;
+  ac.flag = &ctl->abort_flag;
+  ac.status = p.status;
+  ac.limit_ns = p.wait_limit_ns;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctl->q_full), 1);
+    for (int s = 0; s < kStg; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->sdp_full), 1);
+    mbar_init(smem_u32(&ctl->ds_full), 2 * kTileRows);
+    mbar_init(smem_u32(&ctl->done), 1);
+    ctl->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&p.tmap_q);
+    tma_prefetch_desc(&p.tmap_k);
+    tma_prefetch_desc(&p.tmap_v);
+    tma_prefetch_desc(&p.tmap_do);
+  }
+  if (warp == kBwdMmaWarp) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  constexpr uint32_t kColS = 0, kColDp = 128, kColDq = 256;
+
+  if (warp == kBwdProducerWarp) {
+    const bool issuer = elect_one();
+    if (issuer) {
+      const uint32_t bar = smem_u32(&ctl->q_full);
+      mbar_arrive_expect_tx(bar, 2 * kTile);
+      for (int a = 0; a < 2; ++a) {
+        tma_load_3d(q_addr + a * kAtomBytes, &p.tmap_q, a * 64, q0, head, bar);
+        tma_load_3d(do_addr + a * kAtomBytes, &p.tmap_do, a * 64, q0, head, bar);
+      }
+    }
+    __syncwarp();
+    int issued = 0;
+    for (int it = 0; it < n_it; ++it) {
+      const int slot = it % kStg;
+      const uint32_t phase = static_cast<uint32_t>(it / kStg) & 1u;
+      if (!warp_mbar_poll(smem_u32(&ctl->empty[slot]), phase ^ 1u, ac, kAttnTimeoutProducer, lane)) break;
+      if (issuer) {
+        const uint32_t bar = smem_u32(&ctl->full[slot]);
+        mbar_arrive_expect_tx(bar, 2 * kTile);
+        for (int a = 0; a < 2; ++a) {
+          tma_load_3d(ring_addr + slot * 2 * kTile + a * kAtomBytes, &p.tmap_k, a * 64, it * kTileRows, head, bar);
+          tma_load_3d(ring_addr + slot * 2 * kTile + kTile + a * kAtomBytes, &p.tmap_v, a * 64, it * kTileRows, head, bar);
+        }
+      }
+      __syncwarp();
+      ++issued;
+    }
+    if (ctl->abort_flag) {
+      if (lane == 0) {
+        mbar_wait_timed(smem_u32(&ctl->q_full), 0u, ac, kAttnTimeoutDrain);
+        const int first = issued > kStg ? issued - kStg : 0;
+        for (int it = first; it < issued; ++it) {
+          const unsigned long long t0 = global_timer_ns();
+          const uint32_t bar = smem_u32(&ctl->full[it % kStg]);
+          const uint32_t ph = static_cast<uint32_t>(it / kStg) & 1u;
+          while (!mbar_try_wait(bar, ph))
+            if (global_timer_ns() - t0 > ac.limit_ns) break;
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == kBwdMmaWarp) {
+    const bool issuer = elect_one();
+    auto desc64 = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+    const uint32_t desc_hi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+    const uint32_t lbo_unused = 1u << 16;
+    const uint32_t lbo_atom = ((static_cast<uint32_t>(kAtomBytes) >> 4) & 0x3FFFu) << 16;
+    auto lo_of = [](uint32_t addr) { return (addr & 0x3FFFFu) >> 4; };
+    auto kmajor_step = [](int s) { return static_cast<uint32_t>(s >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(s & 3) * 2u; };
+    auto mn_step = [](int s) { return static_cast<uint32_t>(s) * (16u * 128u >> 4); };
+    auto issue_sdp = [&](int it) {  // S = Q K^T, dP = dO V^T
+      const uint32_t k_addr = ring_addr + static_cast<uint32_t>(it % kStg) * 2 * kTile, v_addr = k_addr + kTile;
+#pragma unroll
+      for (int s = 0; s < kD / 16; ++s)
+        if (issuer)
+          umma_f16(tmem_base + kColS, desc64(desc_hi, (lo_of(q_addr) | lbo_unused) + kmajor_step(s)),
+                   desc64(desc_hi, (lo_of(k_addr) | lbo_unused) + kmajor_step(s)), p.idesc_s, s > 0 ? 1u : 0u);
+#pragma unroll
+      for (int s = 0; s < kD / 16; ++s)
+        if (issuer)
+          umma_f16(tmem_base + kColDp, desc64(desc_hi, (lo_of(do_addr) | lbo_unused) + kmajor_step(s)),
+                   desc64(desc_hi, (lo_of(v_addr) | lbo_unused) + kmajor_step(s)), p.idesc_s, s > 0 ? 1u : 0u);
+      if (issuer) tc_commit(smem_u32(&ctl->sdp_full));
+      __syncwarp();
+    };
+    auto wait_stage = [&](int it) {
+      return warp_mbar_poll(smem_u32(&ctl->full[it % kStg]), static_cast<uint32_t>(it / kStg) & 1u, ac, kAttnTimeoutMmaOperand,
+                            lane);
+    };
+    bool ok = warp_mbar_poll(smem_u32(&ctl->q_full), 0u, ac, kAttnTimeoutMmaOperand, lane);
+    if (ok && n_it > 0) ok = wait_stage(0);
+    if (ok && n_it > 0) {
+      tc_fence_after();
+      issue_sdp(0);
+    }
+    for (int it = 0; ok && it < n_it; ++it) {
+      const uint32_t k_addr = ring_addr + static_cast<uint32_t>(it % kStg) * 2 * kTile;
+      if (!warp_mbar_poll(smem_u32(&ctl->ds_full), static_cast<uint32_t>(it) & 1u, ac, kAttnTimeoutMmaP, lane)) break;
+      tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 8; ++s)  // dQ += dS K : 128 x 128 x 16 each
+        if (issuer)
+          umma_f16(tmem_base + kColDq, desc64(desc_hi, (lo_of(ds_addr) | lbo_unused) + kmajor_step(s)),
+                   desc64(desc_hi, (lo_of(k_addr) | lbo_atom) + mn_step(s)), p.idesc_dq, (it > 0 || s > 0) ? 1u : 0u);
+      if (issuer) tc_commit(smem_u32(&ctl->empty[it % kStg]));
+      __syncwarp();
+      if (it + 1 < n_it) {
+        if (!wait_stage(it + 1)) break;
+        tc_fence_after();
+        issue_sdp(it + 1);  // S and dP of block `it` are in the compute warps' registers
+      }
+    }
+    if (issuer) tc_commit(smem_u32(&ctl->done));
+    __syncwarp();
+    if (lane == 0) {
+      const unsigned long long t0 = global_timer_ns();
+      while (!mbar_try_wait(smem_u32(&ctl->done), 0u)) {
+        if (global_timer_ns() - t0 > ac.limit_ns) {
+          ctl->abort_flag = 1;
+          atomicCAS(ac.status, 0u, static_cast<uint32_t>(kAttnTimeoutDrain));
+          break;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int half = warp >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t row_off = static_cast<uint32_t>(half * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128);
+    const int row_xor = r & 7;
+    const int qrow = q0 + r;
+    const long long grow = static_cast<long long>(head) * p.n_ctx + qrow;
+    const float m_row = qrow < p.n_ctx ? p.m[grow] : 0.f;
+    const float delta_row = qrow < p.n_ctx ? p.delta[grow] : 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      if (!warp_mbar_poll(smem_u32(&ctl->sdp_full), static_cast<uint32_t>(it) & 1u, ac, kAttnTimeoutSoftmaxS, lane)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int c0 = it * kTileRows + half * 64;
+      const bool masked = (p.causal && it == i) || (it + 1) * kTileRows > p.n_ctx || q0 + kTileRows > p.n_ctx;
+#pragma unroll
+      for (int c4 = 0; c4 < 2; ++c4) {
+        uint32_t sv[32], dp[32];
+        tmem_ld_32x32(lane_base + kColS + half * 64 + c4 * 32, sv);
+        tmem_ld_32x32(lane_base + kColDp + half * 64 + c4 * 32, dp);
         tmem_ld_wait();
-        if (kv_row < p.n_ctx) {
+#pragma unroll
+        for (int gg = 0; gg < 4; ++gg) {
+          float e[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int c = c4 * 32 + gg * 8 + u;
+            float pv = fast_exp2(fmaf(__uint_as_float(sv[gg * 8 + u]), p.qk_scale, -m_row));
+            if (masked) {
+              const int kvc = c0 + c;
+              const bool valid = kvc < p.n_ctx && qrow < p.n_ctx && (!p.causal || qrow >= kvc);
+              pv = valid ? pv : 0.f;
+            }
+            e[u] = pv * (__uint_as_float(dp[gg * 8 + u]) - delta_row);
+          }
+          const int g = c4 * 4 + gg;
+          st_shared_v4(ds_addr + row_off + ((g ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]), pack_pair<kBf16>(e[2], e[3]),
+                       pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->ds_full));
+    }
+    if (ok && n_it > 0) ok = warp_mbar_poll(smem_u32(&ctl->done), 0u, ac, kAttnTimeoutSoftmaxO, lane);
+    if (ok && n_it > 0) {
+      tc_fence_after();
+      uint4 *dst = reinterpret_cast<uint4 *>(static_cast<char *>(p.dq) + (grow * kD + half * 64) * 2);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(lane_base + kColDq + half * 64 + c * 32, v);
+        tmem_ld_wait();
+        if (qrow < p.n_ctx) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 w;
-            w.x = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 0]) * scale, __uint_as_float(v[q * 8 + 1]) * scale);
-            w.y = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 2]) * scale, __uint_as_float(v[q * 8 + 3]) * scale);
-            w.z = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 4]) * scale, __uint_as_float(v[q * 8 + 5]) * scale);
-            w.w = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 6]) * scale, __uint_as_float(v[q * 8 + 7]) * scale);
-            dst[q] = w;
+            w.x = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 0]) * p.sm_scale, __uint_as_float(v[q * 8 + 1]) * p.sm_scale);
+            w.y = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 2]) * p.sm_scale, __uint_as_float(v[q * 8 + 3]) * p.sm_scale);
+            w.z = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 4]) * p.sm_scale, __uint_as_float(v[q * 8 + 5]) * p.sm_scale);
+            w.w = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 6]) * p.sm_scale, __uint_as_float(v[q * 8 + 7]) * p.sm_scale);
+            dst[c * 4 + q] = w;
           }
         }
       }

@@ -130,8 +130,12 @@ int device_state(DeviceState **out) {
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_dq_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_dq_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     st.attr_set = true;
   }
   *out = &st;
@@ -258,35 +262,38 @@ __global__ void attn_bwd_dq_convert_kernel(const float *acc, T *dq, long long co
     dq[i] = from_f32<T>(acc[i] * sm_scale);
 }
 
-// head_dim 64: one fused kernel (attn_bwd_kernel.cuh) between the delta pre-pass and the dq conversion
+// The fused backward (attn_bwd_kernel.cuh) between the delta pre-pass and, at head_dim 64, the dq conversion;
+// at head_dim 128 a second kernel computes dq.
 template <typename T>
 int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const T *k, const T *v, const T *o, const T *d_o,
                    const float *m, T *dq, T *dk, T *dv, cudaStream_t stream) {
   const bool bf16 = pr->dtype == TXD_BF16;
+  const int d = pr->head_dim;
   const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
   const long long rows = heads_total * pr->n_ctx;
   float *delta = static_cast<float *>(st->bwd_ws);
   float *dq_acc = delta + ((rows + 63) / 64) * 64;
-  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, pr->head_dim);
+  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
   TXA_CUDA(cudaGetLastError());
-  TXA_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(rows) * 64 * sizeof(float), stream));
+  if (d == 64) TXA_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(rows) * 64 * sizeof(float), stream));
+  unsigned long long wait_limit_ns = 2000ull * 1000 * 1000;
+  if (const char *e = getenv("TXD_WAIT_LIMIT_MS")) {
+    const long ms = atol(e);
+    if (ms > 0) wait_limit_ns = static_cast<unsigned long long>(ms) * 1000 * 1000;
+  }
   txa::AttnBwdParams prm = {};
   int rc;
-  if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_do, d_o, bf16, heads_total, pr->n_ctx, 64, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_do, d_o, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
   prm.m = m;
   prm.delta = delta;
   prm.dq_acc = dq_acc;
   prm.dk = dk;
   prm.dv = dv;
   prm.status = st->status;
-  prm.wait_limit_ns = 2000ull * 1000 * 1000;
-  if (const char *e = getenv("TXD_WAIT_LIMIT_MS")) {
-    const long ms = atol(e);
-    if (ms > 0) prm.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000 * 1000;
-  }
+  prm.wait_limit_ns = wait_limit_ns;
   if (const char *e = getenv("TXD_INJECT_STALL")) prm.inject_stall = atoi(e) != 0;
   prm.qk_scale = pr->sm_scale * 1.44269504f;
   prm.sm_scale = pr->sm_scale;
@@ -295,16 +302,45 @@ int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   prm.kv_blocks = (pr->n_ctx + 127) / 128;
   prm.causal = pr->causal ? 1 : 0;
   prm.idesc_st = attn_idesc(bf16, false, 128);
-  prm.idesc_acc = attn_idesc(bf16, true, 64);
+  prm.idesc_acc = attn_idesc(bf16, true, d);
   prm.idesc_dq = attn_idesc(bf16, true, 64) | (1u << 15);  // A operand MN-major as well
-  const size_t smem = 2 * txa::kBwdTileBytes + txa::kBwdStages * 2 * txa::kBwdTileBytes + 2 * txa::kPBytes +
-                      sizeof(txa::AttnBwdCtl) + 1024;
+  const size_t tile = static_cast<size_t>(128) * d * 2;
+  const size_t stages = d == 64 ? txa::kBwdStages : 1;
+  const size_t smem = 2 * tile + stages * 2 * tile + 2 * txa::kPBytes + sizeof(txa::AttnBwdCtl) + 1024;
   const unsigned grid = static_cast<unsigned>(heads_total * prm.kv_blocks);
-  if (bf16) txa::attn_bwd_kernel<true><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
-  else txa::attn_bwd_kernel<false><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
-  TXA_CUDA(cudaGetLastError());
-  attn_bwd_dq_convert_kernel<T><<<148 * 8, 256, 0, stream>>>(dq_acc, dq, rows * 64, pr->sm_scale);
-  TXA_CUDA(cudaGetLastError());
+  if (d == 64) {
+    if (bf16) txa::attn_bwd_kernel<true, 64><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
+    else txa::attn_bwd_kernel<false, 64><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
+    TXA_CUDA(cudaGetLastError());
+    attn_bwd_dq_convert_kernel<T><<<148 * 8, 256, 0, stream>>>(dq_acc, dq, rows * 64, pr->sm_scale);
+    TXA_CUDA(cudaGetLastError());
+  } else {
+    if (bf16) txa::attn_bwd_kernel<true, 128><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
+    else txa::attn_bwd_kernel<false, 128><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
+    TXA_CUDA(cudaGetLastError());
+    txa::AttnBwdDqParams dqp = {};
+    dqp.tmap_q = prm.tmap_q;
+    dqp.tmap_k = prm.tmap_k;
+    dqp.tmap_v = prm.tmap_v;
+    dqp.tmap_do = prm.tmap_do;
+    dqp.m = m;
+    dqp.delta = delta;
+    dqp.dq = dq;
+    dqp.status = st->status;
+    dqp.wait_limit_ns = wait_limit_ns;
+    dqp.qk_scale = prm.qk_scale;
+    dqp.sm_scale = pr->sm_scale;
+    dqp.n_ctx = pr->n_ctx;
+    dqp.heads_total = prm.heads_total;
+    dqp.q_blocks = prm.kv_blocks;
+    dqp.causal = prm.causal;
+    dqp.idesc_s = attn_idesc(bf16, false, 128);
+    dqp.idesc_dq = attn_idesc(bf16, true, 128);
+    const size_t dq_smem = 2 * tile + 2 * 2 * tile + txa::kPBytes + sizeof(txa::AttnBwdDqCtl) + 1024;
+    if (bf16) txa::attn_bwd_dq_kernel<true><<<grid, txa::kBwdThreads, dq_smem, stream>>>(dqp);
+    else txa::attn_bwd_dq_kernel<false><<<grid, txa::kBwdThreads, dq_smem, stream>>>(dqp);
+    TXA_CUDA(cudaGetLastError());
+  }
   g_attn_launches.fetch_add(3);
   return TXD_OK;
 }
@@ -504,9 +540,9 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   const int n = pr->n_ctx, d = pr->head_dim;
   const long long ld = (n + 7) / 8 * 8;
   const char *force_unfused = getenv("TXA_BWD_UNFUSED");
-  if (d == 64 && !(force_unfused && atoi(force_unfused) != 0)) {
+  if (!(force_unfused && atoi(force_unfused) != 0)) {
     const size_t rows = static_cast<size_t>(pr->batch) * pr->heads * n;
-    const size_t need = ((rows + 63) / 64) * 64 * sizeof(float) + rows * 64 * sizeof(float) + 256;
+    const size_t need = ((rows + 63) / 64) * 64 * sizeof(float) + (d == 64 ? rows * 64 * sizeof(float) : 0) + 256;
     {
       std::lock_guard<std::mutex> lock(g_state_mutex);
       if (st->bwd_ws_bytes < need) {
