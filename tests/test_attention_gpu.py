@@ -243,3 +243,24 @@ def test_both_backward_paths_agree(A, monkeypatch, d):
         assert float((a.float() - b.float()).abs().max()) <= 4e-3
         assert float((a.cpu().float() - w).abs().max()) <= 1e-2
 
+
+def test_backward_bounded_wait_reports_timeout(A, monkeypatch):
+    from triton_ext_b200 import backend as B
+    from oracle import attn_oracle as AO
+    q, k, v = draw(1, 1, 256, 64, f16)
+    g = torch.Generator().manual_seed(3)
+    d_o = torch.randn((1, 1, 256, 64), generator=g).to(f16)
+    qc, kc, vc, dc = (x.cuda() for x in (q, k, v, d_o))
+    o, m = A.attention_forward(qc, kc, vc, True, 0.5, return_m=True, check=True)
+    monkeypatch.setenv("TXD_INJECT_STALL", "1")     # the producer loads K and V and never a query block
+    monkeypatch.setenv("TXD_WAIT_LIMIT_MS", "50")
+    with pytest.raises(B.DotError) as e:
+        A.attention_backward(qc, kc, vc, o, m, dc, True, 0.5, check=True)
+    assert e.value.status == B.TXD_ERR_DEVICE_TIMEOUT
+    monkeypatch.delenv("TXD_INJECT_STALL")
+    monkeypatch.delenv("TXD_WAIT_LIMIT_MS")
+    dq, dk, dv = A.attention_backward(qc, kc, vc, o, m, dc, True, 0.5, check=True)   # same context, healthy launch
+    want = AO.attention_grads_eager(q, k, v, d_o, True, 0.5)
+    for got, w in zip((dq, dk, dv), want):
+        assert float((got.cpu().float() - w).abs().max()) <= 1e-2
+
