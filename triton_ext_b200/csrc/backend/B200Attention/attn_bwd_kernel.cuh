@@ -16,7 +16,7 @@
 //   warps 0-7 : two threads per TMEM lane (= KV row for S^T, dP^T, dV, dK; = query row for the dQ partial), each
 //               with half of the columns:
 //               P^T and dS^T into shared memory (the A operands of the next dots), the dQ partial from TMEM
-//               to global memory with vectorised fp32 reductions, dV and dK at the end
+//               through shared memory and a TMA reduce-add into an fp32 accumulator, dV and dK at the end
 //   warp 8    : TMA producer (K, V once; Q, dO per query block) and the M / delta vectors of the block
 //   warp 9    : tcgen05.mma issuer. Order per query block i: dV(i), S^T(i+1) as soon as P^T(i) is written;
 //               dK(i), dQ(i), dP^T(i+1) as soon as dS^T(i) is written: the next block's scores are ready when the
@@ -34,10 +34,12 @@ constexpr int kBwdComputeWarps = 8;   // two threads per TMEM lane, 64 columns e
 constexpr int kBwdProducerWarp = 8;
 constexpr int kBwdMmaWarp = 9;
 constexpr int kBwdThreads = 10 * 32;
-constexpr int kBwdStages = 3;  // ring slots at head_dim 64; head_dim 128 has shared memory for one
+constexpr int kBwdStages = 2;  // ring slots at head_dim 64; head_dim 128 has shared memory for one
+constexpr int kDqSlabBytes = 32 * 128;  // one compute warp's dQ staging: 32 query rows x 32 fp32 columns
 
 struct AttnBwdParams {
-  CUtensorMap tmap_q, tmap_k, tmap_v, tmap_do;  // 3-D {64, n_ctx, batch*heads}, box {64, 128, 1}, SWIZZLE_128B
+  CUtensorMap tmap_q, tmap_k, tmap_v, tmap_do;  // 3-D {head_dim, n_ctx, batch*heads}, box {64, 128, 1}, SWIZZLE_128B
+  CUtensorMap tmap_dq;  // head_dim 64: the fp32 dq accumulator, 3-D {64, n_ctx, batch*heads}, box {32, 32, 1}
   const float *m;       // [batch*heads, n_ctx] from the forward
   const float *delta;   // [batch*heads, n_ctx] rowsum(o * do)
   float *dq_acc;        // [batch*heads, n_ctx, 64] fp32, zero on entry
@@ -62,10 +64,6 @@ struct AttnBwdCtl {
   alignas(16) float m_s[kBwdStages][kTileRows];
   alignas(16) float delta_s[kBwdStages][kTileRows];
 };
-
-__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 // P^T[kv row][query] = exp2(S^T * scale - M[query]) for 64 queries of one KV row: the fp32 values stay in `s` (dS
 // needs them), the rounded ones go to shared memory (one atom of the A operand of dV += P^T dO).
@@ -111,7 +109,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
   const uint32_t ring_addr = base + 2 * kBwdTileBytes;             // per stage: Q tile, dO tile
   const uint32_t pt_addr = ring_addr + kStagesT * 2 * kBwdTileBytes;  // P^T  [128 KV rows][128 queries], 2 atoms
   const uint32_t ds_addr = pt_addr + kPBytes;                      // dS^T, same layout
-  AttnBwdCtl *ctl = reinterpret_cast<AttnBwdCtl *>(attn_bwd_smem_raw + (ds_addr + kPBytes - raw));
+  const uint32_t dqs_addr = ds_addr + kPBytes;                     // (kD 64) dQ staging, one slab per compute warp
+  const uint32_t ctl_addr = dqs_addr + (kWithDq ? kBwdComputeWarps * kDqSlabBytes : 0);
+  AttnBwdCtl *ctl = reinterpret_cast<AttnBwdCtl *>(attn_bwd_smem_raw + (ctl_addr - raw));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     tma_prefetch_desc(&p.tmap_k);
     tma_prefetch_desc(&p.tmap_v);
     tma_prefetch_desc(&p.tmap_do);
+    if (kWithDq) tma_prefetch_desc(&p.tmap_dq);
   }
   if (warp == kBwdMmaWarp) {
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
@@ -331,23 +332,31 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     const int row_xor = r & 7;
     const int kv_row = kv0 + r;
     bool ok = true;
-    // the dQ partial of query block `blk` (lane = query row): this thread's 32 columns, reduced into global memory
+    // The dQ partial of a query block (lane = query row): this warp's 32 rows x 32 columns go through a swizzled
+    // shared-memory slab and one TMA reduce-add into the fp32 accumulator (full-line transactions in the copy
+    // engine; 2048 scattered 16-byte reductions per block from the threads took 2000 cycles). Rows past n_ctx
+    // are clipped by the copy.
+    const uint32_t dq_slab = dqs_addr + static_cast<uint32_t>(warp) * kDqSlabBytes;
     auto dq_readout = [&](int it_done) -> bool {
       if (!warp_mbar_poll(smem_u32(&ctl->dq_full), static_cast<uint32_t>(it_done) & 1u, ac, kAttnTimeoutSoftmaxO, lane)) return false;
       tc_fence_after();
-      const int qrow = (i_lo + it_done) * kTileRows + r;
-      float *dst = p.dq_acc + (static_cast<long long>(head) * p.n_ctx + qrow) * 64 + half * 32;
       uint32_t v[32];
       tmem_ld_32x32(lane_base + kColDq + half * 32, v);
       tmem_ld_wait();
-      if (qrow < p.n_ctx) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          red_add_v4(dst + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
-                     __uint_as_float(v[i + 3]));
-      }
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->dq_free));
+      if (lane == 0) bulk_wait_group_read<0>();  // the slab's previous reduction has been read
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        st_shared_v4(dq_slab + lane * 128 + ((c ^ (lane & 7)) << 4), v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+      fence_proxy_async();
+      __syncwarp();
+      const int row0 = (i_lo + it_done) * kTileRows + quarter * 32;
+      if (lane == 0 && row0 < p.n_ctx) {
+        tma_reduce_add_3d(&p.tmap_dq, dq_slab, half * 32, row0, head);
+        bulk_commit_group();
+      }
       return true;
     };
     for (int it = 0; it < n_it; ++it) {
@@ -442,6 +451,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
         }
       }
     }
+    if (kWithDq && lane == 0) bulk_wait_group_all();  // shared memory stays valid until the reductions have read it
   }
 
   tc_fence_before();

@@ -287,6 +287,19 @@ int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
   if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
   if ((rc = encode_head_map(&prm.tmap_do, d_o, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
+  if (d == 64) {
+    // the fp32 dq accumulator as a 3-D tensor {64, n_ctx, heads}: boxes of 32 columns (128 bytes) x 32 rows
+    EncodeTiledFn enc = attn_encode_fn();
+    if (!enc) return afail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(pr->n_ctx), static_cast<cuuint64_t>(heads_total)};
+    cuuint64_t strides[2] = {64 * sizeof(float), static_cast<cuuint64_t>(pr->n_ctx) * 64 * sizeof(float)};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(&prm.tmap_dq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return afail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled (dq accumulator) failed with code %d", static_cast<int>(r));
+  }
   prm.m = m;
   prm.delta = delta;
   prm.dq_acc = dq_acc;
@@ -306,7 +319,8 @@ int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   prm.idesc_dq = attn_idesc(bf16, true, 64) | (1u << 15);  // A operand MN-major as well
   const size_t tile = static_cast<size_t>(128) * d * 2;
   const size_t stages = d == 64 ? txa::kBwdStages : 1;
-  const size_t smem = 2 * tile + stages * 2 * tile + 2 * txa::kPBytes + sizeof(txa::AttnBwdCtl) + 1024;
+  const size_t smem = 2 * tile + stages * 2 * tile + 2 * txa::kPBytes +
+                      (d == 64 ? txa::kBwdComputeWarps * txa::kDqSlabBytes : 0) + sizeof(txa::AttnBwdCtl) + 1024;
   const unsigned grid = static_cast<unsigned>(heads_total * prm.kv_blocks);
   if (d == 64) {
     if (bf16) txa::attn_bwd_kernel<true, 64><<<grid, txa::kBwdThreads, smem, stream>>>(prm);

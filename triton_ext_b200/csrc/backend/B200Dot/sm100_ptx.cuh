@@ -253,6 +253,13 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, uint32_t src,
                "r"(src), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+// Tiled TMA reduction: global[tile] += shared[tile] element-wise, in the tensor map's data type.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *m, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp writes lane (base+t).
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
   asm volatile(
