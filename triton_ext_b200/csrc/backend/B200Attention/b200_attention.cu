@@ -170,16 +170,26 @@ __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2hal
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
-// delta[row] = sum_d o[row, d] * do[row, d], one warp per row
+// delta[row] = sum_d o[row, d] * do[row, d]: d / 8 lanes per row, 16-byte loads (d is 64 or 128)
 template <typename T>
 __global__ void attn_bwd_delta_kernel(const T *o, const T *d_o, float *delta, long long rows, int d) {
-  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lanes_per_row = d / 8;                 // 8 or 16
+  const int rows_per_warp = 32 / lanes_per_row;    // 4 or 2
+  const long long warp_id = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
+  const long long row = warp_id * rows_per_warp + lane / lanes_per_row;
   float acc = 0.f;
-  for (int c = lane; c < d; c += 32) acc += to_f32(o[row * d + c]) * to_f32(d_o[row * d + c]);
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) delta[row] = acc;
+  if (row < rows) {
+    const long long off = row * d + (lane % lanes_per_row) * 8;
+    const uint4 a = *reinterpret_cast<const uint4 *>(o + off);
+    const uint4 b = *reinterpret_cast<const uint4 *>(d_o + off);
+    const T *pa = reinterpret_cast<const T *>(&a);
+    const T *pb = reinterpret_cast<const T *>(&b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += to_f32(pa[i]) * to_f32(pb[i]);
+  }
+  for (int off = lanes_per_row / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < rows && lane % lanes_per_row == 0) delta[row] = acc;
 }
 
 // p[r, c] = exp2(s[r, c] * qk_scale - m[r]) (m already holds the row's log2-sum), zero above the diagonal
@@ -218,7 +228,7 @@ int attn_bwd_typed(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   float *delta = reinterpret_cast<float *>(ws + kBwdLanes * lane_bytes);
   const float qk_scale = pr->sm_scale * 1.44269504f;
   const long long rows = heads_total * n;
-  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
+  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * (d / 8) + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
   TXA_CUDA(cudaGetLastError());
   // heads are independent: kBwdLanes of them are in flight at a time, so that their small kernels fill the GPU
   TXA_CUDA(cudaEventRecord(st->bwd_fork, stream));
@@ -273,7 +283,7 @@ int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   const long long rows = heads_total * pr->n_ctx;
   float *delta = static_cast<float *>(st->bwd_ws);
   float *dq_acc = delta + ((rows + 63) / 64) * 64;
-  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
+  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * (d / 8) + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
   TXA_CUDA(cudaGetLastError());
   if (d == 64) TXA_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(rows) * 64 * sizeof(float), stream));
   unsigned long long wait_limit_ns = 2000ull * 1000 * 1000;
