@@ -480,7 +480,7 @@ struct AttnBwdDqParams {
 };
 
 struct AttnBwdDqCtl {
-  uint64_t q_full, full[2], empty[2], sdp_full, ds_full, done;
+  uint64_t q_full, full[2], empty[2], sdp_full, sdp_free, ds_full, done;
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
@@ -517,6 +517,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_dq_kernel(const __gri
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
     mbar_init(smem_u32(&ctl->sdp_full), 1);
+    mbar_init(smem_u32(&ctl->sdp_free), 2 * kTileRows);
     mbar_init(smem_u32(&ctl->ds_full), 2 * kTileRows);
     mbar_init(smem_u32(&ctl->done), 1);
     ctl->abort_flag = 0;
@@ -613,6 +614,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_dq_kernel(const __gri
     }
     for (int it = 0; ok && it < n_it; ++it) {
       const uint32_t k_addr = ring_addr + static_cast<uint32_t>(it % kStg) * 2 * kTile;
+      // the next block's S and dP as soon as this block's are in the compute warps' registers: the tensor pipe works
+      // on them while the compute warps turn this block into dS
+      if (it + 1 < n_it) {
+        if (!wait_stage(it + 1)) break;
+        if (!warp_mbar_poll(smem_u32(&ctl->sdp_free), static_cast<uint32_t>(it) & 1u, ac, kAttnTimeoutMmaP, lane)) break;
+        tc_fence_after();
+        issue_sdp(it + 1);
+      }
       if (!warp_mbar_poll(smem_u32(&ctl->ds_full), static_cast<uint32_t>(it) & 1u, ac, kAttnTimeoutMmaP, lane)) break;
       tc_fence_after();
 #pragma unroll
@@ -622,11 +631,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_dq_kernel(const __gri
                    desc64(desc_hi, (lo_of(k_addr) | lbo_atom) + mn_step(s)), p.idesc_dq, (it > 0 || s > 0) ? 1u : 0u);
       if (issuer) tc_commit(smem_u32(&ctl->empty[it % kStg]));
       __syncwarp();
-      if (it + 1 < n_it) {
-        if (!wait_stage(it + 1)) break;
-        tc_fence_after();
-        issue_sdp(it + 1);  // S and dP of block `it` are in the compute warps' registers
-      }
     }
     if (issuer) tc_commit(smem_u32(&ctl->done));
     __syncwarp();
@@ -661,12 +665,25 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_dq_kernel(const __gri
       tc_fence_after();
       const int c0 = it * kTileRows + half * 64;
       const bool masked = (p.causal && it == i) || (it + 1) * kTileRows > p.n_ctx || q0 + kTileRows > p.n_ctx;
+      uint32_t sall[64], dpall[64];
+      tmem_ld_32x32(lane_base + kColS + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&sall[0]));
+      tmem_ld_32x32(lane_base + kColS + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sall[32]));
+      tmem_ld_32x32(lane_base + kColDp + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&dpall[0]));
+      tmem_ld_32x32(lane_base + kColDp + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dpall[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->sdp_free));
+      // dQ += dS K of the previous block is queued behind this block's S and dP: its commit (the ring slot's
+      // "empty" barrier) says when the dS buffer may be overwritten
+      if (it > 0 && !warp_mbar_poll(smem_u32(&ctl->empty[(it - 1) % kStg]), static_cast<uint32_t>((it - 1) / kStg) & 1u, ac,
+                                    kAttnTimeoutSoftmaxO, lane)) {
+        ok = false;
+        break;
+      }
 #pragma unroll
       for (int c4 = 0; c4 < 2; ++c4) {
-        uint32_t sv[32], dp[32];
-        tmem_ld_32x32(lane_base + kColS + half * 64 + c4 * 32, sv);
-        tmem_ld_32x32(lane_base + kColDp + half * 64 + c4 * 32, dp);
-        tmem_ld_wait();
+        const uint32_t *sv = &sall[c4 * 32];
+        const uint32_t *dp = &dpall[c4 * 32];
 #pragma unroll
         for (int gg = 0; gg < 4; ++gg) {
           float e[8];
