@@ -462,6 +462,31 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
   }
 }
 
+// dS[query][kv] = P * (dP - delta) for 64 KV columns of one query row, from the scores and dP in registers; written
+// rounded to shared memory (one atom of the A operand of dQ += dS K). kMasked: diagonal and ragged blocks.
+template <bool kMasked, bool kBf16>
+__device__ __forceinline__ void bwd_row_ds(const uint32_t (&sv)[64], const uint32_t (&dp)[64], float qk_scale, float m_row,
+                                           float delta_row, int kv0, int qrow, int n_ctx, int causal, uint32_t ds_row,
+                                           int row_xor) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float e[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = g * 8 + u;
+      float pv = fast_exp2(fmaf(__uint_as_float(sv[c]), qk_scale, -m_row));
+      if (kMasked) {
+        const int kvc = kv0 + c;
+        const bool valid = kvc < n_ctx && qrow < n_ctx && (!causal || qrow >= kvc);
+        pv = valid ? pv : 0.f;
+      }
+      e[u] = pv * (__uint_as_float(dp[c]) - delta_row);
+    }
+    st_shared_v4(ds_row + ((g ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]), pack_pair<kBf16>(e[2], e[3]),
+                 pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // dQ for head_dim 128 (reference _attn_bwd_dq, :404-448): one CTA per query block of 128 rows walks the KV blocks it
 // sees. S = Q K^T and dP = dO V^T in tensor memory, dS = P * (dP - delta) with the row's own M and delta, written to
@@ -680,29 +705,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_dq_kernel(const __gri
         ok = false;
         break;
       }
-#pragma unroll
-      for (int c4 = 0; c4 < 2; ++c4) {
-        const uint32_t *sv = &sall[c4 * 32];
-        const uint32_t *dp = &dpall[c4 * 32];
-#pragma unroll
-        for (int gg = 0; gg < 4; ++gg) {
-          float e[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int c = c4 * 32 + gg * 8 + u;
-            float pv = fast_exp2(fmaf(__uint_as_float(sv[gg * 8 + u]), p.qk_scale, -m_row));
-            if (masked) {
-              const int kvc = c0 + c;
-              const bool valid = kvc < p.n_ctx && qrow < p.n_ctx && (!p.causal || qrow >= kvc);
-              pv = valid ? pv : 0.f;
-            }
-            e[u] = pv * (__uint_as_float(dp[gg * 8 + u]) - delta_row);
-          }
-          const int g = c4 * 4 + gg;
-          st_shared_v4(ds_addr + row_off + ((g ^ row_xor) << 4), pack_pair<kBf16>(e[0], e[1]), pack_pair<kBf16>(e[2], e[3]),
-                       pack_pair<kBf16>(e[4], e[5]), pack_pair<kBf16>(e[6], e[7]));
-        }
-      }
+      if (masked) bwd_row_ds<true, kBf16>(sall, dpall, p.qk_scale, m_row, delta_row, c0, qrow, p.n_ctx, p.causal, ds_addr + row_off, row_xor);
+      else bwd_row_ds<false, kBf16>(sall, dpall, p.qk_scale, m_row, delta_row, c0, qrow, p.n_ctx, p.causal, ds_addr + row_off, row_xor);
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->ds_full));
