@@ -68,3 +68,34 @@ def test_eager_gradients_match_the_reference_backward(name):
     for got, want in ((dq, t["dq"]), (dk, t["dk"]), (dv, t["dv"])):
         assert float((got - want.float()).abs().max()) <= 1e-2
 
+
+
+def test_attention_entry_points_fail_loudly_without_a_gpu(built_libs):
+    """No CPU path: on a machine without a B200 every attention entry point reports TXD_ERR_NO_DEVICE."""
+    import ctypes
+
+    import torch
+    from triton_ext_b200 import attention as A
+    from triton_ext_b200 import backend as B
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    lib = A._lib()
+    pr = A.make_problem(1, 1, 128, 64, torch.float16, True, 0.5)
+    buf = (ctypes.c_char * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.tx_attn_fwd(ctypes.byref(pr), p, p, p, p, None, None) == B.TXD_ERR_NO_DEVICE
+    assert lib.tx_attn_fwd_host(ctypes.byref(pr), p, p, p, p, None) == B.TXD_ERR_NO_DEVICE
+    assert lib.tx_attn_bwd(ctypes.byref(pr), p, p, p, p, p, p, p, p, p, None) == B.TXD_ERR_NO_DEVICE
+    assert b"CUDA" in lib.tx_attn_last_error() or b"device" in lib.tx_attn_last_error()
+    with pytest.raises(B.DotError):
+        A.attention_forward(torch.zeros(1, 1, 128, 64, dtype=torch.float16), torch.zeros(1, 1, 128, 64, dtype=torch.float16),
+                            torch.zeros(1, 1, 128, 64, dtype=torch.float16), True, 0.5)
+
+
+def test_kv_loop_split_arithmetic():
+    from triton_ext_b200 import attention as A
+    assert A.kv_loop_split(1024, 0, False) == (8, 8)            # full attention, aligned: nothing masked
+    assert A.kv_loop_split(1000, 0, False) == (8, 7)            # ragged last block is the masked one
+    assert A.kv_loop_split(1024, 384, True) == (4, 3)           # causal: diagonal block masked
+    assert A.kv_loop_split(200, 128, True) == (2, 1)
+    assert A.kv_loop_split(200, 256, True) == (0, 0)            # query rows past the sequence
