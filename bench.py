@@ -39,7 +39,8 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures
 # (profiles/*.md name the command); None where no capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 110.2e6, "cfg3": 122.2e6, "cfg4": 462.9e6, "cfg5_nshard": None, "cfg5_kshard": None}
+NCU_TRAFFIC_BYTES = {"cfg2": 110.2e6, "cfg3": 122.2e6, "cfg4": 462.9e6, "cfg5_nshard": None, "cfg5_kshard": None,
+                     "attn_d64": 254.7e6}   # attn_d64: 201.4 MB read + 53.3 MB written at the bench shape (one-pass capture)
 
 
 def measured_peaks() -> dict:
@@ -622,7 +623,7 @@ def run_attention_gpu_arm(args, name: str, w: dict) -> dict | None:
                               "256 query rows per CTA (2 x 128), KV blocks of 128, tcgen05 + TMEM"),
                    "l2": f"one buffer set of {set_bytes / 1e6:.0f} MB > 126 MB L2"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                     "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES.get(name),
                      "peak_source": f"bf16_tflops (burst) of {peaks['_source']}",
                      "note": f"exp2 on the SFU (16 per clock per SM) bounds this shape at {sfu_bound:.0f} TFLOP/s; "
                              f"algorithmic bytes {algo_bytes / 1e6:.0f} MB"},
