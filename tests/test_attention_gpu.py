@@ -202,7 +202,8 @@ def test_backward_matches_reference_kernel_outputs(A, name):
 
 @pytest.mark.parametrize("dtype", [f16, bf16])
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("z,h,n,d", [(1, 2, 1024, 64), (2, 2, 384, 128), (1, 2, 200, 64), (1, 1, 128, 128)])
+@pytest.mark.parametrize("z,h,n,d", [(1, 2, 1024, 64), (2, 2, 384, 128), (1, 2, 200, 64), (1, 1, 128, 128),
+                                     (1, 2, 333, 128), (1, 1, 4224, 64)])
 def test_autograd_function_against_oracle(A, z, h, n, d, causal, dtype):
     """`attention(q, k, v, causal, sm_scale)` as the reference exposes it (`_attention.apply`): forward and backward
     through autograd, against fp32 autograd of the eager formula, atol 1e-2 as in the reference's test_op."""
