@@ -78,6 +78,9 @@ TXIR_API int32_t txir_module_add_loop(txir_module *m, const txir_loop *loop);
 TXIR_API int32_t txir_module_add_dot(txir_module *m, const tx_dot_problem *problem, int32_t block_k);
 TXIR_API int32_t txir_module_num_loops(const txir_module *m);
 TXIR_API int32_t txir_module_get_loop(const txir_module *m, int32_t index, txir_loop *out);
+/* Replace loop `index`, e.g. to give the K loop of a dot the compare the source program really has
+ * (its own split point instead of the canonical floor(K / block_k) * block_k). Returns 0 or -1. */
+TXIR_API int32_t txir_module_set_loop(txir_module *m, int32_t index, const txir_loop *loop);
 TXIR_API int32_t txir_module_num_dots(const txir_module *m);
 /* The problem of dot `dot_index`, and the kernel configuration the passes have attached so far
  * (zero fields = not decided). After `loop_split` has run, config->k_split_point is the mid point. */

@@ -1,0 +1,137 @@
+"""@triton.jit kernels used by the Triton-backend tests: K loops the backend must accept, in the shapes
+users write them, and near misses it must refuse. Triton reads kernel source from a file, hence a module."""
+import triton
+import triton.language as tl
+
+
+@triton.jit
+def split_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn,
+                K_MAIN, BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """The loop LoopSplit takes: the induction variable counts K elements and is compared with a
+    loop-invariant split point; unmasked loads below it, masked loads from it on."""
+    pid_m = tl.program_id(0)
+    pid_n = tl.program_id(1)
+    offs_m = pid_m * BLOCK_M + tl.arange(0, BLOCK_M)
+    offs_n = pid_n * BLOCK_N + tl.arange(0, BLOCK_N)
+    offs_k = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a_ptrs = a_ptr + offs_m[:, None] * stride_am + (k + offs_k)[None, :] * stride_ak
+        b_ptrs = b_ptr + (k + offs_k)[:, None] * stride_bk + offs_n[None, :] * stride_bn
+        if k < K_MAIN:
+            a = tl.load(a_ptrs)
+            b = tl.load(b_ptrs)
+        else:
+            a = tl.load(a_ptrs, mask=(k + offs_k)[None, :] < K, other=0.0)
+            b = tl.load(b_ptrs, mask=(k + offs_k)[:, None] < K, other=0.0)
+        acc = tl.dot(a, b, acc)
+    c_ptrs = c_ptr + offs_m[:, None] * stride_cm + offs_n[None, :] * stride_cn
+    tl.store(c_ptrs, acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def grouped_masked_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm,
+                         stride_cn, alpha, BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr,
+                         GROUP: tl.constexpr):
+    """One-dimensional grid walked in groups of GROUP row tiles, a loop that counts K blocks, pointers
+    advanced by the loop, every load masked on all three bounds, a scalar scale before the cast."""
+    pid = tl.program_id(0)
+    tiles_m = tl.cdiv(M, BLOCK_M)
+    tiles_n = tl.cdiv(N, BLOCK_N)
+    per_group = GROUP * tiles_n
+    first_m = (pid // per_group) * GROUP
+    rows_here = min(tiles_m - first_m, GROUP)
+    pid_m = first_m + (pid % per_group) % rows_here
+    pid_n = (pid % per_group) // rows_here
+    rm = pid_m * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = pid_n * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    a_ptrs = a_ptr + rm[:, None] * stride_am + rk[None, :] * stride_ak
+    b_ptrs = b_ptr + rk[:, None] * stride_bk + rn[None, :] * stride_bn
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for kb in range(0, tl.cdiv(K, BLOCK_K)):
+        left = K - kb * BLOCK_K
+        a = tl.load(a_ptrs, mask=(rm[:, None] < M) & (rk[None, :] < left), other=0.0)
+        b = tl.load(b_ptrs, mask=(rk[:, None] < left) & (rn[None, :] < N), other=0.0)
+        acc = tl.dot(a, b, acc)
+        a_ptrs += BLOCK_K * stride_ak
+        b_ptrs += BLOCK_K * stride_bk
+    out = (acc * alpha).to(c_ptr.dtype.element_ty)
+    c_ptrs = c_ptr + rm[:, None] * stride_cm + rn[None, :] * stride_cn
+    tl.store(c_ptrs, out, mask=(rm[:, None] < M) & (rn[None, :] < N))
+
+
+@triton.jit
+def plain_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm,
+                BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """No masks at all: every extent is a multiple of its block."""
+    rm = tl.program_id(1) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(0) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :] * stride_ak)
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :] * stride_bn)
+        acc += tl.dot(a, b)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def relu_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+               BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: an activation between the loop and the store."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    acc = tl.maximum(acc, 0.0)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def shifted_rows_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+                       BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: C rows are not the rows of A that produced them."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + (rm + 1)[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def strided_k_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+                    BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: the loop skips every other K block."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, 2 * BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def nonzero_fill_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+                       BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: masked-off K elements read as one, not zero."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :], mask=(k + rk)[None, :] < K, other=1.0)
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :], mask=(k + rk)[:, None] < K, other=0.0)
+        acc = tl.dot(a, b, acc)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))

@@ -1,0 +1,216 @@
+"""The Triton backend entry point on CPU: TTIR of @triton.jit K loops -> proof -> bound GEMM -> pass pipeline.
+
+Nothing here needs a GPU: Triton's front end, the analysis, triton.compile() through the backend, and a
+whole `kernel[grid](...)` launch under a driver whose launcher stops before the CUDA call. Run by
+test_triton_backend.py in a process of its own (Triton must not be in interpreter mode here).
+"""
+import math
+
+import pytest
+import torch
+
+triton = pytest.importorskip("triton")
+
+import jit_kernels as jk  # noqa: E402
+from triton_ext_b200 import triton_backend as tbk  # noqa: E402
+from triton_ext_b200.triton_backend import compiler, driver, ttir  # noqa: E402
+
+PTR = {"bf16": "*bf16", "f16": "*fp16", "f8e4m3": "*fp8e4nv"}
+
+
+def split_sig(dt="bf16", out="bf16", ones=("stride_ak", "stride_bn", "stride_cn"), bm=128, bn=128, bk=128):
+    sig = {"a_ptr": PTR[dt], "b_ptr": PTR[dt], "c_ptr": PTR[out], "M": "i32", "N": "i32", "K": "i32"}
+    cx = {}
+    for s in ("stride_am", "stride_ak", "stride_bk", "stride_bn", "stride_cm", "stride_cn"):
+        sig[s] = "constexpr" if s in ones else "i32"
+        if s in ones:
+            cx[s] = 1
+    sig.update({"K_MAIN": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"})
+    cx.update({"BLOCK_M": bm, "BLOCK_N": bn, "BLOCK_K": bk})
+    return sig, cx
+
+
+def small_sig(dt="bf16"):
+    sig = {"a_ptr": PTR[dt], "b_ptr": PTR[dt], "c_ptr": PTR[dt], "K": "i32", "stride_am": "i32", "stride_bk": "i32",
+           "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    return sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32}
+
+
+def grouped_sig(bm=64, bn=128, bk=32, group=4):
+    sig = {"a_ptr": "*fp16", "b_ptr": "*fp16", "c_ptr": "*fp16", "M": "i32", "N": "i32", "K": "i32", "stride_am": "i32",
+           "stride_ak": "constexpr", "stride_bk": "constexpr", "stride_bn": "i32", "stride_cm": "i32",
+           "stride_cn": "constexpr", "alpha": "fp32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr",
+           "BLOCK_K": "constexpr", "GROUP": "constexpr"}
+    cx = {"stride_ak": 1, "stride_bk": 1, "stride_cn": 1, "BLOCK_M": bm, "BLOCK_N": bn, "BLOCK_K": bk, "GROUP": group}
+    return sig, cx
+
+
+def test_ttir_has_the_loop_split_shape():
+    """The IR the analysis reads is the one LoopSplit rewrites: scf.for + cmpi slt on the IV + scf.if."""
+    text = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, *split_sig()))
+    assert "scf.for" in text and "tt.dot" in text and "scf.if" in text
+    assert any("arith.cmpi slt" in l and "%K_MAIN" in l for l in text.splitlines())
+
+
+def test_split_kloop_match():
+    m = compiler.analyse(jk.split_kloop, *split_sig())
+    assert (m.a_arg, m.b_arg, m.c_arg) == ("a_ptr", "b_ptr", "c_ptr")
+    assert (m.block_m, m.block_n, m.block_k) == (128, 128, 128)
+    assert (m.ab_dtype, m.out_dtype) == ("bf16", "bf16")
+    assert (m.a_row_stride, m.a_k_stride, m.b_k_stride, m.b_col_stride) == ("stride_am", "1", "stride_bk", "1")
+    assert (m.row0, m.col0) == ("128*pid_x", "128*pid_y")
+    assert (m.loop_lo, m.loop_hi, m.loop_step, m.k_per_iv) == ("0", "K", 128, 1)
+    assert (m.k_bound, m.split_pred, m.split_comparand) == ("K", "slt", "K_MAIN")
+    assert m.alpha is None
+    assert ttir.DotKernelMatch.from_json(m.to_json()) == m
+
+
+def test_split_kloop_bind_benchmark_shape():
+    """The 8192 x 8192 x 4160 bf16 case: 32 full K blocks of 128 and a 64-wide remainder."""
+    m = compiler.analyse(jk.split_kloop, *split_sig())
+    s = dict(M=8192, N=8192, K=4160, stride_am=4160, stride_bk=8192, stride_cm=8192, K_MAIN=4096)
+    b = ttir.bind(m, s, (64, 64))
+    assert (b.m, b.n, b.k, b.a_layout, b.b_layout, b.lda, b.ldb, b.ldc) == (8192, 8192, 4160, "row", "row", 4160, 8192, 8192)
+    assert (b.block_k, b.k_main, b.alpha) == (128, 4096, 1.0)
+    # an earlier split point is still right (more iterations masked), a later one would read past K unmasked
+    assert ttir.bind(m, dict(s, K_MAIN=2048), (64, 64)).k_main == 2048
+    with pytest.raises(ttir.NotCanonical, match="unmasked load run past"):
+        ttir.bind(m, dict(s, K_MAIN=4160), (64, 64))
+    # this kernel has no row or column masks: the grid alone says how much of C is computed
+    assert ttir.bind(m, s, (64, 63)).n == 63 * 128
+    with pytest.raises(ttir.NotCanonical, match="does not cover"):
+        ttir.bind(m, s, (64, 64, 2))
+
+
+def test_transposed_operands_bind_as_column_major():
+    sig, cx = split_sig("f16", "f16", ones=("stride_am", "stride_bk", "stride_cn"))
+    m = compiler.analyse(jk.split_kloop, sig, cx)
+    b = ttir.bind(m, dict(M=256, N=384, K=200, stride_ak=256, stride_bn=200, stride_cm=384, K_MAIN=128), (2, 3))
+    assert (b.a_layout, b.lda, b.b_layout, b.ldb, b.k_main) == ("col", 256, "col", 200, 128)
+    sig, cx = split_sig("f16", "f16", ones=("stride_cn",))
+    m = compiler.analyse(jk.split_kloop, sig, cx)
+    with pytest.raises(ttir.NotCanonical, match="no unit stride"):
+        ttir.bind(m, dict(M=256, N=384, K=200, stride_am=400, stride_ak=2, stride_bk=384, stride_bn=1, stride_cm=384,
+                          K_MAIN=128), (2, 3))
+
+
+def test_grouped_masked_kloop():
+    """Block-counting loop, pointers carried by the loop, a swizzled 1-D grid, three-way masks, a scalar scale."""
+    m = compiler.analyse(jk.grouped_masked_kloop, *grouped_sig())
+    assert (m.loop_step, m.k_per_iv, m.block_k) == (1, 32, 32)
+    assert (m.k_bound, m.m_bound, m.n_bound, m.alpha, m.split_pred) == ("K", "M", "N", "alpha", None)
+    for M, N, K in ((1000, 300, 1111), (64, 128, 32), (65, 129, 33), (4096, 4096, 64)):
+        grid = (math.ceil(M / 64) * math.ceil(N / 128),)
+        s = dict(M=M, N=N, K=K, stride_am=K, stride_bn=K, stride_cm=N)
+        b = ttir.bind(m, s, grid, {"alpha": 0.5})
+        assert (b.m, b.n, b.k, b.a_layout, b.b_layout, b.alpha) == (M, N, K, "row", "col", 0.5)
+        assert b.k_main == (K // 32) * 32
+        if grid[0] > 1:
+            with pytest.raises(ttir.NotCanonical, match="does not cover"):
+                ttir.bind(m, s, (grid[0] - 1,), {"alpha": 0.5})
+
+
+def test_plain_kloop_without_masks():
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*fp32", "K": "i32", "stride_am": "i32", "stride_ak": "constexpr",
+           "stride_bk": "i32", "stride_bn": "constexpr", "stride_cm": "i32", "BLOCK_M": "constexpr",
+           "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    m = compiler.analyse(jk.plain_kloop, sig, {"stride_ak": 1, "stride_bn": 1, "BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64})
+    assert (m.k_bound, m.m_bound, m.n_bound, m.out_dtype) == (None, None, None, "f32")
+    assert (m.row0, m.col0) == ("128*pid_y", "64*pid_x")
+    b = ttir.bind(m, dict(K=512, stride_am=512, stride_bk=320, stride_cm=320), (5, 3))
+    assert (b.m, b.n, b.k, b.k_main) == (384, 320, 512, 512)
+
+
+@pytest.mark.parametrize("kernel,why", [
+    (jk.relu_kloop, "depends on the result of"),
+    (jk.shifted_rows_kloop, "rows of A"),
+    (jk.strided_k_kloop, "K elements per iteration"),
+    (jk.nonzero_fill_kloop, "must be zero"),
+])
+def test_near_misses_are_refused(kernel, why):
+    with pytest.raises(ttir.NotCanonical, match=why):
+        compiler.analyse(kernel, *small_sig())
+
+
+def test_hand_written_ir_is_refused_with_a_reason():
+    base = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, *split_sig()))
+    with pytest.raises(ttir.NotCanonical, match="stores"):
+        ttir.match_dot_kernel("\n".join(l for l in base.splitlines() if "tt.store" not in l))
+    with pytest.raises(ttir.NotCanonical, match="no tt.func"):
+        ttir.match_dot_kernel("module {\n}\n")
+
+
+def test_triton_compile_through_the_backend():
+    """triton.compile() with the b200dot target: stages source -> ttir -> b200dot, binary = the proof."""
+    from triton.backends.compiler import GPUTarget
+    from triton.compiler import ASTSource
+
+    tbk.install()
+    sig, cx = split_sig()
+    k = triton.compile(ASTSource(jk.split_kloop, sig, cx), target=GPUTarget("b200dot", 100, 32))
+    assert k.name == "split_kloop" and k.metadata.shared == 0
+    assert set(k.asm) >= {"ttir", "b200dot"}
+    m = ttir.DotKernelMatch.from_json(k.asm["b200dot"].decode())
+    assert m == compiler.analyse(jk.split_kloop, sig, cx)
+    with pytest.raises(ttir.NotCanonical):
+        triton.compile(ASTSource(jk.relu_kloop, *small_sig()), target=GPUTarget("b200dot", 100, 32))
+
+
+def test_backend_package_has_the_shape_triton_discovers():
+    """One concrete BaseBackend in compiler.py, one concrete DriverBase in driver.py; the driver never claims
+    to be the process's active driver."""
+    import triton.backends as tb
+
+    assert tb._find_concrete_subclasses(compiler, tb.BaseBackend) is compiler.B200DotBackend
+    assert tb._find_concrete_subclasses(driver, tb.DriverBase) is driver.B200DotDriver
+    assert driver.B200DotDriver.is_active() is False
+
+
+class DryLauncher(driver.B200DotLauncher):
+    calls = []
+
+    def __call__(self, gx, gy, gz, stream, function, packed, launch_md, enter, exit_, *args):
+        entry = self.prepare(function, dict(zip(self.arg_names, args)), (gx, gy, gz))
+        DryLauncher.calls.append(entry)
+
+
+class DryDriver(driver.B200DotDriver):
+    """The real driver with the device queries answered by constants and the launcher stopped before CUDA."""
+
+    def __init__(self):
+        triton.backends.driver.DriverBase.__init__(self)
+        self.utils = driver.B200DotUtils()
+        self.utils.get_device_properties = lambda device: {"max_shared_mem": 232448}
+        self.launcher_cls = DryLauncher
+        self.get_current_device = lambda: 0
+        self.set_current_device = lambda d: None
+        self.get_device_capability = lambda d=0: (10, 0)
+        self.get_current_stream = lambda d: 0
+
+
+def test_jit_launch_reaches_the_pass_pipeline():
+    """`kernel[grid](...)` end to end on CPU tensors: specialisation, compile, bind, loop_split's split point and
+    dot_tile_select's tiles in the lowered loop IR."""
+    from triton.runtime.driver import driver as config
+
+    tbk.install()
+    previous = config._active
+    config.set_active(DryDriver())
+    try:
+        M, N, K = 512, 384, 4160
+        a = torch.zeros(M, K, dtype=torch.bfloat16)
+        b = torch.zeros(K, N, dtype=torch.bfloat16)
+        c = torch.zeros(M, N, dtype=torch.bfloat16)
+        DryLauncher.calls.clear()
+        jk.split_kloop[(M // 128, N // 128)](a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+                                             c.stride(0), c.stride(1), (K // 128) * 128,
+                                             BLOCK_M=128, BLOCK_N=128, BLOCK_K=128)
+    finally:
+        config._active = previous
+        jk.split_kloop.device_caches.clear()
+    (entry,) = DryLauncher.calls
+    bound, cfg, info = entry["bound"], entry["config"], entry["info"]
+    assert (bound.m, bound.n, bound.k, bound.k_main) == (M, N, K, 4096)
+    assert cfg.k_split_point == 4096
+    assert info["k_main_iters"] * info["block_k"] == 4096 and info["k_tail_iters"] == 1
+    assert "4096" in entry["ir"]

@@ -114,6 +114,13 @@ int32_t txir_module_get_loop(const txir_module *m, int32_t index, txir_loop *out
   return 0;
 }
 
+int32_t txir_module_set_loop(txir_module *m, int32_t index, const txir_loop *loop) {
+  if (!m || !loop || index < 0 || index >= static_cast<int32_t>(m->loops.size())) return -1;
+  if (loop->dot_index >= static_cast<int32_t>(m->dots.size())) return -1;
+  m->loops[index] = *loop;
+  return 0;
+}
+
 int32_t txir_module_num_dots(const txir_module *m) { return m ? static_cast<int32_t>(m->dots.size()) : 0; }
 
 int32_t txir_module_get_dot(const txir_module *m, int32_t i, tx_dot_problem *problem, tx_dot_config *config,

@@ -91,6 +91,8 @@ def infra() -> ctypes.CDLL:
     lib.txir_module_num_loops.restype = i32
     lib.txir_module_get_loop.argtypes = [vp, i32, ctypes.POINTER(Loop)]
     lib.txir_module_get_loop.restype = i32
+    lib.txir_module_set_loop.argtypes = [vp, i32, ctypes.POINTER(Loop)]
+    lib.txir_module_set_loop.restype = i32
     lib.txir_module_num_dots.argtypes = [vp]
     lib.txir_module_num_dots.restype = i32
     lib.txir_module_get_dot.argtypes = [vp, i32, ctypes.POINTER(Problem), ctypes.POINTER(Config), ctypes.POINTER(PlanInfo)]
@@ -224,6 +226,9 @@ class Module:
             out.append(l.as_dict())
         return out
 
+    def set_loop(self, index: int, loop: Loop) -> int:
+        return self._lib.txir_module_set_loop(self._h, index, ctypes.byref(loop))
+
     def dot(self, index: int = 0) -> tuple[Problem, Config, dict, bool]:
         pr, cfg, info = Problem(), Config(), PlanInfo()
         rc = self._lib.txir_module_get_dot(self._h, index, ctypes.byref(pr), ctypes.byref(cfg), ctypes.byref(info))
@@ -257,15 +262,23 @@ DEFAULT_PIPELINE = ("loop_split", "dot_tile_select", "b200_dot")
 
 
 def lower_dot(problem: Problem, block_k: int, pipeline: Iterable[str] = DEFAULT_PIPELINE,
-              attrs: Optional[dict] = None) -> tuple[Config, dict, Module]:
+              attrs: Optional[dict] = None, split_comparand: Optional[int] = None) -> tuple[Config, dict, Module]:
     """Run the extension pipeline over one tt.dot K loop and return the kernel configuration it
-    produced (split point from loop_split, tiles from dot_tile_select, accepted by b200_dot)."""
+    produced (split point from loop_split, tiles from dot_tile_select, accepted by b200_dot).
+    `split_comparand` is the value the source program compares its induction variable with
+    (`k < split_comparand` guards the unmasked loads); default: the last multiple of block_k in K."""
     load_default_plugins()
     m = Module()
     for k, v in (attrs or {}).items():
         m.set_attr(k, str(v))
     if m.add_dot(problem, block_k) < 0:
         raise ValueError("txir_module_add_dot rejected the problem")
+    if split_comparand is not None:
+        l = Loop()
+        m._lib.txir_module_get_loop(m._h, 0, ctypes.byref(l))
+        l.comparand = int(split_comparand)
+        if m.set_loop(0, l) != 0:
+            raise ValueError("txir_module_set_loop rejected the loop")
     pm = PassManager()
     for name in pipeline:
         if pm.add(name) != TP_SUCCESS:

@@ -1,0 +1,892 @@
+"""Recognises the canonical ``tt.dot`` K loop in the TTIR of a ``@triton.jit`` kernel.
+
+The reference's extensions see a kernel as Triton IR: an ``scf.for`` over K whose body loads an A and a
+B tile, optionally under ``scf.if %k < %split`` with unmasked loads on one side and masked loads on the
+other (the shape LoopSplit rewrites, pass/LoopSplit/LoopSplit.cpp:107-144), feeds them to ``tt.dot`` with
+the loop-carried fp32 accumulator, and stores the cast result (pass/LoopSplit/06-fused-attention.py:63,85
+for the dots, :237-240 for the cast-and-store). This module reads that IR as text, evaluates every
+integer and pointer value symbolically (sympy expressions over the kernel arguments, the program ids,
+the induction variable and one index symbol per tile axis), and proves that the kernel computes
+
+    C[m, n] = cast(alpha * sum_k A[m, k] * B[k, n])      for m < M, n < N, with zero fill past K
+
+with affine addressing. The result is a :class:`DotKernelMatch`; :func:`bind` turns it, together with
+the argument values and grid of one launch, into the operands of the library GEMM. A kernel that is
+anything else raises :class:`NotCanonical` with the reason: nothing is approximated.
+"""
+from __future__ import annotations
+
+import json
+import re
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import sympy as sp
+
+
+class NotCanonical(ValueError):
+    """The kernel is not the K loop this backend lowers."""
+
+
+# --------------------------------------------------------------------------------------------------
+# Text -> operations
+# --------------------------------------------------------------------------------------------------
+
+_VAL = r"%[\w.$-]+(?:#\d+)?"
+_VAL_RE = re.compile(_VAL)
+
+
+@dataclass
+class Op:
+    results: list
+    name: str
+    operands: list
+    rest: str
+    regions: list = field(default_factory=list)
+    extra: dict = field(default_factory=dict)
+
+
+def strip_locations(text: str) -> str:
+    """Remove ``loc(...)`` annotations and ``#loc`` definitions from a printed module."""
+    out = []
+    for line in text.splitlines():
+        if line.lstrip().startswith("#loc"):
+            continue
+        res, i = [], 0
+        while True:
+            j = line.find(" loc(", i)
+            if j < 0:
+                res.append(line[i:])
+                break
+            res.append(line[i:j])
+            depth, p = 0, j + 4
+            while p < len(line):
+                if line[p] == "(":
+                    depth += 1
+                elif line[p] == ")":
+                    depth -= 1
+                    if depth == 0:
+                        break
+                p += 1
+            i = p + 1
+        out.append("".join(res))
+    return "\n".join(out)
+
+
+def _split_types(rest: str) -> tuple:
+    """(text before the type section, type section) of an operation's tail."""
+    depth, last, i = 0, -1, 0
+    while i < len(rest):
+        ch = rest[i]
+        if rest.startswith("->", i):
+            i += 2
+            continue
+        if ch in "{[(<":
+            depth += 1
+        elif ch in "}])>":
+            depth -= 1
+        elif depth == 0 and rest.startswith(" : ", i):
+            last = i
+        i += 1
+    if last < 0:
+        return rest, ""
+    return rest[:last], rest[last + 3:]
+
+
+def _result_type(types: str) -> str:
+    if " -> " in types:
+        return types.rsplit(" -> ", 1)[1].strip()
+    if " to " in types:
+        return types.rsplit(" to ", 1)[1].strip()
+    depth = 0
+    for i, ch in enumerate(types):
+        if ch in "<(":
+            depth += 1
+        elif ch in ">)":
+            depth -= 1
+        elif ch == "," and depth == 0:
+            return types[:i].strip()
+    return types.strip()
+
+
+def parse_type(ty: str) -> tuple:
+    """(shape, element type) of ``tensor<128x64xbf16>``, ``!tt.ptr<f16>``, ``i32`` ..."""
+    ty = ty.strip()
+    if ty.startswith("tensor<") and ty.endswith(">"):
+        inner = ty[len("tensor<"):-1]
+        shape = []
+        while True:
+            m = re.match(r"(\d+)x", inner)
+            if not m:
+                break
+            shape.append(int(m.group(1)))
+            inner = inner[m.end():]
+        return tuple(shape), inner
+    return (), ty
+
+
+def _expand_results(lhs: str) -> list:
+    out = []
+    for tok in [t.strip() for t in lhs.split(",")]:
+        if ":" in tok:
+            name, n = tok.split(":")
+            out += [f"{name}#{i}" for i in range(int(n))]
+        else:
+            out.append(tok)
+    return out
+
+
+_FUNC_ARG = re.compile(r"(%[\w.$-]+): (![\w.]+<[^<>]*>|[\w]+)(?: \{[^{}]*\})?(?: loc\(\"([^\"]+)\")?")
+
+
+def parse_module(text: str, arg_names: Optional[list] = None) -> tuple:
+    """Parse one printed ``tt.func``. Returns (function name, [(ssa name, source name, type)], ops)."""
+    lines = text.splitlines()
+    header_at = next((i for i, l in enumerate(lines) if "tt.func" in l and "@" in l), None)
+    if header_at is None:
+        raise NotCanonical("no tt.func in the module")
+    if sum(1 for l in lines if re.search(r"\btt\.func\b", l)) != 1:
+        raise NotCanonical("more than one function: calls are not lowered")
+    header = lines[header_at]
+    fname = re.search(r"@([\w.$-]+)\(", header).group(1)
+    arg_text = header[header.index("(") + 1:]
+    args = []
+    for i, m in enumerate(_FUNC_ARG.finditer(arg_text.split(") attributes")[0])):
+        src = m.group(3) or (arg_names[i] if arg_names and i < len(arg_names) else m.group(1)[1:])
+        args.append((m.group(1), src, m.group(2)))
+
+    body = strip_locations("\n".join(lines[header_at + 1:])).splitlines()
+    root: list = []
+    stack = [root]
+    owners: list = []
+    for raw in body:
+        line = raw.strip()
+        if not line or line == "module {":
+            continue
+        if line == "}":
+            if owners:
+                owners.pop()
+                stack.pop()
+                continue
+            break  # end of the function
+        if line == "} else {":
+            op = owners[-1]
+            stack.pop()
+            op.regions.append([])
+            stack.append(op.regions[-1])
+            continue
+        results = []
+        m = re.match(rf"^((?:{_VAL}(?::\d+)?(?:, )?)+) = (.*)$", line)
+        if m:
+            results = _expand_results(m.group(1))
+            line = m.group(2)
+        name, _, rest = line.partition(" ")
+        if name == "scf.for":
+            fm = re.match(rf"({_VAL}) = ({_VAL}) to ({_VAL}) step ({_VAL})(?: iter_args\((.*?)\) -> \((.*?)\))?", rest)
+            if not fm or not line.endswith("{"):
+                raise NotCanonical(f"unreadable scf.for: {line}")
+            iters = []
+            if fm.group(5):
+                for part in fm.group(5).split(", "):
+                    a, b = part.split(" = ")
+                    iters.append((a.strip(), b.strip()))
+            op = Op(results, name, [fm.group(2), fm.group(3), fm.group(4)], rest, [[]],
+                    {"iv": fm.group(1), "iters": iters})
+            stack[-1].append(op)
+            owners.append(op)
+            stack.append(op.regions[0])
+            continue
+        if name == "scf.if":
+            cond = _VAL_RE.match(rest)
+            if not cond or not line.endswith("{"):
+                raise NotCanonical(f"unreadable scf.if: {line}")
+            op = Op(results, name, [cond.group(0)], rest, [[]])
+            stack[-1].append(op)
+            owners.append(op)
+            stack.append(op.regions[0])
+            continue
+        if line.endswith("{"):
+            raise NotCanonical(f"operation with a region is not lowered: {name}")
+        head, _types = _split_types(rest)
+        stack[-1].append(Op(results, name, _VAL_RE.findall(head), rest))
+    return fname, args, root
+
+
+# --------------------------------------------------------------------------------------------------
+# Symbolic values
+# --------------------------------------------------------------------------------------------------
+
+X0, X1, KIV = sp.symbols("x0 x1 k_iv", integer=True)
+PID = {a: sp.Symbol(f"pid_{a}", integer=True, nonnegative=True) for a in "xyz"}
+NPROG = {a: sp.Symbol(f"nprog_{a}", integer=True, positive=True) for a in "xyz"}
+
+
+@dataclass
+class Int:
+    shape: tuple
+    expr: Any
+
+
+@dataclass
+class Ptr:
+    base: str
+    elem: str
+    shape: tuple
+    off: Any
+
+
+@dataclass
+class Cond:
+    shape: tuple
+    terms: tuple  # conjunction of (pred, lhs, rhs)
+
+
+@dataclass
+class Flt:
+    kind: str  # const | arg | load | cast | scale | acc | dot | loop_dot
+    shape: tuple
+    data: dict
+
+
+class _Opaque:
+    """A value the analysis does not model; using it is an error."""
+
+    def __init__(self, why: str):
+        self.why = why
+
+
+def _bshape(a: tuple, b: tuple) -> tuple:
+    if a == b or b == ():
+        return a
+    if a == ():
+        return b
+    if len(a) == len(b) and all(x == y or x == 1 or y == 1 for x, y in zip(a, b)):
+        return tuple(max(x, y) for x, y in zip(a, b))
+    raise NotCanonical(f"shape mismatch {a} vs {b}")
+
+
+def _subst(v: Any, mapping: dict) -> Any:
+    if isinstance(v, Int):
+        return Int(v.shape, v.expr.subs(mapping))
+    if isinstance(v, Ptr):
+        return Ptr(v.base, v.elem, v.shape, v.off.subs(mapping))
+    if isinstance(v, Cond):
+        return Cond(v.shape, tuple((p, l.subs(mapping), r.subs(mapping)) for p, l, r in v.terms))
+    if isinstance(v, Flt):
+        return Flt(v.kind, v.shape, {k: _subst(x, mapping) for k, x in v.data.items()})
+    return v
+
+
+_INT_BIN = {
+    "arith.addi": lambda a, b: a + b,
+    "arith.subi": lambda a, b: a - b,
+    "arith.muli": lambda a, b: a * b,
+    "arith.divsi": lambda a, b: sp.floor(a / b),
+    "arith.divui": lambda a, b: sp.floor(a / b),
+    "arith.floordivsi": lambda a, b: sp.floor(a / b),
+    "arith.ceildivsi": lambda a, b: sp.ceiling(a / b),
+    "arith.remsi": lambda a, b: sp.Mod(a, b),
+    "arith.remui": lambda a, b: sp.Mod(a, b),
+    "arith.minsi": lambda a, b: sp.Min(a, b),
+    "arith.minui": lambda a, b: sp.Min(a, b),
+    "arith.maxsi": lambda a, b: sp.Max(a, b),
+    "arith.maxui": lambda a, b: sp.Max(a, b),
+}
+_INT_CASTS = {"arith.extsi", "arith.extui", "arith.trunci", "arith.index_cast"}
+_FLT_CASTS = {"arith.extf", "arith.truncf", "tt.fp_to_fp"}
+_FLOAT_TYPES = {"f16", "bf16", "f32", "f64", "f8E4M3FN", "f8E5M2", "f8E4M3FNUZ", "f8E5M2FNUZ"}
+
+
+class _Evaluator:
+    def __init__(self, args: list):
+        self.stores: list = []
+        self.loops = 0
+        self.arg_symbols: dict = {}
+        self.env: dict = {}
+        for ssa, src, ty in args:
+            if ty.startswith("!tt.ptr<"):
+                self.env[ssa] = Ptr(src, ty[len("!tt.ptr<"):-1], (), sp.Integer(0))
+            elif ty in _FLOAT_TYPES:
+                self.env[ssa] = Flt("arg", (), {"name": src})
+            elif re.fullmatch(r"i\d+", ty):
+                s = sp.Symbol(src, integer=True)
+                self.arg_symbols[src] = s
+                self.env[ssa] = Int((), s)
+            else:
+                self.env[ssa] = _Opaque(f"argument {src} of type {ty}")
+
+    def get(self, env: dict, name: str) -> Any:
+        v = env.get(name)
+        if v is None:
+            raise NotCanonical(f"use of unknown value {name}")
+        if isinstance(v, _Opaque):
+            raise NotCanonical(f"the kernel depends on {v.why}")
+        return v
+
+    # -- one block ------------------------------------------------------------------------------
+    def run(self, ops: list, env: dict) -> Optional[list]:
+        """Evaluate a block; returns the operands of its scf.yield (or None)."""
+        for op in ops:
+            if op.name == "scf.yield":
+                return [self.get(env, o) for o in op.operands]
+            if op.name == "tt.return":
+                return None
+            self.step(op, env)
+        return None
+
+    def step(self, op: Op, env: dict) -> None:
+        n = op.name
+        head, types = _split_types(op.rest)
+        rshape, relem = parse_type(_result_type(types)) if types else ((), "")
+        g = lambda i: self.get(env, op.operands[i])
+
+        def put(v):
+            env[op.results[0]] = v
+
+        if n == "arith.constant":
+            tok = head.strip()
+            m = re.match(r"dense<(.*)>$", tok)
+            lit = m.group(1) if m else tok
+            if relem in _FLOAT_TYPES:
+                put(Flt("const", rshape, {"value": float(lit)}))
+            elif lit in ("true", "false"):
+                put(Cond(rshape, ()) if lit == "true" else _Opaque("a constant-false condition"))
+            else:
+                put(Int(rshape, sp.Integer(int(lit))))
+        elif n == "tt.get_program_id":
+            put(Int((), PID[head.strip()]))
+        elif n == "tt.get_num_programs":
+            put(Int((), NPROG[head.strip()]))
+        elif n == "tt.make_range":
+            start = int(re.search(r"start = (-?\d+)", head).group(1))
+            put(Int(rshape, X0 + start))
+        elif n == "tt.splat":
+            v = g(0)
+            if isinstance(v, Int):
+                put(Int(rshape, v.expr))
+            elif isinstance(v, Ptr):
+                put(Ptr(v.base, v.elem, rshape, v.off))
+            elif isinstance(v, Flt) and v.kind in ("const", "arg"):
+                put(Flt(v.kind, rshape, dict(v.data)))
+            else:
+                raise NotCanonical("tt.splat of a value that is not an integer, a pointer or a float scalar")
+        elif n == "tt.expand_dims":
+            v = g(0)
+            axis = int(re.search(r"axis = (\d+)", head).group(1))
+            if not isinstance(v, (Int, Cond)) or len(v.shape) != 1:
+                raise NotCanonical("tt.expand_dims is modelled for rank-1 integer tensors only")
+            ren = {X0: X1} if axis == 0 else {}
+            if isinstance(v, Int):
+                put(Int(rshape, v.expr.subs(ren)))
+            else:
+                put(Cond(rshape, tuple((p, l.subs(ren), r.subs(ren)) for p, l, r in v.terms)))
+        elif n == "tt.broadcast":
+            v = g(0)
+            if isinstance(v, Int):
+                put(Int(rshape, v.expr))
+            elif isinstance(v, Ptr):
+                put(Ptr(v.base, v.elem, rshape, v.off))
+            elif isinstance(v, Cond):
+                put(Cond(rshape, v.terms))
+            else:
+                raise NotCanonical("tt.broadcast of a float tensor")
+        elif n in _INT_BIN:
+            a, b = g(0), g(1)
+            if not (isinstance(a, Int) and isinstance(b, Int)):
+                raise NotCanonical(f"{n} on non-integer values")
+            put(Int(_bshape(a.shape, b.shape), _INT_BIN[n](a.expr, b.expr)))
+        elif n == "arith.andi":
+            a, b = g(0), g(1)
+            if not (isinstance(a, Cond) and isinstance(b, Cond)):
+                raise NotCanonical("arith.andi is modelled for conditions only")
+            put(Cond(_bshape(a.shape, b.shape), a.terms + b.terms))
+        elif n in _INT_CASTS:
+            put(g(0))
+        elif n == "arith.cmpi":
+            pred = head.strip().split(",")[0].strip()
+            a, b = g(0), g(1)
+            if not (isinstance(a, Int) and isinstance(b, Int)):
+                raise NotCanonical("arith.cmpi on non-integer values")
+            put(Cond(_bshape(a.shape, b.shape), ((pred, a.expr, b.expr),)))
+        elif n == "tt.addptr":
+            p, o = g(0), g(1)
+            if not (isinstance(p, Ptr) and isinstance(o, Int)):
+                raise NotCanonical("tt.addptr needs a pointer and an integer offset")
+            put(Ptr(p.base, p.elem, _bshape(p.shape, o.shape), p.off + o.expr))
+        elif n == "tt.load":
+            p = g(0)
+            if not isinstance(p, Ptr):
+                raise NotCanonical("tt.load through something that is not a plain pointer")
+            mask = g(1) if len(op.operands) > 1 else None
+            other = g(2) if len(op.operands) > 2 else None
+            if mask is not None and not isinstance(mask, Cond):
+                raise NotCanonical("tt.load mask is not a comparison")
+            if other is not None and not (isinstance(other, Flt) and other.kind == "const" and other.data["value"] == 0.0):
+                raise NotCanonical("tt.load `other` must be zero")
+            put(Flt("load", p.shape, {"ptr": p, "mask": mask, "guard": None}))
+        elif n in _FLT_CASTS:
+            v = g(0)
+            if not isinstance(v, Flt):
+                raise NotCanonical(f"{n} on a non-float value")
+            put(Flt("cast", v.shape, {"src": v, "to": relem}))
+        elif n == "arith.mulf":
+            a, b = g(0), g(1)
+            if isinstance(a, Flt) and a.kind in ("const", "arg"):
+                a, b = b, a
+            if not (isinstance(a, Flt) and isinstance(b, Flt) and b.kind in ("const", "arg")):
+                raise NotCanonical("arith.mulf is modelled only as a scale by a scalar")
+            put(Flt("scale", a.shape, {"src": a, "by": b}))
+        elif n == "tt.dot":
+            a, b, c = g(0), g(1), g(2)
+            if not all(isinstance(v, Flt) for v in (a, b, c)):
+                raise NotCanonical("tt.dot operands are not float tiles")
+            put(Flt("dot", c.shape, {"a": a, "b": b, "c": c}))
+        elif n == "tt.store":
+            p, v = g(0), g(1)
+            mask = g(2) if len(op.operands) > 2 else None
+            if not isinstance(p, Ptr) or not isinstance(v, Flt):
+                raise NotCanonical("tt.store of something that is not a float tile through a plain pointer")
+            if mask is not None and not isinstance(mask, Cond):
+                raise NotCanonical("tt.store mask is not a comparison")
+            self.stores.append((p, v, mask))
+        elif n == "scf.if":
+            self.eval_if(op, env)
+        elif n == "scf.for":
+            self.eval_for(op, env)
+        elif n in ("tt.assume", "llvm.intr.assume"):
+            pass
+        elif not op.results:
+            raise NotCanonical(f"operation with a side effect is not lowered: {n}")
+        else:
+            for r in op.results:
+                env[r] = _Opaque(f"the result of {n}")
+
+    # -- regions --------------------------------------------------------------------------------
+    def eval_if(self, op: Op, env: dict) -> None:
+        cond = self.get(env, op.operands[0])
+        if not isinstance(cond, Cond) or cond.shape != () or len(cond.terms) != 1:
+            raise NotCanonical("scf.if on something that is not one scalar comparison")
+        stores_before = len(self.stores)
+        then_y = self.run(op.regions[0], dict(env))
+        else_y = self.run(op.regions[1], dict(env)) if len(op.regions) > 1 else None
+        if len(self.stores) != stores_before:
+            raise NotCanonical("a store under scf.if is not lowered")
+        if not op.results:
+            return
+        if then_y is None or else_y is None or len(then_y) != len(op.results) or len(else_y) != len(op.results):
+            raise NotCanonical("scf.if without matching yields")
+        for r, t, e in zip(op.results, then_y, else_y):
+            env[r] = self.merge(cond, t, e)
+
+    @staticmethod
+    def merge(cond: Cond, t: Any, e: Any) -> Any:
+        """Both arms of the split: an unmasked load where the compare holds, the masked load of the same
+        addresses elsewhere. The merged value is the masked load, guarded by the compare."""
+        if isinstance(t, Flt) and isinstance(e, Flt):
+            ts, es = t, e
+            casts = []
+            while ts.kind == "cast" and es.kind == "cast" and ts.data["to"] == es.data["to"]:
+                casts.append(ts.data["to"])
+                ts, es = ts.data["src"], es.data["src"]
+            if ts.kind == "load" and es.kind == "load":
+                pt, pe = ts.data["ptr"], es.data["ptr"]
+                same = pt.base == pe.base and pt.shape == pe.shape and sp.expand(pt.off - pe.off) == 0
+                if same and ts.data["mask"] is None and ts.data["guard"] is None and es.data["guard"] is None:
+                    v = Flt("load", es.shape, {"ptr": pe, "mask": es.data["mask"], "guard": cond})
+                    for to in reversed(casts):
+                        v = Flt("cast", v.shape, {"src": v, "to": to})
+                    return v
+        if isinstance(t, Int) and isinstance(e, Int) and t.shape == e.shape and sp.expand(t.expr - e.expr) == 0:
+            return t
+        return _Opaque("an scf.if whose arms are not the unmasked and the masked load of one tile")
+
+    def eval_for(self, op: Op, env: dict) -> None:
+        self.loops += 1
+        if self.loops > 1:
+            raise NotCanonical("more than one loop (nested or persistent kernels are not lowered)")
+        lo, hi, step = (self.get(env, o) for o in op.operands)
+        if not all(isinstance(v, Int) and v.shape == () for v in (lo, hi, step)):
+            raise NotCanonical("loop bounds are not scalar integers")
+        if not step.expr.is_Integer or int(step.expr) <= 0:
+            raise NotCanonical("the loop step is not a positive constant (LoopSplit.cpp:125-131 asks the same)")
+        body = dict(env)
+        body[op.extra["iv"]] = Int((), KIV)
+        holders = []
+        for i, (name, init_name) in enumerate(op.extra["iters"]):
+            init = self.get(env, init_name)
+            if isinstance(init, Int):
+                s = sp.Symbol(f"iter_{i}", integer=True)
+                body[name] = Int(init.shape, s)
+            elif isinstance(init, Ptr):
+                s = sp.Symbol(f"iter_{i}", integer=True)
+                body[name] = Ptr(init.base, init.elem, init.shape, s)
+            elif isinstance(init, Flt):
+                s = None
+                body[name] = Flt("acc", init.shape, {"index": i})
+            else:
+                raise NotCanonical("a loop-carried condition is not lowered")
+            holders.append((s, init))
+        stores_before = len(self.stores)
+        yields = self.run(op.regions[0], body) or []
+        if len(self.stores) != stores_before:
+            raise NotCanonical("a store inside the K loop is not lowered")
+        if len(yields) != len(holders):
+            raise NotCanonical("scf.for yield does not match its iter_args")
+        trip = (KIV - lo.expr) / step.expr
+        closed = {}
+        placeholders = {s for s, _ in holders if s is not None}
+        for (s, init), y in zip(holders, yields):
+            if s is None:
+                continue
+            cur = y.expr if isinstance(y, Int) else y.off if isinstance(y, Ptr) else None
+            if cur is None:
+                raise NotCanonical("a loop-carried integer is yielded as another kind of value")
+            delta = sp.expand(cur - s)
+            if delta.free_symbols & (placeholders | {KIV}):
+                raise NotCanonical("a loop-carried offset does not advance by a loop-invariant amount")
+            start = init.expr if isinstance(init, Int) else init.off
+            closed[s] = start + trip * delta
+        for idx, ((s, init), y) in enumerate(zip(holders, yields)):
+            res = op.results[idx]
+            if s is not None:
+                env[res] = _Opaque("the final value of a loop-carried offset")
+                continue
+            if not (isinstance(y, Flt) and y.kind == "dot" and y.data["c"].kind == "acc" and y.data["c"].data["index"] == idx):
+                raise NotCanonical("the loop-carried float is not `acc = tt.dot(a, b, acc)`")
+            env[res] = Flt("loop_dot", y.shape, {
+                "a": _subst(y.data["a"], closed), "b": _subst(y.data["b"], closed), "init": init,
+                "lo": lo.expr, "hi": hi.expr, "step": step.expr})
+
+
+# --------------------------------------------------------------------------------------------------
+# Matching
+# --------------------------------------------------------------------------------------------------
+
+_DTYPE_NAMES = {"f16": "f16", "bf16": "bf16", "f32": "f32", "f8E4M3FN": "f8e4m3", "f8E5M2": "f8e5m2"}
+
+
+@dataclass
+class DotKernelMatch:
+    """What the K loop of a kernel computes, as expressions over its arguments and program ids."""
+    kernel: str
+    a_arg: str
+    b_arg: str
+    c_arg: str
+    ab_dtype: str
+    out_dtype: str
+    block_m: int
+    block_n: int
+    block_k: int
+    a_row_stride: str
+    a_k_stride: str
+    b_k_stride: str
+    b_col_stride: str
+    c_row_stride: str
+    c_col_stride: str
+    row0: str               # first row of the tile of program (pid_x, pid_y, pid_z)
+    col0: str
+    loop_lo: str
+    loop_hi: str
+    loop_step: int
+    k_per_iv: int           # K elements per unit of the induction variable
+    k_bound: Optional[str]  # the K the load masks compare with; None for unmasked loads
+    m_bound: Optional[str]
+    n_bound: Optional[str]
+    split_pred: Optional[str]       # compare of the induction variable guarding the unmasked loads
+    split_comparand: Optional[str]
+    alpha: Optional[str]            # constant, or the name of a float argument
+    int_args: list = field(default_factory=list)
+
+    def to_json(self) -> str:
+        return json.dumps(self.__dict__, sort_keys=True)
+
+    @staticmethod
+    def from_json(text: str) -> "DotKernelMatch":
+        return DotKernelMatch(**json.loads(text))
+
+
+def _peel(v: Flt) -> tuple:
+    casts, alpha = [], None
+    while v.kind in ("cast", "scale"):
+        if v.kind == "cast":
+            casts.append(v.data["to"])
+            v = v.data["src"]
+        else:
+            if alpha is not None:
+                raise NotCanonical("more than one scalar scale in the epilogue")
+            by = v.data["by"]
+            alpha = repr(by.data["value"]) if by.kind == "const" else by.data["name"]
+            v = v.data["src"]
+    return v, casts, alpha
+
+
+def _affine(expr: Any, what: str) -> tuple:
+    """Coefficients (x0, x1, k_iv, constant) of an address expression that must be affine in them."""
+    try:
+        poly = sp.Poly(sp.expand(expr), X0, X1, KIV)
+    except sp.PolynomialError:
+        raise NotCanonical(f"{what}: the address is not a polynomial in the tile indices")
+    coef = {(1, 0, 0): 0, (0, 1, 0): 0, (0, 0, 1): 0, (0, 0, 0): 0}
+    for mono, c in poly.terms():
+        if mono not in coef:
+            raise NotCanonical(f"{what}: the address is not affine in the tile indices")
+        coef[mono] = c
+    return coef[(1, 0, 0)], coef[(0, 1, 0)], coef[(0, 0, 1)], coef[(0, 0, 0)]
+
+
+def _origin(const: Any, stride: Any, strides: set, what: str) -> Any:
+    o = sp.cancel(const / stride) if const != 0 else sp.Integer(0)
+    if sp.denom(o) != 1 or (o.free_symbols & strides) or (o.free_symbols & {X0, X1, KIV}):
+        raise NotCanonical(f"{what}: the tile origin is not a whole number of rows or columns")
+    return sp.expand(o)
+
+
+def _classify_mask(cond: Optional[Cond], forms: dict, what: str) -> dict:
+    """Each term must be `index < bound` for one of the index forms given; returns {form: bound}."""
+    out: dict = {}
+    if cond is None:
+        return out
+    for pred, l, r in cond.terms:
+        if pred in ("sgt", "ugt"):
+            l, r, pred = r, l, "slt"
+        if pred not in ("slt", "ult"):
+            raise NotCanonical(f"{what}: mask predicate {pred} is not `<`")
+        d = sp.expand(l - r)
+        for key, form in forms.items():
+            bound = sp.expand(form - d)
+            if not (bound.free_symbols & {X0, X1, KIV}):
+                if key in out and sp.expand(out[key] - bound) != 0:
+                    raise NotCanonical(f"{what}: two different bounds on one index")
+                out[key] = bound
+                break
+        else:
+            raise NotCanonical(f"{what}: a mask term is not a bound on the row, column or K index")
+    return out
+
+
+def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMatch:
+    """Analyse the printed TTIR of one kernel. Raises NotCanonical unless it is the K loop described above."""
+    fname, args, ops = parse_module(text, arg_names)
+    ev = _Evaluator(args)
+    ev.run(ops, ev.env)
+    if len(ev.stores) != 1:
+        raise NotCanonical(f"{len(ev.stores)} stores; the K loop has exactly one")
+    c_ptr, value, c_mask = ev.stores[0]
+    value, out_casts, alpha = _peel(value)
+    if value.kind != "loop_dot":
+        raise NotCanonical("the stored value is not the result of the K loop")
+    init = value.data["init"]
+    if not (init.kind == "const" and init.data["value"] == 0.0):
+        raise NotCanonical("the accumulator does not start at zero")
+    a, a_casts, a_alpha = _peel(value.data["a"])
+    b, b_casts, b_alpha = _peel(value.data["b"])
+    if a_alpha or b_alpha or a.kind != "load" or b.kind != "load":
+        raise NotCanonical("the tt.dot operands are not plain loads")
+    pa, pb = a.data["ptr"], b.data["ptr"]
+    if len(pa.shape) != 2 or len(pb.shape) != 2 or len(c_ptr.shape) != 2:
+        raise NotCanonical("tiles are not 2-D")
+    (bm, bk), (bk2, bn) = pa.shape, pb.shape
+    if bk != bk2 or c_ptr.shape != (bm, bn):
+        raise NotCanonical("tile shapes of A, B and C do not agree")
+    if pa.elem != pb.elem or pa.elem not in _DTYPE_NAMES or c_ptr.elem not in _DTYPE_NAMES:
+        raise NotCanonical(f"element types {pa.elem}, {pb.elem} -> {c_ptr.elem} are not supported")
+
+    sa_r, sa_k, sa_iv, ca = _affine(pa.off, "A")
+    sb_k, sb_c, sb_iv, cb = _affine(pb.off, "B")
+    sc_r, sc_c, sc_iv, cc = _affine(c_ptr.off, "C")
+    if sc_iv != 0 or 0 in (sa_r, sa_k, sb_k, sb_c, sc_r, sc_c):
+        raise NotCanonical("an operand has a zero stride or C moves with the loop")
+    kpi_a, kpi_b = sp.cancel(sa_iv / sa_k), sp.cancel(sb_iv / sb_k)
+    if not (kpi_a.is_Integer and kpi_a == kpi_b and int(kpi_a) > 0):
+        raise NotCanonical("A and B do not advance along K by the same whole number of elements per iteration")
+    kpi = int(kpi_a)
+    step = int(value.data["step"])
+    if kpi * step != bk:
+        raise NotCanonical(f"the loop advances {kpi * step} K elements per iteration but the tiles hold {bk}")
+    lo = sp.expand(value.data["lo"])
+    if lo != 0:
+        raise NotCanonical("the K loop does not start at 0")
+
+    stride_syms = set()
+    for s in (sa_r, sa_k, sb_k, sb_c, sc_r, sc_c):
+        stride_syms |= s.free_symbols
+    row0 = _origin(ca, sa_r, stride_syms, "A")
+    col0 = _origin(cb, sb_c, stride_syms, "B")
+    if sp.expand(cc - row0 * sc_r - col0 * sc_c) != 0:
+        raise NotCanonical("C is not stored at the rows of A and the columns of B")
+
+    kk = kpi * KIV
+    a_m = _classify_mask(a.data["mask"], {"k": X1 + kk, "m": row0 + X0}, "A mask")
+    b_m = _classify_mask(b.data["mask"], {"k": X0 + kk, "n": col0 + X1}, "B mask")
+    c_m = _classify_mask(c_mask, {"m": row0 + X0, "n": col0 + X1}, "C mask")
+    if ("k" in a_m) != ("k" in b_m) or ("k" in a_m and sp.expand(a_m["k"] - b_m["k"]) != 0):
+        raise NotCanonical("A and B are not masked by the same K bound")
+    for key, x, y in (("m", a_m, c_m), ("n", b_m, c_m)):
+        if key in x and key in y and sp.expand(x[key] - y[key]) != 0:
+            raise NotCanonical("loads and store disagree on the matrix bounds")
+    m_bound = c_m.get("m", a_m.get("m"))
+    n_bound = c_m.get("n", b_m.get("n"))
+
+    ga, gb = a.data["guard"], b.data["guard"]
+    if (ga is None) != (gb is None):
+        raise NotCanonical("only one operand is loaded under the split compare")
+    split_pred = split_cmp = None
+    if ga is not None:
+        (pa_, la, ra), (pb_, lb, rb) = ga.terms[0], gb.terms[0]
+        if pa_ != pb_ or sp.expand(la - lb) != 0 or sp.expand(ra - rb) != 0:
+            raise NotCanonical("A and B are guarded by different compares")
+        if sp.expand(la - KIV) != 0 or (ra.free_symbols & {KIV, X0, X1}) or pa_ not in ("slt", "ult"):
+            raise NotCanonical("the split compare is not `induction variable < loop-invariant value`")
+        if "k" not in a_m:
+            raise NotCanonical("the guarded-off loads carry no K mask")
+        split_pred, split_cmp = "slt", str(ra)
+
+    return DotKernelMatch(
+        kernel=fname, a_arg=pa.base, b_arg=pb.base, c_arg=c_ptr.base,
+        ab_dtype=_DTYPE_NAMES[pa.elem], out_dtype=_DTYPE_NAMES[c_ptr.elem],
+        block_m=bm, block_n=bn, block_k=bk,
+        a_row_stride=str(sa_r), a_k_stride=str(sa_k), b_k_stride=str(sb_k), b_col_stride=str(sb_c),
+        c_row_stride=str(sc_r), c_col_stride=str(sc_c), row0=str(row0), col0=str(col0),
+        loop_lo=str(lo), loop_hi=str(sp.expand(value.data["hi"])), loop_step=step, k_per_iv=kpi,
+        k_bound=str(a_m["k"]) if "k" in a_m else None,
+        m_bound=str(m_bound) if m_bound is not None else None,
+        n_bound=str(n_bound) if n_bound is not None else None,
+        split_pred=split_pred, split_comparand=split_cmp, alpha=alpha,
+        int_args=sorted(ev.arg_symbols))
+
+
+# --------------------------------------------------------------------------------------------------
+# Binding one launch
+# --------------------------------------------------------------------------------------------------
+
+@dataclass
+class BoundDot:
+    m: int
+    n: int
+    k: int
+    a_layout: str   # "row" | "col"
+    b_layout: str
+    lda: int
+    ldb: int
+    ldc: int
+    alpha: float
+    block_k: int
+    k_main: int     # K elements the unmasked iterations cover
+
+
+def _value(expr: Optional[str], scalars: dict) -> Optional[int]:
+    if expr is None:
+        return None
+    local = {name: sp.Symbol(name, integer=True) for name in scalars}
+    e = sp.sympify(expr, locals=local)
+    v = e.subs({local[n]: scalars[n] for n in local})
+    if not v.is_Integer:
+        raise NotCanonical(f"{expr} does not evaluate to an integer for this launch ({v})")
+    return int(v)
+
+
+def _tile_origins(match: DotKernelMatch, scalars: dict, grid: tuple) -> tuple:
+    import numpy as np
+
+    gx, gy, gz = grid
+    if gx * gy * gz > (1 << 24):
+        raise NotCanonical("grid too large to check")
+    px, py, pz = np.meshgrid(np.arange(gx), np.arange(gy), np.arange(gz), indexing="ij")
+    env = {"pid_x": px.ravel(), "pid_y": py.ravel(), "pid_z": pz.ravel(),
+           "nprog_x": gx, "nprog_y": gy, "nprog_z": gz}
+    names = list(scalars) + list(env)
+    local = {n: sp.Symbol(n, integer=True) for n in names}
+    out = []
+    for text in (match.row0, match.col0):
+        e = sp.sympify(text, locals=local)
+        fn = sp.lambdify([local[n] for n in names], e, modules="numpy")
+        with np.errstate(all="ignore"):
+            v = np.broadcast_to(np.asarray(fn(*[scalars[n] for n in scalars], *[env[n] for n in env]), dtype=np.float64),
+                                px.size)
+        if not np.isfinite(v).all():
+            raise NotCanonical("the tile origin is undefined for some program ids of this grid (division by zero)")
+        out.append(v.astype(np.int64))
+    return out[0], out[1]
+
+
+def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional[dict] = None) -> BoundDot:
+    """Check one launch (integer argument values, grid) against the match and return the GEMM it is.
+
+    Raises NotCanonical when this launch is outside what the library kernel reproduces: a layout with no
+    unit stride, a grid that does not cover C exactly once, a split point past the last full K block.
+    """
+    import numpy as np
+
+    grid = tuple(int(g) for g in grid) + (1,) * (3 - len(grid))
+    sv = {k: int(v) for k, v in scalars.items()}
+    a_r, a_k = _value(match.a_row_stride, sv), _value(match.a_k_stride, sv)
+    b_k, b_c = _value(match.b_k_stride, sv), _value(match.b_col_stride, sv)
+    c_r, c_c = _value(match.c_row_stride, sv), _value(match.c_col_stride, sv)
+    if c_c != 1:
+        raise NotCanonical(f"C must be row-major (column stride {c_c})")
+    if a_k == 1:
+        a_layout, lda = "row", a_r
+    elif a_r == 1:
+        a_layout, lda = "col", a_k
+    else:
+        raise NotCanonical(f"A has no unit stride ({a_r}, {a_k})")
+    if b_c == 1:
+        b_layout, ldb = "row", b_k
+    elif b_k == 1:
+        b_layout, ldb = "col", b_c
+    else:
+        raise NotCanonical(f"B has no unit stride ({b_k}, {b_c})")
+
+    hi = _value(match.loop_hi, sv)
+    n_iter = max(0, -(-hi // match.loop_step))
+    covered = n_iter * match.block_k
+    k = _value(match.k_bound, sv)
+    if k is None:
+        k = covered
+    elif covered < k:
+        raise NotCanonical(f"the loop covers {covered} of K={k}")
+    if k < 1:
+        raise NotCanonical("empty K")
+
+    rows, cols = _tile_origins(match, sv, grid)
+    m = _value(match.m_bound, sv)
+    n = _value(match.n_bound, sv)
+    live = np.ones(rows.shape, bool)
+    if m is not None:
+        live &= rows < m
+    if n is not None:
+        live &= cols < n
+    if m is None:
+        m = int(rows.max()) + match.block_m
+    if n is None:
+        n = int(cols.max()) + match.block_n
+    tm, tn = -(-m // match.block_m), -(-n // match.block_n)
+    r, c = rows[live], cols[live]
+    if (r % match.block_m).any() or (c % match.block_n).any() or (r < 0).any() or (c < 0).any():
+        raise NotCanonical("tile origins are not multiples of the block shape")
+    ids = (r // match.block_m) * tn + (c // match.block_n)
+    if ids.size != tm * tn or np.unique(ids).size != tm * tn:
+        raise NotCanonical(f"the grid {grid} does not cover the {tm}x{tn} tiles of C exactly once")
+
+    k_main = (k // match.block_k) * match.block_k
+    if match.split_comparand is not None:
+        split = _value(match.split_comparand, sv)
+        last = min(split, hi)
+        if last > 0:
+            iv_max = ((last - 1) // match.loop_step) * match.loop_step
+            if iv_max * match.k_per_iv + match.block_k > k:
+                raise NotCanonical(f"split point {split} lets an unmasked load run past K={k}")
+        k_main = min(k_main, max(0, -(-last // match.loop_step)) * match.block_k)
+
+    alpha = 1.0
+    if match.alpha is not None:
+        try:
+            alpha = float(match.alpha)
+        except ValueError:
+            alpha = float((float_args or {})[match.alpha])
+    for name, ld, need in (("A", lda, k if a_layout == "row" else m), ("B", ldb, n if b_layout == "row" else k),
+                           ("C", c_r, n)):
+        if ld < need:
+            raise NotCanonical(f"{name}: leading dimension {ld} is smaller than its extent {need}")
+    return BoundDot(m=m, n=n, k=k, a_layout=a_layout, b_layout=b_layout, lda=lda, ldb=ldb, ldc=c_r,
+                    alpha=alpha, block_k=match.block_k, k_main=k_main)
