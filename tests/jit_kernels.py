@@ -135,3 +135,40 @@ def nonzero_fill_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
         b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :], mask=(k + rk)[:, None] < K, other=0.0)
         acc = tl.dot(a, b, acc)
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def scaled_kloop(a_ptr, b_ptr, c_ptr, rs_ptr, cs_ptr, M, N, K, stride_am, stride_bk, stride_cm, alpha,
+                 BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """The quantised-GEMM epilogue: per-row and per-column fp32 factors and a scalar, then the cast."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :],
+                    mask=(rm[:, None] < M) & ((k + rk)[None, :] < K), other=0.0)
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :],
+                    mask=((k + rk)[:, None] < K) & (rn[None, :] < N), other=0.0)
+        acc = tl.dot(a, b, acc)
+    rs = tl.load(rs_ptr + rm, mask=rm < M, other=0.0)
+    cs = tl.load(cs_ptr + rn, mask=rn < N, other=0.0)
+    out = acc * rs[:, None] * cs[None, :] * alpha
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], out.to(c_ptr.dtype.element_ty),
+             mask=(rm[:, None] < M) & (rn[None, :] < N))
+
+
+@triton.jit
+def wrong_scale_kloop(a_ptr, b_ptr, c_ptr, rs_ptr, K, stride_am, stride_bk, stride_cm,
+                      BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: the row factors are read from the next tile's rows."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    rs = tl.load(rs_ptr + rm + BLOCK_M)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], (acc * rs[:, None]).to(c_ptr.dtype.element_ty))

@@ -121,6 +121,36 @@ def test_plain_kloop_without_masks():
     assert (b.m, b.n, b.k, b.k_main) == (384, 320, 512, 512)
 
 
+def scaled_sig(dt="f8e4m3"):
+    sig = {"a_ptr": PTR[dt], "b_ptr": PTR[dt], "c_ptr": "*bf16", "rs_ptr": "*fp32", "cs_ptr": "*fp32", "M": "i32",
+           "N": "i32", "K": "i32", "stride_am": "i32", "stride_bk": "i32", "stride_cm": "i32", "alpha": "fp32",
+           "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    return sig, {"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 128}
+
+
+@pytest.mark.parametrize("dt", ["f8e4m3", "bf16"])
+def test_scaled_kloop_row_and_column_factors(dt):
+    """The scale idioms of the reference's epilogues (06-fused-attention.py:66,78,237): a scalar and per-row
+    factors, plus per-column factors, all before the cast."""
+    m = compiler.analyse(jk.scaled_kloop, *scaled_sig(dt))
+    assert (m.ab_dtype, m.out_dtype) == (dt, "bf16")
+    assert (m.row_scale_arg, m.col_scale_arg, m.alpha) == ("rs_ptr", "cs_ptr", "alpha")
+    assert (m.k_bound, m.m_bound, m.n_bound) == ("K", "M", "N")
+    b = ttir.bind(m, dict(M=300, N=200, K=500, stride_am=512, stride_bk=256, stride_cm=256), (3, 2), {"alpha": 2.0})
+    assert (b.m, b.n, b.k, b.lda, b.ldb, b.ldc, b.alpha, b.k_main) == (300, 200, 500, 512, 256, 256, 2.0, 384)
+    assert ttir.DotKernelMatch.from_json(m.to_json()) == m
+
+
+def test_scale_vector_of_other_rows_is_refused():
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "rs_ptr": "*fp32", "K": "i32", "stride_am": "i32",
+           "stride_bk": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    with pytest.raises(ttir.NotCanonical, match="not indexed by the tile's own rows"):
+        compiler.analyse(jk.wrong_scale_kloop, sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
+    sig["rs_ptr"] = "*fp16"
+    with pytest.raises(ttir.NotCanonical):  # factors that are not fp32 in memory
+        compiler.analyse(jk.wrong_scale_kloop, sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
+
+
 @pytest.mark.parametrize("kernel,why", [
     (jk.relu_kloop, "depends on the result of"),
     (jk.shifted_rows_kloop, "rows of A"),

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _fresh_kernels():
     yield
-    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop):
+    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop):
         fn.device_caches.clear()
 
 
@@ -95,6 +95,26 @@ def test_plain_kloop_fp32_out(built_libs, cuda_device):
                                             BLOCK_M=128, BLOCK_N=64, BLOCK_K=64)
     torch.cuda.synchronize()
     torch.testing.assert_close(c, a.float() @ b.float(), rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.bfloat16])
+def test_scaled_kloop_with_row_and_column_factors(built_libs, cuda_device, dtype):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 300, 208, 528
+    a, b = _rand((M, K), dtype, cuda_device, 11), _rand((K, N), dtype, cuda_device, 12)
+    rs = torch.rand(M, device=cuda_device) + 0.5
+    cs = torch.rand(N, device=cuda_device) + 0.5
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    with tbk.activate():
+        jk.scaled_kloop[(math.ceil(M / 128), math.ceil(N / 128))](
+            a, b, c, rs, cs, M, N, K, a.stride(0), b.stride(0), c.stride(0), 0.25,
+            BLOCK_M=128, BLOCK_N=128, BLOCK_K=128)
+    torch.cuda.synchronize()
+    ref = 0.25 * rs[:, None] * cs[None, :] * (a.float() @ b.float())
+    tol = 3e-2 if dtype == torch.float8_e4m3fn else 1e-2
+    torch.testing.assert_close(c.float(), ref, rtol=tol, atol=tol * ref.abs().max().item())
+    assert torch.equal(c, backend.dot(a, b, out_dtype=torch.bfloat16, row_scale=rs, col_scale=cs, alpha=0.25, check=True))
 
 
 def test_cpu_tensors_are_refused(built_libs, cuda_device):

@@ -65,7 +65,8 @@ class B200DotLauncher:
             problem = backend.make_problem(
                 bound.m, bound.n, bound.k, getattr(torch, _TORCH_DTYPES[match.ab_dtype]),
                 getattr(torch, _TORCH_DTYPES[match.out_dtype]), a_layout=layouts[bound.a_layout],
-                b_layout=layouts[bound.b_layout], lda=bound.lda, ldb=bound.ldb, ldc=bound.ldc, alpha=bound.alpha)
+                b_layout=layouts[bound.b_layout], lda=bound.lda, ldb=bound.ldb, ldc=bound.ldc, alpha=bound.alpha,
+                row_scale=match.row_scale_arg is not None, col_scale=match.col_scale_arg is not None)
             config, info, module = plugin.lower_dot(problem, bound.block_k, split_comparand=bound.k_main)
             entry = {"bound": bound, "problem": problem, "config": config, "info": info, "ir": str(module), "plan": None}
             self._bound[key] = entry
@@ -87,13 +88,19 @@ class B200DotLauncher:
                 raise TypeError(f"{name} must be a CUDA tensor; there is no CPU path")
             if t.dtype != getattr(torch, _TORCH_DTYPES[dt]):
                 raise TypeError(f"{name} is {t.dtype}, the kernel was compiled for {dt}")
+        scales = []
+        for name in (match.row_scale_arg, match.col_scale_arg):
+            t = values[name] if name is not None else None
+            if t is not None and not (hasattr(t, "data_ptr") and t.is_cuda and t.dtype == torch.float32):
+                raise TypeError(f"{name} must be a CUDA float32 tensor")
+            scales.append(t.data_ptr() if t is not None else None)
         entry = self.prepare(match, values, (grid_x, grid_y, grid_z), torch.cuda.current_device())
         if entry["plan"] is None:
             entry["plan"] = backend.DotPlan(entry["problem"], entry["config"])
         plan = entry["plan"]
         if enter_hook is not None:
             enter_hook(launch_metadata)
-        backend._check(plan._lib.tx_dot_run(plan._h, a.data_ptr(), b.data_ptr(), c.data_ptr(), None, None,
+        backend._check(plan._lib.tx_dot_run(plan._h, a.data_ptr(), b.data_ptr(), c.data_ptr(), scales[0], scales[1],
                                             ctypes.c_void_p(int(stream))))
         self.launches += 1
         if exit_hook is not None:

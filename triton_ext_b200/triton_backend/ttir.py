@@ -373,9 +373,13 @@ class _Evaluator:
         elif n == "tt.expand_dims":
             v = g(0)
             axis = int(re.search(r"axis = (\d+)", head).group(1))
-            if not isinstance(v, (Int, Cond)) or len(v.shape) != 1:
-                raise NotCanonical("tt.expand_dims is modelled for rank-1 integer tensors only")
             ren = {X0: X1} if axis == 0 else {}
+            if isinstance(v, Flt) and v.kind == "load" and len(v.shape) == 1:
+                # a vector of per-row (axis 1 added) or per-column (axis 0 added) factors
+                put(Flt("vec", rshape, {"src": _subst(v, ren), "along": "col" if axis == 0 else "row"}))
+                return
+            if not isinstance(v, (Int, Cond)) or len(v.shape) != 1:
+                raise NotCanonical("tt.expand_dims is modelled for rank-1 tensors only")
             if isinstance(v, Int):
                 put(Int(rshape, v.expr.subs(ren)))
             else:
@@ -388,8 +392,10 @@ class _Evaluator:
                 put(Ptr(v.base, v.elem, rshape, v.off))
             elif isinstance(v, Cond):
                 put(Cond(rshape, v.terms))
+            elif isinstance(v, Flt) and v.kind == "vec":
+                put(Flt("vec", rshape, dict(v.data)))
             else:
-                raise NotCanonical("tt.broadcast of a float tensor")
+                raise NotCanonical("tt.broadcast of a float tile")
         elif n in _INT_BIN:
             a, b = g(0), g(1)
             if not (isinstance(a, Int) and isinstance(b, Int)):
@@ -431,11 +437,14 @@ class _Evaluator:
             put(Flt("cast", v.shape, {"src": v, "to": relem}))
         elif n == "arith.mulf":
             a, b = g(0), g(1)
-            if isinstance(a, Flt) and a.kind in ("const", "arg"):
+            if isinstance(a, Flt) and a.kind in ("const", "arg", "vec"):
                 a, b = b, a
-            if not (isinstance(a, Flt) and isinstance(b, Flt) and b.kind in ("const", "arg")):
-                raise NotCanonical("arith.mulf is modelled only as a scale by a scalar")
-            put(Flt("scale", a.shape, {"src": a, "by": b}))
+            if not (isinstance(a, Flt) and isinstance(b, Flt) and b.kind in ("const", "arg", "vec")):
+                raise NotCanonical("arith.mulf is modelled only as a scale by a scalar or by a row / column vector")
+            if b.kind == "vec":
+                put(Flt("vscale", _bshape(a.shape, b.shape), {"src": a, "vec": b}))
+            else:
+                put(Flt("scale", a.shape, {"src": a, "by": b}))
         elif n == "tt.dot":
             a, b, c = g(0), g(1), g(2)
             if not all(isinstance(v, Flt) for v in (a, b, c)):
@@ -596,6 +605,8 @@ class DotKernelMatch:
     split_comparand: Optional[str]
     alpha: Optional[str]            # constant, or the name of a float argument
     int_args: list = field(default_factory=list)
+    row_scale_arg: Optional[str] = None  # fp32 vector multiplied into the rows before the cast
+    col_scale_arg: Optional[str] = None
 
     def to_json(self) -> str:
         return json.dumps(self.__dict__, sort_keys=True)
@@ -605,11 +616,16 @@ class DotKernelMatch:
         return DotKernelMatch(**json.loads(text))
 
 
-def _peel(v: Flt) -> tuple:
+def _peel(v: Flt, vecs: Optional[list] = None) -> tuple:
     casts, alpha = [], None
-    while v.kind in ("cast", "scale"):
+    while v.kind in ("cast", "scale", "vscale"):
         if v.kind == "cast":
             casts.append(v.data["to"])
+            v = v.data["src"]
+        elif v.kind == "vscale":
+            if vecs is None:
+                raise NotCanonical("a tt.dot operand is scaled by a vector")
+            vecs.append(v.data["vec"])
             v = v.data["src"]
         else:
             if alpha is not None:
@@ -618,6 +634,22 @@ def _peel(v: Flt) -> tuple:
             alpha = repr(by.data["value"]) if by.kind == "const" else by.data["name"]
             v = v.data["src"]
     return v, casts, alpha
+
+
+def _scale_vector(vec: Flt, origin: Any, index: Any, key: str, bounds: dict) -> str:
+    """A scale vector must be an fp32 load of base[origin + index], masked (if at all) by the matrix bound."""
+    load = vec.data["src"]
+    p = load.data["ptr"]
+    if p.elem != "f32":
+        raise NotCanonical(f"the {vec.data['along']} scale vector is {p.elem}, not f32")
+    if sp.expand(p.off - origin - index) != 0:
+        raise NotCanonical(f"the {vec.data['along']} scale vector is not indexed by the tile's own {vec.data['along']}s")
+    m = _classify_mask(load.data["mask"], {key: origin + index}, f"{vec.data['along']} scale mask")
+    if key in m:
+        if bounds.get(key) is not None and sp.expand(bounds[key] - m[key]) != 0:
+            raise NotCanonical("a scale vector and the store disagree on the matrix bounds")
+        bounds.setdefault(key, m[key])
+    return p.base
 
 
 def _affine(expr: Any, what: str) -> tuple:
@@ -672,7 +704,8 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
     if len(ev.stores) != 1:
         raise NotCanonical(f"{len(ev.stores)} stores; the K loop has exactly one")
     c_ptr, value, c_mask = ev.stores[0]
-    value, out_casts, alpha = _peel(value)
+    vecs: list = []
+    value, out_casts, alpha = _peel(value, vecs)
     if value.kind != "loop_dot":
         raise NotCanonical("the stored value is not the result of the K loop")
     init = value.data["init"]
@@ -724,8 +757,18 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
     for key, x, y in (("m", a_m, c_m), ("n", b_m, c_m)):
         if key in x and key in y and sp.expand(x[key] - y[key]) != 0:
             raise NotCanonical("loads and store disagree on the matrix bounds")
-    m_bound = c_m.get("m", a_m.get("m"))
-    n_bound = c_m.get("n", b_m.get("n"))
+    bounds = {"m": c_m.get("m", a_m.get("m")), "n": c_m.get("n", b_m.get("n"))}
+    row_scale = col_scale = None
+    for vec in vecs:
+        if vec.data["along"] == "row":
+            if row_scale is not None:
+                raise NotCanonical("more than one row scale vector")
+            row_scale = _scale_vector(vec, row0, X0, "m", bounds)
+        else:
+            if col_scale is not None:
+                raise NotCanonical("more than one column scale vector")
+            col_scale = _scale_vector(vec, col0, X1, "n", bounds)
+    m_bound, n_bound = bounds["m"], bounds["n"]
 
     ga, gb = a.data["guard"], b.data["guard"]
     if (ga is None) != (gb is None):
@@ -752,7 +795,7 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
         m_bound=str(m_bound) if m_bound is not None else None,
         n_bound=str(n_bound) if n_bound is not None else None,
         split_pred=split_pred, split_comparand=split_cmp, alpha=alpha,
-        int_args=sorted(ev.arg_symbols))
+        int_args=sorted(ev.arg_symbols), row_scale_arg=row_scale, col_scale_arg=col_scale)
 
 
 # --------------------------------------------------------------------------------------------------
