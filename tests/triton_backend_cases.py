@@ -244,3 +244,20 @@ def test_jit_launch_reaches_the_pass_pipeline():
     assert cfg.k_split_point == 4096
     assert info["k_main_iters"] * info["block_k"] == 4096 and info["k_tail_iters"] == 1
     assert "4096" in entry["ir"]
+
+
+def test_text_helpers():
+    """The pieces of the IR reader, on lines as Triton prints them."""
+    line = '    %a = tt.load %p, %m, %cst : tensor<128x64x!tt.ptr<bf16>> loc(#loc12)'
+    assert ttir.strip_locations(line + '\n#loc12 = loc("f.py":3:4)') == line[:-len(" loc(#loc12)")]
+    nested = '%0 = arith.addi %x, %y : i32 loc(callsite(#loc3 at #loc4))'
+    assert ttir.strip_locations(nested) == "%0 = arith.addi %x, %y : i32"
+    assert ttir.parse_type("tensor<128x64x!tt.ptr<bf16>>") == ((128, 64), "!tt.ptr<bf16>")
+    assert ttir.parse_type("tensor<1x32xi1>") == ((1, 32), "i1")
+    assert ttir.parse_type("i32") == ((), "i32")
+    assert ttir._split_types("{end = 128 : i32, start = 0 : i32} : tensor<128xi32>") == \
+        ("{end = 128 : i32, start = 0 : i32}", "tensor<128xi32>")
+    assert ttir._result_type("tensor<128xi32> -> tensor<128x1xi32>") == "tensor<128x1xi32>"
+    assert ttir._result_type("tensor<64x64xf32> to tensor<64x64xbf16>") == "tensor<64x64xbf16>"
+    assert ttir._result_type("tensor<8x!tt.ptr<f16>>, tensor<8xi32>") == "tensor<8x!tt.ptr<f16>>"
+    assert ttir._expand_results("%2:2, %x") == ["%2#0", "%2#1", "%x"]
