@@ -172,3 +172,48 @@ def wrong_scale_kloop(a_ptr, b_ptr, c_ptr, rs_ptr, K, stride_am, stride_bk, stri
         acc = tl.dot(a, b, acc)
     rs = tl.load(rs_ptr + rm + BLOCK_M)
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], (acc * rs[:, None]).to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def wrapped_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn,
+                  BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Row and column indices of the loads wrap around the matrix instead of being masked; only K is masked
+    in the loop and only the store masks rows and columns. Compiler hints on the indices."""
+    pid = tl.program_id(0)
+    tiles_n = tl.cdiv(N, BLOCK_N)
+    pid_m = pid // tiles_n
+    pid_n = pid % tiles_n
+    tl.assume(pid_m >= 0)
+    tl.assume(stride_am > 0)
+    rm = (pid_m * BLOCK_M + tl.arange(0, BLOCK_M)) % M
+    rn = (pid_n * BLOCK_N + tl.arange(0, BLOCK_N)) % N
+    rm = tl.max_contiguous(tl.multiple_of(rm, BLOCK_M), BLOCK_M)
+    rk = tl.arange(0, BLOCK_K)
+    a_ptrs = a_ptr + (rm[:, None] * stride_am + rk[None, :] * stride_ak)
+    b_ptrs = b_ptr + (rk[:, None] * stride_bk + rn[None, :] * stride_bn)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for kb in range(0, tl.cdiv(K, BLOCK_K)):
+        a = tl.load(a_ptrs, mask=rk[None, :] < K - kb * BLOCK_K, other=0.0)
+        b = tl.load(b_ptrs, mask=rk[:, None] < K - kb * BLOCK_K, other=0.0)
+        acc = tl.dot(a, b, acc)
+        a_ptrs += BLOCK_K * stride_ak
+        b_ptrs += BLOCK_K * stride_bk
+    cm = pid_m * BLOCK_M + tl.arange(0, BLOCK_M)
+    cn = pid_n * BLOCK_N + tl.arange(0, BLOCK_N)
+    tl.store(c_ptr + stride_cm * cm[:, None] + stride_cn * cn[None, :], acc.to(c_ptr.dtype.element_ty),
+             mask=(cm[:, None] < M) & (cn[None, :] < N))
+
+
+@triton.jit
+def wrapped_unmasked_store_kloop(a_ptr, b_ptr, c_ptr, M, K, stride_am, stride_bk, stride_cm,
+                                 BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: rows wrap around M but the store keeps the wrapped rows."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + (rm % M)[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))

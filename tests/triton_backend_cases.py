@@ -121,6 +121,21 @@ def test_plain_kloop_without_masks():
     assert (b.m, b.n, b.k, b.k_main) == (384, 320, 512, 512)
 
 
+def test_wrapped_indices_need_a_masked_store():
+    """Loads whose row / column indices are taken modulo M / N (no row or column masks in the loop) are the
+    plain GEMM as long as the store masks with the same bounds."""
+    sig, cx = split_sig("f16", "f16", bm=128, bn=64, bk=64)
+    del sig["K_MAIN"]
+    m = compiler.analyse(jk.wrapped_kloop, sig, cx)
+    assert (m.k_bound, m.m_bound, m.n_bound, m.k_per_iv, m.loop_step) == ("K", "M", "N", 64, 1)
+    b = ttir.bind(m, dict(M=300, N=200, K=500, stride_am=500, stride_bk=200, stride_cm=200), (3 * 4,))
+    assert (b.m, b.n, b.k, b.k_main) == (300, 200, 500, 448)
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "M": "i32", "K": "i32", "stride_am": "i32",
+           "stride_bk": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    with pytest.raises(ttir.NotCanonical, match="wrapped by something that is not the bound the store masks with"):
+        compiler.analyse(jk.wrapped_unmasked_store_kloop, sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
+
+
 def scaled_sig(dt="f8e4m3"):
     sig = {"a_ptr": PTR[dt], "b_ptr": PTR[dt], "c_ptr": "*bf16", "rs_ptr": "*fp32", "cs_ptr": "*fp32", "M": "i32",
            "N": "i32", "K": "i32", "stride_am": "i32", "stride_bk": "i32", "stride_cm": "i32", "alpha": "fp32",

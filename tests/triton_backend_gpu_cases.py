@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _fresh_kernels():
     yield
-    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop):
+    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop, jk.wrapped_kloop):
         fn.device_caches.clear()
 
 
@@ -115,6 +115,45 @@ def test_scaled_kloop_with_row_and_column_factors(built_libs, cuda_device, dtype
     tol = 3e-2 if dtype == torch.float8_e4m3fn else 1e-2
     torch.testing.assert_close(c.float(), ref, rtol=tol, atol=tol * ref.abs().max().item())
     assert torch.equal(c, backend.dot(a, b, out_dtype=torch.bfloat16, row_scale=rs, col_scale=cs, alpha=0.25, check=True))
+
+
+def test_wrapped_kloop_ragged(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 300, 200, 504
+    a, b = _rand((M, K), torch.float16, cuda_device, 13), _rand((K, N), torch.float16, cuda_device, 14)
+    c = torch.full((M, N), float("nan"), dtype=torch.float16, device=cuda_device)
+    with tbk.activate():
+        jk.wrapped_kloop[(math.ceil(M / 128) * math.ceil(N / 64),)](
+            a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
+            BLOCK_M=128, BLOCK_N=64, BLOCK_K=64)
+    torch.cuda.synchronize()
+    assert torch.equal(c, backend.dot(a, b, check=True))
+    ref = a.float() @ b.float()
+    torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
+def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
+    """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 512, 256, 1096
+    a, b = _rand((M, K), torch.bfloat16, cuda_device, 15), _rand((K, N), torch.bfloat16, cuda_device, 16)
+    c = torch.zeros((M, N), dtype=torch.bfloat16, device=cuda_device)
+    with tbk.activate():
+        _launch_split(a, b, c, 1024)
+        torch.cuda.synchronize()
+        want = c.clone()
+        c.zero_()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                _launch_split(a, b, c, 1024)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+    assert torch.equal(c, want) and torch.equal(c, backend.dot(a, b, check=True))
 
 
 def test_cpu_tensors_are_refused(built_libs, cuda_device):

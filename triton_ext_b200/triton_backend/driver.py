@@ -44,6 +44,8 @@ class B200DotUtils:
 class B200DotLauncher:
     """Called as launcher(gridX, gridY, gridZ, stream, function, metadata..., hooks..., *kernel args)."""
 
+    MAX_CACHED_SHAPES = 256
+
     def __init__(self, src: Any, metadata: Any):
         self.arg_names = list(src.fn.arg_names)
         self._bound: dict = {}
@@ -69,6 +71,10 @@ class B200DotLauncher:
                 row_scale=match.row_scale_arg is not None, col_scale=match.col_scale_arg is not None)
             config, info, module = plugin.lower_dot(problem, bound.block_k, split_comparand=bound.k_main)
             entry = {"bound": bound, "problem": problem, "config": config, "info": info, "ir": str(module), "plan": None}
+            if len(self._bound) >= self.MAX_CACHED_SHAPES:  # oldest launch shape goes, with its plan
+                old = self._bound.pop(next(iter(self._bound)))
+                if old["plan"] is not None:
+                    old["plan"].close()
             self._bound[key] = entry
         return entry
 

@@ -666,6 +666,18 @@ def _affine(expr: Any, what: str) -> tuple:
     return coef[(1, 0, 0)], coef[(0, 1, 0)], coef[(0, 0, 1)], coef[(0, 0, 0)]
 
 
+def _unwrap(expr: Any) -> tuple:
+    """Replace every Mod(inner, modulus) whose modulus is loop- and tile-invariant by `inner`; the caller
+    checks afterwards that the wrap cannot reach a stored element. Returns (expression, [(inner, modulus)])."""
+    wraps = []
+    for atom in list(expr.atoms(sp.Mod)):
+        inner, modulus = atom.args
+        if not (modulus.free_symbols & {X0, X1, KIV}) and (inner.free_symbols & {X0, X1}):
+            wraps.append((sp.expand(inner), sp.expand(modulus)))
+            expr = expr.subs(atom, inner)
+    return expr, wraps
+
+
 def _origin(const: Any, stride: Any, strides: set, what: str) -> Any:
     o = sp.cancel(const / stride) if const != 0 else sp.Integer(0)
     if sp.denom(o) != 1 or (o.free_symbols & strides) or (o.free_symbols & {X0, X1, KIV}):
@@ -724,8 +736,10 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
     if pa.elem != pb.elem or pa.elem not in _DTYPE_NAMES or c_ptr.elem not in _DTYPE_NAMES:
         raise NotCanonical(f"element types {pa.elem}, {pb.elem} -> {c_ptr.elem} are not supported")
 
-    sa_r, sa_k, sa_iv, ca = _affine(pa.off, "A")
-    sb_k, sb_c, sb_iv, cb = _affine(pb.off, "B")
+    a_off, a_wraps = _unwrap(pa.off)
+    b_off, b_wraps = _unwrap(pb.off)
+    sa_r, sa_k, sa_iv, ca = _affine(a_off, "A")
+    sb_k, sb_c, sb_iv, cb = _affine(b_off, "B")
     sc_r, sc_c, sc_iv, cc = _affine(c_ptr.off, "C")
     if sc_iv != 0 or 0 in (sa_r, sa_k, sb_k, sb_c, sc_r, sc_c):
         raise NotCanonical("an operand has a zero stride or C moves with the loop")
@@ -769,6 +783,13 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
                 raise NotCanonical("more than one column scale vector")
             col_scale = _scale_vector(vec, col0, X1, "n", bounds)
     m_bound, n_bound = bounds["m"], bounds["n"]
+    # Rows of A (columns of B) taken modulo the matrix extent are the rows themselves wherever the store
+    # writes; the wrapped ones only feed elements the store masks off.
+    for wraps, index, bound, stored, what in ((a_wraps, row0 + X0, m_bound, "m" in c_m, "row"),
+                                              (b_wraps, col0 + X1, n_bound, "n" in c_m, "column")):
+        for inner, modulus in wraps:
+            if sp.expand(inner - index) != 0 or bound is None or not stored or sp.expand(modulus - bound) != 0:
+                raise NotCanonical(f"a {what} index is wrapped by something that is not the bound the store masks with")
 
     ga, gb = a.data["guard"], b.data["guard"]
     if (ga is None) != (gb is None):
