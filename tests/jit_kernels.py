@@ -217,3 +217,34 @@ def wrapped_unmasked_store_kloop(a_ptr, b_ptr, c_ptr, M, K, stride_am, stride_bk
         b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
         acc = tl.dot(a, b, acc)
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def _tile_of(t, tiles_m, tiles_n, GROUP: tl.constexpr):
+    per_group = GROUP * tiles_n
+    first_m = (t // per_group) * GROUP
+    rows_here = min(tiles_m - first_m, GROUP)
+    return first_m + (t % per_group) % rows_here, (t % per_group) // rows_here
+
+
+@triton.jit
+def persistent_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stride_cm,
+                     BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr, GROUP: tl.constexpr):
+    """A persistent kernel: as many programs as the launch gives, each walking the tiles of C with a stride
+    of the program count; a helper function maps the tile number to a grouped (row, column) order."""
+    tiles_m = tl.cdiv(M, BLOCK_M)
+    tiles_n = tl.cdiv(N, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    for t in range(tl.program_id(0), tiles_m * tiles_n, tl.num_programs(0)):
+        pid_m, pid_n = _tile_of(t, tiles_m, tiles_n, GROUP)
+        rm = pid_m * BLOCK_M + tl.arange(0, BLOCK_M)
+        rn = pid_n * BLOCK_N + tl.arange(0, BLOCK_N)
+        acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+        for k in range(0, K, BLOCK_K):
+            a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :],
+                        mask=(rm[:, None] < M) & ((k + rk)[None, :] < K), other=0.0)
+            b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :],
+                        mask=((k + rk)[:, None] < K) & (rn[None, :] < N), other=0.0)
+            acc = tl.dot(a, b, acc)
+        tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty),
+                 mask=(rm[:, None] < M) & (rn[None, :] < N))

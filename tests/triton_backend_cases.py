@@ -136,6 +136,24 @@ def test_wrapped_indices_need_a_masked_store():
         compiler.analyse(jk.wrapped_unmasked_store_kloop, sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
 
 
+def test_persistent_kernel_with_a_tile_loop():
+    """A loop over tiles around the K loop, a helper function (inlined) for the tile order: the origin becomes a
+    function of the tile loop's induction variable and bind() walks every program's iterations."""
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "M": "i32", "N": "i32", "K": "i32", "stride_am": "i32",
+           "stride_bk": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr",
+           "BLOCK_K": "constexpr", "GROUP": "constexpr"}
+    m = compiler.analyse(jk.persistent_kloop, sig, {"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64, "GROUP": 8})
+    assert m.tile_loop == ["pid_x", "floor(M/128 + 127/128)*floor(N/128 + 127/128)", "nprog_x"]
+    assert "tile_iv" in m.row0 and "tile_iv" in m.col0 and "pid_x" not in m.row0
+    assert ttir.DotKernelMatch.from_json(m.to_json()) == m
+    s = dict(M=3000, N=2000, K=500, stride_am=512, stride_bk=2048, stride_cm=2048)
+    for programs in (148, 7, 1, 1000):
+        b = ttir.bind(m, s, (programs,))
+        assert (b.m, b.n, b.k, b.k_main) == (3000, 2000, 500, 448)
+    with pytest.raises(ttir.NotCanonical, match="does not cover"):
+        ttir.bind(m, s, (4, 2))  # programs of the second grid row repeat the tiles of the first
+
+
 def scaled_sig(dt="f8e4m3"):
     sig = {"a_ptr": PTR[dt], "b_ptr": PTR[dt], "c_ptr": "*bf16", "rs_ptr": "*fp32", "cs_ptr": "*fp32", "M": "i32",
            "N": "i32", "K": "i32", "stride_am": "i32", "stride_bk": "i32", "stride_cm": "i32", "alpha": "fp32",

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _fresh_kernels():
     yield
-    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop, jk.wrapped_kloop):
+    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop, jk.wrapped_kloop, jk.persistent_kloop):
         fn.device_caches.clear()
 
 
@@ -127,6 +127,22 @@ def test_wrapped_kloop_ragged(built_libs, cuda_device):
         jk.wrapped_kloop[(math.ceil(M / 128) * math.ceil(N / 64),)](
             a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
             BLOCK_M=128, BLOCK_N=64, BLOCK_K=64)
+    torch.cuda.synchronize()
+    assert torch.equal(c, backend.dot(a, b, check=True))
+    ref = a.float() @ b.float()
+    torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
+def test_persistent_kloop(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 1000, 776, 520
+    a, b = _rand((M, K), torch.bfloat16, cuda_device, 17), _rand((K, N), torch.bfloat16, cuda_device, 18)
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    programs = torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    with tbk.activate():
+        jk.persistent_kloop[(programs,)](a, b, c, M, N, K, a.stride(0), b.stride(0), c.stride(0),
+                                         BLOCK_M=128, BLOCK_N=128, BLOCK_K=64, GROUP=8)
     torch.cuda.synchronize()
     assert torch.equal(c, backend.dot(a, b, check=True))
     ref = a.float() @ b.float()

@@ -163,7 +163,7 @@ def parse_module(text: str, arg_names: Optional[list] = None) -> tuple:
         line = raw.strip()
         if not line or line == "module {":
             continue
-        if line == "}":
+        if line == "}" or re.fullmatch(r"\} \{[^{}]*\}", line):  # a region's end, possibly with attributes
             if owners:
                 owners.pop()
                 stack.pop()
@@ -217,6 +217,7 @@ def parse_module(text: str, arg_names: Optional[list] = None) -> tuple:
 # --------------------------------------------------------------------------------------------------
 
 X0, X1, KIV = sp.symbols("x0 x1 k_iv", integer=True)
+TIV = sp.Symbol("tile_iv", integer=True)  # induction variable of a persistent kernel's loop over tiles
 PID = {a: sp.Symbol(f"pid_{a}", integer=True, nonnegative=True) for a in "xyz"}
 NPROG = {a: sp.Symbol(f"nprog_{a}", integer=True, positive=True) for a in "xyz"}
 
@@ -297,10 +298,18 @@ _FLT_CASTS = {"arith.extf", "arith.truncf", "tt.fp_to_fp"}
 _FLOAT_TYPES = {"f16", "bf16", "f32", "f64", "f8E4M3FN", "f8E5M2", "f8E4M3FNUZ", "f8E5M2FNUZ"}
 
 
+def _walk(ops: list):
+    for o in ops:
+        yield o
+        for r in o.regions:
+            yield from _walk(r)
+
+
 class _Evaluator:
     def __init__(self, args: list):
         self.stores: list = []
         self.loops = 0
+        self.tile_loop: Optional[dict] = None
         self.arg_symbols: dict = {}
         self.env: dict = {}
         for ssa, src, ty in args:
@@ -480,6 +489,8 @@ class _Evaluator:
         else_y = self.run(op.regions[1], dict(env)) if len(op.regions) > 1 else None
         if len(self.stores) != stores_before:
             raise NotCanonical("a store under scf.if is not lowered")
+        if any(o.name == "scf.for" for r in op.regions for o in _walk(r)):
+            raise NotCanonical("a loop under scf.if is not lowered")
         if not op.results:
             return
         if then_y is None or else_y is None or len(then_y) != len(op.results) or len(else_y) != len(op.results):
@@ -509,10 +520,50 @@ class _Evaluator:
             return t
         return _Opaque("an scf.if whose arms are not the unmasked and the masked load of one tile")
 
+    def eval_tile_loop(self, op: Op, env: dict) -> None:
+        """The outer loop of a persistent kernel: each iteration is one tile (a K loop and a store). Its
+        induction variable becomes a symbol of the tile origin; bind() walks it per program."""
+        if self.tile_loop is not None or self.loops:
+            raise NotCanonical("more than one loop over tiles, or a K loop before it")
+        lo, hi, step = (self.get(env, o) for o in op.operands)
+        if not all(isinstance(v, Int) and v.shape == () for v in (lo, hi, step)):
+            raise NotCanonical("tile-loop bounds are not scalar integers")
+        body = dict(env)
+        body[op.extra["iv"]] = Int((), TIV)
+        holders = []
+        for i, (name, init_name) in enumerate(op.extra["iters"]):
+            init = self.get(env, init_name)
+            if not isinstance(init, Int):
+                raise NotCanonical("the loop over tiles carries something that is not an integer")
+            sym = sp.Symbol(f"tile_iter_{i}", integer=True)
+            body[name] = Int(init.shape, sym)
+            holders.append((sym, init))
+        first_store = len(self.stores)
+        yields = self.run(op.regions[0], body) or []
+        if len(yields) != len(holders):
+            raise NotCanonical("scf.for yield does not match its iter_args")
+        trip = (TIV - lo.expr) / step.expr
+        placeholders = {sym for sym, _ in holders}
+        closed = {}
+        for (sym, init), y in zip(holders, yields):
+            if not isinstance(y, Int):
+                raise NotCanonical("a tile-loop-carried integer is yielded as another kind of value")
+            delta = sp.expand(y.expr - sym)
+            if delta.free_symbols & (placeholders | {TIV, KIV}):
+                raise NotCanonical("a tile-loop-carried integer does not advance by a loop-invariant amount")
+            closed[sym] = init.expr + trip * delta
+        for i in range(first_store, len(self.stores)):
+            self.stores[i] = tuple(_subst(x, closed) for x in self.stores[i])
+        for r in op.results:
+            env[r] = _Opaque("the final value of a tile-loop-carried integer")
+        self.tile_loop = {"lo": lo.expr, "hi": hi.expr, "step": step.expr}
+
     def eval_for(self, op: Op, env: dict) -> None:
+        if any(o.name == "scf.for" for o in _walk(op.regions[0])):
+            return self.eval_tile_loop(op, env)
         self.loops += 1
         if self.loops > 1:
-            raise NotCanonical("more than one loop (nested or persistent kernels are not lowered)")
+            raise NotCanonical("more than one K loop")
         lo, hi, step = (self.get(env, o) for o in op.operands)
         if not all(isinstance(v, Int) and v.shape == () for v in (lo, hi, step)):
             raise NotCanonical("loop bounds are not scalar integers")
@@ -607,6 +658,7 @@ class DotKernelMatch:
     int_args: list = field(default_factory=list)
     row_scale_arg: Optional[str] = None  # fp32 vector multiplied into the rows before the cast
     col_scale_arg: Optional[str] = None
+    tile_loop: Optional[list] = None     # [lo, hi, step] of a persistent kernel's loop over tiles (tile_iv)
 
     def to_json(self) -> str:
         return json.dumps(self.__dict__, sort_keys=True)
@@ -816,7 +868,8 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
         m_bound=str(m_bound) if m_bound is not None else None,
         n_bound=str(n_bound) if n_bound is not None else None,
         split_pred=split_pred, split_comparand=split_cmp, alpha=alpha,
-        int_args=sorted(ev.arg_symbols), row_scale_arg=row_scale, col_scale_arg=col_scale)
+        int_args=sorted(ev.arg_symbols), row_scale_arg=row_scale, col_scale_arg=col_scale,
+        tile_loop=[str(sp.expand(ev.tile_loop[k])) for k in ("lo", "hi", "step")] if ev.tile_loop else None)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -850,6 +903,8 @@ def _value(expr: Optional[str], scalars: dict) -> Optional[int]:
 
 
 def _tile_origins(match: DotKernelMatch, scalars: dict, grid: tuple) -> tuple:
+    """Row and column origin of every tile the launch computes: one per program, or, for a persistent
+    kernel, one per iteration of each program's loop over tiles."""
     import numpy as np
 
     gx, gy, gz = grid
@@ -857,20 +912,32 @@ def _tile_origins(match: DotKernelMatch, scalars: dict, grid: tuple) -> tuple:
         raise NotCanonical("grid too large to check")
     px, py, pz = np.meshgrid(np.arange(gx), np.arange(gy), np.arange(gz), indexing="ij")
     env = {"pid_x": px.ravel(), "pid_y": py.ravel(), "pid_z": pz.ravel(),
-           "nprog_x": gx, "nprog_y": gy, "nprog_z": gz}
+           "nprog_x": gx, "nprog_y": gy, "nprog_z": gz, "tile_iv": 0}
     names = list(scalars) + list(env)
     local = {n: sp.Symbol(n, integer=True) for n in names}
-    out = []
-    for text in (match.row0, match.col0):
-        e = sp.sympify(text, locals=local)
-        fn = sp.lambdify([local[n] for n in names], e, modules="numpy")
+
+    def evaluate(text: str) -> "np.ndarray":
+        fn = sp.lambdify([local[n] for n in names], sp.sympify(text, locals=local), modules="numpy")
+        size = np.asarray(env["pid_x"]).size
         with np.errstate(all="ignore"):
-            v = np.broadcast_to(np.asarray(fn(*[scalars[n] for n in scalars], *[env[n] for n in env]), dtype=np.float64),
-                                px.size)
+            v = np.broadcast_to(np.asarray(fn(*[scalars[n] for n in scalars], *[env[n] for n in env]), dtype=np.float64), size)
         if not np.isfinite(v).all():
             raise NotCanonical("the tile origin is undefined for some program ids of this grid (division by zero)")
-        out.append(v.astype(np.int64))
-    return out[0], out[1]
+        return v.astype(np.int64)
+
+    if match.tile_loop is not None:
+        lo, hi, step = (evaluate(t) for t in match.tile_loop)
+        if (step <= 0).any():
+            raise NotCanonical("the loop over tiles has a step that is not positive")
+        count = np.maximum(0, -(-(hi - lo) // step))
+        if int(count.sum()) > (1 << 24):
+            raise NotCanonical("too many tiles to check")
+        owner = np.repeat(np.arange(count.size), count)
+        within = np.arange(owner.size) - np.repeat(np.cumsum(count) - count, count)
+        for key in ("pid_x", "pid_y", "pid_z"):
+            env[key] = env[key][owner]
+        env["tile_iv"] = lo[owner] + within * step[owner]
+    return evaluate(match.row0), evaluate(match.col0)
 
 
 def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional[dict] = None) -> BoundDot:
