@@ -248,3 +248,20 @@ def persistent_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stride_
             acc = tl.dot(a, b, acc)
         tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty),
                  mask=(rm[:, None] < M) & (rn[None, :] < N))
+
+
+@triton.jit
+def descriptor_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stride_cm,
+                     BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Operands and result through in-kernel tensor descriptors: bounds come from the descriptor shapes."""
+    a_desc = tl.make_tensor_descriptor(a_ptr, shape=[M, K], strides=[stride_am, 1], block_shape=[BLOCK_M, BLOCK_K])
+    b_desc = tl.make_tensor_descriptor(b_ptr, shape=[K, N], strides=[stride_bk, 1], block_shape=[BLOCK_K, BLOCK_N])
+    c_desc = tl.make_tensor_descriptor(c_ptr, shape=[M, N], strides=[stride_cm, 1], block_shape=[BLOCK_M, BLOCK_N])
+    row = tl.program_id(0) * BLOCK_M
+    col = tl.program_id(1) * BLOCK_N
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = a_desc.load([row, k])
+        b = b_desc.load([k, col])
+        acc = tl.dot(a, b, acc)
+    c_desc.store([row, col], acc.to(c_ptr.dtype.element_ty))

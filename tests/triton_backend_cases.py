@@ -154,6 +154,19 @@ def test_persistent_kernel_with_a_tile_loop():
         ttir.bind(m, s, (4, 2))  # programs of the second grid row repeat the tiles of the first
 
 
+def test_tensor_descriptor_kernel():
+    """tl.make_tensor_descriptor / desc.load / desc.store (the form of the reference's _attn_fwd_tma,
+    06-fused-attention.py:94-139): the bounds are the descriptor shapes, the fill is zero."""
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "M": "i32", "N": "i32", "K": "i32", "stride_am": "i32",
+           "stride_bk": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    m = compiler.analyse(jk.descriptor_kloop, sig, {"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64})
+    assert (m.k_bound, m.m_bound, m.n_bound) == ("K", "M", "N")
+    assert (m.a_row_stride, m.a_k_stride, m.b_k_stride, m.b_col_stride, m.c_row_stride) == \
+        ("stride_am", "1", "stride_bk", "1", "stride_cm")
+    b = ttir.bind(m, dict(M=300, N=200, K=500, stride_am=512, stride_bk=256, stride_cm=256), (3, 2))
+    assert (b.m, b.n, b.k, b.k_main, b.lda, b.ldb, b.ldc) == (300, 200, 500, 448, 512, 256, 256)
+
+
 def scaled_sig(dt="f8e4m3"):
     sig = {"a_ptr": PTR[dt], "b_ptr": PTR[dt], "c_ptr": "*bf16", "rs_ptr": "*fp32", "cs_ptr": "*fp32", "M": "i32",
            "N": "i32", "K": "i32", "stride_am": "i32", "stride_bk": "i32", "stride_cm": "i32", "alpha": "fp32",

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _fresh_kernels():
     yield
-    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop, jk.wrapped_kloop, jk.persistent_kloop):
+    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop, jk.wrapped_kloop, jk.persistent_kloop, jk.descriptor_kloop):
         fn.device_caches.clear()
 
 
@@ -147,6 +147,19 @@ def test_persistent_kloop(built_libs, cuda_device):
     assert torch.equal(c, backend.dot(a, b, check=True))
     ref = a.float() @ b.float()
     torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
+def test_descriptor_kloop(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 300, 200, 504
+    a, b = _rand((M, K), torch.bfloat16, cuda_device, 19), _rand((K, N), torch.bfloat16, cuda_device, 20)
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    with tbk.activate():
+        jk.descriptor_kloop[(math.ceil(M / 128), math.ceil(N / 128))](
+            a, b, c, M, N, K, a.stride(0), b.stride(0), c.stride(0), BLOCK_M=128, BLOCK_N=128, BLOCK_K=64)
+    torch.cuda.synchronize()
+    assert torch.equal(c, backend.dot(a, b, check=True))
 
 
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):

@@ -249,6 +249,15 @@ class Flt:
     data: dict
 
 
+@dataclass
+class Desc:
+    """A 2-D tensor descriptor: loads and stores through it are bounded by `shape` with zero fill."""
+    base: Ptr
+    shape: tuple
+    strides: tuple
+    block: tuple
+
+
 class _Opaque:
     """A value the analysis does not model; using it is an error."""
 
@@ -459,6 +468,29 @@ class _Evaluator:
             if not all(isinstance(v, Flt) for v in (a, b, c)):
                 raise NotCanonical("tt.dot operands are not float tiles")
             put(Flt("dot", c.shape, {"a": a, "b": b, "c": c}))
+        elif n == "tt.make_tensor_descriptor":
+            base = g(0)
+            rest_ops = [g(i) for i in range(1, len(op.operands))]
+            if not isinstance(base, Ptr) or base.shape != () or len(rest_ops) != 4 or \
+                    not all(isinstance(v, Int) and v.shape == () for v in rest_ops):
+                raise NotCanonical("tt.make_tensor_descriptor is modelled for 2-D descriptors on a plain pointer")
+            bm = re.search(r"tensor<(\d+)x(\d+)x", types)
+            put(Desc(base, (rest_ops[0].expr, rest_ops[1].expr), (rest_ops[2].expr, rest_ops[3].expr),
+                     (int(bm.group(1)), int(bm.group(2)))))
+        elif n in ("tt.descriptor_load", "tt.descriptor_store"):
+            d, i, j = g(0), g(1), g(2)
+            if not isinstance(d, Desc) or not all(isinstance(v, Int) and v.shape == () for v in (i, j)):
+                raise NotCanonical(f"{n} needs a descriptor and two scalar coordinates")
+            r, c = i.expr + X0, j.expr + X1
+            ptr = Ptr(d.base.base, d.base.elem, d.block, d.base.off + r * d.strides[0] + c * d.strides[1])
+            mask = Cond(d.block, (("slt", r, d.shape[0]), ("slt", c, d.shape[1])))
+            if n == "tt.descriptor_load":
+                put(Flt("load", d.block, {"ptr": ptr, "mask": mask, "guard": None}))
+            else:
+                v = g(3)
+                if not isinstance(v, Flt):
+                    raise NotCanonical("tt.descriptor_store of something that is not a float tile")
+                self.stores.append((ptr, v, mask))
         elif n == "tt.store":
             p, v = g(0), g(1)
             mask = g(2) if len(op.operands) > 2 else None
