@@ -56,6 +56,8 @@ def measured_peaks() -> dict:
 WORKLOADS = {
     #  name         m      n      k     dtype  seed dist       scales  k_split  metric unit
     "cfg2": dict(m=4096, n=4096, k=4160, dtype="bf16", seed=1, dist="uniform", scales=False, k_split=4096, block=(128, 128, 128)),
+    # cfg2 launched as a @triton.jit K-loop kernel through the package's Triton backend (same library kernel underneath)
+    "cfg2_jit": dict(m=4096, n=4096, k=4160, dtype="bf16", seed=1, dist="uniform", scales=False, k_split=4096, block=(128, 128, 128), jit=True),
     "cfg3": dict(m=16, n=14336, k=4096, dtype="bf16", seed=2, dist="mlp", scales=False, k_split=0, block=(16, 128, 128)),
     "cfg4": dict(m=8192, n=8192, k=8192, dtype="fp8", seed=3, dist="normal", scales=True, k_split=0, block=(128, 128, 128)),
     "cfg5_nshard": dict(m=16384, n=28672, k=8192, dtype="bf16", seed=4, dist="mlp", scales=False, k_split=0, block=(128, 128, 128)),
@@ -315,6 +317,21 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
         plan.run(a_d, b_d, c_d, None if kshard else rs_d, None if kshard else cs_d, stream)
         return c_d
 
+    if w.get("jit"):
+        # The user-facing call is kernel[grid](...) of a Triton kernel; Triton's front end, the K-loop proof and
+        # the pass pipeline run once, then every launch is tx_dot_run behind Triton's launcher interface.
+        from triton.runtime.driver import driver as triton_driver
+        from triton_ext_b200 import triton_backend as tbk
+        from triton_ext_b200.triton_backend import driver as tb_driver, kernels as tb_kernels
+
+        tbk.install()
+        triton_driver.set_active(tb_driver.B200DotDriver())
+
+        def gemm(i):  # noqa: F811
+            a_d, b_d, c_d = sets[i % n_sets]
+            tb_kernels.launch_dot_kloop(a_d, b_d, c_d, block=w["block"], k_main=w["k_split"])
+            return c_d
+
     if kshard:
         rows = m // world
         scat = torch.empty((rows, n), dtype=torch.float32, device=dev)
@@ -373,6 +390,15 @@ def run_gpu_arm(args, name: str, w: dict) -> dict | None:
             r = step(0)
             return (r if fused else final).cpu()
         h2d, d2h = (m * k + k * n) * es, (m // world) * n * 2
+    elif w.get("jit"):
+        def e2e_step(i):
+            a_d, b_d, c_d = sets[0]
+            a_d.copy_(a_h, non_blocking=True)
+            b_d.copy_(b_h, non_blocking=True)
+            gemm(0)
+            c_h.copy_(c_d, non_blocking=True)
+            torch.cuda.synchronize(dev)
+        h2d, d2h = (m * k + k * n) * es, m * n * c_h.element_size()
     else:
         def e2e_step(i):
             plan.run_host(a_h, b_h, c_h, rs_h, cs_h)
@@ -645,11 +671,18 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-baseline-only", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.cpu_baseline_only:
+        cb = cpu_baseline_single_core(args.workload, w)
+        cb.pop("seconds", None)
+        print(json.dumps(cb), flush=True)
+        return
 
     if args.impl == "reference":
         if rank != 0:
@@ -671,8 +704,16 @@ def main():
     if line is None:
         return
     if world == 1 and not args.no_cpu_baseline:
-        cb = cpu_baseline_single_core(args.workload, w)
-        cb.pop("seconds", None)
+        if w.get("jit"):
+            # The interpreter oracle needs TRITON_INTERPRET=1 from before Triton is imported; this process has
+            # imported Triton's compiler for the timed arm, so the CPU leg runs in a process of its own.
+            import subprocess
+            out = subprocess.run([sys.executable, os.path.abspath(__file__), "--workload", args.workload, "--cpu-baseline-only"],
+                                 capture_output=True, text=True, check=True)
+            cb = json.loads(out.stdout.strip().splitlines()[-1])
+        else:
+            cb = cpu_baseline_single_core(args.workload, w)
+            cb.pop("seconds", None)
         line["cpu_baseline"] = cb
     print(json.dumps(line), flush=True)
 

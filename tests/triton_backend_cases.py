@@ -154,6 +154,16 @@ def test_persistent_kernel_with_a_tile_loop():
         ttir.bind(m, s, (4, 2))  # programs of the second grid row repeat the tiles of the first
 
 
+def test_packaged_kernel_keeps_row_and_column_masks_under_the_split():
+    """kernels.dot_kloop: the side of the split without a K mask still masks rows and columns."""
+    from triton_ext_b200.triton_backend import kernels
+
+    m = compiler.analyse(kernels.dot_kloop, *split_sig())
+    assert (m.k_bound, m.m_bound, m.n_bound, m.split_pred, m.split_comparand) == ("K", "M", "N", "slt", "K_MAIN")
+    b = ttir.bind(m, dict(M=4096, N=4096, K=4160, stride_am=4160, stride_bk=4096, stride_cm=4096, K_MAIN=4096), (32, 32))
+    assert (b.m, b.n, b.k, b.k_main) == (4096, 4096, 4160, 4096)
+
+
 def test_tensor_descriptor_kernel():
     """tl.make_tensor_descriptor / desc.load / desc.store (the form of the reference's _attn_fwd_tma,
     06-fused-attention.py:94-139): the bounds are the descriptor shapes, the fill is zero."""

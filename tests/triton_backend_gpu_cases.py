@@ -162,6 +162,23 @@ def test_descriptor_kloop(built_libs, cuda_device):
     assert torch.equal(c, backend.dot(a, b, check=True))
 
 
+def test_packaged_kernel_ragged(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+    from triton_ext_b200.triton_backend import kernels
+
+    M, N, K = 777, 333, 1096
+    a, b = _rand((M, K), torch.float16, cuda_device, 21), _rand((K, N), torch.float16, cuda_device, 22)
+    b = b.t().contiguous().t()  # column-major B
+    c = torch.full((M, N), float("nan"), dtype=torch.float16, device=cuda_device)
+    try:
+        with tbk.activate():
+            kernels.launch_dot_kloop(a, b, c)
+        torch.cuda.synchronize()
+    finally:
+        kernels.dot_kloop.device_caches.clear()
+    assert torch.equal(c, backend.dot(a, b, check=True))
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk

@@ -307,6 +307,18 @@ _FLT_CASTS = {"arith.extf", "arith.truncf", "tt.fp_to_fp"}
 _FLOAT_TYPES = {"f16", "bf16", "f32", "f64", "f8E4M3FN", "f8E5M2", "f8E4M3FNUZ", "f8E5M2FNUZ"}
 
 
+def _terms_subset(small: Optional[Cond], big: Optional[Cond]) -> bool:
+    """Every term of `small` (None = no mask) is also a term of `big`."""
+    if small is None:
+        return True
+    if big is None:
+        return not small.terms
+    for p, l, r in small.terms:
+        if not any(p == q and sp.expand(l - r - (l2 - r2)) == 0 for q, l2, r2 in big.terms):
+            return False
+    return True
+
+
 def _walk(ops: list):
     for o in ops:
         yield o
@@ -532,8 +544,9 @@ class _Evaluator:
 
     @staticmethod
     def merge(cond: Cond, t: Any, e: Any) -> Any:
-        """Both arms of the split: an unmasked load where the compare holds, the masked load of the same
-        addresses elsewhere. The merged value is the masked load, guarded by the compare."""
+        """Both arms of the split: a load without the K mask where the compare holds (it may keep row or column
+        masks), the fully masked load of the same addresses elsewhere. The merged value is the masked load,
+        guarded by the compare."""
         if isinstance(t, Flt) and isinstance(e, Flt):
             ts, es = t, e
             casts = []
@@ -543,7 +556,8 @@ class _Evaluator:
             if ts.kind == "load" and es.kind == "load":
                 pt, pe = ts.data["ptr"], es.data["ptr"]
                 same = pt.base == pe.base and pt.shape == pe.shape and sp.expand(pt.off - pe.off) == 0
-                if same and ts.data["mask"] is None and ts.data["guard"] is None and es.data["guard"] is None:
+                if same and _terms_subset(ts.data["mask"], es.data["mask"]) and ts.data["guard"] is None \
+                        and es.data["guard"] is None:
                     v = Flt("load", es.shape, {"ptr": pe, "mask": es.data["mask"], "guard": cond})
                     for to in reversed(casts):
                         v = Flt("cast", v.shape, {"src": v, "to": to})
