@@ -265,3 +265,22 @@ def descriptor_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stride_
         b = b_desc.load([k, col])
         acc = tl.dot(a, b, acc)
     c_desc.store([row, col], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def nt_kloop(a_ptr, bt_ptr, c_ptr, M, N, K, stride_am, stride_bn, stride_cm,
+             BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """C = A @ Bt^T with Bt stored [N, K]: the B tile is loaded as [BLOCK_N, BLOCK_K] and transposed in
+    registers, the way the reference's attention feeds K to its first dot."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :],
+                    mask=(rm[:, None] < M) & ((k + rk)[None, :] < K), other=0.0)
+        bt = tl.load(bt_ptr + rn[:, None] * stride_bn + (k + rk)[None, :],
+                     mask=(rn[:, None] < N) & ((k + rk)[None, :] < K), other=0.0)
+        acc = tl.dot(a, tl.trans(bt), acc)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty),
+             mask=(rm[:, None] < M) & (rn[None, :] < N))

@@ -164,6 +164,16 @@ def test_packaged_kernel_keeps_row_and_column_masks_under_the_split():
     assert (b.m, b.n, b.k, b.k_main) == (4096, 4096, 4160, 4096)
 
 
+def test_transposed_tile_in_registers():
+    """tl.trans of the loaded B tile (B stored [N, K]) binds as a column-major B."""
+    sig = {"a_ptr": "*bf16", "bt_ptr": "*bf16", "c_ptr": "*bf16", "M": "i32", "N": "i32", "K": "i32", "stride_am": "i32",
+           "stride_bn": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    m = compiler.analyse(jk.nt_kloop, sig, {"BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64})
+    assert (m.b_arg, m.b_k_stride, m.b_col_stride, m.block_n, m.block_k) == ("bt_ptr", "1", "stride_bn", 64, 64)
+    b = ttir.bind(m, dict(M=300, N=200, K=500, stride_am=512, stride_bn=512, stride_cm=256), (3, 4))
+    assert (b.b_layout, b.ldb, b.m, b.n, b.k) == ("col", 512, 300, 200, 500)
+
+
 def test_tensor_descriptor_kernel():
     """tl.make_tensor_descriptor / desc.load / desc.store (the form of the reference's _attn_fwd_tma,
     06-fused-attention.py:94-139): the bounds are the descriptor shapes, the fill is zero."""

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _fresh_kernels():
     yield
-    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop, jk.wrapped_kloop, jk.persistent_kloop, jk.descriptor_kloop):
+    for fn in (jk.split_kloop, jk.grouped_masked_kloop, jk.plain_kloop, jk.scaled_kloop, jk.wrapped_kloop, jk.persistent_kloop, jk.descriptor_kloop, jk.nt_kloop):
         fn.device_caches.clear()
 
 
@@ -177,6 +177,19 @@ def test_packaged_kernel_ragged(built_libs, cuda_device):
     finally:
         kernels.dot_kloop.device_caches.clear()
     assert torch.equal(c, backend.dot(a, b, check=True))
+
+
+def test_nt_kloop(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 300, 200, 504
+    a, bt = _rand((M, K), torch.bfloat16, cuda_device, 23), _rand((N, K), torch.bfloat16, cuda_device, 24)
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    with tbk.activate():
+        jk.nt_kloop[(math.ceil(M / 128), math.ceil(N / 64))](a, bt, c, M, N, K, a.stride(0), bt.stride(0), c.stride(0),
+                                                             BLOCK_M=128, BLOCK_N=64, BLOCK_K=64)
+    torch.cuda.synchronize()
+    assert torch.equal(c, backend.dot(a, bt.t(), check=True))
 
 
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):

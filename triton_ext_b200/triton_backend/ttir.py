@@ -465,6 +465,11 @@ class _Evaluator:
             if not isinstance(v, Flt):
                 raise NotCanonical(f"{n} on a non-float value")
             put(Flt("cast", v.shape, {"src": v, "to": relem}))
+        elif n == "tt.trans":
+            v = g(0)
+            if not (isinstance(v, Flt) and len(v.shape) == 2 and "1, 0" in head):
+                raise NotCanonical("tt.trans is modelled as the transpose of a 2-D float tile")
+            put(self.transpose(v))
         elif n == "arith.mulf":
             a, b = g(0), g(1)
             if isinstance(a, Flt) and a.kind in ("const", "arg", "vec"):
@@ -522,6 +527,23 @@ class _Evaluator:
         else:
             for r in op.results:
                 env[r] = _Opaque(f"the result of {n}")
+
+    @staticmethod
+    def transpose(v: Flt) -> Flt:
+        """The transposed tile of a load (through casts): the two index symbols change places."""
+        if v.kind == "cast":
+            inner = _Evaluator.transpose(v.data["src"])
+            return Flt("cast", inner.shape, {"src": inner, "to": v.data["to"]})
+        if v.kind != "load":
+            raise NotCanonical("tt.trans of a value that is not a loaded tile")
+        swap = {X0: X1, X1: X0}
+        sw = lambda e: e.subs(swap, simultaneous=True)
+        p, mask, guard = v.data["ptr"], v.data["mask"], v.data["guard"]
+        shape = (v.shape[1], v.shape[0])
+        return Flt("load", shape, {
+            "ptr": Ptr(p.base, p.elem, shape, sw(p.off)),
+            "mask": None if mask is None else Cond(shape, tuple((q, sw(l), sw(r)) for q, l, r in mask.terms)),
+            "guard": guard})
 
     # -- regions --------------------------------------------------------------------------------
     def eval_if(self, op: Op, env: dict) -> None:
