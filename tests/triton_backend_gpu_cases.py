@@ -192,6 +192,27 @@ def test_nt_kloop(built_libs, cuda_device):
     assert torch.equal(c, backend.dot(a, bt.t(), check=True))
 
 
+def test_autotuned_kernel(built_libs, cuda_device):
+    """@triton.autotune over block shapes: every configuration compiles to a proof of the same GEMM, the tuner's
+    benchmark runs through the backend's launcher, the result does not depend on the winner."""
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    tuned = triton.autotune(
+        configs=[triton.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_warps=4, num_stages=3),
+                 triton.Config({"BLOCK_M": 64, "BLOCK_N": 256, "BLOCK_K": 32}, num_warps=8, num_stages=4)],
+        key=["M", "N", "K"])(triton.jit(jk.grouped_masked_kloop.fn))
+    M, N, K = 520, 776, 1100
+    a, b = _rand((M, K), torch.float16, cuda_device, 25), _rand((K, N), torch.float16, cuda_device, 26)
+    c = torch.full((M, N), float("nan"), dtype=torch.float16, device=cuda_device)
+    grid = lambda meta: (math.ceil(M / meta["BLOCK_M"]) * math.ceil(N / meta["BLOCK_N"]),)
+    with tbk.activate():
+        tuned[grid](a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1), 1.0,
+                    GROUP=4)
+    torch.cuda.synchronize()
+    assert tuned.best_config is not None
+    assert torch.equal(c, backend.dot(a, b, check=True))
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk
