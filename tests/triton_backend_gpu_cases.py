@@ -201,7 +201,7 @@ def test_autotuned_kernel(built_libs, cuda_device):
         configs=[triton.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_warps=4, num_stages=3),
                  triton.Config({"BLOCK_M": 64, "BLOCK_N": 256, "BLOCK_K": 32}, num_warps=8, num_stages=4)],
         key=["M", "N", "K"])(triton.jit(jk.grouped_masked_kloop.fn))
-    M, N, K = 520, 776, 1100
+    M, N, K = 520, 776, 1096
     a, b = _rand((M, K), torch.float16, cuda_device, 25), _rand((K, N), torch.float16, cuda_device, 26)
     c = torch.full((M, N), float("nan"), dtype=torch.float16, device=cuda_device)
     grid = lambda meta: (math.ceil(M / meta["BLOCK_M"]) * math.ceil(N / meta["BLOCK_N"]),)
