@@ -284,3 +284,48 @@ def nt_kloop(a_ptr, bt_ptr, c_ptr, M, N, K, stride_am, stride_bn, stride_cm,
         acc = tl.dot(a, tl.trans(bt), acc)
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty),
              mask=(rm[:, None] < M) & (rn[None, :] < N))
+
+
+@triton.jit
+def narrowed_operand_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+                           BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: the operands are rounded to fp8 between the load and the dot."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :]).to(tl.float8e4nv)
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :]).to(tl.float8e4nv)
+        acc = tl.dot(a, b, acc)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def half_accumulator_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+                           BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: the accumulator is fp16."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float16)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc, out_dtype=tl.float16)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc)
+
+
+@triton.jit
+def widened_operand_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+                          BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """bf16 operands widened to fp32 before the dot (exact), fp32 result: what the interpreter oracle's kernel does."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :]).to(tl.float32)
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :]).to(tl.float32)
+        acc = tl.dot(a, b, acc, input_precision="ieee")
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc)

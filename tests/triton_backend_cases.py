@@ -228,6 +228,25 @@ def test_near_misses_are_refused(kernel, why):
         compiler.analyse(kernel, *small_sig())
 
 
+def test_casts_around_the_dot():
+    """Widening the operands before the dot keeps the GEMM; narrowing them or accumulating in fp16 does not."""
+    sig, cx = small_sig("bf16")
+    sig32 = dict(sig, c_ptr="*fp32")
+    m = compiler.analyse(jk.widened_operand_kloop, sig32, cx)
+    assert (m.ab_dtype, m.out_dtype) == ("bf16", "f32")
+    with pytest.raises(ttir.NotCanonical, match="narrowed from bf16 to f8E4M3FN"):
+        compiler.analyse(jk.narrowed_operand_kloop, sig, cx)
+    sig16, _ = small_sig("f16")
+    with pytest.raises(ttir.NotCanonical, match="accumulates in f16"):
+        compiler.analyse(jk.half_accumulator_kloop, sig16, cx)
+    with pytest.raises(ttir.NotCanonical, match="no tensor-core path"):
+        compiler.analyse(jk.plain_kloop, {"a_ptr": "*fp32", "b_ptr": "*fp32", "c_ptr": "*fp32", "K": "i32",
+                                          "stride_am": "i32", "stride_ak": "constexpr", "stride_bk": "i32",
+                                          "stride_bn": "constexpr", "stride_cm": "i32", "BLOCK_M": "constexpr",
+                                          "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"},
+                         {"stride_ak": 1, "stride_bn": 1, "BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
+
+
 def test_hand_written_ir_is_refused_with_a_reason():
     base = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, *split_sig()))
     with pytest.raises(ttir.NotCanonical, match="stores"):

@@ -484,6 +484,8 @@ class _Evaluator:
             a, b, c = g(0), g(1), g(2)
             if not all(isinstance(v, Flt) for v in (a, b, c)):
                 raise NotCanonical("tt.dot operands are not float tiles")
+            if relem != "f32":
+                raise NotCanonical(f"tt.dot accumulates in {relem}; the library kernel accumulates in f32")
             put(Flt("dot", c.shape, {"a": a, "b": b, "c": c}))
         elif n == "tt.make_tensor_descriptor":
             base = g(0)
@@ -690,6 +692,8 @@ class _Evaluator:
 # Matching
 # --------------------------------------------------------------------------------------------------
 
+# (exponent bits, mantissa bits): a cast keeps every value when neither shrinks
+_FLOAT_BITS = {"f8E4M3FN": (4, 3), "f8E5M2": (5, 2), "f16": (5, 10), "bf16": (8, 7), "f32": (8, 23), "f64": (11, 52)}
 _DTYPE_NAMES = {"f16": "f16", "bf16": "bf16", "f32": "f32", "f8E4M3FN": "f8e4m3", "f8E5M2": "f8e5m2"}
 
 
@@ -848,6 +852,17 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
     if a_alpha or b_alpha or a.kind != "load" or b.kind != "load":
         raise NotCanonical("the tt.dot operands are not plain loads")
     pa, pb = a.data["ptr"], b.data["ptr"]
+    for elem, casts, which in ((pa.elem, a_casts, "A"), (pb.elem, b_casts, "B")):
+        # A cast between the load and the dot must keep every value: the kernel multiplies what is in memory.
+        for to in reversed(casts):
+            if _FLOAT_BITS.get(to, (0, 0))[0] < _FLOAT_BITS.get(elem, (99, 99))[0] or \
+                    _FLOAT_BITS.get(to, (0, 0))[1] < _FLOAT_BITS.get(elem, (99, 99))[1]:
+                raise NotCanonical(f"operand {which} is narrowed from {elem} to {to} before the dot")
+            elem = to
+    if pa.elem not in ("f16", "bf16", "f8E4M3FN", "f8E5M2"):
+        raise NotCanonical(f"operands of type {pa.elem} have no tensor-core path in the library")
+    if out_casts not in ([], [c_ptr.elem]) or (not out_casts and c_ptr.elem != "f32"):
+        raise NotCanonical("the epilogue is not a single cast of the f32 sum to the stored type")
     if len(pa.shape) != 2 or len(pb.shape) != 2 or len(c_ptr.shape) != 2:
         raise NotCanonical("tiles are not 2-D")
     (bm, bk), (bk2, bn) = pa.shape, pb.shape
