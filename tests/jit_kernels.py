@@ -329,3 +329,19 @@ def widened_operand_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_c
         b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :]).to(tl.float32)
         acc = tl.dot(a, b, acc, input_precision="ieee")
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc)
+
+
+@triton.jit
+def counting_kloop(a_ptr, b_ptr, c_ptr, count_ptr, K, stride_am, stride_bk, stride_cm,
+                   BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: a correct GEMM that also counts its programs with an atomic."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    tl.atomic_add(count_ptr, 1)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))

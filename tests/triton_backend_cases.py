@@ -247,6 +247,13 @@ def test_casts_around_the_dot():
                          {"stride_ak": 1, "stride_bn": 1, "BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
 
 
+def test_side_effects_outside_the_gemm_are_refused():
+    sig, cx = small_sig("bf16")
+    sig = dict(list(sig.items())[:3] + [("count_ptr", "*i32")] + list(sig.items())[3:])
+    with pytest.raises(ttir.NotCanonical, match="may have a side effect: tt.atomic_rmw"):
+        compiler.analyse(jk.counting_kloop, sig, cx)
+
+
 def test_hand_written_ir_is_refused_with_a_reason():
     base = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, *split_sig()))
     with pytest.raises(ttir.NotCanonical, match="stores"):

@@ -304,6 +304,9 @@ _INT_BIN = {
 }
 _INT_CASTS = {"arith.extsi", "arith.extui", "arith.trunci", "arith.index_cast"}
 _FLT_CASTS = {"arith.extf", "arith.truncf", "tt.fp_to_fp"}
+_PURE_TT_OPS = {"tt.bitcast", "tt.int_to_ptr", "tt.ptr_to_int", "tt.reshape", "tt.join", "tt.split", "tt.cat",
+                "tt.clampf", "tt.precise_sqrt", "tt.precise_divf", "tt.mulhiui", "tt.unsplat", "tt.gather",
+                "tt.histogram"}
 _FLOAT_TYPES = {"f16", "bf16", "f32", "f64", "f8E4M3FN", "f8E5M2", "f8E4M3FNUZ", "f8E5M2FNUZ"}
 
 
@@ -524,11 +527,13 @@ class _Evaluator:
             self.eval_for(op, env)
         elif n in ("tt.assume", "llvm.intr.assume"):
             pass
-        elif not op.results:
-            raise NotCanonical(f"operation with a side effect is not lowered: {n}")
-        else:
+        elif op.results and (n.startswith("arith.") or n.startswith("math.") or n in _PURE_TT_OPS):
+            # A value the analysis does not model: harmless while nothing the GEMM depends on uses it.
             for r in op.results:
                 env[r] = _Opaque(f"the result of {n}")
+        else:
+            # Anything else may write memory or synchronise (atomics, calls, prints, inline assembly, ...).
+            raise NotCanonical(f"operation that is not modelled and may have a side effect: {n}")
 
     @staticmethod
     def transpose(v: Flt) -> Flt:
