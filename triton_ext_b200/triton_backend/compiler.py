@@ -72,7 +72,10 @@ class B200DotBackend(BaseBackend):
         self.binary_ext = TARGET_NAME
 
     def hash(self) -> str:
-        return f"{TARGET_NAME}-{self.target.arch}-1"
+        # Part of Triton's cache key: a proof written by another version of the matcher must not be reused.
+        with open(_ttir.__file__, "rb") as f:
+            matcher = hashlib.sha256(f.read()).hexdigest()[:16]
+        return f"{TARGET_NAME}-{self.target.arch}-{matcher}"
 
     def parse_options(self, opts: dict) -> Any:
         known = B200DotOptions.__dataclass_fields__.keys()
