@@ -53,7 +53,7 @@ def test_ttir_has_the_loop_split_shape():
 
 
 def test_split_kloop_match():
-    m = compiler.analyse(jk.split_kloop, *split_sig())
+    m = compiler.analyse(jk.split_kloop, *split_sig(), split=False)
     assert (m.a_arg, m.b_arg, m.c_arg) == ("a_ptr", "b_ptr", "c_ptr")
     assert (m.block_m, m.block_n, m.block_k) == (128, 128, 128)
     assert (m.ab_dtype, m.out_dtype) == ("bf16", "bf16")
@@ -63,6 +63,127 @@ def test_split_kloop_match():
     assert (m.k_bound, m.split_pred, m.split_comparand) == ("K", "slt", "K_MAIN")
     assert m.alpha is None
     assert ttir.DotKernelMatch.from_json(m.to_json()) == m
+
+
+def test_loop_split_on_the_kernels_own_ir():
+    """LoopSplit as a rewrite of the real IR: two scf.for where there was one, the compare gone, unmasked loads
+    only in the first and masked loads only in the second (after Triton's canonicaliser), accepted by Triton's
+    MLIR parser; and the matcher reads the pair back as one loop split at the mid point."""
+    from triton_ext_b200.triton_backend import loop_split_ir
+
+    sig, cx = split_sig()
+    before = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, sig, cx))
+    assert before.count("scf.for") == 1 and before.count("scf.if") == 1
+    raw, n = loop_split_ir.split_loops(before)
+    assert n == 1 and raw.count("scf.for") == 2 and "arith.constant true" in raw and "arith.constant false" in raw
+    names: list = []
+    after = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, sig, cx, split=True, arg_names_out=names))
+    assert names[:3] == ["a_ptr", "b_ptr", "c_ptr"] and names[-1] == "K_MAIN"
+    assert after.count("scf.for") == 2 and "scf.if" not in after
+    first, second = after.split("scf.for")[1:]
+    assert "tt.load" in first and "arith.cmpi" not in first       # main loop: no compare, no mask
+    assert second.count("arith.cmpi slt") == 2                      # remainder loop: the two K masks
+    assert "arith.ceildivsi" in after and "arith.minsi" in after    # the mid point
+    m = ttir.match_dot_kernel(after, names)
+    assert (m.loop_lo, m.loop_hi, m.split_pred) == ("0", "K", "slt")
+    assert m.split_comparand == "Min(128*ceiling(Max(0, K_MAIN)/128), Max(0, K))"
+    s = dict(M=1024, N=512, K=4160, stride_am=4160, stride_bk=512, stride_cm=512)
+    assert ttir.bind(m, dict(s, K_MAIN=4096), (8, 4)).k_main == 4096
+    assert ttir.bind(m, dict(s, K_MAIN=1000), (8, 4)).k_main == 1024   # mid rounds up to the step
+    assert ttir.bind(m, dict(s, K_MAIN=0), (8, 4)).k_main == 0
+    with pytest.raises(ttir.NotCanonical, match="unmasked load run past"):
+        ttir.bind(m, dict(s, K_MAIN=4160), (8, 4))
+    # a loop without a compare on its induction variable is left alone
+    plain = ttir.strip_locations(compiler.lower_to_ttir(jk.plain_kloop, *plain_sig()))
+    assert loop_split_ir.split_loops(plain)[1] == 0
+
+
+LIT_CASE = """
+module {
+  tt.func public @lit(%out: !tt.ptr<i32>, %n: i32, %c: i32) {
+    %c0 = arith.constant 0 : i32
+    %c1 = arith.constant 1 : i32
+    %cS = arith.constant STEP : i32
+    %r = scf.for %i = %c0 to %n step %cS iter_args(%acc = %c0) -> (i32)  : i32 {
+      %p = arith.cmpi PRED, LHS, RHS : i32
+      %v = arith.addi %i, %c1 : i32
+      %a = arith.addi %acc, %v : i32
+      %s = arith.subi %acc, %v : i32
+      %x = arith.select %p, %a, %s : i32
+      scf.yield %x : i32
+    }
+    tt.store %out, %r : !tt.ptr<i32>
+    tt.return
+  }
+}
+"""
+
+
+@pytest.mark.parametrize("pred,swap,step", [("slt", False, 1), ("sle", False, 1), ("sgt", False, 1), ("sge", False, 1),
+                                            ("slt", False, 10), ("sgt", True, 3), ("sle", True, 7)])
+def test_loop_split_ir_keeps_the_meaning_of_the_lit_test_loops(pred, swap, step):
+    """The loops of the reference's lit test (pass/LoopSplit/test/loop-split.mlir: acc +/- (iv + 1) selected by a
+    compare of the induction variable; sgt / sge / slt / sle and a step-10 case), bisected on the IR text and
+    executed before and after by a tiny interpreter over every small bound and comparand."""
+    from triton_ext_b200.triton_backend import loop_split_ir
+
+    text = (LIT_CASE.replace("STEP", str(step)).replace("PRED", pred)
+            .replace("LHS", "%c" if swap else "%i").replace("RHS", "%i" if swap else "%c"))
+    new, n = loop_split_ir.split_loops(text)
+    assert n == 1 and new.count("scf.for") == 2
+    for bound in range(0, 24, 5):
+        for comparand in range(-3, 27, 2):
+            assert run_scalar_ir(new, bound, comparand) == run_scalar_ir(text, bound, comparand), (bound, comparand)
+
+
+def run_scalar_ir(text: str, n: int, c: int) -> int:
+    """Execute the scalar i32 subset the lit loops use (constants, addi, subi, muli, maxsi, minsi, ceildivsi, cmpi,
+    select, scf.for with one iter_arg) and return the stored value."""
+    _, _, ops = ttir.parse_module(text)
+    cmp = {"slt": lambda a, b: a < b, "sle": lambda a, b: a <= b, "sgt": lambda a, b: a > b, "sge": lambda a, b: a >= b}
+    arith = {"arith.addi": lambda a, b: a + b, "arith.subi": lambda a, b: a - b, "arith.muli": lambda a, b: a * b,
+             "arith.maxsi": max, "arith.minsi": min, "arith.ceildivsi": lambda a, b: -((-a) // b)}
+
+    def run(block, env):
+        for op in block:
+            g = lambda k: env[op.operands[k]]
+            if op.name == "arith.constant":
+                tok = op.rest.split(" :")[0].strip()
+                env[op.results[0]] = {"true": True, "false": False}.get(tok, None if tok in ("true", "false") else tok)
+                if not isinstance(env[op.results[0]], bool):
+                    env[op.results[0]] = int(tok)
+            elif op.name in arith:
+                env[op.results[0]] = arith[op.name](g(0), g(1))
+            elif op.name == "arith.cmpi":
+                env[op.results[0]] = cmp[op.rest.split(",")[0].strip()](g(0), g(1))
+            elif op.name == "arith.select":
+                env[op.results[0]] = g(1) if g(0) else g(2)
+            elif op.name == "scf.for":
+                lo, hi, st = (env[o] for o in op.operands)
+                (name, init), = op.extra["iters"]
+                acc = env[init]
+                for i in range(lo, hi, st):
+                    inner = dict(env)
+                    inner[op.extra["iv"]] = i
+                    inner[name] = acc
+                    acc = run(op.regions[0], inner)
+                env[op.results[0]] = acc
+            elif op.name == "scf.yield":
+                return g(0)
+            elif op.name == "tt.store":
+                env["stored"] = g(1)
+        return None
+
+    env = {"%out": None, "%n": n, "%c": c}
+    run(ops, env)
+    return env["stored"]
+
+
+def plain_sig():
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*fp32", "K": "i32", "stride_am": "i32", "stride_ak": "constexpr",
+           "stride_bk": "i32", "stride_bn": "constexpr", "stride_cm": "i32", "BLOCK_M": "constexpr",
+           "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    return sig, {"stride_ak": 1, "stride_bn": 1, "BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64}
 
 
 def test_split_kloop_bind_benchmark_shape():
@@ -158,8 +279,11 @@ def test_packaged_kernel_keeps_row_and_column_masks_under_the_split():
     """kernels.dot_kloop: the side of the split without a K mask still masks rows and columns."""
     from triton_ext_b200.triton_backend import kernels
 
-    m = compiler.analyse(kernels.dot_kloop, *split_sig())
+    m = compiler.analyse(kernels.dot_kloop, *split_sig(), split=False)
     assert (m.k_bound, m.m_bound, m.n_bound, m.split_pred, m.split_comparand) == ("K", "M", "N", "slt", "K_MAIN")
+    m = compiler.analyse(kernels.dot_kloop, *split_sig())  # the same after LoopSplit has made two loops of it
+    assert (m.k_bound, m.m_bound, m.n_bound, m.split_pred) == ("K", "M", "N", "slt")
+    assert m.split_comparand == "Min(128*ceiling(Max(0, K_MAIN)/128), Max(0, K))"
     b = ttir.bind(m, dict(M=4096, N=4096, K=4160, stride_am=4160, stride_bk=4096, stride_cm=4096, K_MAIN=4096), (32, 32))
     assert (b.m, b.n, b.k, b.k_main) == (4096, 4096, 4160, 4096)
 

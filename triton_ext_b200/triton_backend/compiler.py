@@ -97,6 +97,7 @@ class B200DotBackend(BaseBackend):
         if language != Language.TRITON:
             raise RuntimeError("the b200dot backend lowers Triton kernels only")
         stages["ttir"] = lambda src, metadata: self.make_ttir(src, metadata, options)
+        stages["ttsplit"] = lambda src, metadata: self.make_loop_split(src, metadata, options)
         stages[TARGET_NAME] = lambda src, metadata: self.make_match(src, metadata, options)
 
     @staticmethod
@@ -114,8 +115,40 @@ class B200DotBackend(BaseBackend):
         return mod
 
     @staticmethod
+    def make_loop_split(mod, metadata: dict, options: Any):
+        """LoopSplit on the kernel's own IR (loop_split_ir.split_loops), parsed back and canonicalised by
+        Triton's MLIR context so that each half keeps only the arm of the scf.if its constant compare selects."""
+        import os
+        import tempfile
+
+        from . import loop_split_ir
+
+        text = str(mod)
+        _, args, _ = _ttir.parse_module(text)
+        metadata["arg_names"] = [src for _, src, _ in args]
+        new_text, n_split = loop_split_ir.split_loops(text)
+        metadata["loops_split"] = n_split
+        if n_split == 0:
+            return mod
+        fd, path = tempfile.mkstemp(suffix=".ttir")
+        try:
+            with os.fdopen(fd, "w") as f:
+                f.write(new_text)
+            split = ir.parse_mlir_module(path, mod.context)
+        finally:
+            os.unlink(path)
+        split.context = mod.context
+        pm = ir.pass_manager(split.context)
+        pm.enable_debug()
+        passes.common.add_canonicalizer(pm)
+        passes.common.add_cse(pm)
+        passes.common.add_canonicalizer(pm)
+        pm.run(split, "loop_split_cleanup")
+        return split
+
+    @staticmethod
     def make_match(mod, metadata: dict, options: Any) -> bytes:
-        match = _ttir.match_dot_kernel(str(mod))
+        match = _ttir.match_dot_kernel(str(mod), metadata.get("arg_names"))
         metadata["name"] = match.kernel
         metadata["shared"] = 0
         metadata["num_warps"] = options.num_warps
@@ -126,7 +159,8 @@ class B200DotBackend(BaseBackend):
         return match.to_json().encode()
 
 
-def lower_to_ttir(fn, signature: dict, constexprs: Optional[dict] = None) -> str:
+def lower_to_ttir(fn, signature: dict, constexprs: Optional[dict] = None, split: bool = False,
+                  arg_names_out: Optional[list] = None) -> str:
     """Front end + the ``ttir`` stage for one specialisation of a ``@triton.jit`` function; needs no GPU.
 
     `signature` maps every parameter to its Triton type string ("*bf16", "i32", "fp32", "constexpr").
@@ -140,9 +174,17 @@ def lower_to_ttir(fn, signature: dict, constexprs: Optional[dict] = None) -> str
     context = ir.context()
     ir.load_dialects(context)
     mod = src.make_ir(target, options, backend.get_codegen_implementation(options), backend.get_module_map(), context)
-    return str(backend.make_ttir(mod, {}, options))
+    mod = backend.make_ttir(mod, {}, options)
+    if split:
+        meta: dict = {}
+        mod = backend.make_loop_split(mod, meta, options)
+        if arg_names_out is not None:
+            arg_names_out.extend(meta["arg_names"])
+    return str(mod)
 
 
-def analyse(fn, signature: dict, constexprs: Optional[dict] = None) -> "_ttir.DotKernelMatch":
-    """lower_to_ttir() followed by the K-loop match."""
-    return _ttir.match_dot_kernel(lower_to_ttir(fn, signature, constexprs))
+def analyse(fn, signature: dict, constexprs: Optional[dict] = None, split: bool = True) -> "_ttir.DotKernelMatch":
+    """The compile pipeline without a launch: front end, `ttir`, LoopSplit on the IR (`split`), the K-loop match."""
+    names: list = []
+    text = lower_to_ttir(fn, signature, constexprs, split=split, arg_names_out=names)
+    return _ttir.match_dot_kernel(text, names or None)

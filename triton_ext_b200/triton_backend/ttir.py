@@ -136,7 +136,7 @@ def _expand_results(lhs: str) -> list:
     return out
 
 
-_FUNC_ARG = re.compile(r"(%[\w.$-]+): (![\w.]+<[^<>]*>|[\w]+)(?: \{[^{}]*\})?(?: loc\(\"([^\"]+)\")?")
+_FUNC_ARG = re.compile(r"(%[\w.$-]+): (![\w.]+<[^<>]*>|[\w]+)(?: \{[^{}]*\})?(?: loc\(\"([^\"]+)\"\()?")
 
 
 def parse_module(text: str, arg_names: Optional[list] = None) -> tuple:
@@ -152,7 +152,7 @@ def parse_module(text: str, arg_names: Optional[list] = None) -> tuple:
     arg_text = header[header.index("(") + 1:]
     args = []
     for i, m in enumerate(_FUNC_ARG.finditer(arg_text.split(") attributes")[0])):
-        src = m.group(3) or (arg_names[i] if arg_names and i < len(arg_names) else m.group(1)[1:])
+        src = arg_names[i] if arg_names and i < len(arg_names) else (m.group(3) or m.group(1)[1:])
         args.append((m.group(1), src, m.group(2)))
 
     body = strip_locations("\n".join(lines[header_at + 1:])).splitlines()
@@ -637,8 +637,8 @@ class _Evaluator:
         if any(o.name == "scf.for" for o in _walk(op.regions[0])):
             return self.eval_tile_loop(op, env)
         self.loops += 1
-        if self.loops > 1:
-            raise NotCanonical("more than one K loop")
+        if self.loops > 2:
+            raise NotCanonical("more than two K loops in sequence")
         lo, hi, step = (self.get(env, o) for o in op.operands)
         if not all(isinstance(v, Int) and v.shape == () for v in (lo, hi, step)):
             raise NotCanonical("loop bounds are not scalar integers")
@@ -837,6 +837,45 @@ def _classify_mask(cond: Optional[Cond], forms: dict, what: str) -> dict:
     return out
 
 
+def _fuse_split_loops(second: Flt) -> Flt:
+    """Two K loops in sequence, the second starting from the first's result at the point where the first stops,
+    are what LoopSplit makes of one loop whose compare `iv < mid` guarded the loads without a K mask
+    (pass/LoopSplit/LoopSplit.cpp:169-190). Read them back as that one loop."""
+    first = second.data["init"]
+    if first.kind != "loop_dot":
+        return second
+    if first.data["init"].kind == "loop_dot":
+        raise NotCanonical("more than two K loops in sequence")
+    if sp.expand(first.data["hi"] - second.data["lo"]) != 0 or sp.expand(first.data["step"] - second.data["step"]) != 0:
+        raise NotCanonical("the second K loop does not continue where the first stops")
+    mid = sp.expand(first.data["hi"])
+    fused = {}
+    same_masks = True
+    for key in ("a", "b"):
+        f, f_casts, f_alpha = _peel(first.data[key])
+        g, g_casts, g_alpha = _peel(second.data[key])
+        if f_alpha or g_alpha or f.kind != "load" or g.kind != "load" or f_casts != g_casts:
+            raise NotCanonical("the two K loops do not feed the dot with the same kind of loads")
+        pf, pg = f.data["ptr"], g.data["ptr"]
+        if pf.base != pg.base or pf.elem != pg.elem or pf.shape != pg.shape or sp.expand(pf.off - pg.off) != 0:
+            raise NotCanonical("the two K loops do not load from the same addresses")
+        if f.data["guard"] is not None or g.data["guard"] is not None:
+            raise NotCanonical("a split K loop still carries a compare on its induction variable")
+        if not _terms_subset(f.data["mask"], g.data["mask"]):
+            raise NotCanonical("the first K loop masks more than the second")
+        same_masks = same_masks and _terms_subset(g.data["mask"], f.data["mask"])
+        fused[key] = (g, g_casts)
+    out = {}
+    for key, (g, casts) in fused.items():
+        guard = None if same_masks else Cond((), (("slt", KIV, mid),))
+        v = Flt("load", g.shape, {"ptr": g.data["ptr"], "mask": g.data["mask"], "guard": guard})
+        for to in reversed(casts):
+            v = Flt("cast", v.shape, {"src": v, "to": to})
+        out[key] = v
+    return Flt("loop_dot", second.shape, {"a": out["a"], "b": out["b"], "init": first.data["init"],
+                                          "lo": first.data["lo"], "hi": second.data["hi"], "step": second.data["step"]})
+
+
 def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMatch:
     """Analyse the printed TTIR of one kernel. Raises NotCanonical unless it is the K loop described above."""
     fname, args, ops = parse_module(text, arg_names)
@@ -849,6 +888,7 @@ def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMa
     value, out_casts, alpha = _peel(value, vecs)
     if value.kind != "loop_dot":
         raise NotCanonical("the stored value is not the result of the K loop")
+    value = _fuse_split_loops(value)
     init = value.data["init"]
     if not (init.kind == "const" and init.data["value"] == 0.0):
         raise NotCanonical("the accumulator does not start at zero")
