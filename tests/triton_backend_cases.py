@@ -477,3 +477,111 @@ def test_text_helpers():
     assert ttir._result_type("tensor<64x64xf32> to tensor<64x64xbf16>") == "tensor<64x64xbf16>"
     assert ttir._result_type("tensor<8x!tt.ptr<f16>>, tensor<8xi32>") == "tensor<8x!tt.ptr<f16>>"
     assert ttir._expand_results("%2:2, %x") == ["%2#0", "%2#1", "%x"]
+
+
+# ---- the reference's own lit test, when the reference tree is present --------------------------------------------
+
+REFERENCE_LIT = "/root/reference/pass/LoopSplit/test/loop-split.mlir"
+
+
+def _filecheck(output: str, source: str) -> list:
+    """A small FileCheck: CHECK-LABEL / CHECK / CHECK-NOT in order, {{regex}}, [[VAR:regex]] and [[VAR]].
+    Returns the directives that failed, in order."""
+    import re
+
+    directives = re.findall(r"//\s*(CHECK(?:-LABEL|-NOT)?):\s*(.*)", source)
+    variables, pos, failed, pending_not = {}, 0, [], []
+
+    def to_regex(pat: str) -> str:
+        out, i = "", 0
+        while i < len(pat):
+            if pat.startswith("{{", i):
+                j = pat.index("}}", i)
+                out += f"(?:{pat[i + 2:j]})"
+                i = j + 2
+            elif pat.startswith("[[", i):
+                j = pat.index("]]", i)
+                body = pat[i + 2:j]
+                if ":" in body:
+                    name, rx = body.split(":", 1)
+                    out += f"(?P<{name}>{rx.replace('.*', '[^ ,]*')})"
+                else:
+                    out += re.escape(variables.get(body, "<undefined>"))
+                i = j + 2
+            else:
+                out += re.escape(pat[i])
+                i += 1
+        return re.sub(r"(\\ )+", r"\\s+", out)
+
+    for kind, pat in directives:
+        pat = pat.strip()
+        if kind == "CHECK-NOT":
+            pending_not.append(pat)
+            continue
+        m = re.compile(to_regex(pat)).search(output, pos)
+        if not m:
+            failed.append(f"{kind}: {pat}")
+            continue
+        for nt in pending_not:
+            if re.compile(to_regex(nt)).search(output, pos, m.start()):
+                failed.append(f"CHECK-NOT: {nt}")
+        pending_not = []
+        variables.update({k: v for k, v in m.groupdict().items() if v is not None})
+        pos = m.end()
+    for nt in pending_not:
+        if re.compile(to_regex(nt)).search(output, pos):
+            failed.append(f"CHECK-NOT: {nt}")
+    return failed
+
+
+def _canonicalised(text: str) -> str:
+    import os
+    import tempfile
+
+    from triton._C.libtriton import ir, passes
+
+    context = ir.context()
+    ir.load_dialects(context)
+    fd, path = tempfile.mkstemp(suffix=".mlir")
+    try:
+        with os.fdopen(fd, "w") as f:
+            f.write(text)
+        mod = ir.parse_mlir_module(path, context)
+    finally:
+        os.unlink(path)
+    mod.context = context
+    pm = ir.pass_manager(context)
+    passes.common.add_canonicalizer(pm)
+    pm.run(mod, "canonicalize")
+    return ttir.strip_locations(str(mod))
+
+
+@pytest.mark.skipif(not __import__("os").path.exists(REFERENCE_LIT), reason="the reference tree is not on this machine")
+def test_reference_lit_test_against_the_ir_rewrite():
+    """`triton-opt -triton-loop-split -canonicalize | FileCheck` of the reference's lit file
+    (pass/LoopSplit/test/loop-split.mlir:1) with this package's pieces: split_loops in its as-written mode,
+    Triton's canonicaliser, a small FileCheck. The four step-1 cases pass every directive. The step-10 case passes
+    the loop structure but not the mid-point lines: the lit file expects `mid + (mid % step != 0)` there, the
+    reference's source computes `mid + (step - mid % step)` (LoopSplit.cpp:163-167), and neither is the rounded-up
+    mid point that the "intent" mode computes."""
+    from triton_ext_b200.triton_backend import loop_split_ir
+
+    cases = open(REFERENCE_LIT).read().split("// -----")
+    assert len(cases) == 5
+    seen = {}
+    for case in cases:
+        code = "\n".join(l for l in case.splitlines() if not l.strip().startswith("//"))
+        label = __import__("re").search(r"@(\w+)\(", code).group(1)
+        new, n = loop_split_ir.split_loops("module {\n" + code + "\n}\n", mode="as-written")
+        assert n == 1, label
+        out = _canonicalised(new)
+        assert out.count("scf.for") == 2 and "scf.if" not in out, label
+        seen[label] = _filecheck(out, case)
+        # the corrected arithmetic gives verified IR of the same shape
+        fixed = _canonicalised(loop_split_ir.split_loops("module {\n" + code + "\n}\n")[0])
+        assert fixed.count("scf.for") == 2 and "scf.if" not in fixed, label
+    step10 = seen.pop("split_kernel_step10")
+    assert all(v == [] for v in seen.values()), seen
+    assert len(seen) == 4
+    assert step10 and step10[0].startswith("CHECK: %[[CMP:.*]] = arith.cmpi ne"), step10
+    assert all("MIDP" in d or "CMP" in d or "EXT" in d for d in step10), step10  # only mid-point lines differ
