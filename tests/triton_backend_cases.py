@@ -585,3 +585,55 @@ def test_reference_lit_test_against_the_ir_rewrite():
     assert len(seen) == 4
     assert step10 and step10[0].startswith("CHECK: %[[CMP:.*]] = arith.cmpi ne"), step10
     assert all("MIDP" in d or "CMP" in d or "EXT" in d for d in step10), step10  # only mid-point lines differ
+
+
+REFERENCE_ATTENTION = "/root/reference/pass/LoopSplit/06-fused-attention.py"
+
+
+def _load_reference_attention():
+    """The reference's demo kernel file, executed from its text with the three queries it makes of a GPU at import
+    (:28-41, :268) answered by constants. Nothing of it is written anywhere."""
+    import linecache
+    import re
+    import types
+
+    src = open(REFERENCE_ATTENTION).read()
+    src = src.replace("DEVICE = triton.runtime.driver.active.get_active_torch_device()", 'DEVICE = "cpu"')
+    src = re.sub(r"def is_hip\(\):\n    return .*\n", "def is_hip():\n    return False\n", src)
+    src = re.sub(r"def is_cuda\(\):\n    return .*\n", "def is_cuda():\n    return False\n", src)
+    src = src.replace("torch.cuda.get_device_capability()", "(0, 0)")
+    mod = types.ModuleType("reference_fused_attention")
+    mod.__file__ = REFERENCE_ATTENTION
+    linecache.cache[REFERENCE_ATTENTION] = (len(src), None, src.splitlines(True), REFERENCE_ATTENTION)
+    exec(compile(src, REFERENCE_ATTENTION, "exec"), mod.__dict__)
+    return mod
+
+
+@pytest.mark.skipif(not __import__("os").path.exists(REFERENCE_ATTENTION), reason="the reference tree is not on this machine")
+@pytest.mark.parametrize("head_dim,block_m,block_n", [(64, 128, 64), (128, 128, 64)])
+def test_loop_split_on_the_reference_attention_kernel(head_dim, block_m, block_n):
+    """The loop LoopSplit was written for: `_attn_fwd`'s KV loop with `if start_n >= causal_start`
+    (06-fused-attention.py:59-89). Its TTIR, from Triton's front end, has one scf.for, one scf.if on a compare of
+    the induction variable and two tt.dot; the IR rewrite plus Triton's canonicaliser leave an off-band loop with
+    neither compare nor mask and an on-band loop with the causal mask, each with both dots."""
+    from triton_ext_b200.triton_backend import loop_split_ir
+
+    fn = _load_reference_attention()._attn_fwd.fn  # below the autotuner
+    sig = {"Q": "*fp16", "K": "*fp16", "V": "*fp16", "sm_scale": "fp32", "M": "*fp32", "Out": "*fp16"}
+    for s in ("qz", "qh", "qm", "qk", "kz", "kh", "kn", "kk", "vz", "vh", "vk", "vn", "oz", "oh", "om", "on"):
+        sig["stride_" + s] = "i32"
+    sig.update({"Z": "i32", "H": "i32", "N_CTX": "i32", "HEAD_DIM": "constexpr", "BLOCK_M": "constexpr",
+                "BLOCK_N": "constexpr", "CAUSAL": "constexpr"})
+    cx = {"HEAD_DIM": head_dim, "BLOCK_M": block_m, "BLOCK_N": block_n, "CAUSAL": True}
+    before = ttir.strip_locations(compiler.lower_to_ttir(fn, sig, cx))
+    assert (before.count("scf.for"), before.count("scf.if"), before.count("tt.dot")) == (1, 1, 2)
+    new, n = loop_split_ir.split_loops(before)
+    assert n == 1
+    after = _canonicalised(new)
+    assert (after.count("scf.for"), after.count("scf.if"), after.count("tt.dot")) == (2, 0, 4)
+    off_band, on_band = after.split("scf.for")[1:]
+    assert "arith.cmpi" not in off_band and "arith.select" not in off_band
+    assert on_band.count("arith.cmpi sge") == 1 and "arith.select" in on_band.split("tt.return")[0]
+    # the K-loop matcher rightly refuses it: this is attention, not a GEMM
+    with pytest.raises(ttir.NotCanonical):
+        ttir.match_dot_kernel(after)
