@@ -345,3 +345,38 @@ def counting_kloop(a_ptr, b_ptr, c_ptr, count_ptr, K, stride_am, stride_bk, stri
         acc = tl.dot(a, b, acc)
     tl.atomic_add(count_ptr, 1)
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def vector_add(x_ptr, y_ptr, out_ptr, n, BLOCK: tl.constexpr):
+    """Not a GEMM at all."""
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    tl.store(out_ptr + offs, tl.load(x_ptr + offs, mask=mask) + tl.load(y_ptr + offs, mask=mask), mask=mask)
+
+
+@triton.jit
+def row_softmax(x_ptr, out_ptr, n_cols, stride, BLOCK: tl.constexpr):
+    """Not a GEMM: a reduction (an operation with a region) and exponentials."""
+    row = tl.program_id(0)
+    offs = tl.arange(0, BLOCK)
+    x = tl.load(x_ptr + row * stride + offs, mask=offs < n_cols, other=-float("inf"))
+    e = tl.exp(x - tl.max(x, axis=0))
+    tl.store(out_ptr + row * stride + offs, e / tl.sum(e, axis=0), mask=offs < n_cols)
+
+
+@triton.jit
+def two_dots_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
+                   BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Near miss: the product of A with B is multiplied by B's first tile again (two tt.dot)."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + rm[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    w = tl.load(b_ptr + tl.arange(0, BLOCK_N)[:, None] * stride_bk + rn[None, :])
+    out = tl.dot(acc.to(tl.bfloat16), w)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], out.to(c_ptr.dtype.element_ty))

@@ -378,6 +378,19 @@ def test_side_effects_outside_the_gemm_are_refused():
         compiler.analyse(jk.counting_kloop, sig, cx)
 
 
+def test_kernels_that_are_not_gemms_are_refused_cleanly():
+    with pytest.raises(ttir.NotCanonical, match="depends on the result of arith.addf"):
+        compiler.analyse(jk.vector_add, {"x_ptr": "*fp32", "y_ptr": "*fp32", "out_ptr": "*fp32", "n": "i32",
+                                         "BLOCK": "constexpr"}, {"BLOCK": 1024})
+    with pytest.raises(ttir.NotCanonical, match="region"):
+        compiler.analyse(jk.row_softmax, {"x_ptr": "*fp32", "out_ptr": "*fp32", "n_cols": "i32", "stride": "i32",
+                                          "BLOCK": "constexpr"}, {"BLOCK": 1024})
+    with pytest.raises(ttir.NotCanonical):
+        compiler.analyse(jk.two_dots_kloop, *small_sig())
+    with pytest.raises(ttir.NotCanonical, match="could not be analysed|unreadable|unknown value"):
+        ttir.match_dot_kernel("module {\n  tt.func public @f(%a: i32) {\n    %x = scf.for broken {\n    }\n    tt.return\n  }\n}\n")
+
+
 def test_hand_written_ir_is_refused_with_a_reason():
     base = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, *split_sig()))
     with pytest.raises(ttir.NotCanonical, match="stores"):

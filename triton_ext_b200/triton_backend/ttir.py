@@ -878,6 +878,15 @@ def _fuse_split_loops(second: Flt) -> Flt:
 
 def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMatch:
     """Analyse the printed TTIR of one kernel. Raises NotCanonical unless it is the K loop described above."""
+    try:
+        return _match_dot_kernel(text, arg_names)
+    except NotCanonical:
+        raise
+    except Exception as e:  # IR this reader was not written for: refuse, never guess
+        raise NotCanonical(f"the IR could not be analysed ({type(e).__name__}: {e})") from e
+
+
+def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
     fname, args, ops = parse_module(text, arg_names)
     ev = _Evaluator(args)
     ev.run(ops, ev.env)
