@@ -380,3 +380,19 @@ def two_dots_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
     w = tl.load(b_ptr + tl.arange(0, BLOCK_N)[:, None] * stride_bk + rn[None, :])
     out = tl.dot(acc.to(tl.bfloat16), w)
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], out.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def batched_kloop(a_ptr, b_ptr, c_ptr, K, stride_ab, stride_am, stride_bb, stride_bk, stride_cb, stride_cm,
+                  BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Not lowered: one matrix product per program_id(2), each at its own base offset."""
+    batch = tl.program_id(2)
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_ptr + batch * stride_ab + rm[:, None] * stride_am + (k + rk)[None, :])
+        b = tl.load(b_ptr + batch * stride_bb + (k + rk)[:, None] * stride_bk + rn[None, :])
+        acc = tl.dot(a, b, acc)
+    tl.store(c_ptr + batch * stride_cb + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))

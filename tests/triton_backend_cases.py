@@ -391,6 +391,19 @@ def test_kernels_that_are_not_gemms_are_refused_cleanly():
         ttir.match_dot_kernel("module {\n  tt.func public @f(%a: i32) {\n    %x = scf.for broken {\n    }\n    tt.return\n  }\n}\n")
 
 
+def test_batched_gemm_is_refused_not_misread():
+    """A base offset per program_id(2) is not part of the single-GEMM proof: whichever step sees it first refuses
+    (the compile when a stride argument makes the offset visible, else the launch, whose tiles no longer fit C)."""
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "K": "i32", "stride_ab": "i32", "stride_am": "i32",
+           "stride_bb": "i32", "stride_bk": "i32", "stride_cb": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr",
+           "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    cx = {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32}
+    with pytest.raises(ttir.NotCanonical):
+        m = compiler.analyse(jk.batched_kloop, sig, cx)
+        ttir.bind(m, dict(K=64, stride_ab=128 * 64, stride_am=64, stride_bb=64 * 128, stride_bk=128,
+                          stride_cb=128 * 128, stride_cm=128), (2, 2, 3))
+
+
 def test_hand_written_ir_is_refused_with_a_reason():
     base = ttir.strip_locations(compiler.lower_to_ttir(jk.split_kloop, *split_sig()))
     with pytest.raises(ttir.NotCanonical, match="stores"):
