@@ -1,0 +1,47 @@
+/*
+ * triton_ext_loop_split_text.h — LoopSplit over printed Triton IR, exported by the loop_split extension library.
+ *
+ * The reference's LoopSplit is an MLIR pass (pass/LoopSplit/LoopSplit.cpp:124-196: clone the scf.for, run the
+ * first copy over [lo, mid) and the second over [mid, hi), replace the compare of the induction variable by a
+ * constant in each). MLIR's C++ API is not available to this library, so the same rewrite is offered on the
+ * textual form every Triton tool prints and parses (`tt.func` / `scf.for` / `arith.cmpi` as printed by
+ * mlir::Operation::print without locations); the caller parses the result back with its own MLIR context, which
+ * verifies it, and canonicalises it (the lit test's `-canonicalize`, pass/LoopSplit/test/loop-split.mlir:1).
+ *
+ * Accepted loops are the reference's (LoopSplit.cpp:107-144): a positive constant step; an arith.cmpi with
+ * predicate slt / sle / sgt / sge or the unsigned forms on the induction variable; the other operand defined
+ * outside the loop; the first such compare in the body decides the split. Loops nested in a loop that is not
+ * split are looked at too.
+ */
+#ifndef TRITON_EXT_LOOP_SPLIT_TEXT_H
+#define TRITON_EXT_LOOP_SPLIT_TEXT_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TXLS_API __attribute__((visibility("default")))
+
+typedef enum tx_loop_split_mode {
+  /* mid = min(lo + ceildiv(max(T - lo, 0), step) * step, max(hi, lo)), T = comparand (slt, sge) or comparand + 1
+   * (sle, sgt); a compare with the induction variable on the right is read with the swapped predicate. Keeps the
+   * meaning of the loop for every bound. */
+  TXLS_INTENT = 0,
+  /* Exactly the operations the reference emits (LoopSplit.cpp:147-190): the comparand as mid point, +step / -step
+   * for sle / sge, `mid_diff += step - mid_diff % step` when the step is not 1, no clamping, the inverted
+   * predicate for a swapped compare. For running the reference's lit test. */
+  TXLS_AS_WRITTEN = 1
+} tx_loop_split_mode;
+
+/* Rewrites `ir_text` (one module, printed without locations). On success returns 0, stores a malloc'ed,
+ * NUL-terminated result in *out_text (release it with tx_loop_split_free) and the number of loops that were
+ * split in *loops_split. Returns 1 for invalid arguments and 2 for text whose regions do not balance. */
+TXLS_API int tx_loop_split_text(const char *ir_text, int mode, char **out_text, int32_t *loops_split);
+TXLS_API void tx_loop_split_free(char *text);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITON_EXT_LOOP_SPLIT_TEXT_H */

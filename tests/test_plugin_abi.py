@@ -37,6 +37,11 @@ def test_every_declared_symbol_is_exported(built_libs):
         assert name in infra_syms or name in dot_syms, name
     for name in _declared("b200_dot.h", r"\b(tx_dot_\w+)\s*\("):
         assert name in dot_syms, name
+    split_syms = _exported(P.plugin_path("loop_split"))
+    text_api = _declared("triton_ext_loop_split_text.h", r"\b(tx_loop_split_\w+)\s*\(")
+    assert set(text_api) == {"tx_loop_split_text", "tx_loop_split_free"}
+    for name in text_api:
+        assert name in split_syms, name
     attn = _declared("b200_attention.h", r"\b(tx_attn_\w+)\s*\(")
     assert len(attn) >= 6
     for name in attn:

@@ -30,7 +30,7 @@ INCLUDE = os.path.join(ROOT, "include")
 
 # (directory under csrc, pass class, sources, needs nvcc)
 EXTENSIONS = [
-    ("pass/LoopSplit", "LoopBisectPass", ["LoopSplitPass.cpp"], False),
+    ("pass/LoopSplit", "LoopBisectPass", ["LoopSplitPass.cpp", "LoopSplitText.cpp"], False),
     ("pass/DotTileSelect", "DotTileSelectPass", ["DotTileSelectPass.cpp"], False),
     ("backend/B200Dot", "B200DotLoweringPass", ["b200_dot.cu", "b200_dot_static.cu", "B200DotLowering.cpp",
                                                    "../B200Attention/b200_attention.cu"], True),

@@ -1,0 +1,380 @@
+// LoopSplit over printed Triton IR (include/triton_ext_loop_split_text.h). Line-oriented: the printer puts one
+// operation on a line, a region's opening brace at the end of its operation's line and its closing brace on a line
+// of its own, which is all the structure this rewrite needs.
+#include "triton_ext_loop_split_text.h"
+
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <set>
+#include <string>
+#include <vector>
+
+namespace {
+
+std::string trim(const std::string &s) {
+  size_t a = s.find_first_not_of(" \t\r");
+  if (a == std::string::npos) return "";
+  size_t b = s.find_last_not_of(" \t\r");
+  return s.substr(a, b - a + 1);
+}
+
+bool ends_with(const std::string &s, const char *suffix) {
+  const size_t n = strlen(suffix);
+  return s.size() >= n && s.compare(s.size() - n, n, suffix) == 0;
+}
+
+// An SSA value name at s[pos]: %[A-Za-z0-9_.$-]+ with an optional #N result index. Advances pos.
+bool parse_value(const std::string &s, size_t &pos, std::string &out) {
+  if (pos >= s.size() || s[pos] != '%') return false;
+  size_t p = pos + 1;
+  while (p < s.size() && (isalnum(static_cast<unsigned char>(s[p])) || s[p] == '_' || s[p] == '.' || s[p] == '$' || s[p] == '-')) ++p;
+  if (p == pos + 1) return false;
+  if (p < s.size() && s[p] == '#') {
+    size_t q = p + 1;
+    while (q < s.size() && isdigit(static_cast<unsigned char>(s[q]))) ++q;
+    if (q > p + 1) p = q;
+  }
+  out = s.substr(pos, p - pos);
+  pos = p;
+  return true;
+}
+
+bool eat(const std::string &s, size_t &pos, const char *lit) {
+  const size_t n = strlen(lit);
+  if (s.compare(pos, n, lit) != 0) return false;
+  pos += n;
+  return true;
+}
+
+// The text between the parenthesis at s[pos] and its partner. Advances pos past the partner.
+bool parse_parens(const std::string &s, size_t &pos, std::string &inner) {
+  if (pos >= s.size() || s[pos] != '(') return false;
+  int depth = 0;
+  for (size_t p = pos; p < s.size(); ++p) {
+    if (s[p] == '(') ++depth;
+    if (s[p] == ')' && --depth == 0) {
+      inner = s.substr(pos + 1, p - pos - 1);
+      pos = p + 1;
+      return true;
+    }
+  }
+  return false;
+}
+
+std::vector<std::string> split_list(const std::string &s) {
+  std::vector<std::string> out;
+  size_t a = 0;
+  while (a <= s.size()) {
+    size_t b = s.find(", ", a);
+    if (b == std::string::npos) b = s.size();
+    if (b > a) out.push_back(trim(s.substr(a, b - a)));
+    a = b + 2;
+  }
+  return out;
+}
+
+struct ForHeader {
+  std::string indent, results, iv, lo, hi, step, iters, types, ity;
+  std::vector<std::pair<std::string, std::string>> iter_pairs;  // (region argument, initial value)
+};
+
+bool parse_for(const std::string &line, ForHeader &h) {
+  const std::string t = trim(line);
+  if (!ends_with(t, "{")) return false;
+  const size_t at = line.find("scf.for ");
+  if (at == std::string::npos) return false;
+  const size_t first = line.find_first_not_of(" \t");
+  h.indent = line.substr(0, first);
+  h.results.clear();
+  if (at > first) {
+    const std::string lhs = line.substr(first, at - first);
+    if (!ends_with(lhs, " = ") || lhs[0] != '%') return false;
+    h.results = lhs.substr(0, lhs.size() - 3);
+  }
+  size_t p = at + 8;
+  if (!parse_value(line, p, h.iv) || !eat(line, p, " = ") || !parse_value(line, p, h.lo) || !eat(line, p, " to ") ||
+      !parse_value(line, p, h.hi) || !eat(line, p, " step ") || !parse_value(line, p, h.step))
+    return false;
+  h.iters.clear();
+  h.types.clear();
+  h.iter_pairs.clear();
+  if (line.compare(p, 11, " iter_args(") == 0) {
+    p += 10;
+    if (!parse_parens(line, p, h.iters) || !eat(line, p, " -> ") || !parse_parens(line, p, h.types)) return false;
+    for (const std::string &item : split_list(h.iters)) {
+      const size_t eq = item.find(" = ");
+      if (eq == std::string::npos) return false;
+      h.iter_pairs.emplace_back(trim(item.substr(0, eq)), trim(item.substr(eq + 3)));
+    }
+  }
+  const std::string tail = trim(line.substr(p));
+  h.ity.clear();
+  if (tail == "{") return true;  // index-typed loop: left alone by the caller
+  if (tail.size() > 4 && tail.compare(0, 2, ": ") == 0 && ends_with(tail, " {")) {
+    h.ity = trim(tail.substr(2, tail.size() - 4));
+    return !h.ity.empty() && h.ity[0] == 'i';
+  }
+  return false;
+}
+
+struct Cmp {
+  std::string indent, result, pred, lhs, rhs;
+};
+
+bool parse_cmp(const std::string &line, Cmp &c) {
+  const size_t first = line.find_first_not_of(" \t");
+  if (first == std::string::npos) return false;
+  c.indent = line.substr(0, first);
+  size_t p = first;
+  if (!parse_value(line, p, c.result) || !eat(line, p, " = arith.cmpi ")) return false;
+  const size_t comma = line.find(", ", p);
+  if (comma == std::string::npos) return false;
+  c.pred = line.substr(p, comma - p);
+  p = comma + 2;
+  if (!parse_value(line, p, c.lhs) || !eat(line, p, ", ") || !parse_value(line, p, c.rhs) || !eat(line, p, " : i")) return false;
+  for (size_t q = p; q < line.size(); ++q)
+    if (!isdigit(static_cast<unsigned char>(line[q]))) return trim(line.substr(q)).empty();
+  return true;
+}
+
+// `%x = arith.constant <integer> : iN`
+bool parse_int_constant(const std::string &line, std::string &name, long long &value) {
+  size_t p = line.find_first_not_of(" \t");
+  if (p == std::string::npos || !parse_value(line, p, name) || !eat(line, p, " = arith.constant ")) return false;
+  char *end = nullptr;
+  value = strtoll(line.c_str() + p, &end, 10);
+  if (end == line.c_str() + p) return false;
+  return strncmp(end, " : i", 4) == 0;
+}
+
+// Names a block of lines defines: operation results, loop induction variables and region arguments.
+std::set<std::string> defined_inside(const std::vector<std::string> &lines, size_t a, size_t b) {
+  std::set<std::string> names;
+  for (size_t i = a; i < b; ++i) {
+    const std::string &l = lines[i];
+    const size_t first = l.find_first_not_of(" \t");
+    if (first != std::string::npos && l[first] == '%') {
+      const size_t eq = l.find(" = ", first);
+      if (eq != std::string::npos)
+        for (std::string tok : split_list(l.substr(first, eq - first))) {
+          const size_t colon = tok.find(':');
+          names.insert(colon == std::string::npos ? tok : tok.substr(0, colon));
+        }
+    }
+    ForHeader h;
+    if (parse_for(l, h)) {
+      names.insert(h.iv);
+      for (const auto &pr : h.iter_pairs) names.insert(pr.first);
+    }
+  }
+  return names;
+}
+
+// Index of the line that closes the region opened by lines[start], or -1.
+long region_end(const std::vector<std::string> &lines, size_t start) {
+  int depth = 0;
+  for (size_t i = start; i < lines.size(); ++i) {
+    const std::string t = trim(lines[i]);
+    if (t == "} else {") continue;
+    if (ends_with(t, "{")) {
+      ++depth;
+    } else if (!t.empty() && t[0] == '}') {
+      if (--depth == 0) return static_cast<long>(i);
+    }
+  }
+  return -1;
+}
+
+}  // namespace
+
+namespace {
+
+struct PredInfo {
+  bool holds_below;  // the compare is true for iv < T (slt, sle) rather than for iv >= T (sge, sgt)
+  int adjust;        // T = comparand + adjust
+  bool equal;        // sge / sle (LoopSplit.cpp:35-44: CmpType::equal)
+};
+
+bool pred_info(const std::string &p, PredInfo &out) {
+  static const std::map<std::string, PredInfo> table = {
+      {"slt", {true, 0, false}},  {"ult", {true, 0, false}},  {"sle", {true, 1, true}},  {"ule", {true, 1, true}},
+      {"sge", {false, 0, true}},  {"uge", {false, 0, true}},  {"sgt", {false, 1, false}}, {"ugt", {false, 1, false}}};
+  auto it = table.find(p);
+  if (it == table.end()) return false;
+  out = it->second;
+  return true;
+}
+
+std::string swapped(const std::string &p) {  // a < b  <=>  b > a
+  static const std::map<std::string, std::string> m = {{"slt", "sgt"}, {"sgt", "slt"}, {"sle", "sge"}, {"sge", "sle"},
+                                                       {"ult", "ugt"}, {"ugt", "ult"}, {"ule", "uge"}, {"uge", "ule"}};
+  auto it = m.find(p);
+  return it == m.end() ? "" : it->second;
+}
+
+std::string inverted(const std::string &p) {  // arith::invertPredicate, which the reference applies instead
+  static const std::map<std::string, std::string> m = {{"slt", "sge"}, {"sge", "slt"}, {"sle", "sgt"}, {"sgt", "sle"},
+                                                       {"ult", "uge"}, {"uge", "ult"}, {"ule", "ugt"}, {"ugt", "ule"}};
+  auto it = m.find(p);
+  return it == m.end() ? "" : it->second;
+}
+
+int split_text(const std::string &text, int mode, std::string &result, int32_t &n_split) {
+  std::vector<std::string> lines;
+  for (size_t a = 0; a <= text.size();) {
+    size_t b = text.find('\n', a);
+    if (b == std::string::npos) b = text.size();
+    lines.push_back(text.substr(a, b - a));
+    a = b + 1;
+  }
+  std::map<std::string, long long> consts;
+  for (const std::string &l : lines) {
+    std::string name;
+    long long v;
+    if (parse_int_constant(l, name, v)) consts[name] = v;
+  }
+  std::vector<std::string> out;
+  n_split = 0;
+  for (size_t i = 0; i < lines.size();) {
+    ForHeader h;
+    if (!parse_for(lines[i], h)) {
+      out.push_back(lines[i++]);
+      continue;
+    }
+    const long end = region_end(lines, i);
+    if (end < 0) return 2;
+    const size_t b0 = i + 1, b1 = static_cast<size_t>(end);
+    const std::set<std::string> inside = defined_inside(lines, b0, b1);
+    const auto step_it = consts.find(h.step);
+    long chosen = -1;
+    Cmp cmp;
+    std::string pred, comparand;
+    PredInfo info{};
+    if (!h.ity.empty() && step_it != consts.end() && step_it->second > 0) {
+      for (size_t bi = b0; bi < b1; ++bi) {
+        Cmp c;
+        if (!parse_cmp(lines[bi], c)) continue;
+        std::string p = c.pred, x = c.lhs, y = c.rhs;
+        if (y == h.iv && x != h.iv) {
+          p = mode == TXLS_AS_WRITTEN ? inverted(p) : swapped(p);
+          std::swap(x, y);
+        }
+        PredInfo pi{};
+        if (x != h.iv || y == h.iv || !pred_info(p, pi) || inside.count(y)) continue;
+        chosen = static_cast<long>(bi);
+        cmp = c;
+        pred = p;
+        comparand = y;
+        info = pi;
+        break;
+      }
+    }
+    if (chosen < 0) {  // not a loop to split; loops nested inside it are still looked at
+      out.push_back(lines[i++]);
+      continue;
+    }
+    const std::string tag = "%ls" + std::to_string(n_split);
+    const std::string &in = h.indent, &ty = h.ity;
+    const long long stepv = step_it->second;
+    std::vector<std::string> pre;
+    std::string midp;
+    bool first_true;
+    if (mode == TXLS_AS_WRITTEN) {
+      const bool greater = !info.holds_below;
+      midp = comparand;
+      if (info.equal) {
+        pre.push_back(in + tag + "_inc = arith.constant " + std::to_string(greater ? -stepv : stepv) + " : " + ty);
+        pre.push_back(in + tag + "_t = arith.addi " + comparand + ", " + tag + "_inc : " + ty);
+        midp = tag + "_t";
+      }
+      if (stepv != 1) {
+        pre.push_back(in + tag + "_d = arith.subi " + midp + ", " + h.lo + " : " + ty);
+        pre.push_back(in + tag + "_r = arith.remui " + tag + "_d, " + h.step + " : " + ty);
+        pre.push_back(in + tag + "_u = arith.subi " + h.step + ", " + tag + "_r : " + ty);
+        pre.push_back(in + tag + "_e = arith.addi " + tag + "_d, " + tag + "_u : " + ty);
+        pre.push_back(in + tag + "_mid = arith.addi " + h.lo + ", " + tag + "_e : " + ty);
+        midp = tag + "_mid";
+      }
+      first_true = !greater;
+    } else {
+      std::string thr = comparand;
+      pre.push_back(in + tag + "_c0 = arith.constant 0 : " + ty);
+      if (info.adjust) {
+        pre.push_back(in + tag + "_c1 = arith.constant 1 : " + ty);
+        pre.push_back(in + tag + "_t = arith.addi " + comparand + ", " + tag + "_c1 : " + ty);
+        thr = tag + "_t";
+      }
+      pre.push_back(in + tag + "_d = arith.subi " + thr + ", " + h.lo + " : " + ty);
+      pre.push_back(in + tag + "_p = arith.maxsi " + tag + "_d, " + tag + "_c0 : " + ty);
+      pre.push_back(in + tag + "_q = arith.ceildivsi " + tag + "_p, " + h.step + " : " + ty);
+      pre.push_back(in + tag + "_m = arith.muli " + tag + "_q, " + h.step + " : " + ty);
+      pre.push_back(in + tag + "_a = arith.addi " + h.lo + ", " + tag + "_m : " + ty);
+      pre.push_back(in + tag + "_h = arith.maxsi " + h.hi + ", " + h.lo + " : " + ty);
+      pre.push_back(in + tag + "_mid = arith.minsi " + tag + "_a, " + tag + "_h : " + ty);
+      midp = tag + "_mid";
+      first_true = info.holds_below;
+    }
+    const size_t n_res = h.iter_pairs.size();
+    const std::string main_name = tag + "_main";
+    std::string head1 = in, head2 = in;
+    if (n_res) head1 += main_name + (n_res == 1 ? "" : ":" + std::to_string(n_res)) + " = ";
+    if (!h.results.empty()) head2 += h.results + " = ";
+    head1 += "scf.for " + h.iv + " = " + h.lo + " to " + midp + " step " + h.step;
+    head2 += "scf.for " + h.iv + " = " + midp + " to " + h.hi + " step " + h.step;
+    if (n_res) {
+      std::string second;
+      for (size_t k = 0; k < n_res; ++k) {
+        if (k) second += ", ";
+        second += h.iter_pairs[k].first + " = " + main_name + (n_res == 1 ? "" : "#" + std::to_string(k));
+      }
+      head1 += " iter_args(" + h.iters + ") -> (" + h.types + ")";
+      head2 += " iter_args(" + second + ") -> (" + h.types + ")";
+    }
+    head1 += "  : " + ty + " {";
+    head2 += "  : " + ty + " {";
+    out.insert(out.end(), pre.begin(), pre.end());
+    for (int copy = 0; copy < 2; ++copy) {
+      out.push_back(copy == 0 ? head1 : head2);
+      const bool value = (copy == 0) == first_true;
+      for (size_t bi = b0; bi < b1; ++bi) {
+        if (static_cast<long>(bi) == chosen)
+          out.push_back(cmp.indent + cmp.result + " = arith.constant " + (value ? "true" : "false"));
+        else
+          out.push_back(lines[bi]);
+      }
+      out.push_back(lines[b1]);
+    }
+    ++n_split;
+    i = b1 + 1;
+  }
+  result.clear();
+  for (size_t k = 0; k < out.size(); ++k) {
+    result += out[k];
+    if (k + 1 < out.size()) result += '\n';
+  }
+  if (result.empty() || result.back() != '\n') result += '\n';
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tx_loop_split_text(const char *ir_text, int mode, char **out_text, int32_t *loops_split) {
+  if (!ir_text || !out_text || !loops_split || (mode != TXLS_INTENT && mode != TXLS_AS_WRITTEN)) return 1;
+  std::string result;
+  int32_t n = 0;
+  const int rc = split_text(ir_text, mode, result, n);
+  if (rc != 0) return rc;
+  char *buf = static_cast<char *>(malloc(result.size() + 1));
+  if (!buf) return 1;
+  memcpy(buf, result.c_str(), result.size() + 1);
+  *out_text = buf;
+  *loops_split = n;
+  return 0;
+}
+
+void tx_loop_split_free(char *text) { free(text); }
+
+}  // extern "C"
