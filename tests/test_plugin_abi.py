@@ -143,3 +143,46 @@ def test_threaded_lookups(built_libs):
     [t.start() for t in ts]
     [t.join() for t in ts]
     assert not errs
+
+
+def test_loop_split_text_entry_point(built_libs):
+    """tx_loop_split_text through its C-ABI: argument checks, a loop it must leave alone, one it must bisect."""
+    lib = P.load_plugin(P.plugin_path("loop_split"))
+    lib.tx_loop_split_text.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                       ctypes.POINTER(ctypes.c_int32)]
+    lib.tx_loop_split_free.argtypes = [ctypes.c_void_p]
+    out, n = ctypes.c_void_p(), ctypes.c_int32(-1)
+    assert lib.tx_loop_split_text(None, 0, ctypes.byref(out), ctypes.byref(n)) == 1
+    assert lib.tx_loop_split_text(b"module {\n}\n", 7, ctypes.byref(out), ctypes.byref(n)) == 1
+    unbalanced = b"  scf.for %i = %a to %b step %c  : i32 {\n    %x = arith.addi %i, %i : i32\n"
+    assert lib.tx_loop_split_text(unbalanced, 0, ctypes.byref(out), ctypes.byref(n)) == 2
+
+    def run(text: str, mode: int = 0):
+        o, k = ctypes.c_void_p(), ctypes.c_int32(-1)
+        assert lib.tx_loop_split_text(text.encode(), mode, ctypes.byref(o), ctypes.byref(k)) == 0
+        try:
+            return ctypes.string_at(o).decode(), k.value
+        finally:
+            lib.tx_loop_split_free(o)
+
+    loop = ("  %c4 = arith.constant 4 : i32\n"
+            "  %r = scf.for %i = %lo to %hi step %c4 iter_args(%acc = %z) -> (i32)  : i32 {\n"
+            "    %p = arith.cmpi PRED, %i, CMP : i32\n"
+            "    %s = arith.select %p, %i, %acc : i32\n"
+            "    scf.yield %s : i32\n"
+            "  }\n")
+    text, k = run(loop.replace("PRED", "slt").replace("CMP", "%mid"))
+    assert k == 1 and text.count("scf.for") == 2
+    assert "%ls0_main = scf.for %i = %lo to %ls0_mid step %c4 iter_args(%acc = %z) -> (i32)  : i32 {" in text
+    assert "%r = scf.for %i = %ls0_mid to %hi step %c4 iter_args(%acc = %ls0_main) -> (i32)  : i32 {" in text
+    assert text.index("%p = arith.constant true") < text.index("%p = arith.constant false")
+    assert "arith.ceildivsi" in text and "arith.minsi" in text
+    written, _ = run(loop.replace("PRED", "sge").replace("CMP", "%mid"), 1)
+    assert "%ls0_inc = arith.constant -4 : i32" in written and "arith.remui" in written and "arith.minsi" not in written
+    assert written.index("%p = arith.constant false") < written.index("%p = arith.constant true")
+    # not split: equality compare; comparand defined inside the loop; non-constant step
+    for variant in (loop.replace("PRED", "eq").replace("CMP", "%mid"),
+                    loop.replace("PRED", "slt").replace("CMP", "%s"),
+                    loop.replace("PRED", "slt").replace("CMP", "%mid").replace("step %c4", "step %step")):
+        same, k = run(variant)
+        assert k == 0 and same == variant
