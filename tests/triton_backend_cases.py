@@ -507,7 +507,15 @@ def test_text_helpers():
 
 # ---- the reference's own lit test, when the reference tree is present --------------------------------------------
 
-REFERENCE_LIT = "/root/reference/pass/LoopSplit/test/loop-split.mlir"
+def _reference_root() -> str:
+    """The reference checkout: $TRITON_EXT_REFERENCE, else a directory `reference` beside this repository."""
+    import os
+
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.environ.get("TRITON_EXT_REFERENCE", os.path.join(os.path.dirname(here), "reference"))
+
+
+REFERENCE_LIT = _reference_root() + "/pass/LoopSplit/test/loop-split.mlir"
 
 
 def _filecheck(output: str, source: str) -> list:
@@ -613,7 +621,7 @@ def test_reference_lit_test_against_the_ir_rewrite():
     assert all("MIDP" in d or "CMP" in d or "EXT" in d for d in step10), step10  # only mid-point lines differ
 
 
-REFERENCE_ATTENTION = "/root/reference/pass/LoopSplit/06-fused-attention.py"
+REFERENCE_ATTENTION = _reference_root() + "/pass/LoopSplit/06-fused-attention.py"
 
 
 def _load_reference_attention():
