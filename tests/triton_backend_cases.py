@@ -671,3 +671,29 @@ def test_loop_split_on_the_reference_attention_kernel(head_dim, block_m, block_n
     # the K-loop matcher rightly refuses it: this is attention, not a GEMM
     with pytest.raises(ttir.NotCanonical):
         ttir.match_dot_kernel(after)
+
+
+class OtherDryDriver(DryDriver):
+    pass
+
+
+def test_jit_keeps_one_cache_per_driver():
+    """triton_backend.jit: the same kernel object under two drivers in turn, each with its own compile cache."""
+    from triton.runtime.driver import driver as config
+
+    tbk.install()
+    kernel = tbk.jit(jk.split_kloop.fn)
+    a = torch.zeros(128, 256, dtype=torch.bfloat16)
+    b = torch.zeros(256, 128, dtype=torch.bfloat16)
+    c = torch.zeros(128, 128, dtype=torch.bfloat16)
+    previous = config._active
+    try:
+        for drv in (DryDriver(), OtherDryDriver(), DryDriver()):
+            config.set_active(drv)
+            DryLauncher.calls.clear()
+            kernel[(1, 1)](a, b, c, 128, 128, 256, 256, 1, 128, 1, 128, 1, 256, BLOCK_M=128, BLOCK_N=128, BLOCK_K=128)
+            assert len(DryLauncher.calls) == 1 and DryLauncher.calls[0]["bound"].k == 256
+    finally:
+        config._active = previous
+    assert set(kernel._caches_by_driver) == {"DryDriver", "OtherDryDriver"}
+    assert all(len(v[0][0]) == 1 for v in kernel._caches_by_driver.values())  # one compiled kernel per driver, device 0

@@ -213,6 +213,35 @@ def test_autotuned_kernel(built_libs, cuda_device):
     assert torch.equal(c, backend.dot(a, b, check=True))
 
 
+def test_per_driver_jit_alternates_between_lowerings(built_libs, cuda_device):
+    """triton_backend.jit: one kernel object launched under Triton's stock driver, this backend, and the stock
+    driver again, without touching its caches; all three results agree."""
+    from triton_ext_b200 import triton_backend as tbk
+
+    kernel = tbk.jit(jk.split_kloop.fn)
+    M, N, K = 256, 256, 576
+    a, b = _rand((M, K), torch.bfloat16, cuda_device, 27), _rand((K, N), torch.bfloat16, cuda_device, 28)
+    outs = [torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device) for _ in range(3)]
+
+    def launch(c):
+        kernel[(M // 64, N // 64)](a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+                                   c.stride(0), c.stride(1), 576, BLOCK_M=64, BLOCK_N=64, BLOCK_K=64)
+
+    try:
+        launch(outs[0])
+        torch.cuda.synchronize()
+    except Exception as e:  # the stock tool chain (ptxas) is not part of this package
+        pytest.skip(f"Triton's CUDA backend could not compile here: {type(e).__name__}")
+    with tbk.activate():
+        launch(outs[1])
+    launch(outs[2])
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[2])
+    scale = (a.float() @ b.float()).abs().max().item()
+    assert (outs[1].float() - outs[0].float()).abs().max().item() <= 2.0 ** -7 * scale
+    assert set(kernel._caches_by_driver) == {"CudaDriver", "B200DotDriver"}
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk

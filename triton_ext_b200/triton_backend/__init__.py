@@ -13,7 +13,8 @@ stock CUDA driver stays Triton's default; :func:`activate` switches a block of c
         kernel[grid](a, b, c, M, N, K, ...)     # analysed once, then tx_dot_run on the current stream
 
 A ``JITFunction`` remembers the backend of its first launch on a device, so launch a given kernel object
-under one driver only.
+under one driver only, or decorate it with :func:`jit` instead of ``triton.jit``: that kernel object keeps one
+compile cache per driver and can be launched under the stock driver and under this one in turn.
 
 This fills the reference's empty ``backend/`` slot (backend/CMakeLists.txt is empty upstream) from the
 Python side; the pass plug-ins it drives are the ones TRITON_PASS_PLUGIN_PATH would load.
@@ -24,7 +25,7 @@ import contextlib
 
 from .ttir import BoundDot, DotKernelMatch, NotCanonical, bind, match_dot_kernel
 
-__all__ = ["install", "activate", "NotCanonical", "DotKernelMatch", "BoundDot", "bind", "match_dot_kernel"]
+__all__ = ["install", "activate", "jit", "NotCanonical", "DotKernelMatch", "BoundDot", "bind", "match_dot_kernel"]
 
 
 def install() -> None:
@@ -52,3 +53,26 @@ def activate():
         yield config.active
     finally:
         config._active = previous
+
+
+def jit(fn=None, **options):
+    """``triton.jit`` for kernels that are launched under more than one driver: the compile cache of the returned
+    kernel object (target, backend, binder, compiled kernels per device) is kept per active driver."""
+    from collections import defaultdict
+
+    from triton.runtime.driver import driver as config
+    from triton.runtime.jit import JITFunction
+
+    class PerDriverJITFunction(JITFunction):
+        def run(self, *args, **kwargs):
+            caches = self.__dict__.setdefault("_caches_by_driver", {})
+            key = type(config.active).__qualname__
+            if key not in caches:
+                caches[key] = defaultdict(self.create_binder)
+            self.device_caches = caches[key]
+            return super().run(*args, **kwargs)
+
+    def wrap(f):
+        return PerDriverJITFunction(f, **options)
+
+    return wrap(fn) if fn is not None else wrap
