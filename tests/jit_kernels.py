@@ -95,7 +95,7 @@ def relu_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
 @triton.jit
 def shifted_rows_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
                        BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
-    """Near miss: C rows are not the rows of A that produced them."""
+    """A is read one row further down than C is written: the product of A without its first row."""
     rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
     rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
     rk = tl.arange(0, BLOCK_K)
@@ -385,7 +385,7 @@ def two_dots_kloop(a_ptr, b_ptr, c_ptr, K, stride_am, stride_bk, stride_cm,
 @triton.jit
 def batched_kloop(a_ptr, b_ptr, c_ptr, K, stride_ab, stride_am, stride_bb, stride_bk, stride_cb, stride_cm,
                   BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
-    """Not lowered: one matrix product per program_id(2), each at its own base offset."""
+    """One matrix product per program_id(2), each at its own base offset in A, B and C."""
     batch = tl.program_id(2)
     rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
     rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)

@@ -343,7 +343,6 @@ def test_scale_vector_of_other_rows_is_refused():
 
 @pytest.mark.parametrize("kernel,why", [
     (jk.relu_kloop, "depends on the result of"),
-    (jk.shifted_rows_kloop, "rows of A"),
     (jk.strided_k_kloop, "K elements per iteration"),
     (jk.nonzero_fill_kloop, "must be zero"),
 ])
@@ -391,17 +390,31 @@ def test_kernels_that_are_not_gemms_are_refused_cleanly():
         ttir.match_dot_kernel("module {\n  tt.func public @f(%a: i32) {\n    %x = scf.for broken {\n    }\n    tt.return\n  }\n}\n")
 
 
-def test_batched_gemm_is_refused_not_misread():
-    """A base offset per program_id(2) is not part of the single-GEMM proof: whichever step sees it first refuses
-    (the compile when a stride argument makes the offset visible, else the launch, whose tiles no longer fit C)."""
+def test_batched_gemm_binds_one_product_per_offset_triple():
+    """A base offset per program_id(2): terms of an address that are not whole blocks of the tile's own stride are
+    offsets of the whole matrix; bind() groups the programs by their (A, B, C) offsets and every group must tile
+    its C exactly once."""
     sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "K": "i32", "stride_ab": "i32", "stride_am": "i32",
            "stride_bb": "i32", "stride_bk": "i32", "stride_cb": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr",
            "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
-    cx = {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32}
-    with pytest.raises(ttir.NotCanonical):
-        m = compiler.analyse(jk.batched_kloop, sig, cx)
-        ttir.bind(m, dict(K=64, stride_ab=128 * 64, stride_am=64, stride_bb=64 * 128, stride_bk=128,
-                          stride_cb=128 * 128, stride_cm=128), (2, 2, 3))
+    m = compiler.analyse(jk.batched_kloop, sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
+    assert m.batch_offsets == ["pid_z*stride_ab", "pid_z*stride_bb", "pid_z*stride_cb"]
+    assert (m.row0, m.col0) == ("64*pid_x", "64*pid_y")
+    s = dict(K=64, stride_ab=128 * 64, stride_am=64, stride_bb=64 * 128, stride_bk=128, stride_cb=128 * 128, stride_cm=128)
+    b = ttir.bind(m, s, (2, 2, 3))
+    assert (b.m, b.n, b.k) == (128, 128, 64)
+    assert b.batches == [(0, 0, 0), (8192, 8192, 16384), (16384, 16384, 32768)]
+    with pytest.raises(ttir.NotCanonical, match="store to the same C"):
+        ttir.bind(m, dict(s, stride_cb=0), (2, 2, 3))
+    assert ttir.DotKernelMatch.from_json(m.to_json()) == m
+
+
+def test_operand_read_at_an_offset():
+    """Rows of A shifted by one against C: the product of the matrix that starts one row further down."""
+    m = compiler.analyse(jk.shifted_rows_kloop, *small_sig())
+    assert m.batch_offsets == ["stride_am", "0", "0"]
+    b = ttir.bind(m, dict(K=64, stride_am=64, stride_bk=128, stride_cm=128), (2, 2))
+    assert b.batches == [(64, 0, 0)] and (b.m, b.n, b.k) == (128, 128, 64)
 
 
 def test_hand_written_ir_is_refused_with_a_reason():

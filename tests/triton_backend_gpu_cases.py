@@ -242,6 +242,42 @@ def test_per_driver_jit_alternates_between_lowerings(built_libs, cuda_device):
     assert set(kernel._caches_by_driver) == {"CudaDriver", "B200DotDriver"}
 
 
+def test_batched_kloop(built_libs, cuda_device):
+    """Four matrix products in one launch (program_id(2) picks the matrices): one library launch each."""
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    B, M, N, K = 4, 256, 192, 160
+    a = _rand((B, M, K), torch.bfloat16, cuda_device, 29)
+    b = _rand((B, K, N), torch.bfloat16, cuda_device, 30)
+    c = torch.full((B, M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    before = backend.kernel_launches()
+    kernel = triton.jit(jk.batched_kloop.fn)
+    with tbk.activate():
+        kernel[(M // 64, N // 64, B)](a, b, c, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0),
+                                      c.stride(1), BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    torch.cuda.synchronize()
+    assert backend.kernel_launches() - before == B
+    for i in range(B):
+        assert torch.equal(c[i], backend.dot(a[i], b[i], check=True)), i
+    ref = torch.bmm(a.float(), b.float())
+    torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
+def test_operand_at_an_offset(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 128, 128, 64
+    a = _rand((M + 8, K), torch.bfloat16, cuda_device, 31)   # the kernel reads rows 1 .. M of it
+    b = _rand((K, N), torch.bfloat16, cuda_device, 32)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device)
+    kernel = triton.jit(jk.shifted_rows_kloop.fn)
+    with tbk.activate():
+        kernel[(M // 64, N // 64)](a, b, c, K, a.stride(0), b.stride(0), c.stride(0), BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    torch.cuda.synchronize()
+    ref = a[1:M + 1].float() @ b.float()
+    torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk

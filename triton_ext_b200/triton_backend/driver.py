@@ -106,9 +106,12 @@ class B200DotLauncher:
         plan = entry["plan"]
         if enter_hook is not None:
             enter_hook(launch_metadata)
-        backend._check(plan._lib.tx_dot_run(plan._h, a.data_ptr(), b.data_ptr(), c.data_ptr(), scales[0], scales[1],
-                                            ctypes.c_void_p(int(stream))))
-        self.launches += 1
+        ab_size, c_size = a.element_size(), c.element_size()
+        for off_a, off_b, off_c in entry["bound"].batches or [(0, 0, 0)]:  # one library launch per matrix product
+            backend._check(plan._lib.tx_dot_run(plan._h, a.data_ptr() + off_a * ab_size, b.data_ptr() + off_b * ab_size,
+                                                c.data_ptr() + off_c * c_size, scales[0], scales[1],
+                                                ctypes.c_void_p(int(stream))))
+            self.launches += 1
         if exit_hook is not None:
             exit_hook(launch_metadata)
 

@@ -736,6 +736,7 @@ class DotKernelMatch:
     row_scale_arg: Optional[str] = None  # fp32 vector multiplied into the rows before the cast
     col_scale_arg: Optional[str] = None
     tile_loop: Optional[list] = None     # [lo, hi, step] of a persistent kernel's loop over tiles (tile_iv)
+    batch_offsets: Optional[list] = None  # [A, B, C] element offsets of the program's matrices (batched GEMM)
 
     def to_json(self) -> str:
         return json.dumps(self.__dict__, sort_keys=True)
@@ -807,11 +808,23 @@ def _unwrap(expr: Any) -> tuple:
     return expr, wraps
 
 
-def _origin(const: Any, stride: Any, strides: set, what: str) -> Any:
-    o = sp.cancel(const / stride) if const != 0 else sp.Integer(0)
-    if sp.denom(o) != 1 or (o.free_symbols & strides) or (o.free_symbols & {X0, X1, KIV}):
-        raise NotCanonical(f"{what}: the tile origin is not a whole number of rows or columns")
-    return sp.expand(o)
+def _origin(const: Any, stride: Any, block: int, strides: set, what: str) -> tuple:
+    """Split the constant part of an address into (tile origin in rows or columns, batch offset in elements).
+
+    A term belongs to the origin when it is `stride` times a symbolic multiple of the block extent (tile origins
+    are whole blocks); every other term is an offset of the whole matrix, as a batched kernel adds per program id.
+    A term put on the wrong side cannot slip through: bind() checks numerically that the origins tile C exactly."""
+    origin, batch = sp.Integer(0), sp.Integer(0)
+    for term in sp.Add.make_args(sp.expand(const)):
+        q = sp.cancel(term / (stride * block))
+        if sp.denom(q) == 1 and not (q.free_symbols & strides):
+            origin += q * block
+        else:
+            batch += term
+    bad = {X0, X1, KIV}
+    if (origin.free_symbols & bad) or (batch.free_symbols & bad):
+        raise NotCanonical(f"{what}: the tile origin moves with the tile indices")
+    return sp.expand(origin), sp.expand(batch)
 
 
 def _classify_mask(cond: Optional[Cond], forms: dict, what: str) -> dict:
@@ -946,10 +959,15 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
     stride_syms = set()
     for s in (sa_r, sa_k, sb_k, sb_c, sc_r, sc_c):
         stride_syms |= s.free_symbols
-    row0 = _origin(ca, sa_r, stride_syms, "A")
-    col0 = _origin(cb, sb_c, stride_syms, "B")
-    if sp.expand(cc - row0 * sc_r - col0 * sc_c) != 0:
+    row0, a_batch = _origin(ca, sa_r, bm, stride_syms, "A")
+    col0, b_batch = _origin(cb, sb_c, bn, stride_syms, "B")
+    # What is left of C's address after the tile's rows and columns is the offset of its matrix.
+    c_batch = sp.expand(cc - row0 * sc_r - col0 * sc_c)
+    c_row, c_rest = _origin(c_batch, sc_r, bm, stride_syms, "C")
+    c_col, c_rest = _origin(c_rest, sc_c, bn, stride_syms, "C")
+    if c_row != 0 or c_col != 0 or (c_batch.free_symbols & {X0, X1, KIV}):
         raise NotCanonical("C is not stored at the rows of A and the columns of B")
+    batched = any(e != 0 for e in (a_batch, b_batch, c_batch))
 
     kk = kpi * KIV
     a_m = _classify_mask(a.data["mask"], {"k": X1 + kk, "m": row0 + X0}, "A mask")
@@ -1006,7 +1024,8 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
         n_bound=str(n_bound) if n_bound is not None else None,
         split_pred=split_pred, split_comparand=split_cmp, alpha=alpha,
         int_args=sorted(ev.arg_symbols), row_scale_arg=row_scale, col_scale_arg=col_scale,
-        tile_loop=[str(sp.expand(ev.tile_loop[k])) for k in ("lo", "hi", "step")] if ev.tile_loop else None)
+        tile_loop=[str(sp.expand(ev.tile_loop[k])) for k in ("lo", "hi", "step")] if ev.tile_loop else None,
+        batch_offsets=[str(a_batch), str(b_batch), str(c_batch)] if batched else None)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -1026,6 +1045,7 @@ class BoundDot:
     alpha: float
     block_k: int
     k_main: int     # K elements the unmasked iterations cover
+    batches: Optional[list] = None  # batched GEMM: one (A, B, C) element-offset triple per matrix product
 
 
 def _value(expr: Optional[str], scalars: dict) -> Optional[int]:
@@ -1074,7 +1094,8 @@ def _tile_origins(match: DotKernelMatch, scalars: dict, grid: tuple) -> tuple:
         for key in ("pid_x", "pid_y", "pid_z"):
             env[key] = env[key][owner]
         env["tile_iv"] = lo[owner] + within * step[owner]
-    return evaluate(match.row0), evaluate(match.col0)
+    extra = [evaluate(t) for t in (match.batch_offsets or [])]
+    return evaluate(match.row0), evaluate(match.col0), extra
 
 
 def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional[dict] = None) -> BoundDot:
@@ -1116,7 +1137,7 @@ def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional
     if k < 1:
         raise NotCanonical("empty K")
 
-    rows, cols = _tile_origins(match, sv, grid)
+    rows, cols, offsets = _tile_origins(match, sv, grid)
     m = _value(match.m_bound, sv)
     n = _value(match.n_bound, sv)
     live = np.ones(rows.shape, bool)
@@ -1133,7 +1154,22 @@ def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional
     if (r % match.block_m).any() or (c % match.block_n).any() or (r < 0).any() or (c < 0).any():
         raise NotCanonical("tile origins are not multiples of the block shape")
     ids = (r // match.block_m) * tn + (c // match.block_n)
-    if ids.size != tm * tn or np.unique(ids).size != tm * tn:
+    batches = None
+    if offsets:
+        # One matrix product per distinct (A, B, C) offset triple; each must tile its C exactly once.
+        triples = np.stack([o[live] for o in offsets], axis=1)
+        uniq, inverse = np.unique(triples, axis=0, return_inverse=True)
+        inverse = np.asarray(inverse).reshape(-1)
+        if len(uniq) > 4096:
+            raise NotCanonical(f"{len(uniq)} matrix products in one launch")
+        if np.unique(uniq[:, 2]).size != len(uniq):
+            raise NotCanonical("two matrix products of the launch store to the same C")
+        for g in range(len(uniq)):
+            mine = ids[inverse == g]
+            if mine.size != tm * tn or np.unique(mine).size != tm * tn:
+                raise NotCanonical(f"the grid {grid} does not cover the {tm}x{tn} tiles of every C exactly once")
+        batches = [tuple(int(v) for v in row) for row in uniq]
+    elif ids.size != tm * tn or np.unique(ids).size != tm * tn:
         raise NotCanonical(f"the grid {grid} does not cover the {tm}x{tn} tiles of C exactly once")
 
     k_main = (k // match.block_k) * match.block_k
@@ -1157,4 +1193,4 @@ def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional
         if ld < need:
             raise NotCanonical(f"{name}: leading dimension {ld} is smaller than its extent {need}")
     return BoundDot(m=m, n=n, k=k, a_layout=a_layout, b_layout=b_layout, lda=lda, ldb=ldb, ldc=c_r,
-                    alpha=alpha, block_k=match.block_k, k_main=k_main)
+                    alpha=alpha, block_k=match.block_k, k_main=k_main, batches=batches)
