@@ -690,6 +690,21 @@ class OtherDryDriver(DryDriver):
     pass
 
 
+def test_narrow_source_blocks_past_the_last_library_block():
+    """K = 160 in source blocks of 32 (all whole) but library blocks of 64: the split handed to the passes is 128."""
+    launcher = driver.B200DotLauncher.__new__(driver.B200DotLauncher)
+    launcher.arg_names, launcher._bound, launcher.launches = [], {}, 0
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "K": "i32", "stride_ab": "i32", "stride_am": "i32",
+           "stride_bb": "i32", "stride_bk": "i32", "stride_cb": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr",
+           "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    m = compiler.analyse(jk.batched_kloop, sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 32})
+    values = dict(K=160, stride_ab=256 * 160, stride_am=160, stride_bb=160 * 192, stride_bk=192, stride_cb=256 * 192,
+                  stride_cm=192)
+    entry = launcher.prepare(m, values, (4, 3, 2))
+    assert entry["bound"].k_main == 160 and entry["config"].k_split_point == 128
+    assert len(entry["bound"].batches) == 2
+
+
 def test_jit_keeps_one_cache_per_driver():
     """triton_backend.jit: the same kernel object under two drivers in turn, each with its own compile cache."""
     from triton.runtime.driver import driver as config

@@ -69,7 +69,11 @@ class B200DotLauncher:
                 getattr(torch, _TORCH_DTYPES[match.out_dtype]), a_layout=layouts[bound.a_layout],
                 b_layout=layouts[bound.b_layout], lda=bound.lda, ldb=bound.ldb, ldc=bound.ldc, alpha=bound.alpha,
                 row_scale=match.row_scale_arg is not None, col_scale=match.col_scale_arg is not None)
-            config, info, module = plugin.lower_dot(problem, bound.block_k, split_comparand=bound.k_main)
+            # The library's K blocks are 128 bytes of K wide; a source block may be narrower. Whole source blocks
+            # past the last whole library block belong to the library's masked remainder block.
+            phys = 128 // {"f8e4m3": 1, "f8e5m2": 1}.get(match.ab_dtype, 2)
+            split = min(bound.k_main, (bound.k // phys) * phys)
+            config, info, module = plugin.lower_dot(problem, bound.block_k, split_comparand=split)
             entry = {"bound": bound, "problem": problem, "config": config, "info": info, "ir": str(module), "plan": None}
             if len(self._bound) >= self.MAX_CACHED_SHAPES:  # oldest launch shape goes, with its plan
                 old = self._bound.pop(next(iter(self._bound)))
