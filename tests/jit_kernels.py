@@ -396,3 +396,26 @@ def batched_kloop(a_ptr, b_ptr, c_ptr, K, stride_ab, stride_am, stride_bb, strid
         b = tl.load(b_ptr + batch * stride_bb + (k + rk)[:, None] * stride_bk + rn[None, :])
         acc = tl.dot(a, b, acc)
     tl.store(c_ptr + batch * stride_cb + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty))
+
+
+@triton.jit
+def block_pointer_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stride_cm,
+                        BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Operands through block pointers advanced by the loop, with boundary checks on both axes, as the
+    reference's attention kernel addresses Q, K and V (tl.make_block_ptr / tl.advance)."""
+    pid_m = tl.program_id(0)
+    pid_n = tl.program_id(1)
+    a_blk = tl.make_block_ptr(base=a_ptr, shape=(M, K), strides=(stride_am, 1), offsets=(pid_m * BLOCK_M, 0),
+                              block_shape=(BLOCK_M, BLOCK_K), order=(1, 0))
+    b_blk = tl.make_block_ptr(base=b_ptr, shape=(K, N), strides=(stride_bk, 1), offsets=(0, pid_n * BLOCK_N),
+                              block_shape=(BLOCK_K, BLOCK_N), order=(1, 0))
+    c_blk = tl.make_block_ptr(base=c_ptr, shape=(M, N), strides=(stride_cm, 1),
+                              offsets=(pid_m * BLOCK_M, pid_n * BLOCK_N), block_shape=(BLOCK_M, BLOCK_N), order=(1, 0))
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = tl.load(a_blk, boundary_check=(0, 1), padding_option="zero")
+        b = tl.load(b_blk, boundary_check=(0, 1), padding_option="zero")
+        acc = tl.dot(a, b, acc)
+        a_blk = tl.advance(a_blk, (0, BLOCK_K))
+        b_blk = tl.advance(b_blk, (BLOCK_K, 0))
+    tl.store(c_blk, acc.to(c_ptr.dtype.element_ty), boundary_check=(0, 1))

@@ -298,6 +298,18 @@ def test_transposed_tile_in_registers():
     assert (b.b_layout, b.ldb, b.m, b.n, b.k) == ("col", 512, 300, 200, 500)
 
 
+def test_block_pointer_kernel():
+    """tl.make_block_ptr / tl.advance with boundary checks (how the reference's attention addresses its operands,
+    06-fused-attention.py:180-215): Triton rewrites them to pointer arithmetic on loop-carried i64 offsets and
+    two-sided masks; the `index >= 0` halves are trivially true."""
+    sig = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16", "M": "i32", "N": "i32", "K": "i32", "stride_am": "i32",
+           "stride_bk": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    m = compiler.analyse(jk.block_pointer_kloop, sig, {"BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64})
+    assert (m.k_bound, m.m_bound, m.n_bound, m.row0, m.col0) == ("K", "M", "N", "128*pid_x", "64*pid_y")
+    b = ttir.bind(m, dict(M=300, N=200, K=500, stride_am=512, stride_bk=256, stride_cm=256), (3, 4))
+    assert (b.m, b.n, b.k, b.k_main) == (300, 200, 500, 448)
+
+
 def test_tensor_descriptor_kernel():
     """tl.make_tensor_descriptor / desc.load / desc.store (the form of the reference's _attn_fwd_tma,
     06-fused-attention.py:94-139): the bounds are the descriptor shapes, the fill is zero."""

@@ -278,6 +278,20 @@ def test_operand_at_an_offset(built_libs, cuda_device):
     torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
 
 
+def test_block_pointer_kloop(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 300, 200, 504
+    a, b = _rand((M, K), torch.bfloat16, cuda_device, 33), _rand((K, N), torch.bfloat16, cuda_device, 34)
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    kernel = triton.jit(jk.block_pointer_kloop.fn)
+    with tbk.activate():
+        kernel[(math.ceil(M / 128), math.ceil(N / 64))](a, b, c, M, N, K, a.stride(0), b.stride(0), c.stride(0),
+                                                         BLOCK_M=128, BLOCK_N=64, BLOCK_K=64)
+    torch.cuda.synchronize()
+    assert torch.equal(c, backend.dot(a, b, check=True))
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk

@@ -833,6 +833,8 @@ def _classify_mask(cond: Optional[Cond], forms: dict, what: str) -> dict:
     if cond is None:
         return out
     for pred, l, r in cond.terms:
+        if pred in ("sge", "uge") and any(sp.expand(l - r - form) == 0 for form in forms.values()):
+            continue  # `index >= 0`, the lower half of a block pointer's boundary check: indices are never negative
         if pred in ("sgt", "ugt"):
             l, r, pred = r, l, "slt"
         if pred not in ("slt", "ult"):
