@@ -419,3 +419,17 @@ def block_pointer_kloop(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stri
         a_blk = tl.advance(a_blk, (0, BLOCK_K))
         b_blk = tl.advance(b_blk, (BLOCK_K, 0))
     tl.store(c_blk, acc.to(c_ptr.dtype.element_ty), boundary_check=(0, 1))
+
+
+@triton.jit
+def single_dot(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stride_cm,
+               BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """No K loop: K fits one tile (masked against K), one tt.dot."""
+    rm = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    rn = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rk = tl.arange(0, BLOCK_K)
+    a = tl.load(a_ptr + rm[:, None] * stride_am + rk[None, :], mask=(rm[:, None] < M) & (rk[None, :] < K), other=0.0)
+    b = tl.load(b_ptr + rk[:, None] * stride_bk + rn[None, :], mask=(rk[:, None] < K) & (rn[None, :] < N), other=0.0)
+    acc = tl.dot(a, b)
+    tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty),
+             mask=(rm[:, None] < M) & (rn[None, :] < N))

@@ -310,6 +310,17 @@ def test_block_pointer_kernel():
     assert (b.m, b.n, b.k, b.k_main) == (300, 200, 500, 448)
 
 
+def test_single_dot_without_a_loop():
+    sig = {"a_ptr": "*fp8e5", "b_ptr": "*fp8e5", "c_ptr": "*fp16", "M": "i32", "N": "i32", "K": "i32", "stride_am": "i32",
+           "stride_bk": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    m = compiler.analyse(jk.single_dot, sig, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_K": 128})
+    assert (m.ab_dtype, m.out_dtype, m.loop_lo, m.loop_hi, m.loop_step, m.k_bound) == ("f8e5m2", "f16", "0", "128", 128, "K")
+    b = ttir.bind(m, dict(M=100, N=70, K=96, stride_am=96, stride_bk=80, stride_cm=80), (2, 2))
+    assert (b.m, b.n, b.k, b.k_main) == (100, 70, 96, 0)
+    with pytest.raises(ttir.NotCanonical, match="covers 128 of K=200"):
+        ttir.bind(m, dict(M=100, N=70, K=200, stride_am=208, stride_bk=80, stride_cm=80), (2, 2))
+
+
 def test_tensor_descriptor_kernel():
     """tl.make_tensor_descriptor / desc.load / desc.store (the form of the reference's _attn_fwd_tma,
     06-fused-attention.py:94-139): the bounds are the descriptor shapes, the fill is zero."""

@@ -292,6 +292,21 @@ def test_block_pointer_kloop(built_libs, cuda_device):
     assert torch.equal(c, backend.dot(a, b, check=True))
 
 
+def test_single_dot_fp8_e5m2(built_libs, cuda_device):
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 100, 80, 96
+    a, b = _rand((M, K), torch.float8_e5m2, cuda_device, 35), _rand((K, N), torch.float8_e5m2, cuda_device, 36)
+    c = torch.full((M, N), float("nan"), dtype=torch.float16, device=cuda_device)
+    kernel = triton.jit(jk.single_dot.fn)
+    with tbk.activate():
+        kernel[(2, 2)](a, b, c, M, N, K, a.stride(0), b.stride(0), c.stride(0), BLOCK_M=64, BLOCK_N=64, BLOCK_K=128)
+    torch.cuda.synchronize()
+    ref = a.float() @ b.float()
+    torch.testing.assert_close(c.float(), ref, rtol=3e-2, atol=3e-2 * ref.abs().max().item())
+    assert torch.equal(c, backend.dot(a, b, out_dtype=torch.float16, check=True))
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk

@@ -910,6 +910,12 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
     c_ptr, value, c_mask = ev.stores[0]
     vecs: list = []
     value, out_casts, alpha = _peel(value, vecs)
+    single = value.kind == "dot" and value.data["c"].kind == "const"
+    if single:
+        # One tt.dot outside any loop: a K loop of exactly one iteration over the whole K extent of the tiles.
+        k_extent = value.data["a"].shape[1] if len(value.data["a"].shape) == 2 else 0
+        value = Flt("loop_dot", value.shape, {"a": value.data["a"], "b": value.data["b"], "init": value.data["c"],
+                                              "lo": sp.Integer(0), "hi": sp.Integer(k_extent), "step": sp.Integer(k_extent)})
     if value.kind != "loop_dot":
         raise NotCanonical("the stored value is not the result of the K loop")
     value = _fuse_split_loops(value)
@@ -948,6 +954,8 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
     if sc_iv != 0 or 0 in (sa_r, sa_k, sb_k, sb_c, sc_r, sc_c):
         raise NotCanonical("an operand has a zero stride or C moves with the loop")
     kpi_a, kpi_b = sp.cancel(sa_iv / sa_k), sp.cancel(sb_iv / sb_k)
+    if single and kpi_a == 0 and kpi_b == 0:
+        kpi_a = kpi_b = sp.Integer(1)  # no induction variable to advance along
     if not (kpi_a.is_Integer and kpi_a == kpi_b and int(kpi_a) > 0):
         raise NotCanonical("A and B do not advance along K by the same whole number of elements per iteration")
     kpi = int(kpi_a)
@@ -971,7 +979,7 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
         raise NotCanonical("C is not stored at the rows of A and the columns of B")
     batched = any(e != 0 for e in (a_batch, b_batch, c_batch))
 
-    kk = kpi * KIV
+    kk = kpi * KIV if not (single and sa_iv == 0) else sp.Integer(0)
     a_m = _classify_mask(a.data["mask"], {"k": X1 + kk, "m": row0 + X0}, "A mask")
     b_m = _classify_mask(b.data["mask"], {"k": X0 + kk, "n": col0 + X1}, "B mask")
     c_m = _classify_mask(c_mask, {"m": row0 + X0, "n": col0 + X1}, "C mask")
