@@ -215,6 +215,19 @@ def test_transposed_operands_bind_as_column_major():
                           K_MAIN=128), (2, 3))
 
 
+def test_column_major_output_exchanges_the_operands():
+    sig, cx = split_sig("f16", "f16", ones=("stride_ak", "stride_bn", "stride_cm"))
+    m = compiler.analyse(jk.split_kloop, sig, cx)
+    b = ttir.bind(m, dict(M=256, N=384, K=200, stride_am=208, stride_bk=384, stride_cn=256, K_MAIN=128), (2, 3))
+    # C^T [384, 256] = B^T [384, 200] (column-major view of the row-major B) @ A^T [200, 256]
+    assert b.swapped and (b.m, b.n, b.k) == (384, 256, 200)
+    assert (b.a_layout, b.lda, b.b_layout, b.ldb, b.ldc) == ("col", 384, "col", 208, 256)
+    with pytest.raises(ttir.NotCanonical, match="no unit stride"):
+        sig2, cx2 = split_sig("f16", "f16", ones=("stride_ak", "stride_bn"))
+        ttir.bind(compiler.analyse(jk.split_kloop, sig2, cx2),
+                  dict(M=256, N=384, K=200, stride_am=208, stride_bk=384, stride_cm=2, stride_cn=512, K_MAIN=128), (2, 3))
+
+
 def test_grouped_masked_kloop():
     """Block-counting loop, pointers carried by the loop, a swizzled 1-D grid, three-way masks, a scalar scale."""
     m = compiler.analyse(jk.grouped_masked_kloop, *grouped_sig())

@@ -307,6 +307,21 @@ def test_single_dot_fp8_e5m2(built_libs, cuda_device):
     assert torch.equal(c, backend.dot(a, b, out_dtype=torch.float16, check=True))
 
 
+def test_column_major_output(built_libs, cuda_device):
+    from triton_ext_b200 import triton_backend as tbk
+
+    M, N, K = 256, 384, 200
+    a, b = _rand((M, K), torch.float16, cuda_device, 37), _rand((K, N), torch.float16, cuda_device, 38)
+    c = torch.full((N, M), float("nan"), dtype=torch.float16, device=cuda_device).t()   # [M, N] view, column-major
+    kernel = triton.jit(jk.split_kloop.fn)
+    with tbk.activate():
+        kernel[(M // 128, N // 128)](a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+                                     c.stride(0), c.stride(1), 128, BLOCK_M=128, BLOCK_N=128, BLOCK_K=128)
+    torch.cuda.synchronize()
+    ref = a.float() @ b.float()
+    torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk

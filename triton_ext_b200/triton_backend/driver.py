@@ -68,7 +68,8 @@ class B200DotLauncher:
                 bound.m, bound.n, bound.k, getattr(torch, _TORCH_DTYPES[match.ab_dtype]),
                 getattr(torch, _TORCH_DTYPES[match.out_dtype]), a_layout=layouts[bound.a_layout],
                 b_layout=layouts[bound.b_layout], lda=bound.lda, ldb=bound.ldb, ldc=bound.ldc, alpha=bound.alpha,
-                row_scale=match.row_scale_arg is not None, col_scale=match.col_scale_arg is not None)
+                row_scale=(match.col_scale_arg if bound.swapped else match.row_scale_arg) is not None,
+                col_scale=(match.row_scale_arg if bound.swapped else match.col_scale_arg) is not None)
             # The library's K blocks are 128 bytes of K wide; a source block may be narrower. Whole source blocks
             # past the last whole library block belong to the library's masked remainder block.
             phys = 128 // {"f8e4m3": 1, "f8e5m2": 1}.get(match.ab_dtype, 2)
@@ -111,6 +112,8 @@ class B200DotLauncher:
         if enter_hook is not None:
             enter_hook(launch_metadata)
         ab_size, c_size = a.element_size(), c.element_size()
+        if entry["bound"].swapped:  # column-major C: the library's A is the kernel's B (offsets were exchanged by bind)
+            a, b, scales = b, a, scales[::-1]
         for off_a, off_b, off_c in entry["bound"].batches or [(0, 0, 0)]:  # one library launch per matrix product
             backend._check(plan._lib.tx_dot_run(plan._h, a.data_ptr() + off_a * ab_size, b.data_ptr() + off_b * ab_size,
                                                 c.data_ptr() + off_c * c_size, scales[0], scales[1],

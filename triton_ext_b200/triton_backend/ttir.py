@@ -1056,6 +1056,7 @@ class BoundDot:
     block_k: int
     k_main: int     # K elements the unmasked iterations cover
     batches: Optional[list] = None  # batched GEMM: one (A, B, C) element-offset triple per matrix product
+    swapped: bool = False           # the library computes C^T = B^T A^T: its A is the kernel's B and vice versa
 
 
 def _value(expr: Optional[str], scalars: dict) -> Optional[int]:
@@ -1121,8 +1122,9 @@ def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional
     a_r, a_k = _value(match.a_row_stride, sv), _value(match.a_k_stride, sv)
     b_k, b_c = _value(match.b_k_stride, sv), _value(match.b_col_stride, sv)
     c_r, c_c = _value(match.c_row_stride, sv), _value(match.c_col_stride, sv)
-    if c_c != 1:
-        raise NotCanonical(f"C must be row-major (column stride {c_c})")
+    transposed_out = c_c != 1
+    if transposed_out and c_r != 1:
+        raise NotCanonical(f"C has no unit stride ({c_r}, {c_c})")
     if a_k == 1:
         a_layout, lda = "row", a_r
     elif a_r == 1:
@@ -1199,8 +1201,17 @@ def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional
         except ValueError:
             alpha = float((float_args or {})[match.alpha])
     for name, ld, need in (("A", lda, k if a_layout == "row" else m), ("B", ldb, n if b_layout == "row" else k),
-                           ("C", c_r, n)):
+                           ("C", c_r, n if not transposed_out else 0)):
         if ld < need:
             raise NotCanonical(f"{name}: leading dimension {ld} is smaller than its extent {need}")
+    if transposed_out:
+        # A column-major C is the row-major C^T = B^T A^T: the library runs with the operands exchanged. B^T[n, k]
+        # sits at b + n * b_c + k * b_k (row-major when b_k == 1), A^T[k, m] at a + k * a_k + m * a_r.
+        if c_c < m:
+            raise NotCanonical(f"C: leading dimension {c_c} is smaller than its extent {m}")
+        return BoundDot(m=n, n=m, k=k, a_layout="row" if b_layout == "col" else "col",
+                        b_layout="row" if a_layout == "col" else "col", lda=ldb, ldb=lda, ldc=c_c, alpha=alpha,
+                        block_k=match.block_k, k_main=k_main, swapped=True,
+                        batches=[(ob, oa, oc) for oa, ob, oc in batches] if batches else None)
     return BoundDot(m=m, n=n, k=k, a_layout=a_layout, b_layout=b_layout, lda=lda, ldb=ldb, ldc=c_r,
                     alpha=alpha, block_k=match.block_k, k_main=k_main, batches=batches)
