@@ -433,3 +433,17 @@ def single_dot(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_bk, stride_cm,
     acc = tl.dot(a, b)
     tl.store(c_ptr + rm[:, None] * stride_cm + rn[None, :], acc.to(c_ptr.dtype.element_ty),
              mask=(rm[:, None] < M) & (rn[None, :] < N))
+
+
+@triton.jit
+def host_descriptor_kloop(a_desc, b_desc, c_desc, K, BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr):
+    """Operands and result as tensor descriptors built on the host and passed as arguments, the form of the
+    reference's `_attn_fwd_tma`."""
+    row = tl.program_id(0) * BLOCK_M
+    col = tl.program_id(1) * BLOCK_N
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, K, BLOCK_K):
+        a = a_desc.load([row, k])
+        b = b_desc.load([k, col])
+        acc = tl.dot(a, b, acc)
+    c_desc.store([row, col], acc.to(c_desc.dtype))

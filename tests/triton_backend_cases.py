@@ -741,6 +741,40 @@ def test_narrow_source_blocks_past_the_last_library_block():
     assert len(entry["bound"].batches) == 2
 
 
+def test_host_tensor_descriptors_through_a_jit_launch():
+    """Descriptors built on the host and passed as arguments (the form of the reference's `_attn_fwd_tma`,
+    06-fused-attention.py:275-329): shapes and strides are read from the descriptor objects at launch, and the three
+    descriptors must agree on M, N and K."""
+    from triton.runtime.driver import driver as config
+    from triton.tools.tensor_descriptor import TensorDescriptor
+
+    sig = {"a_desc": "tensordesc<bf16[128,64]>", "b_desc": "tensordesc<bf16[64,128]>", "c_desc": "tensordesc<bf16[128,128]>",
+           "K": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    m = compiler.analyse(jk.host_descriptor_kloop, sig, {"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64})
+    assert (m.a_arg, m.k_bound, m.m_bound, m.n_bound) == ("a_desc", "a_desc__shape1", "c_desc__shape0", "c_desc__shape1")
+    assert [e[0] for e in m.equal_at_launch] == ["K", "M", "N"]
+
+    M, N, K = 300, 200, 504
+    a = torch.zeros(M, K, dtype=torch.bfloat16)
+    b = torch.zeros(K, N, dtype=torch.bfloat16)
+    c = torch.zeros(M, N, dtype=torch.bfloat16)
+    desc = lambda t, blk: TensorDescriptor(t, list(t.shape), list(t.stride()), blk)
+    kernel = triton.jit(jk.host_descriptor_kloop.fn)
+    tbk.install()
+    previous = config._active
+    config.set_active(DryDriver())
+    try:
+        DryLauncher.calls.clear()
+        kernel[(3, 2)](desc(a, [128, 64]), desc(b, [64, 128]), desc(c, [128, 128]), K, BLOCK_M=128, BLOCK_N=128, BLOCK_K=64)
+        (entry,) = DryLauncher.calls
+        assert (entry["bound"].m, entry["bound"].n, entry["bound"].k, entry["bound"].lda) == (M, N, K, K)
+        with pytest.raises(ttir.NotCanonical, match="disagree on K"):
+            kernel[(3, 2)](desc(a, [128, 64]), desc(torch.zeros(K + 8, N, dtype=torch.bfloat16), [64, 128]),
+                           desc(c, [128, 128]), K, BLOCK_M=128, BLOCK_N=128, BLOCK_K=64)
+    finally:
+        config._active = previous
+
+
 def test_jit_keeps_one_cache_per_driver():
     """triton_backend.jit: the same kernel object under two drivers in turn, each with its own compile cache."""
     from triton.runtime.driver import driver as config

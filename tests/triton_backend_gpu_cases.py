@@ -322,6 +322,21 @@ def test_column_major_output(built_libs, cuda_device):
     torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
 
 
+def test_host_descriptor_kloop(built_libs, cuda_device):
+    from triton.tools.tensor_descriptor import TensorDescriptor
+    from triton_ext_b200 import backend, triton_backend as tbk
+
+    M, N, K = 300, 200, 504
+    a, b = _rand((M, K), torch.bfloat16, cuda_device, 39), _rand((K, N), torch.bfloat16, cuda_device, 40)
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    desc = lambda t, blk: TensorDescriptor(t, list(t.shape), list(t.stride()), blk)
+    kernel = triton.jit(jk.host_descriptor_kloop.fn)
+    with tbk.activate():
+        kernel[(3, 2)](desc(a, [128, 64]), desc(b, [64, 128]), desc(c, [128, 128]), K, BLOCK_M=128, BLOCK_N=128, BLOCK_K=64)
+    torch.cuda.synchronize()
+    assert torch.equal(c, backend.dot(a, b, check=True))
+
+
 def test_launch_inside_a_cuda_graph(built_libs, cuda_device):
     """After one eager launch (compile, plan) the same launch is capturable: nothing allocates or synchronises."""
     from triton_ext_b200 import backend, triton_backend as tbk

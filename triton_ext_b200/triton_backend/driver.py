@@ -41,6 +41,21 @@ class B200DotUtils:
         return match, match, 0, 0, 1024
 
 
+def _integer_argument(values: dict, name: str) -> int:
+    """An integer kernel argument, or a field of a host tensor descriptor (<arg>__shape<d>, <arg>__stride<d>)."""
+    if name in values:
+        return int(values[name])
+    arg, _, field = name.rpartition("__")
+    desc = values[arg]
+    kind, d = field.rstrip("0123456789"), int(field[len(field.rstrip("0123456789")):])
+    return int((desc.shape if kind == "shape" else desc.strides)[d])
+
+
+def _tensor_of(value: Any) -> Any:
+    """The tensor behind a kernel argument: the argument itself, or the base of a host tensor descriptor."""
+    return value.base if hasattr(value, "base") and hasattr(value, "block_shape") else value
+
+
 class B200DotLauncher:
     """Called as launcher(gridX, gridY, gridZ, stream, function, metadata..., hooks..., *kernel args)."""
 
@@ -57,7 +72,7 @@ class B200DotLauncher:
 
         from .. import backend, plugin
 
-        scalars = {n: int(values[n]) for n in match.int_args}
+        scalars = {n: _integer_argument(values, n) for n in match.int_args}
         alpha_arg = values.get(match.alpha) if match.alpha in values else None
         key = (tuple(sorted(scalars.items())), tuple(grid), alpha_arg, device)
         entry = self._bound.get(key)
@@ -93,7 +108,7 @@ class B200DotLauncher:
 
         match: _ttir.DotKernelMatch = function
         values = dict(zip(self.arg_names, args))
-        a, b, c = values[match.a_arg], values[match.b_arg], values[match.c_arg]
+        a, b, c = (_tensor_of(values[n]) for n in (match.a_arg, match.b_arg, match.c_arg))
         for t, name, dt in ((a, match.a_arg, match.ab_dtype), (b, match.b_arg, match.ab_dtype), (c, match.c_arg, match.out_dtype)):
             if not hasattr(t, "data_ptr") or not t.is_cuda:
                 raise TypeError(f"{name} must be a CUDA tensor; there is no CPU path")

@@ -136,7 +136,7 @@ def _expand_results(lhs: str) -> list:
     return out
 
 
-_FUNC_ARG = re.compile(r"(%[\w.$-]+): (![\w.]+<[^<>]*>|[\w]+)(?: \{[^{}]*\})?(?: loc\(\"([^\"]+)\"\()?")
+_FUNC_ARG = re.compile(r"(%[\w.$-]+): (![\w.]+<(?:[^<>]|<[^<>]*>)*>|[\w]+)(?: \{[^{}]*\})?(?: loc\(\"([^\"]+)\"\()?")
 
 
 def parse_module(text: str, arg_names: Optional[list] = None) -> tuple:
@@ -336,9 +336,30 @@ class _Evaluator:
         self.tile_loop: Optional[dict] = None
         self.arg_symbols: dict = {}
         self.env: dict = {}
-        for ssa, src, ty in args:
+        i = 0
+        while i < len(args):
+            ssa, src, ty = args[i]
+            i += 1
             if ty.startswith("!tt.ptr<"):
                 self.env[ssa] = Ptr(src, ty[len("!tt.ptr<"):-1], (), sp.Integer(0))
+            elif ty.startswith("!tt.tensordesc<"):
+                # A tensor descriptor built on the host: the front end passes it as the descriptor followed by its
+                # shape (i32 each) and its strides (i64 each). They become the integer arguments <name>__shape<d>,
+                # <name>__stride<d>, which the launcher reads from the descriptor object.
+                block, elem = parse_type(ty[len("!tt.tensordesc<"):-1])
+                rank = len(block)
+                if rank != 2 or i + 2 * rank > len(args):
+                    self.env[ssa] = _Opaque(f"tensor descriptor {src} of rank {rank}")
+                    continue
+                fields = []
+                for d, (fs, _, fty) in enumerate(args[i:i + 2 * rank]):
+                    name = f"{src}__{'shape' if d < rank else 'stride'}{d % rank}"
+                    sym = sp.Symbol(name, integer=True)
+                    self.arg_symbols[name] = sym
+                    self.env[fs] = Int((), sym)
+                    fields.append(sym)
+                i += 2 * rank
+                self.env[ssa] = Desc(Ptr(src, elem, (), sp.Integer(0)), tuple(fields[:rank]), tuple(fields[rank:]), block)
             elif ty in _FLOAT_TYPES:
                 self.env[ssa] = Flt("arg", (), {"name": src})
             elif re.fullmatch(r"i\d+", ty):
@@ -737,6 +758,7 @@ class DotKernelMatch:
     col_scale_arg: Optional[str] = None
     tile_loop: Optional[list] = None     # [lo, hi, step] of a persistent kernel's loop over tiles (tile_iv)
     batch_offsets: Optional[list] = None  # [A, B, C] element offsets of the program's matrices (batched GEMM)
+    equal_at_launch: list = field(default_factory=list)  # [name, expr, expr]: bounds written differently that must agree
 
     def to_json(self) -> str:
         return json.dumps(self.__dict__, sort_keys=True)
@@ -983,11 +1005,15 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
     a_m = _classify_mask(a.data["mask"], {"k": X1 + kk, "m": row0 + X0}, "A mask")
     b_m = _classify_mask(b.data["mask"], {"k": X0 + kk, "n": col0 + X1}, "B mask")
     c_m = _classify_mask(c_mask, {"m": row0 + X0, "n": col0 + X1}, "C mask")
-    if ("k" in a_m) != ("k" in b_m) or ("k" in a_m and sp.expand(a_m["k"] - b_m["k"]) != 0):
+    if ("k" in a_m) != ("k" in b_m):
         raise NotCanonical("A and B are not masked by the same K bound")
-    for key, x, y in (("m", a_m, c_m), ("n", b_m, c_m)):
-        if key in x and key in y and sp.expand(x[key] - y[key]) != 0:
-            raise NotCanonical("loads and store disagree on the matrix bounds")
+    # Bounds that are different expressions (the shapes of two host descriptors, say) must agree at every launch.
+    equal_at_launch = []
+    for what, x, y in (("K", a_m.get("k"), b_m.get("k")), ("M", a_m.get("m"), c_m.get("m")), ("N", b_m.get("n"), c_m.get("n"))):
+        if x is not None and y is not None and sp.expand(x - y) != 0:
+            if not (x.free_symbols and y.free_symbols):
+                raise NotCanonical(f"loads and store disagree on the {what} bound")
+            equal_at_launch.append([what, str(x), str(y)])
     bounds = {"m": c_m.get("m", a_m.get("m")), "n": c_m.get("n", b_m.get("n"))}
     row_scale = col_scale = None
     for vec in vecs:
@@ -1035,7 +1061,8 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
         split_pred=split_pred, split_comparand=split_cmp, alpha=alpha,
         int_args=sorted(ev.arg_symbols), row_scale_arg=row_scale, col_scale_arg=col_scale,
         tile_loop=[str(sp.expand(ev.tile_loop[k])) for k in ("lo", "hi", "step")] if ev.tile_loop else None,
-        batch_offsets=[str(a_batch), str(b_batch), str(c_batch)] if batched else None)
+        batch_offsets=[str(a_batch), str(b_batch), str(c_batch)] if batched else None,
+        equal_at_launch=equal_at_launch)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -1138,6 +1165,9 @@ def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional
     else:
         raise NotCanonical(f"B has no unit stride ({b_k}, {b_c})")
 
+    for what, x, y in match.equal_at_launch:
+        if _value(x, sv) != _value(y, sv):
+            raise NotCanonical(f"the operands disagree on {what}: {x} = {_value(x, sv)}, {y} = {_value(y, sv)}")
     hi = _value(match.loop_hi, sv)
     n_iter = max(0, -(-hi // match.loop_step))
     covered = n_iter * match.block_k
