@@ -42,10 +42,14 @@ def install() -> None:
 @contextlib.contextmanager
 def activate():
     """Make the b200dot driver Triton's active driver inside the block; needs an sm_100 device."""
+    import os
+
     from triton.runtime.driver import driver as config
 
     from .driver import B200DotDriver
 
+    if os.environ.get("TRITON_INTERPRET") == "1":
+        raise RuntimeError("TRITON_INTERPRET=1: kernels of this process run in Triton's interpreter, which no backend sees")
     install()
     previous = config._active
     config.set_active(B200DotDriver())
