@@ -795,3 +795,30 @@ def test_jit_keeps_one_cache_per_driver():
         config._active = previous
     assert set(kernel._caches_by_driver) == {"DryDriver", "OtherDryDriver"}
     assert all(len(v[0][0]) == 1 for v in kernel._caches_by_driver.values())  # one compiled kernel per driver, device 0
+
+
+def test_tile_origins_agree_with_the_kernels_own_arithmetic():
+    """The symbolic tile origin, evaluated numerically over a whole grid, against a direct Python transcription of
+    grouped_masked_kloop's program-id arithmetic, over random shapes (hypothesis)."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    m = compiler.analyse(jk.grouped_masked_kloop, *grouped_sig())
+
+    @settings(max_examples=60, deadline=None)
+    @given(M=st.integers(1, 3000), N=st.integers(1, 3000), extra=st.integers(0, 3))
+    def check(M, N, extra):
+        tiles_m, tiles_n = -(-M // 64), -(-N // 128)
+        grid = tiles_m * tiles_n
+        rows, cols, _ = ttir._tile_origins(m, dict(M=M, N=N, K=64, stride_am=64, stride_bn=64, stride_cm=N), (grid, 1, 1))
+        for pid in {0, grid - 1, grid // 2, min(grid - 1, extra)}:
+            per_group = 4 * tiles_n
+            first_m = (pid // per_group) * 4
+            rows_here = min(tiles_m - first_m, 4)
+            pid_m = first_m + (pid % per_group) % rows_here
+            pid_n = (pid % per_group) // rows_here
+            assert (rows[pid], cols[pid]) == (pid_m * 64, pid_n * 128), (M, N, pid)
+        b = ttir.bind(m, dict(M=M, N=N, K=64, stride_am=64, stride_bn=64, stride_cm=N), (grid,), {"alpha": 1.0})
+        assert (b.m, b.n) == (M, N)
+
+    check()
