@@ -822,3 +822,27 @@ def test_tile_origins_agree_with_the_kernels_own_arithmetic():
         assert (b.m, b.n) == (M, N)
 
     check()
+
+
+def test_loop_split_text_preserves_meaning_on_random_loops():
+    """Random lower bound, upper bound, step, comparand, predicate and operand order (hypothesis): the bisected IR
+    computes what the original computes (intent mode; the as-written mode is known not to, for sgt / sle and for
+    distances that are already multiples of the step)."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    from triton_ext_b200.triton_backend import loop_split_ir
+
+    @settings(max_examples=150, deadline=None)
+    @given(lo=st.integers(-6, 12), n=st.integers(-4, 40), c=st.integers(-10, 45), step=st.integers(1, 9),
+           pred=st.sampled_from(["slt", "sle", "sgt", "sge"]), swap=st.booleans())
+    def check(lo, n, c, step, pred, swap):
+        text = (LIT_CASE.replace("STEP", str(step)).replace("PRED", pred)
+                .replace("LHS", "%c" if swap else "%i").replace("RHS", "%i" if swap else "%c")
+                .replace("%c0 = arith.constant 0 : i32", f"%c0 = arith.constant {lo} : i32\n    %zero = arith.constant 0 : i32")
+                .replace("iter_args(%acc = %c0)", "iter_args(%acc = %zero)"))
+        new, k = loop_split_ir.split_loops(text)
+        assert k == 1
+        assert run_scalar_ir(new, n, c) == run_scalar_ir(text, n, c)
+
+    check()
