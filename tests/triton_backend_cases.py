@@ -142,7 +142,8 @@ def run_scalar_ir(text: str, n: int, c: int) -> int:
     _, _, ops = ttir.parse_module(text)
     cmp = {"slt": lambda a, b: a < b, "sle": lambda a, b: a <= b, "sgt": lambda a, b: a > b, "sge": lambda a, b: a >= b}
     arith = {"arith.addi": lambda a, b: a + b, "arith.subi": lambda a, b: a - b, "arith.muli": lambda a, b: a * b,
-             "arith.maxsi": max, "arith.minsi": min, "arith.ceildivsi": lambda a, b: -((-a) // b)}
+             "arith.maxsi": max, "arith.minsi": min, "arith.ceildivsi": lambda a, b: -((-a) // b),
+             "arith.remui": lambda a, b: a % b}
 
     def run(block, env):
         for op in block:
@@ -846,3 +847,31 @@ def test_loop_split_text_preserves_meaning_on_random_loops():
         assert run_scalar_ir(new, n, c) == run_scalar_ir(text, n, c)
 
     check()
+
+
+def test_as_written_mode_reproduces_the_reference_and_its_off_by_one():
+    """The as-written rewrite follows the reference's arithmetic to the letter, including where that changes what the
+    loop computes: `iv > c` is split at c (the iteration iv == c lands in the loop whose compare reads true), a
+    comparand beyond the upper bound makes the first loop run past it, and a distance that is already a multiple of
+    the step is pushed one step further. The intent mode is exact on both."""
+    from triton_ext_b200.triton_backend import loop_split_ir
+
+    def case(pred, step):
+        return (LIT_CASE.replace("STEP", str(step)).replace("PRED", pred).replace("LHS", "%i").replace("RHS", "%c"))
+
+    sgt = case("sgt", 1)
+    written, _ = loop_split_ir.split_loops(sgt, mode="as-written")
+    exact, _ = loop_split_ir.split_loops(sgt)
+    assert run_scalar_ir(exact, 10, 5) == run_scalar_ir(sgt, 10, 5)
+    assert run_scalar_ir(written, 10, 5) != run_scalar_ir(sgt, 10, 5)
+    assert run_scalar_ir(written, 10, 20) != run_scalar_ir(sgt, 10, 20)      # no clamping: the first loop runs past hi
+    assert run_scalar_ir(exact, 10, 20) == run_scalar_ir(sgt, 10, 20)
+    slt = case("slt", 1)
+    written, _ = loop_split_ir.split_loops(slt, mode="as-written")
+    assert run_scalar_ir(written, 10, 5) == run_scalar_ir(slt, 10, 5)        # the case the pass was written for
+    step10 = case("slt", 10)
+    written, _ = loop_split_ir.split_loops(step10, mode="as-written")
+    exact, _ = loop_split_ir.split_loops(step10)
+    assert run_scalar_ir(exact, 100, 20) == run_scalar_ir(step10, 100, 20)
+    assert run_scalar_ir(written, 100, 20) != run_scalar_ir(step10, 100, 20)   # mid 20 -> 30: iteration 20 reads true
+    assert run_scalar_ir(written, 100, 25) == run_scalar_ir(step10, 100, 25)   # mid 25 -> 30: correct
