@@ -12,6 +12,13 @@
  * predicate slt / sle / sgt / sge or the unsigned forms on the induction variable; the other operand defined
  * outside the loop; the first such compare in the body decides the split. Loops nested in a loop that is not
  * split are looked at too.
+ *
+ * Beyond the reference (its LoopSplit.cpp:105 leaves "mask logic" as a TODO), in TXLS_INTENT mode only: a loop with
+ * no such scalar compare but with tensor compares of the form
+ *     arith.cmpi slt|sle, <expand_dims/broadcast of (tt.splat iv + tt.make_range [0, E))>, <... of tt.splat bound>
+ * (the K masks of a tt.dot operand: `k + arange(BLOCK_K) < K`), bound defined outside the loop, is split where those
+ * masks stop being all-true (iv + E <= bound): in the first copy every such compare over the same range and bound
+ * becomes `arith.constant dense<true>`, which a canonicaliser folds out of the loads; the second copy keeps them.
  */
 #ifndef TRITON_EXT_LOOP_SPLIT_TEXT_H
 #define TRITON_EXT_LOOP_SPLIT_TEXT_H

@@ -186,3 +186,41 @@ def test_loop_split_text_entry_point(built_libs):
                     loop.replace("PRED", "slt").replace("CMP", "%mid").replace("step %c4", "step %step")):
         same, k = run(variant)
         assert k == 0 and same == variant
+
+
+def test_loop_split_text_peels_masked_remainder(built_libs):
+    """The mask form through the C-ABI: tensor compares of (splat iv + range) with a splat bound."""
+    lib = P.load_plugin(P.plugin_path("loop_split"))
+    lib.tx_loop_split_text.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                       ctypes.POINTER(ctypes.c_int32)]
+    lib.tx_loop_split_free.argtypes = [ctypes.c_void_p]
+    text = ("  %c32 = arith.constant 32 : i32\n"
+            "  %range = tt.make_range {end = 32 : i32, start = 0 : i32} : tensor<32xi32>\n"
+            "  %r = scf.for %k = %c0 to %K step %c32 iter_args(%acc = %z) -> (tensor<16x16xf32>)  : i32 {\n"
+            "    %s = tt.splat %k : i32 -> tensor<32xi32>\n"
+            "    %idx = arith.addi %s, %range : tensor<32xi32>\n"
+            "    %row = tt.expand_dims %idx {axis = 0 : i32} : tensor<32xi32> -> tensor<1x32xi32>\n"
+            "    %kb = tt.splat %K : i32 -> tensor<1x32xi32>\n"
+            "    %m = arith.cmpi slt, %row, %kb : tensor<1x32xi32>\n"
+            "    %mb = tt.broadcast %m : tensor<1x32xi1> -> tensor<16x32xi1>\n"
+            "    %a = tt.load %p, %mb, %zero : tensor<16x32x!tt.ptr<f16>>\n"
+            "    scf.yield %acc : tensor<16x16xf32>\n"
+            "  }\n")
+
+    def run(t: str, mode: int):
+        o, k = ctypes.c_void_p(), ctypes.c_int32(-1)
+        assert lib.tx_loop_split_text(t.encode(), mode, ctypes.byref(o), ctypes.byref(k)) == 0
+        try:
+            return ctypes.string_at(o).decode(), k.value
+        finally:
+            lib.tx_loop_split_free(o)
+
+    out, k = run(text, 0)
+    assert k == 1 and out.count("scf.for") == 2
+    assert "%ls0_e = arith.constant 31 : i32" in out and "%ls0_b = arith.subi %K, %ls0_e : i32" in out
+    first, second = out.split("scf.for")[1:]
+    assert "%m = arith.constant dense<true> : tensor<1x32xi1>" in first and "arith.cmpi" not in first
+    assert "%m = arith.cmpi slt, %row, %kb : tensor<1x32xi32>" in second
+    assert run(text, 1) == (text, 0)                                             # not in the as-written mode
+    assert run(text.replace("tt.splat %K", "tt.splat %k"), 0)[1] == 0            # bound is the induction variable
+    assert run(text.replace("start = 0", "start = 1"), 0)[1] == 0                # range does not start at 0

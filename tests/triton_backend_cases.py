@@ -98,6 +98,34 @@ def test_loop_split_on_the_kernels_own_ir():
     assert loop_split_ir.split_loops(plain)[1] == 0
 
 
+def test_loop_split_peels_the_remainder_of_an_always_masked_k_loop():
+    """What the reference leaves open (LoopSplit.cpp:105, "TODO: add support for mask logic"): a K loop whose loads
+    are masked by `k + arange(BLOCK_K) < K` in every iteration has no scalar compare to split on, but its masks are
+    all-true while k + BLOCK_K <= K. The rewrite splits there, the first loop loses its K masks (Triton's canonicaliser
+    folds a constant-true mask away) and keeps the row / column masks, the second is the masked remainder."""
+    from triton_ext_b200.triton_backend import loop_split_ir
+
+    sig = {"a_ptr": "*bf16", "bt_ptr": "*bf16", "c_ptr": "*bf16", "M": "i32", "N": "i32", "K": "i32", "stride_am": "i32",
+           "stride_bn": "i32", "stride_cm": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr", "BLOCK_K": "constexpr"}
+    cx = {"BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64}
+    before = ttir.strip_locations(compiler.lower_to_ttir(jk.nt_kloop, sig, cx))
+    assert before.count("scf.for") == 1 and "scf.if" not in before
+    raw, n = loop_split_ir.split_loops(before)
+    assert n == 1 and raw.count("arith.constant dense<true> : tensor<1x64xi1>") >= 1
+    assert loop_split_ir.split_loops(before, mode="as-written")[1] == 0      # the reference's pass does not split it
+    names: list = []
+    after = ttir.strip_locations(compiler.lower_to_ttir(jk.nt_kloop, sig, cx, split=True, arg_names_out=names))
+    main, rest = after.split("scf.for")[1:]
+    k_mask = lambda body: sum(1 for l in body.split("scf.yield")[0].splitlines() if "arith.cmpi slt" in l and "1x64" in l)
+    assert k_mask(main) == 0 and k_mask(rest) >= 1
+    assert main.count("tt.load") == 2 and rest.split("scf.yield")[0].count("tt.load") == 2
+    m = ttir.match_dot_kernel(after, names)
+    assert m.split_comparand == "Min(64*ceiling(Max(0, K - 63)/64), Max(0, K))" and m.k_bound == "K"
+    for K in list(range(1, 200)) + [500, 512, 4096, 4160]:
+        b = ttir.bind(m, dict(M=300, N=200, K=K, stride_am=4224, stride_bn=4224, stride_cm=256), (3, 4))
+        assert (b.k, b.k_main) == (K, (K // 64) * 64), K
+
+
 LIT_CASE = """
 module {
   tt.func public @lit(%out: !tt.ptr<i32>, %n: i32, %c: i32) {

@@ -171,6 +171,101 @@ std::set<std::string> defined_inside(const std::vector<std::string> &lines, size
   return names;
 }
 
+// `%r = op.name <anything with %operands> : types` -> result, name, operands, text after the name.
+struct OpLine {
+  std::string indent, result, name, rest;
+  std::vector<std::string> operands;
+};
+
+bool parse_op(const std::string &line, OpLine &o) {
+  const size_t first = line.find_first_not_of(" \t");
+  if (first == std::string::npos || line[first] != '%') return false;
+  o.indent = line.substr(0, first);
+  size_t p = first;
+  if (!parse_value(line, p, o.result) || !eat(line, p, " = ")) return false;
+  const size_t sp = line.find(' ', p);
+  o.name = line.substr(p, sp == std::string::npos ? std::string::npos : sp - p);
+  o.rest = sp == std::string::npos ? "" : line.substr(sp + 1);
+  o.operands.clear();
+  for (size_t q = 0; q < o.rest.size();) {
+    std::string v;
+    if (o.rest[q] == '%' && parse_value(o.rest, q, v)) o.operands.push_back(v);
+    else ++q;
+  }
+  return !o.name.empty();
+}
+
+// A tensor compare of the loop body that is all-true while iv + extent <= bound: the K mask of a tt.dot operand,
+//   cmpi slt, expand/broadcast(addi(splat(iv), make_range[0, extent))), expand/broadcast(splat(bound))
+struct MaskCmp {
+  size_t line;
+  std::string indent, result, i1_type;
+};
+
+struct Defs {
+  const std::vector<std::string> *lines;
+  std::map<std::string, size_t> body, global;
+  bool lookup(const std::string &name, OpLine &o) const {
+    auto it = body.find(name);
+    if (it == body.end()) {
+      it = global.find(name);
+      if (it == global.end()) return false;
+    }
+    return parse_op((*lines)[it->second], o);
+  }
+  // Follow shape-only operations back to the value they reshape.
+  bool root(std::string name, OpLine &o) const {
+    for (int hops = 0; hops < 8; ++hops) {
+      if (!lookup(name, o)) return false;
+      if ((o.name == "tt.expand_dims" || o.name == "tt.broadcast") && o.operands.size() == 1) name = o.operands[0];
+      else return true;
+    }
+    return false;
+  }
+};
+
+bool make_range_from_zero(const OpLine &o, long long &extent) {
+  if (o.name != "tt.make_range") return false;
+  const size_t e = o.rest.find("end = "), s = o.rest.find("start = ");
+  if (e == std::string::npos || s == std::string::npos) return false;
+  extent = strtoll(o.rest.c_str() + e + 6, nullptr, 10);
+  return strtoll(o.rest.c_str() + s + 8, nullptr, 10) == 0 && extent > 0;
+}
+
+// Is `line` a K mask in the sense above? On success: the extent of the index range and the bound's SSA name.
+bool match_mask_cmp(const std::string &line, const Defs &defs, const std::string &iv, const std::set<std::string> &inside,
+                    MaskCmp &out, long long &extent, std::string &bound, int &adjust) {
+  OpLine c;
+  if (!parse_op(line, c) || c.name != "arith.cmpi" || c.operands.size() != 2) return false;
+  const size_t comma = c.rest.find(',');
+  const std::string pred = trim(c.rest.substr(0, comma));
+  if (pred == "slt" || pred == "ult") adjust = 0;
+  else if (pred == "sle" || pred == "ule") adjust = 1;
+  else return false;
+  const size_t colon = c.rest.rfind(" : ");
+  if (colon == std::string::npos) return false;
+  std::string ty = trim(c.rest.substr(colon + 3));
+  if (ty.compare(0, 7, "tensor<") != 0) return false;
+  const size_t x = ty.rfind("xi");
+  if (x == std::string::npos) return false;
+  out.i1_type = ty.substr(0, x) + "xi1>";
+  OpLine lhs, rhs, part;
+  if (!defs.root(c.operands[0], lhs) || !defs.root(c.operands[1], rhs)) return false;
+  if (lhs.name != "arith.addi" || lhs.operands.size() != 2 || rhs.name != "tt.splat" || rhs.operands.size() != 1) return false;
+  if (rhs.operands[0] == iv || inside.count(rhs.operands[0])) return false;  // the bound must be loop-invariant
+  bool has_iv = false, has_range = false;
+  for (const std::string &opnd : lhs.operands) {
+    if (!defs.root(opnd, part)) return false;
+    if (part.name == "tt.splat" && part.operands.size() == 1 && part.operands[0] == iv) has_iv = true;
+    else if (make_range_from_zero(part, extent)) has_range = true;
+  }
+  if (!has_iv || !has_range) return false;
+  bound = rhs.operands[0];
+  out.indent = c.indent;
+  out.result = c.result;
+  return true;
+}
+
 // Index of the line that closes the region opened by lines[start], or -1.
 long region_end(const std::vector<std::string> &lines, size_t start) {
   int depth = 0;
@@ -270,7 +365,41 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
         break;
       }
     }
-    if (chosen < 0) {  // not a loop to split; loops nested inside it are still looked at
+    // No scalar compare of the induction variable: look for the K masks of the loads instead (the reference leaves
+    // this open, LoopSplit.cpp:105 "TODO: add support for mask logic"). All masks over the same index range and
+    // bound are all-true while iv + extent <= bound, so the loop splits there and its first half loses them.
+    std::vector<MaskCmp> masks;
+    long long mask_extent = 0;
+    std::string mask_bound;
+    int mask_adjust = 0;
+    if (chosen < 0 && mode == TXLS_INTENT && !h.ity.empty() && step_it != consts.end() && step_it->second > 0) {
+      Defs defs;
+      defs.lines = &lines;
+      for (size_t k = 0; k < lines.size(); ++k) {
+        OpLine o;
+        if (parse_op(lines[k], o)) {
+          defs.global.emplace(o.result, k);
+          if (k >= b0 && k < b1) defs.body.emplace(o.result, k);
+        }
+      }
+      for (size_t bi = b0; bi < b1; ++bi) {
+        MaskCmp mc;
+        long long e = 0;
+        std::string bnd;
+        int adj = 0;
+        if (!match_mask_cmp(lines[bi], defs, h.iv, inside, mc, e, bnd, adj)) continue;
+        if (masks.empty()) {
+          mask_extent = e;
+          mask_bound = bnd;
+          mask_adjust = adj;
+        } else if (e != mask_extent || bnd != mask_bound || adj != mask_adjust) {
+          continue;  // another range or bound: stays a mask in both halves
+        }
+        mc.line = bi;
+        masks.push_back(mc);
+      }
+    }
+    if (chosen < 0 && masks.empty()) {  // not a loop to split; loops nested inside it are still looked at
       out.push_back(lines[i++]);
       continue;
     }
@@ -280,6 +409,13 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
     std::vector<std::string> pre;
     std::string midp;
     bool first_true;
+    if (chosen < 0) {
+      // iv + extent <= bound + adjust  <=>  iv < bound - (extent - 1 - adjust): the threshold of an `slt` compare.
+      pre.push_back(in + tag + "_e = arith.constant " + std::to_string(mask_extent - 1 - mask_adjust) + " : " + ty);
+      pre.push_back(in + tag + "_b = arith.subi " + mask_bound + ", " + tag + "_e : " + ty);
+      comparand = tag + "_b";
+      info = PredInfo{true, 0, false};
+    }
     if (mode == TXLS_AS_WRITTEN) {
       const bool greater = !info.holds_below;
       midp = comparand;
@@ -338,8 +474,13 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
       out.push_back(copy == 0 ? head1 : head2);
       const bool value = (copy == 0) == first_true;
       for (size_t bi = b0; bi < b1; ++bi) {
+        const MaskCmp *mask = nullptr;
+        for (const MaskCmp &mc : masks)
+          if (mc.line == bi) mask = &mc;
         if (static_cast<long>(bi) == chosen)
           out.push_back(cmp.indent + cmp.result + " = arith.constant " + (value ? "true" : "false"));
+        else if (mask && copy == 0)
+          out.push_back(mask->indent + mask->result + " = arith.constant dense<true> : " + mask->i1_type);
         else
           out.push_back(lines[bi]);
       }
