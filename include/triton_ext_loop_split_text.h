@@ -19,6 +19,9 @@
  * (the K masks of a tt.dot operand: `k + arange(BLOCK_K) < K`), bound defined outside the loop, is split where those
  * masks stop being all-true (iv + E <= bound): in the first copy every such compare over the same range and bound
  * becomes `arith.constant dense<true>`, which a canonicaliser folds out of the loads; the second copy keeps them.
+ * The form of loops that count K blocks is recognised too:
+ *     arith.cmpi slt|sle, <... of tt.make_range [0, E)>, <... of tt.splat (bound - iv * c)>,   c a positive constant,
+ * all-true while iv * c + E <= bound.
  */
 #ifndef TRITON_EXT_LOOP_SPLIT_TEXT_H
 #define TRITON_EXT_LOOP_SPLIT_TEXT_H

@@ -261,7 +261,10 @@ def test_grouped_masked_kloop():
     """Block-counting loop, pointers carried by the loop, a swizzled 1-D grid, three-way masks, a scalar scale."""
     m = compiler.analyse(jk.grouped_masked_kloop, *grouped_sig())
     assert (m.loop_step, m.k_per_iv, m.block_k) == (1, 32, 32)
-    assert (m.k_bound, m.m_bound, m.n_bound, m.alpha, m.split_pred) == ("K", "M", "N", "alpha", None)
+    assert (m.k_bound, m.m_bound, m.n_bound, m.alpha) == ("K", "M", "N", "alpha")
+    # LoopSplit peels this loop's masked remainder; without that stage the kernel reads as one unsplit loop
+    assert m.split_pred == "slt" and m.split_is_loop_bound
+    assert compiler.analyse(jk.grouped_masked_kloop, *grouped_sig(), split=False).split_pred is None
     for M, N, K in ((1000, 300, 1111), (64, 128, 32), (65, 129, 33), (4096, 4096, 64)):
         grid = (math.ceil(M / 64) * math.ceil(N / 128),)
         s = dict(M=M, N=N, K=K, stride_am=K, stride_bn=K, stride_cm=N)
@@ -282,6 +285,24 @@ def test_plain_kloop_without_masks():
     assert (m.row0, m.col0) == ("128*pid_y", "64*pid_x")
     b = ttir.bind(m, dict(K=512, stride_am=512, stride_bk=320, stride_cm=320), (5, 3))
     assert (b.m, b.n, b.k, b.k_main) == (384, 320, 512, 512)
+
+
+def test_loop_split_peels_a_block_counting_loop_with_carried_pointers():
+    """The other common form: the loop counts K blocks, the pointers are carried by the loop, the masks compare
+    arange(BLOCK_K) with `K - kb * BLOCK_K`. Split where kb * BLOCK_K + BLOCK_K <= K stops holding; the second loop
+    starts from the pointers the first one leaves behind."""
+    sig, cx = split_sig("f16", "f16", bm=128, bn=64, bk=64)
+    del sig["K_MAIN"]
+    names: list = []
+    after = ttir.strip_locations(compiler.lower_to_ttir(jk.wrapped_kloop, sig, cx, split=True, arg_names_out=names))
+    assert after.count("scf.for") == 2 and "arith.floordivsi" in after or "arith.divsi" in after
+    main, rest = after.split("scf.for")[1:]
+    assert "arith.cmpi" not in main.split("scf.yield")[0] and "arith.cmpi slt" in rest.split("scf.yield")[0]
+    m = ttir.match_dot_kernel(after, names)
+    assert m.split_is_loop_bound and (m.loop_step, m.k_per_iv) == (1, 64)
+    for K in (1, 63, 64, 65, 500, 4160):
+        b = ttir.bind(m, dict(M=300, N=200, K=K, stride_am=4224, stride_bk=200, stride_cm=200), (3 * 4,))
+        assert (b.k, b.k_main) == (K, (K // 64) * 64), K
 
 
 def test_wrapped_indices_need_a_masked_store():

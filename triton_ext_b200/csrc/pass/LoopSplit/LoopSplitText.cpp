@@ -234,7 +234,9 @@ bool make_range_from_zero(const OpLine &o, long long &extent) {
 
 // Is `line` a K mask in the sense above? On success: the extent of the index range and the bound's SSA name.
 bool match_mask_cmp(const std::string &line, const Defs &defs, const std::string &iv, const std::set<std::string> &inside,
-                    MaskCmp &out, long long &extent, std::string &bound, int &adjust) {
+                    const std::map<std::string, long long> &consts, MaskCmp &out, long long &extent, std::string &bound,
+                    int &adjust, long long &iv_scale) {
+  iv_scale = 0;  // 0: the index is iv + range; c > 0: the index is the range alone and the bound is `bound - iv * c`
   OpLine c;
   if (!parse_op(line, c) || c.name != "arith.cmpi" || c.operands.size() != 2) return false;
   const size_t comma = c.rest.find(',');
@@ -251,7 +253,25 @@ bool match_mask_cmp(const std::string &line, const Defs &defs, const std::string
   out.i1_type = ty.substr(0, x) + "xi1>";
   OpLine lhs, rhs, part;
   if (!defs.root(c.operands[0], lhs) || !defs.root(c.operands[1], rhs)) return false;
-  if (lhs.name != "arith.addi" || lhs.operands.size() != 2 || rhs.name != "tt.splat" || rhs.operands.size() != 1) return false;
+  if (rhs.name != "tt.splat" || rhs.operands.size() != 1) return false;
+  if (make_range_from_zero(lhs, extent)) {
+    // Loops that count K blocks: `arange(E) < bound - iv * c`, all-true while iv * c + E <= bound.
+    OpLine left, prod;
+    if (!defs.lookup(rhs.operands[0], left) || left.name != "arith.subi" || left.operands.size() != 2) return false;
+    if (left.operands[0] == iv || inside.count(left.operands[0])) return false;
+    if (!defs.lookup(left.operands[1], prod) || prod.name != "arith.muli" || prod.operands.size() != 2) return false;
+    const std::string &x = prod.operands[0], &y = prod.operands[1];
+    const std::string &scale = x == iv ? y : x;
+    if ((x != iv && y != iv) || scale == iv) return false;
+    auto it = consts.find(scale);
+    if (it == consts.end() || it->second <= 0) return false;
+    iv_scale = it->second;
+    bound = left.operands[0];
+    out.indent = c.indent;
+    out.result = c.result;
+    return true;
+  }
+  if (lhs.name != "arith.addi" || lhs.operands.size() != 2) return false;
   if (rhs.operands[0] == iv || inside.count(rhs.operands[0])) return false;  // the bound must be loop-invariant
   bool has_iv = false, has_range = false;
   for (const std::string &opnd : lhs.operands) {
@@ -369,7 +389,7 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
     // this open, LoopSplit.cpp:105 "TODO: add support for mask logic"). All masks over the same index range and
     // bound are all-true while iv + extent <= bound, so the loop splits there and its first half loses them.
     std::vector<MaskCmp> masks;
-    long long mask_extent = 0;
+    long long mask_extent = 0, mask_scale = 0;
     std::string mask_bound;
     int mask_adjust = 0;
     if (chosen < 0 && mode == TXLS_INTENT && !h.ity.empty() && step_it != consts.end() && step_it->second > 0) {
@@ -387,12 +407,14 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
         long long e = 0;
         std::string bnd;
         int adj = 0;
-        if (!match_mask_cmp(lines[bi], defs, h.iv, inside, mc, e, bnd, adj)) continue;
+        long long scale = 0;
+        if (!match_mask_cmp(lines[bi], defs, h.iv, inside, consts, mc, e, bnd, adj, scale)) continue;
         if (masks.empty()) {
           mask_extent = e;
           mask_bound = bnd;
           mask_adjust = adj;
-        } else if (e != mask_extent || bnd != mask_bound || adj != mask_adjust) {
+          mask_scale = scale;
+        } else if (e != mask_extent || bnd != mask_bound || adj != mask_adjust || scale != mask_scale) {
           continue;  // another range or bound: stays a mask in both halves
         }
         mc.line = bi;
@@ -411,8 +433,18 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
     bool first_true;
     if (chosen < 0) {
       // iv + extent <= bound + adjust  <=>  iv < bound - (extent - 1 - adjust): the threshold of an `slt` compare.
-      pre.push_back(in + tag + "_e = arith.constant " + std::to_string(mask_extent - 1 - mask_adjust) + " : " + ty);
-      pre.push_back(in + tag + "_b = arith.subi " + mask_bound + ", " + tag + "_e : " + ty);
+      if (mask_scale == 0) {
+        pre.push_back(in + tag + "_e = arith.constant " + std::to_string(mask_extent - 1 - mask_adjust) + " : " + ty);
+        pre.push_back(in + tag + "_b = arith.subi " + mask_bound + ", " + tag + "_e : " + ty);
+      } else {
+        // iv * c + extent <= bound + adjust  <=>  iv < floor((bound + adjust - extent) / c) + 1
+        pre.push_back(in + tag + "_e = arith.constant " + std::to_string(mask_extent - mask_adjust) + " : " + ty);
+        pre.push_back(in + tag + "_s = arith.constant " + std::to_string(mask_scale) + " : " + ty);
+        pre.push_back(in + tag + "_o = arith.constant 1 : " + ty);
+        pre.push_back(in + tag + "_g = arith.subi " + mask_bound + ", " + tag + "_e : " + ty);
+        pre.push_back(in + tag + "_f = arith.floordivsi " + tag + "_g, " + tag + "_s : " + ty);
+        pre.push_back(in + tag + "_b = arith.addi " + tag + "_f, " + tag + "_o : " + ty);
+      }
       comparand = tag + "_b";
       info = PredInfo{true, 0, false};
     }

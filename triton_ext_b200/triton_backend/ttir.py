@@ -702,16 +702,27 @@ class _Evaluator:
                 raise NotCanonical("a loop-carried offset does not advance by a loop-invariant amount")
             start = init.expr if isinstance(init, Int) else init.off
             closed[s] = start + trip * delta
+        # What a carried offset holds after the loop: its start plus one advance per iteration. The trip count is
+        # kept as one symbol so that a loop continuing from here can be compared with this one (_fuse_split_loops).
+        trips = sp.Symbol(f"trips_{id(op)}", integer=True, nonnegative=True)
+        trips_value = sp.ceiling(sp.Max(hi.expr - lo.expr, 0) / step.expr)
+        deltas = {}
+        for (s, init), y in zip(holders, yields):
+            if s is not None:
+                deltas[s] = sp.expand((y.expr if isinstance(y, Int) else y.off) - s)
         for idx, ((s, init), y) in enumerate(zip(holders, yields)):
             res = op.results[idx]
             if s is not None:
-                env[res] = _Opaque("the final value of a loop-carried offset")
+                if isinstance(init, Int):
+                    env[res] = Int(init.shape, init.expr + trips * deltas[s])
+                else:
+                    env[res] = Ptr(init.base, init.elem, init.shape, init.off + trips * deltas[s])
                 continue
             if not (isinstance(y, Flt) and y.kind == "dot" and y.data["c"].kind == "acc" and y.data["c"].data["index"] == idx):
                 raise NotCanonical("the loop-carried float is not `acc = tt.dot(a, b, acc)`")
             env[res] = Flt("loop_dot", y.shape, {
                 "a": _subst(y.data["a"], closed), "b": _subst(y.data["b"], closed), "init": init,
-                "lo": lo.expr, "hi": hi.expr, "step": step.expr})
+                "lo": lo.expr, "hi": hi.expr, "step": step.expr, "trips": trips, "trips_value": trips_value})
 
 
 # --------------------------------------------------------------------------------------------------
@@ -759,6 +770,7 @@ class DotKernelMatch:
     tile_loop: Optional[list] = None     # [lo, hi, step] of a persistent kernel's loop over tiles (tile_iv)
     batch_offsets: Optional[list] = None  # [A, B, C] element offsets of the program's matrices (batched GEMM)
     equal_at_launch: list = field(default_factory=list)  # [name, expr, expr]: bounds written differently that must agree
+    split_is_loop_bound: bool = False  # the split point is where a first K loop ends (LoopSplit's output), not a compare
 
     def to_json(self) -> str:
         return json.dumps(self.__dict__, sort_keys=True)
@@ -886,11 +898,14 @@ def _fuse_split_loops(second: Flt) -> Flt:
     if sp.expand(first.data["hi"] - second.data["lo"]) != 0 or sp.expand(first.data["step"] - second.data["step"]) != 0:
         raise NotCanonical("the second K loop does not continue where the first stops")
     mid = sp.expand(first.data["hi"])
+    # Offsets the second loop inherits hold `start + trips * advance`. The first loop runs (mid - lo) / step times when
+    # mid is not below lo and a whole number of steps from it, which bind() checks for the launch's values.
+    exact = {first.data["trips"]: (first.data["hi"] - first.data["lo"]) / first.data["step"]}
     fused = {}
     same_masks = True
     for key in ("a", "b"):
         f, f_casts, f_alpha = _peel(first.data[key])
-        g, g_casts, g_alpha = _peel(second.data[key])
+        g, g_casts, g_alpha = _peel(_subst(second.data[key], exact))
         if f_alpha or g_alpha or f.kind != "load" or g.kind != "load" or f_casts != g_casts:
             raise NotCanonical("the two K loops do not feed the dot with the same kind of loads")
         pf, pg = f.data["ptr"], g.data["ptr"]
@@ -910,7 +925,9 @@ def _fuse_split_loops(second: Flt) -> Flt:
             v = Flt("cast", v.shape, {"src": v, "to": to})
         out[key] = v
     return Flt("loop_dot", second.shape, {"a": out["a"], "b": out["b"], "init": first.data["init"],
-                                          "lo": first.data["lo"], "hi": second.data["hi"], "step": second.data["step"]})
+                                          "lo": first.data["lo"], "hi": second.data["hi"], "step": second.data["step"],
+                                          "trips": second.data["trips"], "trips_value": second.data["trips_value"],
+                                          "fused": True})
 
 
 def match_dot_kernel(text: str, arg_names: Optional[list] = None) -> DotKernelMatch:
@@ -937,7 +954,8 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
         # One tt.dot outside any loop: a K loop of exactly one iteration over the whole K extent of the tiles.
         k_extent = value.data["a"].shape[1] if len(value.data["a"].shape) == 2 else 0
         value = Flt("loop_dot", value.shape, {"a": value.data["a"], "b": value.data["b"], "init": value.data["c"],
-                                              "lo": sp.Integer(0), "hi": sp.Integer(k_extent), "step": sp.Integer(k_extent)})
+                                              "lo": sp.Integer(0), "hi": sp.Integer(k_extent), "step": sp.Integer(k_extent),
+                                              "trips": sp.Symbol("trips_single"), "trips_value": sp.Integer(1)})
     if value.kind != "loop_dot":
         raise NotCanonical("the stored value is not the result of the K loop")
     value = _fuse_split_loops(value)
@@ -1062,7 +1080,7 @@ def _match_dot_kernel(text: str, arg_names: Optional[list]) -> DotKernelMatch:
         int_args=sorted(ev.arg_symbols), row_scale_arg=row_scale, col_scale_arg=col_scale,
         tile_loop=[str(sp.expand(ev.tile_loop[k])) for k in ("lo", "hi", "step")] if ev.tile_loop else None,
         batch_offsets=[str(a_batch), str(b_batch), str(c_batch)] if batched else None,
-        equal_at_launch=equal_at_launch)
+        equal_at_launch=equal_at_launch, split_is_loop_bound=bool(value.data.get("fused")) and split_cmp is not None)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -1217,6 +1235,8 @@ def bind(match: DotKernelMatch, scalars: dict, grid: tuple, float_args: Optional
     k_main = (k // match.block_k) * match.block_k
     if match.split_comparand is not None:
         split = _value(match.split_comparand, sv)
+        if match.split_is_loop_bound and split < hi and (split < 0 or split % match.loop_step):  # a second loop runs
+            raise NotCanonical(f"split point {split} is not a whole number of steps of {match.loop_step} from 0")
         last = min(split, hi)
         if last > 0:
             iv_max = ((last - 1) // match.loop_step) * match.loop_step
