@@ -71,7 +71,13 @@ SWEEP = [(1, 8, 8), (7, 16, 24), (8, 8, 8), (63, 64, 72), (64, 64, 64), (65, 72,
 @pytest.mark.parametrize("dt", [bf16, f16, f8])
 def test_shape_sweep(B, dot_lib, m, n, k, dt):
     if dt == f8 and (k % 16 or n % 16):
-        pytest.skip("fp8 rows must be 16-byte aligned for TMA")
+        # fp8 rows of A (K bytes) or of B (N bytes) that are not 16-byte multiples cannot be described to TMA:
+        # the documented answer is TXD_ERR_UNSUPPORTED at plan creation, not a wrong result
+        dev = torch.device("cuda:0")
+        with pytest.raises(B.DotError) as e:
+            B.dot(torch.zeros(m, k, device=dev).to(f8), torch.zeros(k, n, device=dev).to(f8), out_dtype=bf16)
+        assert e.value.status == B.TXD_ERR_UNSUPPORTED
+        return
     case = Case(f"sweep_{m}x{n}x{k}", m, n, k, dt, bf16 if dt == f8 else dt, seed=100 + m + n + k,
                 scales=(dt == f8), block=(64, 64, 64), rtol=3e-2 if dt == f8 else 1e-2, atol=3e-2 if dt == f8 else 1e-2)
     a, b, rs, cs = make_inputs(case)
@@ -91,6 +97,8 @@ CONFIGS = [
     dict(block_n=128, cta_pair=2, schedule=1, stages=2), dict(block_n=256, cta_pair=1, max_ctas=6),
     dict(block_n=256, cta_pair=1, schedule=3, max_ctas=10), dict(block_n=128, cta_pair=1, schedule=2), dict(block_n=64, cta_pair=2, schedule=3, max_ctas=50),
     dict(block_n=256, cta_pair=1, atoms=2), dict(block_n=64, cta_pair=2, schedule=2, atoms=2),
+    # the wide pair tile (256 x 512: two 256-column MMA halves per K block)
+    dict(block_n=512, cta_pair=1), dict(block_n=512, cta_pair=1, stages=2, group_m=1), dict(block_n=512, cta_pair=1, max_ctas=4),
 ]
 
 
@@ -158,7 +166,7 @@ def test_cfg3_decode_skinny(B, dot_lib):
     a, b, rs, cs, got = check_full_size(B, dot_lib, CFG3, 112, 4)
     dev = torch.device("cuda:0")
     again = B.dot(a.to(dev), b.to(dev), out_dtype=bf16, check=True).cpu()
-    assert torch.equal(bits(again), bits(got)), "stream-K fix-up must be deterministic"
+    assert torch.equal(bits(again), bits(got)), "two runs of one plan must agree bit for bit"
 
 
 def test_cfg4_fp8_scaled(B, dot_lib):

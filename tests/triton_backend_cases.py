@@ -168,7 +168,10 @@ def run_scalar_ir(text: str, n: int, c: int) -> int:
     """Execute the scalar i32 subset the lit loops use (constants, addi, subi, muli, maxsi, minsi, ceildivsi, cmpi,
     select, scf.for with one iter_arg) and return the stored value."""
     _, _, ops = ttir.parse_module(text)
-    cmp = {"slt": lambda a, b: a < b, "sle": lambda a, b: a <= b, "sgt": lambda a, b: a > b, "sge": lambda a, b: a >= b}
+    u = lambda v: v & 0xFFFFFFFF      # an i32 read as unsigned
+    cmp = {"slt": lambda a, b: a < b, "sle": lambda a, b: a <= b, "sgt": lambda a, b: a > b, "sge": lambda a, b: a >= b,
+           "ult": lambda a, b: u(a) < u(b), "ule": lambda a, b: u(a) <= u(b), "ugt": lambda a, b: u(a) > u(b),
+           "uge": lambda a, b: u(a) >= u(b)}
     arith = {"arith.addi": lambda a, b: a + b, "arith.subi": lambda a, b: a - b, "arith.muli": lambda a, b: a * b,
              "arith.maxsi": max, "arith.minsi": min, "arith.ceildivsi": lambda a, b: -((-a) // b),
              "arith.remui": lambda a, b: a % b}
@@ -896,6 +899,23 @@ def test_loop_split_text_preserves_meaning_on_random_loops():
         assert run_scalar_ir(new, n, c) == run_scalar_ir(text, n, c)
 
     check()
+
+    # Unsigned compares: split (behind a run-time guard on the comparand's sign bit) only when the lower bound is a
+    # non-negative constant; with a negative lower bound the compare is not monotone in the induction variable and the
+    # loop is left alone. Either way the meaning is kept, for negative comparands too.
+    @settings(max_examples=200, deadline=None)
+    @given(lo=st.integers(-6, 12), n=st.integers(-4, 40), c=st.one_of(st.integers(-10, 45), st.sampled_from([-1, -2**31])),
+           step=st.integers(1, 9), pred=st.sampled_from(["ult", "ule", "ugt", "uge"]), swap=st.booleans())
+    def check_unsigned(lo, n, c, step, pred, swap):
+        text = (LIT_CASE.replace("STEP", str(step)).replace("PRED", pred)
+                .replace("LHS", "%c" if swap else "%i").replace("RHS", "%i" if swap else "%c")
+                .replace("%c0 = arith.constant 0 : i32", f"%c0 = arith.constant {lo} : i32\n    %zero = arith.constant 0 : i32")
+                .replace("iter_args(%acc = %c0)", "iter_args(%acc = %zero)"))
+        new, k = loop_split_ir.split_loops(text)
+        assert k == (1 if lo >= 0 else 0)
+        assert run_scalar_ir(new, n, c) == run_scalar_ir(text, n, c)
+
+    check_unsigned()
 
 
 def test_as_written_mode_reproduces_the_reference_and_its_off_by_one():

@@ -173,8 +173,30 @@ def preview(problem: Problem, config: Optional[Config] = None, sm_count: int = 1
     return info.as_dict()
 
 
+def _check_scale(t: Optional[torch.Tensor], length: int, device: torch.device, name: str) -> None:
+    """A scale vector is read by the kernel as `length` consecutive floats: anything else is refused here,
+    before a launch could read past it."""
+    if t is None:
+        return
+    if t.dtype != torch.float32:
+        raise TypeError(f"{name} must be float32, got {t.dtype}")
+    if t.dim() != 1 or t.numel() != length or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous vector of {length} elements, got shape {tuple(t.shape)} "
+                         f"strides {t.stride()}")
+    if not t.is_cuda or t.device != device:
+        raise ValueError(f"{name} must be a CUDA tensor on {device}, got {t.device}")
+
+
+def _span_elements(t: torch.Tensor) -> int:
+    """Elements between the first and one past the last element a strided 2-D tensor addresses."""
+    if t.numel() == 0:
+        return 0
+    return 1 + sum((n - 1) * abs(st) for n, st in zip(t.shape, t.stride()))
+
+
 class DotPlan:
-    """Owns one tx_dot_plan. Create once per (shape, dtype, layout); run many times."""
+    """Owns one tx_dot_plan. Create once per (shape, dtype, layout); run many times.
+    One plan serves one host thread at a time (it caches tensor maps keyed by the last pointers)."""
 
     def __init__(self, problem: Problem, config: Optional[Config] = None):
         lib = load_library()
@@ -192,11 +214,36 @@ class DotPlan:
             row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None,
             stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream(c.device)
+        self._check_buffers(a, b, c, row_scale, col_scale)
         _check(self._lib.tx_dot_run(
             self._h, a.data_ptr(), b.data_ptr(), c.data_ptr(),
             row_scale.data_ptr() if row_scale is not None else None,
             col_scale.data_ptr() if col_scale is not None else None,
             ctypes.c_void_p(s.cuda_stream)))
+
+    def _check_buffers(self, a, b, c, row_scale, col_scale) -> None:
+        """The buffers must hold what the plan's problem says the kernel will read and write."""
+        pr = self.problem
+        dev = c.device
+        if not (a.is_cuda and b.is_cuda and c.is_cuda) or a.device != dev or b.device != dev:
+            raise ValueError(f"a, b and c must be CUDA tensors on one device (got {a.device}, {b.device}, {c.device})")
+        if _DTYPES.get(a.dtype) != pr.ab_dtype or _DTYPES.get(b.dtype) != pr.ab_dtype:
+            raise TypeError(f"operand dtypes {a.dtype}, {b.dtype} do not match the plan")
+        if _DTYPES.get(c.dtype) != pr.out_dtype:
+            raise TypeError(f"output dtype {c.dtype} does not match the plan's")
+        if pr.m == 0 or pr.n == 0:
+            return
+        a_need = ((pr.m - 1) * pr.lda + pr.k) if pr.a_layout == TXD_ROW_MAJOR else ((pr.k - 1) * pr.lda + pr.m)
+        b_need = ((pr.k - 1) * pr.ldb + pr.n) if pr.b_layout == TXD_ROW_MAJOR else ((pr.n - 1) * pr.ldb + pr.k)
+        c_need = (pr.m - 1) * pr.ldc + pr.n
+        if pr.k > 0 and (_span_elements(a) < a_need or _span_elements(b) < b_need):
+            raise ValueError(f"operand buffers are smaller than the plan's {pr.m}x{pr.n}x{pr.k} problem needs")
+        if _span_elements(c) < c_need:
+            raise ValueError(f"output buffer addresses {_span_elements(c)} elements, the plan writes {c_need}")
+        if (pr.has_row_scale != 0) != (row_scale is not None) or (pr.has_col_scale != 0) != (col_scale is not None):
+            raise ValueError("scale vectors must be given exactly when the plan was created with them")
+        _check_scale(row_scale, pr.m, dev, "row_scale")
+        _check_scale(col_scale, pr.n, dev, "col_scale")
 
     def run_to_slots(self, a: torch.Tensor, b: torch.Tensor, slot_ptrs: list, rank: int,
                      stream: Optional[torch.cuda.Stream] = None) -> None:
@@ -262,8 +309,6 @@ def dot(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
     `a` is [M, K], `b` is [K, N]; either may be a transposed view (unit stride in one dimension).
     Default output dtype: the operand dtype for f16/bf16, bf16 for fp8 operands.
     """
-    if not (a.is_cuda and b.is_cuda):
-        raise ValueError("dot() takes CUDA tensors; there is no CPU path")
     if a.dtype != b.dtype:
         raise TypeError(f"tt.dot operands must share a dtype, got {a.dtype} and {b.dtype}")
     m, k = a.shape
@@ -272,10 +317,28 @@ def dot(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
         raise ValueError(f"shape mismatch: A is {tuple(a.shape)}, B is {tuple(b.shape)}")
     if out_dtype is None:
         out_dtype = out.dtype if out is not None else (a.dtype if a.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16)
+    # A caller's buffer is written as m x n elements of out_dtype, and a scale vector is read as m (n) floats:
+    # anything that is not exactly that is refused here, before any launch.
+    if out is not None:
+        if tuple(out.shape) != (m, n):
+            raise ValueError(f"out has shape {tuple(out.shape)}, the product is {(m, n)}")
+        if out.dtype != out_dtype:
+            raise TypeError(f"out is {out.dtype} but out_dtype is {out_dtype}")
+        if out.stride(1) != 1 and n > 1:
+            raise ValueError("out must be row-major")
+    for t, length, name in ((row_scale, m, "row_scale"), (col_scale, n, "col_scale")):
+        if t is not None and (t.dtype != torch.float32 or t.dim() != 1 or t.numel() != length or not t.is_contiguous()):
+            _check_scale(t, length, a.device, name)  # raises with the reason
+    if not (a.is_cuda and b.is_cuda):
+        raise ValueError("dot() takes CUDA tensors; there is no CPU path")
+    if a.device != b.device:
+        raise ValueError(f"a is on {a.device}, b on {b.device}")
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
-    if out.stride(1) != 1 and n > 1:
-        raise ValueError("out must be row-major")
+    elif not out.is_cuda or out.device != a.device:
+        raise ValueError(f"out is on {out.device}, the operands on {a.device}")
+    _check_scale(row_scale, m, a.device, "row_scale")
+    _check_scale(col_scale, n, a.device, "col_scale")
     a_layout, lda = _layout_and_ld(a, "a")
     b_layout, ldb = _layout_and_ld(b, "b")
     ldc = max(out.stride(0), n) if m > 1 else n

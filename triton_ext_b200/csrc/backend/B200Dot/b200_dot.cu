@@ -20,6 +20,7 @@
 
 #include "dot_tile_model.h"
 #include "dot_umma_kernel.cuh"
+#include "dot_plan_host.h"
 
 namespace {
 
@@ -42,24 +43,6 @@ int fail(int code, const char *fmt, ...) {
     if (e_ != cudaSuccess)                                                                 \
       return fail(TXD_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_));           \
   } while (0)
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
 
 __global__ void dot_zero_fill_kernel(void *out, long long ldo, int rows, int cols, int elem_bytes) {
   // K == 0: the accumulator of an empty K loop is zero, and so is every scaled/cast result.
@@ -88,6 +71,9 @@ struct tx_dot_plan {
   void *scratch = nullptr;      // partials, then counters
   uint32_t *status = nullptr;   // device status word
   MapKey p_cache, q_cache, out_cache;
+  // store maps of the K-sharded exchange, one per destination rank, kept while the slot bases stay the same
+  MapKey remote_cache[8];
+  int remote_cached_world = 0;
   // host-buffer path
   cudaStream_t host_stream = nullptr;
   void *dev_a = nullptr, *dev_b = nullptr, *dev_c = nullptr;
@@ -106,106 +92,25 @@ struct tx_dot_plan {
 namespace {
 
 int validate(const tx_dot_problem &pr) {
-  if (pr.m < 0 || pr.n < 0 || pr.k < 0) return fail(TXD_ERR_INVALID, "negative extent m=%d n=%d k=%d", pr.m, pr.n, pr.k);
-  const int es = txd::elem_bytes(pr.ab_dtype);
-  if (pr.ab_dtype == TXD_F32 || (es != 1 && es != 2))
-    return fail(TXD_ERR_UNSUPPORTED, "operand dtype %d: tt.dot operands must be f16, bf16, f8e4m3 or f8e5m2", pr.ab_dtype);
-  if (pr.out_dtype != TXD_F16 && pr.out_dtype != TXD_BF16 && pr.out_dtype != TXD_F32)
-    return fail(TXD_ERR_UNSUPPORTED, "output dtype %d: must be f16, bf16 or f32", pr.out_dtype);
-  if ((pr.a_layout != TXD_ROW_MAJOR && pr.a_layout != TXD_COL_MAJOR) ||
-      (pr.b_layout != TXD_ROW_MAJOR && pr.b_layout != TXD_COL_MAJOR))
-    return fail(TXD_ERR_INVALID, "layout must be TXD_ROW_MAJOR or TXD_COL_MAJOR");
-  const long long a_min = pr.a_layout == TXD_ROW_MAJOR ? pr.k : pr.m;
-  const long long b_min = pr.b_layout == TXD_ROW_MAJOR ? pr.n : pr.k;
-  if (pr.lda < a_min || pr.ldb < b_min || pr.ldc < pr.n)
-    return fail(TXD_ERR_INVALID, "leading dimension smaller than the row length (lda=%lld ldb=%lld ldc=%lld)",
-                (long long)pr.lda, (long long)pr.ldb, (long long)pr.ldc);
-  // TMA: every global stride is a multiple of 16 bytes (no operand is read when an extent is zero).
-  const bool empty = pr.m == 0 || pr.n == 0 || pr.k == 0;
-  if (!empty && ((pr.lda * es) % 16 != 0 || (pr.ldb * es) % 16 != 0))
-    return fail(TXD_ERR_UNSUPPORTED,
-                "lda and ldb must be multiples of %d elements (TMA needs 16-byte row strides); pad the operands",
-                16 / es);
-  return TXD_OK;
+  std::string msg;
+  const int rc = txd::host::validate_problem(pr, &msg);
+  if (rc) g_last_error = msg;
+  return rc;
 }
 
-uint32_t make_idesc(int ab_dtype, bool p_mn, bool q_mn, int block_m, int block_n) {
-  uint32_t fmt = 0;
-  if (ab_dtype == TXD_BF16) fmt = 1;        // kind::f16: 0 = f16, 1 = bf16
-  if (ab_dtype == TXD_F8E4M3) fmt = 0;      // kind::f8f6f4: 0 = e4m3, 1 = e5m2
-  if (ab_dtype == TXD_F8E5M2) fmt = 1;
-  uint32_t d = 0;
-  d |= 1u << 4;                              // accumulator format: f32
-  d |= fmt << 7;                             // A format
-  d |= fmt << 10;                            // B format
-  d |= (p_mn ? 1u : 0u) << 15;               // A is MN-major
-  d |= (q_mn ? 1u : 0u) << 16;               // B is MN-major
-  d |= static_cast<uint32_t>(block_n >> 3) << 17;
-  d |= static_cast<uint32_t>(block_m >> 4) << 24;  // 128, or 256 across a CTA pair
-  return d;
+int encode_operand_map(CUtensorMap *map, const void *ptr, int dtype, bool mn_major, long long rows, long long k,
+                       long long ld, int tile_rows, int bk_elems) {
+  std::string msg;
+  const int rc = txd::host::encode_operand_map(map, ptr, dtype, mn_major, rows, k, ld, tile_rows, bk_elems, &msg);
+  if (rc) g_last_error = msg;
+  return rc;
 }
 
-// Shared-memory matrix descriptor pieces for a SWIZZLE_128B operand stage.
-void make_smem_desc(bool mn_major, int bk_elems, int umma_k, uint32_t *hi, uint32_t *lbo, uint32_t *kstep) {
-  // 8 rows (K-major) or 8 K-slices (MN-major) of 128 bytes form one 1024-byte swizzle atom.
-  const uint32_t sbo_bytes = 1024;
-  // MN-major: consecutive 128-byte-wide boxes along the row index are bk_elems*128 bytes apart.
-  const uint32_t lbo_bytes = mn_major ? static_cast<uint32_t>(bk_elems) * 128u : 16u;
-  *hi = ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) /* descriptor version for sm_100 */ |
-        (2u << 29) /* SWIZZLE_128B */;
-  *lbo = ((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  // Start-address step per MMA: 32 bytes along K (K-major) or umma_k 128-byte slices (MN-major).
-  *kstep = mn_major ? static_cast<uint32_t>(umma_k) * 128u / 16u : 2u;
-}
-
-int encode_operand_map(CUtensorMap *map, const void *ptr, int dtype, bool mn_major, long long rows,
-                       long long k, long long ld, int tile_rows, int bk_elems) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-  const int es = txd::elem_bytes(dtype);
-  CUtensorMapDataType dt = es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                   : (dtype == TXD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  cuuint64_t dims[2], strides[1];
-  cuuint32_t box[2], estr[2] = {1, 1};
-  if (!mn_major) {
-    dims[0] = static_cast<cuuint64_t>(k);       // contiguous: K
-    dims[1] = static_cast<cuuint64_t>(rows);
-    box[0] = static_cast<cuuint32_t>(128 / es);  // one 128-byte K atom; a stage takes `atoms` such boxes
-    box[1] = static_cast<cuuint32_t>(tile_rows);
-  } else {
-    dims[0] = static_cast<cuuint64_t>(rows);    // contiguous: the row (M or N) index
-    dims[1] = static_cast<cuuint64_t>(k);
-    box[0] = static_cast<cuuint32_t>(128 / es);
-    box[1] = static_cast<cuuint32_t>(bk_elems);
-  }
-  strides[0] = static_cast<cuuint64_t>(ld) * es;
-  if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(TXD_ERR_INVALID, "operand pointer %p is not 16-byte aligned", ptr);
-  CUresult r = enc(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return fail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, stride %llu, box %u x %u)",
-                (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)strides[0], box[0], box[1]);
-  return TXD_OK;
-}
-
-// Tensor map for the epilogue's TMA store: C is row-major [m, n]; one box is 32 rows x 128 bytes.
 int encode_store_map(CUtensorMap *map, void *ptr, int out_dtype, long long m, long long n, long long ldc) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-  const int os = txd::elem_bytes(out_dtype);
-  CUtensorMapDataType dt = out_dtype == TXD_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                                 : (out_dtype == TXD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * os};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / os), 32};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, dt, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled (store map) failed with CUresult %d", (int)r);
-  return TXD_OK;
+  std::string msg;
+  const int rc = txd::host::encode_store_map(map, ptr, out_dtype, m, n, ldc, &msg);
+  if (rc) g_last_error = msg;
+  return rc;
 }
 
 int build_plan_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg, int sm_count, txd::TileChoice &tc) {
@@ -273,8 +178,14 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
   pl->device = dev;
   pl->sm_count = prop.multiProcessorCount;
   const tx_dot_problem &pr = pl->problem;
-  TXD_CUDA(cudaMalloc(&pl->status, 256));
-  TXD_CUDA(cudaMemset(pl->status, 0, 256));
+  // From here on every failure releases the plan before it returns.
+  auto cuda_step = [&](cudaError_t e, const char *what) -> int {
+    if (e == cudaSuccess) return TXD_OK;
+    tx_dot_plan_destroy(pl);
+    return fail(TXD_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+  };
+  if ((rc = cuda_step(cudaMalloc(&pl->status, 256), "cudaMalloc (status word)"))) return rc;
+  if ((rc = cuda_step(cudaMemset(pl->status, 0, 256), "cudaMemset (status word)"))) return rc;
   if (pr.m == 0 || pr.n == 0 || pr.k == 0) {  // nothing for the tensor pipe to do
     *out_plan = pl;
     return TXD_OK;
@@ -285,59 +196,13 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
     return rc;
   }
   const txd::TileChoice &tc = pl->tc;
-  const int es = txd::elem_bytes(pr.ab_dtype);
-  const bool swap = tc.swap_ab != 0;
-  // Roles: P feeds the 128 TMEM lanes, Q the block_n TMEM columns.
-  const bool p_mn = swap ? (pr.b_layout == TXD_ROW_MAJOR) : (pr.a_layout == TXD_COL_MAJOR);
-  const bool q_mn = swap ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
-
   txd::DotParams &bp = pl->base;
-  memset(&bp, 0, sizeof bp);
-  bp.ldo = pr.ldc;
-  bp.wait_limit_ns = 2000000000ull;  // 2 s per wait; a healthy kernel waits microseconds
-  if (const char *e = getenv("TXD_WAIT_LIMIT_MS")) {
-    const long v = atol(e);
-    if (v > 0) bp.wait_limit_ns = static_cast<unsigned long long>(v) * 1000000ull;
-  }
-  bp.alpha = pr.alpha;
-  bp.p_extent = tc.p_extent;
-  bp.q_extent = tc.q_extent;
-  bp.k_extent = pr.k;
-  bp.trans_out = swap ? 1 : 0;
-  bp.out_dtype = pr.out_dtype;
-  bp.block_n = tc.block_n;
-  bp.bk_elems = tc.block_k;
-  bp.stages = tc.stages;
-  bp.k_blocks = tc.k_blocks;
-  bp.k_main_blocks = tc.k_main_blocks;
-  bp.tail_mmas = tc.tail_mmas;
-  bp.tiles_p = tc.tiles_p;
-  bp.tiles_q = tc.tiles_q;
-  bp.group_p = tc.group_m;
-  bp.stream_k = tc.schedule != TXD_SCHED_DATA_PARALLEL ? 1 : 0;
-  bp.sk_first_tile = tc.sk_first_tile;
-  bp.kind_f8 = es == 1 ? 1 : 0;
-  bp.idesc = make_idesc(pr.ab_dtype, p_mn, q_mn, tc.block_m, tc.block_n);
-  bp.tma_store = tc.tma_store;
-  bp.atoms = tc.atoms;
-  const int umma_k = 32 / es;
-  make_smem_desc(p_mn, tc.block_k, umma_k, &bp.p_desc_hi, &bp.p_desc_lbo, &bp.p_kstep);
-  make_smem_desc(q_mn, tc.block_k, umma_k, &bp.q_desc_hi, &bp.q_desc_lbo, &bp.q_kstep);
-  bp.p_mn_major = p_mn;
-  bp.q_mn_major = q_mn;
-  bp.chunk_elems = 128 / es;
-  bp.p_stage_bytes = tc.p_stage_bytes;
-  bp.q_stage_bytes = tc.q_stage_bytes;
-  bp.tmem_cols = tc.tmem_cols;
+  txd::host::fill_params(pr, tc, &bp);
   bp.status = pl->status;
-  if (const char *e = getenv("TXD_DEBUG_FLAGS")) bp.debug_flags = atoi(e) & 7;   // measurement switches
-  if (const char *e = getenv("TXD_INJECT_STALL")) {                                   // host-side fault injection
-    if (atoi(e) != 0) bp.debug_flags |= 128;
-  }
 
   if (tc.scratch_bytes > 0) {
-    TXD_CUDA(cudaMalloc(&pl->scratch, static_cast<size_t>(tc.scratch_bytes)));
-    TXD_CUDA(cudaMemset(pl->scratch, 0, static_cast<size_t>(tc.scratch_bytes)));
+    if ((rc = cuda_step(cudaMalloc(&pl->scratch, static_cast<size_t>(tc.scratch_bytes)), "cudaMalloc (stream-K scratch)"))) return rc;
+    if ((rc = cuda_step(cudaMemset(pl->scratch, 0, static_cast<size_t>(tc.scratch_bytes)), "cudaMemset (stream-K scratch)"))) return rc;
     bp.partials = static_cast<float *>(pl->scratch);
     bp.tile_counters = reinterpret_cast<uint32_t *>(static_cast<char *>(pl->scratch) +
                                                     static_cast<size_t>(tc.grid) * 2 * tc.block_n * 128 * 4);
@@ -497,7 +362,7 @@ int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
   }
   if (pl->q_cache.ptr != q_ptr) {
     int rc = encode_operand_map(&pl->q_cache.map, q_ptr, pr.ab_dtype, pl->base.q_mn_major != 0, tc.q_extent, pr.k, q_ld,
-                                tc.cta_pair ? tc.block_n / 2 : tc.block_n, tc.block_k);
+                                txd::host::q_box_rows(tc), tc.block_k);
     if (rc) return rc;
     pl->q_cache.ptr = q_ptr;
   }
@@ -525,9 +390,18 @@ int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
     // Rank r starts on the tile rows owned by rank r+1 and ends on its own, so that at any moment every owner
     // receives from about one peer instead of all peers storing to the same owner.
     prm.tp_rotate = ((remote->rank + 1) % remote->world) * (prm.rows_per_rank / (tc.cta_pair ? 256 : 128));
+    if (pl->remote_cached_world != remote->world) {
+      for (auto &mk : pl->remote_cache) mk.ptr = nullptr;
+      pl->remote_cached_world = remote->world;
+    }
     for (int r = 0; r < remote->world; ++r) {
-      int rc = encode_store_map(&prm.tmap_remote[r], remote->slot_bases[r], pr.out_dtype, pr.m, pr.n, pr.n);
-      if (rc) return rc;
+      MapKey &mk = pl->remote_cache[r];
+      if (mk.ptr != remote->slot_bases[r]) {
+        int rc = encode_store_map(&mk.map, remote->slot_bases[r], pr.out_dtype, pr.m, pr.n, pr.n);
+        if (rc) return rc;
+        mk.ptr = remote->slot_bases[r];
+      }
+      prm.tmap_remote[r] = mk.map;
     }
   }
   if (tc.cta_pair) {
@@ -731,6 +605,16 @@ int tx_dot_run_host(tx_dot_plan *pl, const void *a_host, const void *b_host, voi
   TXD_CUDA(cudaMemcpyAsync(c_host, pl->dev_c, pl->c_bytes, cudaMemcpyDeviceToHost, s));
   return tx_dot_plan_check(pl, s);
 }
+
+#ifdef TXD_MEASURE
+// Measurement builds only: {cycles at start, cycles at end, ns at start, ns at end} of CTA 0 of the plan's last launch.
+__attribute__((visibility("default"))) int tx_dot_debug_stamps(tx_dot_plan *pl, unsigned long long *out4) {
+  if (!pl || !out4) return TXD_ERR_INVALID;
+  TXD_CUDA(cudaDeviceSynchronize());
+  TXD_CUDA(cudaMemcpy(out4, reinterpret_cast<char *>(pl->status) + 64, 32, cudaMemcpyDeviceToHost));
+  return TXD_OK;
+}
+#endif
 
 int tx_dot_plan_destroy(tx_dot_plan *pl) {
   if (!pl) return TXD_OK;

@@ -39,6 +39,7 @@
 #include "dot_tile_model.h"
 #define TXD_NO_KERNEL_ENTRY_POINTS  // this file launches its own instantiation only
 #include "dot_umma_kernel.cuh"
+#include "dot_plan_host.h"
 
 namespace {
 
@@ -105,61 +106,6 @@ int setup_device(int dev, DeviceSetup **out) {
   return TXD_OK;
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-// SWIZZLE_128B tensor map of one operand: K-major boxes are bk x tile_rows, MN-major boxes 128 bytes x bk.
-int encode_operand(CUtensorMap *map, const void *ptr, int dtype, bool mn_major, long long rows, long long k,
-                   long long ld, int tile_rows, int bk) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return fail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-  if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(TXD_ERR_INVALID, "operand pointer %p is not 16-byte aligned", ptr);
-  const int es = txd::elem_bytes(dtype);
-  const CUtensorMapDataType dt = es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                         : (dtype == TXD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_major ? rows : k), static_cast<cuuint64_t>(mn_major ? k : rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(mn_major ? bk : tile_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return TXD_OK;
-}
-
-int encode_store(CUtensorMap *map, void *ptr, int out_dtype, long long m, long long n, long long ldc) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return fail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-  const int os = txd::elem_bytes(out_dtype);
-  const CUtensorMapDataType dt = out_dtype == TXD_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                                       : (out_dtype == TXD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * os};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / os), 32};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, dt, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled (store map) failed with CUresult %d", (int)r);
-  return TXD_OK;
-}
-
-uint32_t smem_desc_hi() { return ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29); }  // SBO 1024, sm_100, SWIZZLE_128B
-
 }  // namespace
 
 extern "C" {
@@ -173,14 +119,17 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   if (!problem) return fail(TXD_ERR_INVALID, "null problem");
   const tx_dot_problem &pr = *problem;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  const int es = txd::elem_bytes(pr.ab_dtype), os = txd::elem_bytes(pr.out_dtype);
-  if (pr.m < 0 || pr.n < 0 || pr.k < 0) return fail(TXD_ERR_INVALID, "negative extent");
-  if (pr.ab_dtype == TXD_F32 || (es != 1 && es != 2)) return fail(TXD_ERR_UNSUPPORTED, "operand dtype must be f16, bf16, f8e4m3 or f8e5m2");
-  if (pr.out_dtype != TXD_F16 && pr.out_dtype != TXD_BF16 && pr.out_dtype != TXD_F32)
-    return fail(TXD_ERR_UNSUPPORTED, "output dtype must be f16, bf16 or f32");
+  const int os = txd::elem_bytes(pr.out_dtype);
+  {
+    std::string msg;
+    const int vrc = txd::host::validate_problem(pr, &msg);  // the same checks as tx_dot_plan_create
+    if (vrc) {
+      g_error = msg;
+      return vrc;
+    }
+  }
   if (pr.m == 0 || pr.n == 0) return TXD_OK;
   if (!c) return fail(TXD_ERR_INVALID, "null output pointer");
-  if (pr.ldc < pr.n) return fail(TXD_ERR_INVALID, "ldc smaller than n");
   if (pr.k == 0) {  // empty K loop: C = 0
     TXS_CUDA(cudaMemset2DAsync(c, static_cast<size_t>(pr.ldc) * os, 0, static_cast<size_t>(pr.n) * os, pr.m, stream));
     return TXD_OK;
@@ -188,12 +137,6 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   if (!a || !b) return fail(TXD_ERR_INVALID, "null operand pointer");
   if ((pr.has_row_scale != 0) != (row_scale != nullptr) || (pr.has_col_scale != 0) != (col_scale != nullptr))
     return fail(TXD_ERR_INVALID, "scale pointers must be given exactly when the problem asks for them");
-  const long long a_min = pr.a_layout == TXD_ROW_MAJOR ? pr.k : pr.m;
-  const long long b_min = pr.b_layout == TXD_ROW_MAJOR ? pr.n : pr.k;
-  if (pr.lda < a_min || pr.ldb < b_min) return fail(TXD_ERR_INVALID, "leading dimension smaller than the row length");
-  if ((pr.lda * es) % 16 != 0 || (pr.ldb * es) % 16 != 0)
-    return fail(TXD_ERR_UNSUPPORTED, "lda and ldb must be multiples of %d elements (TMA needs 16-byte row strides)", 16 / es);
-
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) {
     cudaGetLastError();
@@ -222,20 +165,19 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
                 partial_need, counter_need, kPartialBytes, kCounterBytes);
 
   const bool swap = tc.swap_ab != 0;
-  const bool p_mn = swap ? (pr.b_layout == TXD_ROW_MAJOR) : (pr.a_layout == TXD_COL_MAJOR);
-  const bool q_mn = swap ? (pr.a_layout == TXD_COL_MAJOR) : (pr.b_layout == TXD_ROW_MAJOR);
-  const int umma_k = 32 / es;
-
   txd::DotParams prm;
-  memset(&prm, 0, sizeof prm);
-  rc = encode_operand(&prm.tmap_p, swap ? b : a, pr.ab_dtype, p_mn, tc.p_extent, pr.k, swap ? pr.ldb : pr.lda, txd::kBlockM, tc.block_k);
-  if (rc) return rc;
-  rc = encode_operand(&prm.tmap_q, swap ? a : b, pr.ab_dtype, q_mn, tc.q_extent, pr.k, swap ? pr.lda : pr.ldb, tc.block_n, tc.block_k);
-  if (rc) return rc;
+  txd::host::fill_params(pr, tc, &prm);  // honours TXD_WAIT_LIMIT_MS and TXD_INJECT_STALL like the plan path
+  std::string msg;
+  rc = txd::host::encode_operand_map(&prm.tmap_p, swap ? b : a, pr.ab_dtype, prm.p_mn_major != 0, tc.p_extent, pr.k,
+                                     swap ? pr.ldb : pr.lda, txd::kBlockM, tc.block_k, &msg);
+  if (!rc)
+    rc = txd::host::encode_operand_map(&prm.tmap_q, swap ? a : b, pr.ab_dtype, prm.q_mn_major != 0, tc.q_extent, pr.k,
+                                       swap ? pr.lda : pr.ldb, txd::host::q_box_rows(tc), tc.block_k, &msg);
   const bool tma_store = tc.tma_store && (reinterpret_cast<uintptr_t>(c) & 15) == 0;
-  if (tma_store) {
-    rc = encode_store(&prm.tmap_out, c, pr.out_dtype, pr.m, pr.n, pr.ldc);
-    if (rc) return rc;
+  if (!rc && tma_store) rc = txd::host::encode_store_map(&prm.tmap_out, c, pr.out_dtype, pr.m, pr.n, pr.ldc, &msg);
+  if (rc) {
+    g_error = msg;
+    return rc;
   }
   unsigned char *base = setup->scratch;
   prm.out = c;
@@ -244,47 +186,7 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   prm.partials = reinterpret_cast<float *>(base);
   prm.tile_counters = reinterpret_cast<uint32_t *>(base + kPartialBytes);
   prm.status = reinterpret_cast<uint32_t *>(base + kPartialBytes + kCounterBytes);
-  prm.ldo = pr.ldc;
-  prm.wait_limit_ns = 2000000000ull;
-  if (const char *e = getenv("TXD_WAIT_LIMIT_MS")) {
-    const long v = atol(e);
-    if (v > 0) prm.wait_limit_ns = static_cast<unsigned long long>(v) * 1000000ull;
-  }
-  prm.alpha = pr.alpha;
-  prm.p_extent = tc.p_extent;
-  prm.q_extent = tc.q_extent;
-  prm.k_extent = pr.k;
-  prm.trans_out = swap ? 1 : 0;
-  prm.out_dtype = pr.out_dtype;
-  prm.block_n = tc.block_n;
-  prm.bk_elems = tc.block_k;
-  prm.stages = tc.stages;
-  prm.k_blocks = tc.k_blocks;
-  prm.k_main_blocks = tc.k_main_blocks;
-  prm.tail_mmas = tc.tail_mmas;
-  prm.tiles_p = tc.tiles_p;
-  prm.tiles_q = tc.tiles_q;
-  prm.group_p = tc.group_m;
-  prm.stream_k = 1;
-  prm.kind_f8 = es == 1 ? 1 : 0;
-  {
-    uint32_t fmt = (pr.ab_dtype == TXD_BF16 || pr.ab_dtype == TXD_F8E5M2) ? 1u : 0u;
-    prm.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((p_mn ? 1u : 0u) << 15) | ((q_mn ? 1u : 0u) << 16) |
-                (static_cast<uint32_t>(tc.block_n >> 3) << 17) | (static_cast<uint32_t>(txd::kBlockM >> 4) << 24);
-  }
-  prm.p_desc_hi = prm.q_desc_hi = smem_desc_hi();
-  prm.p_desc_lbo = (((p_mn ? static_cast<uint32_t>(tc.block_k) * 128u : 16u) >> 4) & 0x3FFFu) << 16;
-  prm.q_desc_lbo = (((q_mn ? static_cast<uint32_t>(tc.block_k) * 128u : 16u) >> 4) & 0x3FFFu) << 16;
-  prm.p_kstep = p_mn ? static_cast<uint32_t>(umma_k) * 128u / 16u : 2u;
-  prm.q_kstep = q_mn ? static_cast<uint32_t>(umma_k) * 128u / 16u : 2u;
-  prm.p_mn_major = p_mn;
-  prm.q_mn_major = q_mn;
-  prm.chunk_elems = 128 / es;
-  prm.p_stage_bytes = tc.p_stage_bytes;
-  prm.q_stage_bytes = tc.q_stage_bytes;
-  prm.tmem_cols = tc.tmem_cols;
   prm.tma_store = tma_store ? 1 : 0;
-  prm.atoms = tc.atoms;
 
   // The counters of the tiles this call touches must be zero when its kernel starts; an earlier call
   // that gave up on a wait may have left some non-zero.

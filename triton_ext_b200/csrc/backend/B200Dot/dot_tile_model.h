@@ -49,6 +49,7 @@ inline int elem_bytes(int dtype) {
 
 struct TileChoice {
   int block_m = 128, block_n = 0, block_k = 0;
+  int mma_n = 0;         // N extent of one tcgen05.mma: block_n, or 256 for the 512-column wide pair tile
   int stages = 0;
   int swap_ab = 0;       // 0/1 (resolved)
   int cta_pair = 0;      // 0/1 (resolved): two-CTA clusters, 256-row tiles
@@ -157,7 +158,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
 
   double best = 1e30;
   bool found = false;
-  static const int kBlockNs[] = {256, 128, 64, 32, 16};
+  static const int kBlockNs[] = {512, 256, 128, 64, 32, 16};
   for (int swap = 0; swap <= 1; ++swap) {
     if (cfg.swap_ab == 1 && !swap) continue;
     if (cfg.swap_ab == 2 && swap) continue;
@@ -175,14 +176,19 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
       for (int pair = 0; pair <= 1; ++pair) {
         if (cfg.cta_pair == 1 && !pair) continue;
         if (cfg.cta_pair == 2 && pair) continue;
+        // 512 columns = the wide pair tile: two 256-column MMA halves per K block sharing one P stage.
+        if (bn == 512 && !pair) continue;
+        if (bn == 512 && cfg.block_n != 512) continue;  // TEMP: explicit only until calibrated
+        const int mma_n = bn == 512 ? 256 : bn;
         if (pair) {
           // Each CTA of a pair holds half of the Q tile, in whole 128-byte-wide boxes when Q is
           // MN-major; pairs are for big problems in the natural orientation only.
-          if (swap || bn < 128 || (q_mn && (bn / 2) % bk != 0)) continue;
+          if (swap || bn < 128 || (q_mn && (mma_n / 2) % bk != 0)) continue;
           if (cfg.cta_pair == 0 && p_extent < 512) continue;
         }
         for (int atoms = 1; atoms <= 4; atoms *= 2) {
         if (cfg.atoms && atoms != cfg.atoms) continue;
+        if (bn == 512 && atoms != 1) continue;  // a wide stage is 48 KiB; deeper blocks leave too few stages
         // An MN-major operand is loaded as boxes atoms*bk K-slices tall; a TMA box dimension is at most 256.
         if ((p_mn_c || q_mn) && atoms * bk > 256) continue;
         {
@@ -197,6 +203,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
         const int k_blocks = cdiv(pr.k, bk * atoms);
         for (int sched = TXD_SCHED_DATA_PARALLEL; sched <= TXD_SCHED_HYBRID; ++sched) {
           if (cfg.schedule && sched != cfg.schedule) continue;
+          if (bn == 512 && sched != TXD_SCHED_DATA_PARALLEL) continue;  // both accumulators belong to one tile
           long long units = (long long)tiles * (sched == TXD_SCHED_STREAM_K ? k_blocks : 1);
           if (units < 1) units = 1;
           const int max_workers = pair ? max_grid / 2 : max_grid;
@@ -229,6 +236,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
             found = true;
             out.swap_ab = swap;
             out.block_n = bn;
+            out.mma_n = mma_n;
             out.cta_pair = pair;
             out.atoms = atoms;
             out.schedule = sched;

@@ -23,6 +23,10 @@
 //            memory and write both CTAs' TMEM. A CTA then ingests 2/3 of the bytes per FLOP of the
 //            single variant, which is what the SM's shared-memory fill rate asks for.
 //            No TMA load here uses multicast.
+//   wide pair : the pair variant with a 256 x 512 tile: every K block feeds two 256-column MMA halves
+//            from one P stage, so a CTA ingests 48 KiB per 1024 tensor cycles instead of 32 KiB per 512.
+//            Both TMEM accumulators belong to the tile, so a half's epilogue overlaps only the
+//            other half's MMAs of the neighbouring K blocks, not a whole main loop.
 //
 // Epilogue stores go through a swizzled shared-memory slab and a TMA tensor store (full 128-byte
 // lines) when C allows it, else straight from registers.
@@ -38,6 +42,14 @@
 #include <stdint.h>
 
 #include "sm100_ptx.cuh"
+
+// Measurement switches (bits 1, 2, 4, 8 of DotParams::debug_flags) make results wrong by design; they
+// exist only in builds made with -DTXD_MEASURE. The shipped library compiles them out.
+#ifdef TXD_MEASURE
+#define TXD_DBG(p, bit) (((p).debug_flags & (bit)) != 0)
+#else
+#define TXD_DBG(p, bit) false
+#endif
 
 namespace txd {
 
@@ -100,6 +112,8 @@ struct alignas(64) DotParams {
   int32_t tmem_cols;
   int32_t tma_store;                 // 1 = epilogue stores through shared memory + TMA
   int32_t atoms;                     // 128-byte K atoms per stage: 1, 2 or 4 (0 reads as 1)
+  int32_t wide;                      // pair kernel only: 1 = a tile is 256 x (2 * block_n): two MMA column halves
+                                     // share each P stage and each fill one of the two TMEM accumulators
   // K-sharded GEMM fused with its exchange: instead of C, a tile is stored into the slot this rank owns
   // inside the memory of the rank that owns the tile's rows (plain TMA stores over NVLink, no multicast):
   // slot buffer of rank o = [remote_world][rows_per_rank][n], this rank writes slot `remote_rank`.
@@ -107,11 +121,12 @@ struct alignas(64) DotParams {
   int32_t remote_rank;
   int32_t rows_per_rank;             // m / remote_world, a multiple of the tile height
   int32_t tp_rotate;                 // tile rows are visited starting here (mod tiles_p): ranks start on different owners
-  int32_t debug_flags;               // measurement / test switches, 0 in production (results are wrong
-                                     // when set): 1 = do not refill stages (tensor-pipe-only timing),
+  int32_t debug_flags;               // 128 = producer stops after its first K block (host-side fault
+                                     // injection: exercises the bounded waits). Builds with -DTXD_MEASURE
+                                     // also honour 1 = do not refill stages (tensor-pipe-only timing),
                                      // 2 = one MMA per tile (load-only timing), 4 = skip C stores,
-                                     // 128 = producer stops after its first K block (exercises the
-                                     // bounded waits)
+                                     // 8 = one tcgen05.commit per CTA of a pair instead of one for both;
+                                     // results are wrong with 1, 2 or 4 set
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -213,7 +228,7 @@ __device__ __forceinline__ void scale_chunk(const DotParams &p, float (&f)[32], 
 // Store straight from registers (any alignment, either orientation).
 template <int kCols>
 __device__ __forceinline__ void store_chunk_direct(const DotParams &p, float (&f)[32], int prow, int qcol0) {
-  if (prow >= p.p_extent || (p.debug_flags & 4)) return;
+  if (prow >= p.p_extent || TXD_DBG(p, 4)) return;
   if (p.trans_out) {
     // out[q*ldo + p]: lanes of a warp hold consecutive p -> coalesced per column
     if (p.out_dtype == 3) {
@@ -327,10 +342,17 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
   const uint32_t my_slabs = staging + static_cast<uint32_t>(quarter) * 2u * kStoreSlabBytes;
   const int slab_cols = p.out_dtype == 3 ? 32 : 64;  // 128 bytes of output per slab row
   uint32_t stores = 0;                               // TMA stores issued by this warp (slab parity)
+  // A wide tile is drained as two 256-column halves, one per TMEM accumulator: to this role they are
+  // two consecutive segments, so accumulator index and barrier phase follow the same arithmetic.
+  const int halves = (kPair && p.wide) ? 2 : 1;
   WorkIter it(p, worker, workers);
   Segment s;
   uint32_t seg_i = 0;
-  while (it.next(s)) {
+  bool alive = true;
+  while (alive && it.next(s)) {
+   int tp, tq_tile;
+   tile_coords(p, s.tile, tp, tq_tile);
+   for (int half = 0; half < halves; ++half) {
     const uint32_t acc = seg_i & 1u;
     const uint32_t acc_phase = (seg_i >> 1) & 1u;
     // One thread watches the barrier and publishes the outcome, so that all 128 epilogue threads
@@ -340,10 +362,12 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
     epilogue_bar_sync();
     const bool seg_ok = ctl->epi_ok != 0;
     epilogue_bar_sync();
-    if (!seg_ok) break;
+    if (!seg_ok) {
+      alive = false;
+      break;
+    }
     tc_fence_after();
-    int tp, tq;
-    tile_coords(p, s.tile, tp, tq);
+    const int tq = tq_tile * halves + half;
     const int prow0 = tp * rows_per_tile + static_cast<int>(cta_rank) * kBlockM;  // first row of this CTA
     const int prow = prow0 + row_in_tile;
     const int qcol_tile = tq * p.block_n;
@@ -378,7 +402,7 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
         if (c0 + slab_cols >= p.block_n) release_accumulator();
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0 && !(p.debug_flags & 4)) {
+        if (lane == 0 && !TXD_DBG(p, 4)) {
           if (p.remote_world > 0) {
             const int owner = prow0 / p.rows_per_rank;
             const int y = (p.remote_rank - owner) * p.rows_per_rank + prow0 + quarter * 32;
@@ -456,6 +480,7 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
       }
     }
     ++seg_i;
+   }
   }
   // Shared memory must stay valid until every TMA store has read it.
   if (lane == 0) bulk_wait_group_all();
@@ -486,6 +511,9 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   const int q_rows_per_cta = kPair ? p.block_n / 2 : p.block_n;  // Q rows this CTA loads per tile
   const int atoms = p.atoms > 1 ? p.atoms : 1;
   const int mmas_per_block = kMmasPerAtom * atoms;
+  const int halves = (kPair && p.wide) ? 2 : 1;       // MMA column halves per tile
+  const int tile_n = p.block_n * halves;               // Q rows (C columns) per tile
+  const uint32_t q_half_bytes = static_cast<uint32_t>(p.q_stage_bytes) / static_cast<uint32_t>(halves);
 
   AbortCtl ac;
   ac.flag = &ctl->abort_flag;
@@ -518,10 +546,20 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   if (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+#ifdef TXD_MEASURE
+  // Measurement builds: SM cycles and wall time of CTA 0, so that cycles per K block and the effective SM
+  // clock of a launch can be told apart.
+  unsigned long long stamp_c0 = 0, stamp_n0 = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    stamp_c0 = clock64();
+    stamp_n0 = global_timer_ns();
+  }
+#endif
 
   // ------------------------------ TMA producer (one warp per operand) ------------------------------
   // The whole warp walks the loop; one elected lane arms the barrier (P side) and issues the copies.
-  auto producer_role = [&](const bool load_p, const bool load_q) {
+  // `q_halves`: bit h set = this warp loads the Q rows of MMA column half h.
+  auto producer_role = [&](const bool load_p, const int q_halves) {
     {
       WorkIter it(p, worker, workers);
       Segment s;
@@ -534,7 +572,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         int tp, tq;
         tile_coords(p, s.tile, tp, tq);
         const int p0 = tp * rows_per_tile + static_cast<int>(cta_rank) * kBlockM;
-        const int q0 = tq * p.block_n + static_cast<int>(cta_rank) * q_rows_per_cta;
+        const int q0 = tq * tile_n + static_cast<int>(cta_rank) * q_rows_per_cta;
         for (int kb = s.kb0; kb < s.kb1; ++kb) {
           // `have_slot`: the probe issued at the end of the previous block already saw this stage free.
           if (!have_slot && !warp_mbar_wait(smem_u32(&ctl->empty_bar[stage]), phase ^ 1u, ac, kDevTimeoutProducer, lane)) {
@@ -548,7 +586,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           const uint32_t full_local = smem_u32(&ctl->full_bar[stage]);
           // Pair: every byte of both CTAs is counted on the leader's barrier.
           const uint32_t full = kPair ? map_to_cta(full_local, 0) : full_local;
-          if ((p.debug_flags & 1) && issued >= static_cast<uint32_t>(p.stages)) {
+          if (TXD_DBG(p, 1) && issued >= static_cast<uint32_t>(p.stages)) {
             if (leader && issuer && load_p) mbar_arrive(full_local);
             ++issued;
             if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1u; }
@@ -576,12 +614,16 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
             for (int c = 0; c * p.chunk_elems < kBlockM; ++c)
               load(p_dst + c * box_bytes, &p.tmap_p, p0 + c * p.chunk_elems, k0);
           }
-          if (!load_q) {
-          } else if (!p.q_mn_major) {
-            for (int at = 0; at < atoms; ++at) load(q_dst + at * q_atom_bytes, &p.tmap_q, k0 + at * p.chunk_elems, q0);
-          } else {
-            for (int c = 0; c * p.chunk_elems < q_rows_per_cta; ++c)
-              load(q_dst + c * box_bytes, &p.tmap_q, q0 + c * p.chunk_elems, k0);
+          for (int h = 0; h < halves; ++h) {
+            if (!((q_halves >> h) & 1)) continue;
+            const uint32_t qh_dst = q_dst + static_cast<uint32_t>(h) * q_half_bytes;
+            const int qh0 = q0 + h * p.block_n;
+            if (!p.q_mn_major) {
+              for (int at = 0; at < atoms; ++at) load(qh_dst + at * q_atom_bytes, &p.tmap_q, k0 + at * p.chunk_elems, qh0);
+            } else {
+              for (int c = 0; c * p.chunk_elems < q_rows_per_cta; ++c)
+                load(qh_dst + c * box_bytes, &p.tmap_q, qh0 + c * p.chunk_elems, k0);
+            }
           }
           }
           __syncwarp();
@@ -618,9 +660,9 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
     }
   };
   if (warp == 0) {
-    producer_role(true, false);
+    producer_role(true, halves == 2 ? 2 : 0);  // P, and the second Q half of a wide tile
   } else if (warp == 2) {
-    producer_role(false, true);
+    producer_role(false, 1);
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only in a pair) ------------------------------
     // The whole warp walks the loop; one elected lane issues tcgen05 instructions.
@@ -632,9 +674,14 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
       const bool issuer = elect_one();
       auto commit_to = [&](uint32_t local_bar) {
         if (kPair) {
-          // Same barrier in both CTAs: the follower's producer / epilogue wait on their own copy.
-          tc_commit_pair(map_to_cta(local_bar, 0));
-          tc_commit_pair(map_to_cta(local_bar, 1));
+          // The same barrier in both CTAs (the follower's producer / epilogue wait on their own copy),
+          // signalled by one commit.
+          if (TXD_DBG(p, 8)) {
+            tc_commit_pair(map_to_cta(local_bar, 0));
+            tc_commit_pair(map_to_cta(local_bar, 1));
+          } else {
+            tc_commit_pair_mask(local_bar, 3);
+          }
         } else {
           tc_commit(local_bar);
         }
@@ -644,10 +691,11 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
       const uint32_t p_lo_base = p.p_desc_lbo | ((stage_base & 0x3FFFFu) >> 4);
       const uint32_t q_lo_base = p.q_desc_lbo | (((stage_base + static_cast<uint32_t>(p.p_stage_bytes)) & 0x3FFFFu) >> 4);
       const uint32_t stage16 = stage_bytes >> 4;
+      const uint32_t q_half16 = q_half_bytes >> 4;  // second MMA column half of a wide tile inside the Q stage
       const uint32_t full0 = smem_u32(&ctl->full_bar[0]), empty0 = smem_u32(&ctl->empty_bar[0]);
       const uint32_t n_stages = static_cast<uint32_t>(p.stages);
       const uint32_t p_hi = p.p_desc_hi, q_hi = p.q_desc_hi, p_kstep = p.p_kstep, q_kstep = p.q_kstep;
-      const bool slow_mode = (p.debug_flags & 2) != 0;
+      const bool slow_mode = TXD_DBG(p, 2);
       // Start-address step (16-byte units) from one K atom of a stage to the next: K-major atoms lie side
       // by side (rows x 128 bytes each); MN-major stages are linear in K.
       const uint32_t p_atom_step = p.p_mn_major ? 4u * p.p_kstep : static_cast<uint32_t>(kBlockM) * kStageRowBytes / 16u;
@@ -663,16 +711,20 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         }
       };
       while (ok && it.next(s)) {
-        const uint32_t acc = seg_i & 1u;
-        const uint32_t acc_phase = (seg_i >> 1) & 1u;
+        // Accumulator of the tile (of its first column half when the tile is wide; the second half then
+        // uses the other accumulator, in the same barrier phase).
+        const uint32_t vseg = seg_i * static_cast<uint32_t>(halves);
+        const uint32_t acc = vseg & 1u;
+        const uint32_t acc_phase = (vseg >> 1) & 1u;
         ok = warp_mbar_wait(smem_u32(&ctl->tmem_empty_bar[acc]), acc_phase ^ 1u, ac, kDevTimeoutMmaTmem, lane);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * static_cast<uint32_t>(p.block_n);
+        const uint32_t d_tmem1 = tmem_base + static_cast<uint32_t>(p.block_n);  // wide: second half
         uint32_t accumulate = 0;
         // The tensor pipe does not run ahead of the issuing thread: every cycle this thread spends on
         // anything but MMA issue between two MMAs of consecutive K blocks was measured to be a pipe bubble
-        // of the same length, and each tcgen05.commit costs a further ~140 cycles of drain. So the probe
+        // of the same length, and a tcgen05.commit costs further cycles of drain. So the probe
         // of the NEXT stage's barrier and the warp vote on it are interleaved with this block's MMAs
         // (whose issue is back-pressured by the pipe anyway), and only the commit, the loop counters and
         // one branch separate the last MMA of a block from the first MMA of the next.
@@ -681,25 +733,43 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           tc_fence_after();
           return true;
         };
+        // Wide tile, between the two column halves of a block. First block of the tile: the second
+        // accumulator must have been drained (the epilogue hands the halves back one after the other, so
+        // the first half's MMAs of this block run while the second half is still being read out).
+        // Last block: the first half is complete, publish it before the second half's MMAs.
+        auto between_halves = [&](bool first, bool last) -> bool {
+          if (first) {
+            if (!warp_mbar_wait(smem_u32(&ctl->tmem_empty_bar[1]), acc_phase ^ 1u, ac, kDevTimeoutMmaTmem, lane)) return false;
+            tc_fence_after();
+          }
+          if (last && issuer) commit_to(smem_u32(&ctl->tmem_full_bar[0]));
+          return true;
+        };
         // Generic block: any MMA count (the remainder's last block, measurement modes); no probe.
-        auto issue_block = [&](uint32_t st, int n_mma) {
+        auto issue_block = [&](uint32_t st, int n_mma, bool first, bool last) {
           // Low descriptor words (start address in 16-byte units | leading-dimension field); shared
           // memory ends below 256 KiB, so adding offsets never carries out of the 14-bit address field.
           const uint32_t plo = p_lo_base + st * stage16;
           const uint32_t qlo = q_lo_base + st * stage16;
-          if (p.debug_flags & 2) n_mma = (accumulate == 0) ? 1 : 0;
-          if (issuer) {
+          if (TXD_DBG(p, 2)) n_mma = (accumulate == 0) ? 1 : 0;
+          for (int h = 0; h < halves; ++h) {
+            if (h == 1 && !between_halves(first, last)) {
+              ok = false;
+              return;
+            }
+            if (issuer) {
 #pragma unroll 1
-            for (int j = 0; j < n_mma; ++j)
-              mma(d_tmem, desc64(p.p_desc_hi, plo + (j >> 2) * p_atom_step + (j & 3) * p.p_kstep),
-                  desc64(p.q_desc_hi, qlo + (j >> 2) * q_atom_step + (j & 3) * p.q_kstep),
-                  (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
-            commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
+              for (int j = 0; j < n_mma; ++j)
+                mma(h ? d_tmem1 : d_tmem, desc64(p.p_desc_hi, plo + (j >> 2) * p_atom_step + (j & 3) * p.p_kstep),
+                    desc64(p.q_desc_hi, qlo + h * q_half16 + (j >> 2) * q_atom_step + (j & 3) * p.q_kstep),
+                    (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
+            }
           }
+          if (issuer) commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
           if (n_mma > 0) accumulate = 1;
         };
         // Full block on the fast path. Returns the warp-uniform probe result for stage `nst`.
-        auto full_block = [&](uint32_t st, uint32_t nst, uint32_t nph, bool more) -> bool {
+        auto full_block = [&](uint32_t st, uint32_t nst, uint32_t nph, bool more, bool first, bool last) -> bool {
           const uint32_t plo = p_lo_base + st * stage16;
           const uint32_t qlo = q_lo_base + st * stage16;
           if (issuer) mma(d_tmem, desc64(p_hi, plo), desc64(q_hi, qlo), accumulate);
@@ -717,8 +787,27 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
               for (int j = 0; j < kMmasPerAtom; ++j)
                 mma(d_tmem, desc64(p_hi, pa + j * p_kstep), desc64(q_hi, qa + j * q_kstep), 1u);
             }
-            commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
           }
+          if (halves == 2) {
+            if ((first || last) && !between_halves(first, last)) {
+              ok = false;
+              return false;
+            }
+            if (issuer) {
+              const uint32_t qh = qlo + q_half16;
+              mma(d_tmem1, desc64(p_hi, plo), desc64(q_hi, qh), accumulate);
+              mma(d_tmem1, desc64(p_hi, plo + p_kstep), desc64(q_hi, qh + q_kstep), 1u);
+              mma(d_tmem1, desc64(p_hi, plo + 2u * p_kstep), desc64(q_hi, qh + 2u * q_kstep), 1u);
+              mma(d_tmem1, desc64(p_hi, plo + 3u * p_kstep), desc64(q_hi, qh + 3u * q_kstep), 1u);
+              for (int at = 1; at < atoms; ++at) {
+                const uint32_t pa = plo + at * p_atom_step, qa = qh + at * q_atom_step;
+#pragma unroll
+                for (int j = 0; j < kMmasPerAtom; ++j)
+                  mma(d_tmem1, desc64(p_hi, pa + j * p_kstep), desc64(q_hi, qa + j * q_kstep), 1u);
+              }
+            }
+          }
+          if (issuer) commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
           accumulate = 1;
           return peek_all;
         };
@@ -737,16 +826,16 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           const bool full = (kb < mid || kb != p.k_blocks - 1 || p.tail_mmas == mmas_per_block) && !slow_mode;
           bool next_ready = false;
           if (full) {
-            next_ready = full_block(stage, next_stage, next_phase, more);
+            next_ready = full_block(stage, next_stage, next_phase, more, kb == s.kb0, !more);
           } else {
-            issue_block(stage, kb == p.k_blocks - 1 ? p.tail_mmas : mmas_per_block);
+            issue_block(stage, kb == p.k_blocks - 1 ? p.tail_mmas : mmas_per_block, kb == s.kb0, !more);
             __syncwarp();
           }
-          if (more && !next_ready) ok = wait_full(next_stage, next_phase);
+          if (ok && more && !next_ready) ok = wait_full(next_stage, next_phase);
           stage = next_stage;
           phase = next_phase;
         }
-        if (ok && issuer) commit_to(smem_u32(&ctl->tmem_full_bar[acc]));
+        if (ok && issuer) commit_to(smem_u32(&ctl->tmem_full_bar[halves == 2 ? 1u : acc]));
         __syncwarp();
         ++seg_i;
       }
@@ -774,6 +863,15 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
 
   tc_fence_before();
   __syncthreads();
+#ifdef TXD_MEASURE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long *st = reinterpret_cast<unsigned long long *>(p.status) + 8;
+    st[0] = stamp_c0;
+    st[1] = clock64();
+    st[2] = stamp_n0;
+    st[3] = global_timer_ns();
+  }
+#endif
   // Pair: neither CTA may leave while the other can still signal its barriers, read its shared
   // memory (MMA) or write its TMEM.
   if (kPair) cluster_sync_all();

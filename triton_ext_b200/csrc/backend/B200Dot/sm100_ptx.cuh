@@ -200,6 +200,15 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
                    cluster_bar)
                : "memory");
 }
+// One commit for a CTA pair: the arrival is delivered to the barrier at this shared-memory offset in
+// every CTA named by `cta_mask` (bit r = CTA r of the cluster). Signals only; no data is multicast.
+__device__ __forceinline__ void tc_commit_pair_mask(uint32_t local_bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          local_bar),
+      "h"(cta_mask)
+      : "memory");
+}
 __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                               uint32_t idesc, uint32_t accumulate) {
   asm volatile(

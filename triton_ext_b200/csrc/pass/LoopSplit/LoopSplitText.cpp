@@ -291,7 +291,8 @@ long region_end(const std::vector<std::string> &lines, size_t start) {
   int depth = 0;
   for (size_t i = start; i < lines.size(); ++i) {
     const std::string t = trim(lines[i]);
-    if (t == "} else {") continue;
+    // "} else {" of scf.if and "} do {" of scf.while close one region and open the next: depth-neutral
+    if (!t.empty() && t[0] == '}' && ends_with(t, "{")) continue;
     if (ends_with(t, "{")) {
       ++depth;
     } else if (!t.empty() && t[0] == '}') {
@@ -343,11 +344,22 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
     lines.push_back(text.substr(a, b - a));
     a = b + 1;
   }
-  std::map<std::string, long long> consts;
-  for (const std::string &l : lines) {
+  // SSA names repeat from one tt.func to the next (%0, %c1_i32, %cst ...): constants and definitions are looked
+  // up among the lines of the function that holds the loop only. Lines outside any function form scope 0.
+  std::vector<long> scope_of(lines.size(), 0);
+  {
+    long scope = 0, next_scope = 0;
+    for (size_t k = 0; k < lines.size(); ++k) {
+      const std::string t = trim(lines[k]);
+      if (t.rfind("tt.func", 0) == 0 || t.rfind("func.func", 0) == 0) scope = ++next_scope;
+      scope_of[k] = scope;
+    }
+  }
+  std::map<long, std::map<std::string, long long>> consts_by_scope;
+  for (size_t k = 0; k < lines.size(); ++k) {
     std::string name;
     long long v;
-    if (parse_int_constant(l, name, v)) consts[name] = v;
+    if (parse_int_constant(lines[k], name, v)) consts_by_scope[scope_of[k]][name] = v;
   }
   std::vector<std::string> out;
   n_split = 0;
@@ -361,6 +373,8 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
     if (end < 0) return 2;
     const size_t b0 = i + 1, b1 = static_cast<size_t>(end);
     const std::set<std::string> inside = defined_inside(lines, b0, b1);
+    const long scope = scope_of[i];
+    const std::map<std::string, long long> &consts = consts_by_scope[scope];
     const auto step_it = consts.find(h.step);
     long chosen = -1;
     Cmp cmp;
@@ -377,6 +391,14 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
         }
         PredInfo pi{};
         if (x != h.iv || y == h.iv || !pred_info(p, pi) || inside.count(y)) continue;
+        if (mode == TXLS_INTENT && p[0] == 'u') {
+          // An unsigned compare is monotone in the induction variable only while that is non-negative, and the
+          // comparand is a run-time value that may have its sign bit set (then `ult` holds, and `uge` fails, for
+          // every non-negative iv). With a constant lower bound >= 0 the split is made safe by a run-time guard
+          // below; otherwise this compare is left alone.
+          const auto lo_it = consts.find(h.lo);
+          if (lo_it == consts.end() || lo_it->second < 0) continue;
+        }
         chosen = static_cast<long>(bi);
         cmp = c;
         pred = p;
@@ -398,6 +420,7 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
       for (size_t k = 0; k < lines.size(); ++k) {
         OpLine o;
         if (parse_op(lines[k], o)) {
+          if (scope_of[k] != scope) continue;
           defs.global.emplace(o.result, k);
           if (k >= b0 && k < b1) defs.body.emplace(o.result, k);
         }
@@ -479,7 +502,15 @@ int split_text(const std::string &text, int mode, std::string &result, int32_t &
       pre.push_back(in + tag + "_m = arith.muli " + tag + "_q, " + h.step + " : " + ty);
       pre.push_back(in + tag + "_a = arith.addi " + h.lo + ", " + tag + "_m : " + ty);
       pre.push_back(in + tag + "_h = arith.maxsi " + h.hi + ", " + h.lo + " : " + ty);
-      pre.push_back(in + tag + "_mid = arith.minsi " + tag + "_a, " + tag + "_h : " + ty);
+      if (chosen >= 0 && pred[0] == 'u') {
+        // comparand with the sign bit set = an unsigned value above every non-negative iv: the compare has one
+        // value over the whole range, which stays in the first copy (mid = hi)
+        pre.push_back(in + tag + "_cl = arith.minsi " + tag + "_a, " + tag + "_h : " + ty);
+        pre.push_back(in + tag + "_neg = arith.cmpi slt, " + comparand + ", " + tag + "_c0 : " + ty);
+        pre.push_back(in + tag + "_mid = arith.select " + tag + "_neg, " + tag + "_h, " + tag + "_cl : " + ty);
+      } else {
+        pre.push_back(in + tag + "_mid = arith.minsi " + tag + "_a, " + tag + "_h : " + ty);
+      }
       midp = tag + "_mid";
       first_true = info.holds_below;
     }

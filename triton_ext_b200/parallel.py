@@ -147,14 +147,24 @@ class FusedKShardedDot:
         self.out = torch.empty((self.rows, n), dtype=out_dtype, device=dev)
 
     def __call__(self, a_shard: torch.Tensor, b_shard: torch.Tensor, *, row_scale: Optional[torch.Tensor] = None,
-                 col_scale: Optional[torch.Tensor] = None, alpha: float = 1.0) -> torch.Tensor:
+                 col_scale: Optional[torch.Tensor] = None, alpha: float = 1.0, events: Optional[list] = None) -> torch.Tensor:
+        """One K-sharded GEMM + exchange. `events`, if given, is a list of five CUDA events recorded on the current
+        stream before the first phase and after each of the four phases (for per-phase timing)."""
+        def mark(i):
+            if events is not None:
+                events[i].record()
+        mark(0)
         # 1. nobody may still be reading the slots of the previous call
         self.handle.barrier(channel=0)
+        mark(1)
         # 2. GEMM with the exchange in its epilogue
         self.plan.run_to_slots(a_shard, b_shard, self.slot_ptrs, self.rank)
+        mark(2)
         # 3. every rank's stores have landed
         self.handle.barrier(channel=1)
+        mark(3)
         # 4. local sum of the slots + scale + cast
         rs = row_scale[self.rank * self.rows:(self.rank + 1) * self.rows] if row_scale is not None else None
         self.B.reduce_slots(self.slots, self.out, row_scale=rs, col_scale=col_scale, alpha=alpha)
+        mark(4)
         return self.out
