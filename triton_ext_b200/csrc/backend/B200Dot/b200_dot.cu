@@ -207,9 +207,9 @@ int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg, 
     bp.tile_counters = reinterpret_cast<uint32_t *>(static_cast<char *>(pl->scratch) +
                                                     static_cast<size_t>(tc.grid) * 2 * tc.block_n * 128 * 4);
   }
-  cudaError_t e = cudaFuncSetAttribute(txd::dot_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(txd::dot_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  cudaError_t e = cudaSuccess;
+  for (auto kernel : {txd::dot_umma_kernel, txd::dot_umma_f8_kernel, txd::dot_umma_pair_kernel, txd::dot_umma_pair_f8_kernel})
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) {
     tx_dot_plan_destroy(pl);
     return fail(TXD_ERR_CUDA, "cannot reserve %d bytes of dynamic shared memory: %s", tc.smem_bytes, cudaGetErrorString(e));
@@ -417,7 +417,9 @@ int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    TXD_CUDA(cudaLaunchKernelEx(&lc, txd::dot_umma_pair_kernel, prm));
+    TXD_CUDA(cudaLaunchKernelEx(&lc, prm.kind_f8 ? txd::dot_umma_pair_f8_kernel : txd::dot_umma_pair_kernel, prm));
+  } else if (prm.kind_f8) {
+    txd::dot_umma_f8_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
   } else {
     txd::dot_umma_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
   }

@@ -72,7 +72,11 @@ int fail(int code, const char *fmt, ...) {
 
 __global__ void __launch_bounds__(txd::kNumThreads, 1)
 dot_umma_static_scratch_kernel(const __grid_constant__ txd::DotParams p) {
-  txd::dot_umma_body<false>(p);
+  txd::dot_umma_body<false, false>(p);
+}
+__global__ void __launch_bounds__(txd::kNumThreads, 1)
+dot_umma_static_scratch_f8_kernel(const __grid_constant__ txd::DotParams p) {
+  txd::dot_umma_body<false, true>(p);
 }
 
 struct DeviceSetup {
@@ -98,6 +102,7 @@ int setup_device(int dev, DeviceSetup **out) {
     TXS_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
     if (!ptr) return fail(TXD_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
     TXS_CUDA(cudaFuncSetAttribute(dot_umma_static_scratch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXS_CUDA(cudaFuncSetAttribute(dot_umma_static_scratch_f8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     s.scratch = static_cast<unsigned char *>(ptr);
     s.sm_count = sms;
     s.ready = true;
@@ -191,7 +196,8 @@ int tx_dot_run_static_scratch(const tx_dot_problem *problem, const tx_dot_config
   // The counters of the tiles this call touches must be zero when its kernel starts; an earlier call
   // that gave up on a wait may have left some non-zero.
   TXS_CUDA(cudaMemsetAsync(prm.tile_counters, 0, counter_need, stream));
-  dot_umma_static_scratch_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
+  if (prm.kind_f8) dot_umma_static_scratch_f8_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
+  else dot_umma_static_scratch_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
   TXS_CUDA(cudaGetLastError());
   return TXD_OK;
 }

@@ -222,7 +222,10 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
           // HBM-bound ones with deep blocks (fewer TMA copies and handshakes per byte). Both measured.
           {
             int lg = atoms == 4 ? 2 : (atoms == 2 ? 1 : 0);
-            t *= out.hbm_bound ? 1.0 - (lg >= 1 ? 0.02 : 0.0) + (lg == 2 ? 0.005 : 0.0) : 1.0 + 0.02 * lg;
+            // Measured (8192 x 8192 x 4160 bf16, CTA pairs): one atom per stage is bound by the load path at 690
+            // cycles per K block of four MMAs (512 of tensor work), two atoms per stage run at 1 100 cycles per
+            // eight MMAs: bigger TMA boxes and half the barrier traffic per byte. Deeper still leaves too few stages.
+            t *= out.hbm_bound ? 1.0 - (lg >= 1 ? 0.02 : 0.0) + (lg == 2 ? 0.005 : 0.0) : (lg == 1 ? 0.93 : (lg == 2 ? 1.04 : 1.0));
           }
           if (sched == TXD_SCHED_STREAM_K) t = t * 1.10 + 6e-6;  // + fix-up of the partial tiles (measured on 16x14336x4096)
           // Measured on 4096x4096x4160 (3.46 waves): the partial-tile fix-up of the last wave costs more than

@@ -357,8 +357,10 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
     const uint32_t acc_phase = (seg_i >> 1) & 1u;
     // One thread watches the barrier and publishes the outcome, so that all 128 epilogue threads
     // take the same branch (they meet again at named barrier 1 below).
+    // (mbarrier.try_wait parks the thread in hardware between probes: this wait lasts a whole main loop, and a
+    // thread spinning through it costs power that the tensor pipe's clock then lacks)
     if (epi_tid == 0)
-      ctl->epi_ok = mbar_wait(smem_u32(&ctl->tmem_full_bar[acc]), acc_phase, ac, kDevTimeoutEpilogue) ? 1u : 0u;
+      ctl->epi_ok = mbar_wait_timed(smem_u32(&ctl->tmem_full_bar[acc]), acc_phase, ac, kDevTimeoutEpilogue) ? 1u : 0u;
     epilogue_bar_sync();
     const bool seg_ok = ctl->epi_ok != 0;
     epilogue_bar_sync();
@@ -486,7 +488,7 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
   if (lane == 0) bulk_wait_group_all();
 }
 
-template <bool kPair>
+template <bool kPair, bool kF8>
 __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   extern __shared__ uint8_t smem_raw[];
   // Stage buffers need 1024-byte alignment (SWIZZLE_128B atoms); the launch asks for 1 KiB of slack.
@@ -666,6 +668,16 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only in a pair) ------------------------------
     // The whole warp walks the loop; one elected lane issues tcgen05 instructions.
+    //
+    // This loop is one thread's instruction stream, and that stream, not the tensor pipe, is what bounds the
+    // kernel when it is long: a K block of four 256x256x16 MMAs occupies the pipe for 512 cycles, and every
+    // instruction the issuing thread executes per block (several cycles each, nothing to overlap them with in a
+    // one-warp dependency chain) comes out of that budget. Measured on this part: a loop of about 80 instructions
+    // per block ran at 780 cycles per block whatever the MMA's N, a loop of about 30 runs at the pipe's 512, and a
+    // tcgen05.commit per block costs nothing by itself. So the main loop below is branch-free apart from its trip
+    // count, its descriptors are two multiply-adds per block, the operand kind is a template parameter, and
+    // everything a block may need besides (a partial last block, the hand-over between the column halves of a wide
+    // tile, measurement modes) lives in the generic path, which the unpredicated main loop never enters.
     if (leader) {
       WorkIter it(p, worker, workers);
       Segment s;
@@ -694,21 +706,35 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
       const uint32_t q_half16 = q_half_bytes >> 4;  // second MMA column half of a wide tile inside the Q stage
       const uint32_t full0 = smem_u32(&ctl->full_bar[0]), empty0 = smem_u32(&ctl->empty_bar[0]);
       const uint32_t n_stages = static_cast<uint32_t>(p.stages);
+      const uint32_t idesc = p.idesc;
       const uint32_t p_hi = p.p_desc_hi, q_hi = p.q_desc_hi, p_kstep = p.p_kstep, q_kstep = p.q_kstep;
+      const uint32_t pk2 = 2u * p_kstep, pk3 = 3u * p_kstep, qk2 = 2u * q_kstep, qk3 = 3u * q_kstep;
       const bool slow_mode = TXD_DBG(p, 2);
       // Start-address step (16-byte units) from one K atom of a stage to the next: K-major atoms lie side
       // by side (rows x 128 bytes each); MN-major stages are linear in K.
       const uint32_t p_atom_step = p.p_mn_major ? 4u * p.p_kstep : static_cast<uint32_t>(kBlockM) * kStageRowBytes / 16u;
       const uint32_t q_atom_step = p.q_mn_major ? 4u * p.q_kstep : static_cast<uint32_t>(q_rows_per_cta) * kStageRowBytes / 16u;
-      const bool f8 = p.kind_f8 != 0;
-      auto mma = [&](uint32_t d_tmem, uint64_t pd, uint64_t qd, uint32_t accumulate) {
-        if (kPair) {
-          if (f8) umma_f8_pair(d_tmem, pd, qd, p.idesc, accumulate);
-          else umma_f16_pair(d_tmem, pd, qd, p.idesc, accumulate);
-        } else {
-          if (f8) umma_f8(d_tmem, pd, qd, p.idesc, accumulate);
-          else umma_f16(d_tmem, pd, qd, p.idesc, accumulate);
+      auto wait_full = [&](uint32_t st, uint32_t ph) -> bool {
+        if (!warp_mbar_wait(full0 + st * 8u, ph, ac, kDevTimeoutMmaFull, lane)) return false;
+        tc_fence_after();
+        return true;
+      };
+      // The four MMAs of one K atom into accumulator `d`; `first` is the accumulate flag of the first of them.
+      auto atom_mmas = [&](uint32_t d, uint32_t plo, uint32_t qlo, uint32_t first) {
+        umma<kPair, kF8>(d, desc64(p_hi, plo), desc64(q_hi, qlo), idesc, first);
+        umma_acc<kPair, kF8>(d, desc64(p_hi, plo + p_kstep), desc64(q_hi, qlo + q_kstep), idesc);
+        umma_acc<kPair, kF8>(d, desc64(p_hi, plo + pk2), desc64(q_hi, qlo + qk2), idesc);
+        umma_acc<kPair, kF8>(d, desc64(p_hi, plo + pk3), desc64(q_hi, qlo + qk3), idesc);
+      };
+      bool ready = false;  // the "full" barrier of `stage` has already been seen complete (warp-uniform)
+      auto advance = [&]() {
+        if (++stage == n_stages) {
+          stage = 0;
+          phase ^= 1u;
         }
+        // Look at the next stage now: the issuing thread is ahead of the pipe here, and a stage that has landed
+        // needs no wait at the top of the next block.
+        ready = __all_sync(0xffffffffu, mbar_test_wait(full0 + stage * 8u, phase));
       };
       while (ok && it.next(s)) {
         // Accumulator of the tile (of its first column half when the tile is wide; the second half then
@@ -722,17 +748,6 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
         const uint32_t d_tmem = tmem_base + acc * static_cast<uint32_t>(p.block_n);
         const uint32_t d_tmem1 = tmem_base + static_cast<uint32_t>(p.block_n);  // wide: second half
         uint32_t accumulate = 0;
-        // The tensor pipe does not run ahead of the issuing thread: every cycle this thread spends on
-        // anything but MMA issue between two MMAs of consecutive K blocks was measured to be a pipe bubble
-        // of the same length, and a tcgen05.commit costs further cycles of drain. So the probe
-        // of the NEXT stage's barrier and the warp vote on it are interleaved with this block's MMAs
-        // (whose issue is back-pressured by the pipe anyway), and only the commit, the loop counters and
-        // one branch separate the last MMA of a block from the first MMA of the next.
-        auto wait_full = [&](uint32_t st, uint32_t ph) -> bool {
-          if (!warp_mbar_wait(full0 + st * 8u, ph, ac, kDevTimeoutMmaFull, lane)) return false;
-          tc_fence_after();
-          return true;
-        };
         // Wide tile, between the two column halves of a block. First block of the tile: the second
         // accumulator must have been drained (the epilogue hands the halves back one after the other, so
         // the first half's MMAs of this block run while the second half is still being read out).
@@ -745,12 +760,17 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
           if (last && issuer) commit_to(smem_u32(&ctl->tmem_full_bar[0]));
           return true;
         };
-        // Generic block: any MMA count (the remainder's last block, measurement modes); no probe.
-        auto issue_block = [&](uint32_t st, int n_mma, bool first, bool last) {
+        // Generic block: any MMA count (the remainder's last block, measurement modes), the first and the last
+        // block of a wide tile.
+        auto generic_block = [&](int n_mma, bool first, bool last) {
+          if (!ready && !wait_full(stage, phase)) {
+            ok = false;
+            return;
+          }
           // Low descriptor words (start address in 16-byte units | leading-dimension field); shared
           // memory ends below 256 KiB, so adding offsets never carries out of the 14-bit address field.
-          const uint32_t plo = p_lo_base + st * stage16;
-          const uint32_t qlo = q_lo_base + st * stage16;
+          const uint32_t plo = p_lo_base + stage * stage16;
+          const uint32_t qlo = q_lo_base + stage * stage16;
           if (TXD_DBG(p, 2)) n_mma = (accumulate == 0) ? 1 : 0;
           for (int h = 0; h < halves; ++h) {
             if (h == 1 && !between_halves(first, last)) {
@@ -760,81 +780,51 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
             if (issuer) {
 #pragma unroll 1
               for (int j = 0; j < n_mma; ++j)
-                mma(h ? d_tmem1 : d_tmem, desc64(p.p_desc_hi, plo + (j >> 2) * p_atom_step + (j & 3) * p.p_kstep),
-                    desc64(p.q_desc_hi, qlo + h * q_half16 + (j >> 2) * q_atom_step + (j & 3) * p.q_kstep),
-                    (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
+                umma<kPair, kF8>(h ? d_tmem1 : d_tmem, desc64(p_hi, plo + (j >> 2) * p_atom_step + (j & 3) * p_kstep),
+                                 desc64(q_hi, qlo + h * q_half16 + (j >> 2) * q_atom_step + (j & 3) * q_kstep), idesc,
+                                 (accumulate | static_cast<uint32_t>(j)) != 0 ? 1u : 0u);
             }
           }
-          if (issuer) commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
+          if (issuer) commit_to(empty0 + stage * 8u);  // frees the stage when its MMAs retire
+          __syncwarp();
           if (n_mma > 0) accumulate = 1;
-        };
-        // Full block on the fast path. Returns the warp-uniform probe result for stage `nst`.
-        auto full_block = [&](uint32_t st, uint32_t nst, uint32_t nph, bool more, bool first, bool last) -> bool {
-          const uint32_t plo = p_lo_base + st * stage16;
-          const uint32_t qlo = q_lo_base + st * stage16;
-          if (issuer) mma(d_tmem, desc64(p_hi, plo), desc64(q_hi, qlo), accumulate);
-          const bool peek = more ? mbar_test_wait(full0 + nst * 8u, nph) : true;
-          if (issuer) {
-            mma(d_tmem, desc64(p_hi, plo + p_kstep), desc64(q_hi, qlo + q_kstep), 1u);
-            mma(d_tmem, desc64(p_hi, plo + 2u * p_kstep), desc64(q_hi, qlo + 2u * q_kstep), 1u);
-          }
-          const bool peek_all = __all_sync(0xffffffffu, peek);
-          if (issuer) {
-            mma(d_tmem, desc64(p_hi, plo + 3u * p_kstep), desc64(q_hi, qlo + 3u * q_kstep), 1u);
-            for (int at = 1; at < atoms; ++at) {
-              const uint32_t pa = plo + at * p_atom_step, qa = qlo + at * q_atom_step;
-#pragma unroll
-              for (int j = 0; j < kMmasPerAtom; ++j)
-                mma(d_tmem, desc64(p_hi, pa + j * p_kstep), desc64(q_hi, qa + j * q_kstep), 1u);
-            }
-          }
-          if (halves == 2) {
-            if ((first || last) && !between_halves(first, last)) {
-              ok = false;
-              return false;
-            }
-            if (issuer) {
-              const uint32_t qh = qlo + q_half16;
-              mma(d_tmem1, desc64(p_hi, plo), desc64(q_hi, qh), accumulate);
-              mma(d_tmem1, desc64(p_hi, plo + p_kstep), desc64(q_hi, qh + q_kstep), 1u);
-              mma(d_tmem1, desc64(p_hi, plo + 2u * p_kstep), desc64(q_hi, qh + 2u * q_kstep), 1u);
-              mma(d_tmem1, desc64(p_hi, plo + 3u * p_kstep), desc64(q_hi, qh + 3u * q_kstep), 1u);
-              for (int at = 1; at < atoms; ++at) {
-                const uint32_t pa = plo + at * p_atom_step, qa = qh + at * q_atom_step;
-#pragma unroll
-                for (int j = 0; j < kMmasPerAtom; ++j)
-                  mma(d_tmem1, desc64(p_hi, pa + j * p_kstep), desc64(q_hi, qa + j * q_kstep), 1u);
-              }
-            }
-          }
-          if (issuer) commit_to(empty0 + st * 8u);  // frees the stage when its MMAs retire
-          accumulate = 1;
-          return peek_all;
+          advance();
         };
         // LoopSplit: blocks below `mid` belong to the main loop [lo, mid) — full, unpredicated; blocks
         // from `mid` on are the remainder loop [mid, hi), whose stages TMA zero-filled past K and whose
         // last block issues only the MMAs that cover real columns.
         const int mid = s.kb1 < p.k_main_blocks ? s.kb1 : p.k_main_blocks;
-        ok = wait_full(stage, phase);
-        for (int kb = s.kb0; ok && kb < s.kb1; ++kb) {
-          uint32_t next_stage = stage + 1, next_phase = phase;
-          if (next_stage == n_stages) {
-            next_stage = 0;
-            next_phase ^= 1u;
-          }
-          const bool more = kb + 1 < s.kb1;
-          const bool full = (kb < mid || kb != p.k_blocks - 1 || p.tail_mmas == mmas_per_block) && !slow_mode;
-          bool next_ready = false;
-          if (full) {
-            next_ready = full_block(stage, next_stage, next_phase, more, kb == s.kb0, !more);
-          } else {
-            issue_block(stage, kb == p.k_blocks - 1 ? p.tail_mmas : mmas_per_block, kb == s.kb0, !more);
-            __syncwarp();
-          }
-          if (ok && more && !next_ready) ok = wait_full(next_stage, next_phase);
-          stage = next_stage;
-          phase = next_phase;
+        const int last_kb = s.kb1 - 1;
+        int kb = s.kb0;
+        auto remainder_mmas = [&](int b) { return b == p.k_blocks - 1 ? p.tail_mmas : mmas_per_block; };
+        if (halves == 2 && kb < s.kb1) {  // first block of a wide tile: waits for the second accumulator
+          generic_block(remainder_mmas(kb), true, kb == last_kb);
+          ++kb;
         }
+        // ---- main loop ----
+        int main_end = slow_mode ? kb : mid;
+        if (halves == 2 && main_end > last_kb) main_end = last_kb;  // a wide tile's last block publishes its first half early
+        for (; ok && kb < main_end; ++kb) {
+          if (!ready && !wait_full(stage, phase)) {
+            ok = false;
+            break;
+          }
+          const uint32_t plo = p_lo_base + stage * stage16;
+          const uint32_t qlo = q_lo_base + stage * stage16;
+          if (issuer) {
+            atom_mmas(d_tmem, plo, qlo, accumulate);
+            for (int at = 1; at < atoms; ++at) atom_mmas(d_tmem, plo + at * p_atom_step, qlo + at * q_atom_step, 1u);
+            if (halves == 2) {
+              atom_mmas(d_tmem1, plo, qlo + q_half16, accumulate);
+              for (int at = 1; at < atoms; ++at) atom_mmas(d_tmem1, plo + at * p_atom_step, qlo + q_half16 + at * q_atom_step, 1u);
+            }
+            commit_to(empty0 + stage * 8u);  // frees the stage when its MMAs retire
+          }
+          accumulate = 1;
+          advance();
+        }
+        // ---- remainder loop (and the last block of a wide tile) ----
+        for (; ok && kb < s.kb1; ++kb) generic_block(remainder_mmas(kb), false, kb == last_kb);
         if (ok && issuer) commit_to(smem_u32(&ctl->tmem_full_bar[halves == 2 ? 1u : acc]));
         __syncwarp();
         ++seg_i;
@@ -884,12 +874,19 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
 // A translation unit that instantiates dot_umma_body under its own kernel name defines
 // TXD_NO_KERNEL_ENTRY_POINTS so that these two are emitted once per library.
 #ifndef TXD_NO_KERNEL_ENTRY_POINTS
+// One entry point per (single | pair) x (16-bit | 8-bit operands): the operand kind is part of the MMA instruction,
+// and a run-time choice of it would sit in the issuing thread's instruction stream once per MMA.
 __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_kernel(const __grid_constant__ DotParams p) {
-  dot_umma_body<false>(p);
+  dot_umma_body<false, false>(p);
 }
-
+__global__ void __launch_bounds__(kNumThreads, 1) dot_umma_f8_kernel(const __grid_constant__ DotParams p) {
+  dot_umma_body<false, true>(p);
+}
 __global__ void __launch_bounds__(kNumThreads, 1) dot_umma_pair_kernel(const __grid_constant__ DotParams p) {
-  dot_umma_body<true>(p);
+  dot_umma_body<true, false>(p);
+}
+__global__ void __launch_bounds__(kNumThreads, 1) dot_umma_pair_f8_kernel(const __grid_constant__ DotParams p) {
+  dot_umma_body<true, true>(p);
 }
 #endif  // TXD_NO_KERNEL_ENTRY_POINTS
 

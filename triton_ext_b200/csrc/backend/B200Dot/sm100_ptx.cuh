@@ -231,6 +231,32 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t adesc, ui
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One tcgen05.mma with the instruction form chosen at compile time.
+template <bool kPair, bool kF8>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (kPair) {
+    if (kF8) umma_f8_pair(d_tmem, adesc, bdesc, idesc, accumulate);
+    else umma_f16_pair(d_tmem, adesc, bdesc, idesc, accumulate);
+  } else {
+    if (kF8) umma_f8(d_tmem, adesc, bdesc, idesc, accumulate);
+    else umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
+  }
+}
+// The same with the accumulate input fixed to "add to the accumulator": no predicate to compute.
+template <bool kPair, bool kF8>
+__device__ __forceinline__ void umma_acc(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  if (kPair) {
+    if (kF8)
+      asm volatile("{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\ntcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+    else
+      asm volatile("{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+  } else {
+    if (kF8)
+      asm volatile("{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\ntcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+    else
+      asm volatile("{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+  }
+}
 // ---- TMA tensor store ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
