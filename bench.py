@@ -48,10 +48,10 @@ L2_BYTES = 126 * 1024 * 1024
 # beside each figure gives the command); None where no capture exists. These are citations of a profile, not
 # measurements of the run that prints them.
 NCU_TRAFFIC = {
-    "cfg2": (110.2e6, "profiles/dot_umma_pair_kernel_cfg2_bf16_4096x4096x4160.md"),
-    "cfg3": (122.2e6, "profiles/dot_umma_kernel_cfg3_bf16_16x14336x4096.md"),
-    "cfg4": (462.9e6, "profiles/dot_umma_pair_kernel_cfg4_fp8_8192x8192x8192.md"),
-    "attn_d64": (254.7e6, "profiles/attn_fwd_kernel_f16_batch4_heads32_nctx2048.md (scaled to the bench shape)"),
+    "cfg2": (107.9e6, "profiles/dot_umma_pair_kernel_cfg2_bf16_4096x4096x4160.md"),
+    "cfg3": (122.0e6, "profiles/dot_umma_kernel_cfg3_bf16_16x14336x4096.md"),
+    "cfg4": (459.1e6, "profiles/dot_umma_pair_f8_kernel_cfg4_fp8_8192x8192x8192.md"),
+    "attn_d64": (368.0e6, "profiles/attn_fwd_kernel_f16_batch4_heads32_nctx4096_d64.md"),
 }
 
 
@@ -538,7 +538,7 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
     # clock samples to say anything about the clocks.
     windows = [ms_per_step]
     spent = ms
-    while spent < 500.0 and len(windows) < 200:
+    while spent < 500.0 and len(windows) < 200 and not args.kernel_only:
         t = timed_window(ctx, step, steps, stream)
         windows.append(t / steps)
         spent += t
@@ -559,10 +559,13 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
         check_plan()
 
     # ---- result check (outside every timed region) -----------------------------------------------------------
-    check = check_result(ctx, name, w, shp, part, sets[0], step, rs_d, cs_d, info, slot_dt if fused else None, rows)
+    if args.kernel_only:
+        check = {"ok": True, "skipped": "--kernel-only"}
+    else:
+        check = check_result(ctx, name, w, shp, part, sets[0], step, rs_d, cs_d, info, slot_dt if fused else None, rows)
 
     # ---- the library GEMM of the same per-GPU problem, same run (context, not part of any timed step) ------
-    lib_ms = library_gemm_ms(ctx, w, sets, rs_d, cs_d, n_sets, out_dt) if not w.get("jit") else None
+    lib_ms = library_gemm_ms(ctx, args, w, sets, rs_d, cs_d, n_sets, out_dt, steps) if not (w.get("jit") or args.kernel_only) else None
 
     peaks = measured_peaks()
     per_gpu_flops = info["flops"]
@@ -582,7 +585,7 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
         peak, peak_src = peaks["bf16_tflops"], f"bf16_tflops (burst) of {peaks['_source']}"
         speak, speak_src = peaks.get("bf16_tflops_sustained", peak), f"bf16_tflops_sustained of {peaks['_source']}"
         if w["dtype"] == "fp8":
-            f8 = fp8_peak(ctx)
+            f8 = None if args.kernel_only else fp8_peak(ctx)
             if f8:
                 peak, peak_src = f8["burst_tflops"], "torch._scaled_mm e4m3 8192^3 (tensor-wide scales) measured in this run, best of 10"
                 speak, speak_src = f8["sustained_tflops"], "torch._scaled_mm e4m3 8192^3 measured in this run, 2 s back to back"
@@ -608,11 +611,11 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
         rec.update(lib_ms)
     if name == "cfg3":
         rec["gbps"] = roof["achieved"]
-    if fused:
+    if fused and not args.kernel_only:
         rec["exchange"] = exchange_phases(ctx, fused_op, sets, n_sets, slot_dt, m, n)
 
     # ---- end to end through the host-buffer entry point (H2D + kernel + D2H every step) -------------------
-    if headline:
+    if headline and not args.kernel_only:
         a_p, b_p = a_h.pin_memory(), b_h.pin_memory()
         c_p = torch.empty((rows, n), dtype=out_dt).pin_memory()
         e2e_steps = max(1, min(steps, 10))
@@ -670,7 +673,6 @@ def check_result(ctx: Ctx, name, w, shp, part, bufs, step, rs_d, cs_d, info, slo
             for owner in range(world):
                 idx = rows + owner * rows_owned
                 refs.append(a_d[idx].float() @ b_d.float())              # this rank's partial of owner's sampled rows
-            mine = torch.empty_like(refs[0])
             stacked = torch.stack(refs)
             out_sum = torch.empty_like(refs[0])
             dist.reduce_scatter_tensor(out_sum, stacked, op=dist.ReduceOp.SUM)   # fp32 sum of the partials: the reference
@@ -680,7 +682,6 @@ def check_result(ctx: Ctx, name, w, shp, part, bufs, step, rs_d, cs_d, info, slo
                 dist.reduce_scatter_tensor(mag, stacked.abs(), op=dist.ReduceOp.SUM)
                 extra = mag * 2.0 ** -8      # every partial is rounded to bf16 once before the sum
                 tol += " + 2^-8 of the sum of |partials| (bf16 slots)"
-            del mine
             parts.append(check_against_fp32(got_full[rows], out_sum, extra, rtol, atol))
         else:
             rows = torch.tensor(rows_to_check(m, tile_rows, 64, 17), device=ctx.dev)
@@ -704,9 +705,10 @@ def check_result(ctx: Ctx, name, w, shp, part, bufs, step, rs_d, cs_d, info, slo
         torch.backends.cuda.matmul.allow_tf32 = prev
 
 
-def library_gemm_ms(ctx: Ctx, w, sets, rs_d, cs_d, n_sets, out_dt):
-    """torch.matmul (cuBLAS) on this rank's problem, timed like the bench's own window; fp8: torch._scaled_mm with the
-    same row and column scales. Never part of a timed step of this library."""
+def library_gemm_ms(ctx: Ctx, args, w, sets, rs_d, cs_d, n_sets, out_dt, steps: int):
+    """torch.matmul (cuBLAS) on this rank's problem in both regimes this bench reports for its own kernel: `steps`
+    launches after an idle second and the same warm-up (the burst window), and a loop of about two seconds (sustained).
+    fp8: torch._scaled_mm with the same row and column scales. Never part of a timed step of this library."""
     torch = ctx.torch
     try:
         if w["dtype"] == "fp8":
@@ -715,15 +717,25 @@ def library_gemm_ms(ctx: Ctx, w, sets, rs_d, cs_d, n_sets, out_dt):
 
             def lib(i):
                 torch._scaled_mm(sets[i % n_sets][0], bt[i % n_sets], scale_a=sa, scale_b=sb, out_dtype=out_dt)
-            key = "scaled_mm_ms"
+            key = "scaled_mm"
         else:
             def lib(i):
                 torch.matmul(sets[i % n_sets][0], sets[i % n_sets][1])
-            key = "cublas_ms"
-        for i in range(3):
+            key = "cublas"
+        stream = torch.cuda.current_stream(ctx.dev)
+        lib(0)
+        ctx.barrier()
+        time.sleep(1.0)   # the bench's own first window also starts from an idle GPU
+        for i in range(args.warmup):
             lib(i)
-        ms = timed_window(ctx, lib, 20, torch.cuda.current_stream(ctx.dev)) / 20
-        return {key: ms}
+        ms = timed_window(ctx, lib, steps, stream) / steps
+        out = {key + "_ms": ms}
+        if not args.no_sustained:
+            iters = int(max(steps, math.ceil(2000.0 / max(ms, 1e-3))))
+            half = iters // 2
+            timed_window(ctx, lib, half, stream)
+            out[key + "_sustained_ms"] = timed_window(ctx, lib, iters - half, stream, first=half) / (iters - half)
+        return out
     except Exception as e:  # a library that refuses the shape is not this bench's failure
         return {"cublas_ms": None, "cublas_error": str(e)[:200]}
 
@@ -820,7 +832,7 @@ def headline_line(args, rec: dict, w: dict) -> dict:
         "config": rec["config"], "roofline": rec["roofline"], "e2e": rec.get("e2e"), "gpu_launches": rec["gpu_launches"],
         "clocks": rec["clocks"], "windows": rec["windows"], "sustained": rec["sustained"], "check": rec["check"],
     }
-    for key in ("cublas_ms", "scaled_mm_ms", "cublas_error", "gbps", "exchange"):
+    for key in ("cublas_ms", "cublas_sustained_ms", "scaled_mm_ms", "scaled_mm_sustained_ms", "cublas_error", "gbps", "exchange"):
         if key in rec:
             line[key] = rec[key]
     return line
@@ -832,7 +844,7 @@ def compact(rec: dict) -> dict:
            "frac": rec["roofline"]["frac"], "peak_source": rec["roofline"]["peak_source"], "steps": rec["steps"],
            "windows": rec["windows"], "sustained": rec["sustained"], "check": rec["check"], "clocks": rec["clocks"],
            "kernel": rec["config"]["kernel"], "per_gpu": rec["config"]["per_gpu"], "parallelism": rec["config"]["parallelism"]}
-    for key in ("cublas_ms", "scaled_mm_ms", "exchange"):
+    for key in ("cublas_ms", "cublas_sustained_ms", "scaled_mm_ms", "scaled_mm_sustained_ms", "exchange"):
         if key in rec:
             out[key] = rec[key]
     return out
@@ -965,7 +977,7 @@ def run_attention_gpu_arm(ctx: Ctx, args, name: str, w: dict) -> dict | None:
     launches = int(ctx.sum_over_ranks(A.kernel_launches() - launches0))
     ms_per_step = ms / args.steps
     windows, spent = [ms_per_step], ms
-    while spent < 500.0 and len(windows) < 200:
+    while spent < 500.0 and len(windows) < 200 and not args.kernel_only:
         t = timed_window(ctx, step, args.steps, stream)
         windows.append(t / args.steps)
         spent += t
@@ -992,13 +1004,18 @@ def run_attention_gpu_arm(ctx: Ctx, args, name: str, w: dict) -> dict | None:
         def e2e_step():
             A.attention_forward_host(q_h, k_h, v_h, w["causal"], ATTN_SM_SCALE, out=o_h)
         h2d_bytes, d2h_bytes = 3 * q.numel() * 2, q.numel() * 2
-    e2e_step()
+    if args.kernel_only:
+        e2e_steps = 0
+    else:
+        e2e_step()
     ctx.barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
         e2e_step()
     ctx.barrier()
-    e2e_s = ctx.max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+    e2e_s = ctx.max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
+    if args.kernel_only:
+        e2e_s = float("inf")
 
     peaks = measured_peaks()
     achieved = per_gpu_flops / (ms_per_step * 1e-3) / 1e12
@@ -1035,10 +1052,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="time the named workload only")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second back-to-back window")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="for profilers: warm-up and the one timed window of the named workload, nothing else "
+                         "(no further windows, sustained loop, result check, library GEMM, end-to-end or CPU leg)")
     ap.add_argument("--cpu-baseline-only", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    default_run = args.workload is None
+    default_run = args.workload is None and not args.kernel_only
+    if args.kernel_only:
+        args.no_also = args.no_sustained = args.no_cpu_baseline = True
     name = args.workload or DEFAULT_WORKLOAD
     w = WORKLOADS[name]
     rank = int(os.environ.get("RANK", "0"))

@@ -35,8 +35,10 @@ typedef struct tx_attn_problem {
 /* Asynchronous launch on `stream` (a cudaStream_t); all pointers are device pointers, 16-byte aligned.
  * `m` may be NULL when the caller does not need it (the library then writes it to a per-device scratch vector, which the
  * first such call of a size allocates: make that call before capturing a CUDA graph). Launches of one device may come from
- * several host threads; the per-device scratch and workspaces are shared, so calls that use them (m == NULL, tx_attn_bwd,
- * tx_attn_fwd_host) must not overlap on one device from different threads. */
+ * several host threads; the per-device scratch and workspaces are single buffers shared by every stream, so calls that use
+ * them (m == NULL, tx_attn_bwd, tx_attn_fwd_host) must not overlap on one device: not from different threads, and not from
+ * one thread on different streams either (two backward calls in flight would both accumulate into the one fp32 dq buffer).
+ * Order such calls on one stream, or with events. */
 TXD_API int tx_attn_fwd(const tx_attn_problem *problem, const void *q, const void *k, const void *v, void *out,
                         float *m, void *stream);
 

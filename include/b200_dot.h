@@ -82,7 +82,9 @@ typedef struct tx_dot_problem {
 
 /* Kernel configuration. Zero in a field = let the arithmetic-intensity analysis choose. */
 typedef struct tx_dot_config {
-  int32_t block_n;       /* MMA N extent per tile: 16, 32, 64, 128 or 256 */
+  int32_t block_n;       /* columns of C per tile: 16, 32, 64, 128 or 256 (the MMA's N extent), or 512 = the wide
+                            pair tile: two 256-column MMA halves per K block sharing one stage of A (CTA pairs,
+                            whole-tile schedule, one K atom per stage) */
   int32_t stages;        /* depth of the TMA shared-memory ring (2..12) */
   int32_t swap_ab;       /* 1 = compute C^T = B^T A^T (skinny m), 2 = never swap, 0 = auto */
   int32_t schedule;      /* tx_dot_schedule */
@@ -127,7 +129,10 @@ TXD_API int tx_dot_device_count(void);
 TXD_API const char *tx_dot_last_error(void);
 
 /* Validate the problem, run the tile-selection analysis for unset config fields, and allocate
- * plan-owned scratch on the current device. `cfg` may be NULL. Needs a CUDA device. */
+ * plan-owned scratch on the current device. `cfg` may be NULL. Needs a CUDA device. On failure nothing stays allocated.
+ * A plan is not thread-safe: it caches the tensor maps of the last operand pointers and rewrites them in
+ * tx_dot_run, so one plan serves one host thread at a time (create one plan per thread, or lock around the calls).
+ * Launches of one plan that use its scratch (stream-K, hybrid) must not overlap on the device either. */
 TXD_API int tx_dot_plan_create(const tx_dot_problem *problem, const tx_dot_config *cfg,
                                tx_dot_plan **out_plan);
 

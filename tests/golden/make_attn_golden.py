@@ -28,12 +28,17 @@ CASES = {
     "full_d64": (1, 2, 256, 64, False, 64, 32),
     "causal_d128_n384": (1, 1, 384, 128, True, 128, 64),
     "full_d128": (2, 1, 128, 128, False, 64, 64),
+    # the narrow heads of the reference's domain (HEAD_DIM in {16, 32, 64, 128, 256}, :589)
+    "causal_d32": (1, 2, 256, 32, True, 64, 32),
+    "full_d16_n192": (1, 2, 192, 16, False, 64, 16),   # the kernel asserts BLOCK_N <= HEAD_DIM (:175)
 }
 SM_SCALE = 0.5
 # name: (Z, H, N_CTX, HEAD_DIM, causal); the reference's backward asserts N_CTX % 128 == 0 and is causal-only
 BWD_CASES = {
     "bwd_causal_d64": (1, 2, 256, 64, True),
     "bwd_causal_d128": (1, 1, 256, 128, True),
+    "bwd_causal_d32": (1, 2, 256, 32, True),   # HEAD_DIM 16 has no forward configuration with BLOCK_N <= HEAD_DIM in the
+                                               # reference's autotuning list, so its autograd function cannot run there
 }
 
 
@@ -75,8 +80,10 @@ def main():
         print(name, "done", flush=True)
     # forward + backward through the reference's autograd function (`attention = _attention.apply`, :690). With a
     # single autotuning configuration the autotuner does not try to time kernels on a device.
-    mod._attn_fwd.configs = mod._attn_fwd.configs[:1]
+    all_configs = list(mod._attn_fwd.configs)
     for name, (z, h, n, d, causal) in BWD_CASES.items():
+        mod._attn_fwd.configs = [c for c in all_configs if c.kwargs["BLOCK_N"] <= d][:1]
+        mod._attn_fwd.cache.clear()
         torch.manual_seed(20)
         q, k, v = (torch.empty((z, h, n, d), dtype=torch.float16).normal_(mean=0.0, std=0.5).requires_grad_() for _ in range(3))
         d_o = torch.randn_like(q)

@@ -143,6 +143,7 @@ def test_cfg1_fp16_512(B, dot_lib):
 def test_cfg2_loop_split_tail(B, dot_lib):
     cfg = B.make_config(k_split_point=4096)       # BLOCK_K = 128: main [0, 4096), 64-wide remainder
     a, b, rs, cs, got = check_full_size(B, dot_lib, CFG2, 12, 2, config=cfg)
+    check_whole_matrix(CFG2, a, b, rs, cs, got)
     dev = torch.device("cuda:0")
     ad, bd = a.to(dev), b.to(dev)
     # the split point never changes a bit of the result
@@ -155,8 +156,9 @@ def test_cfg2_loop_split_tail(B, dot_lib):
     # (A B)^T = B^T A^T: swapping the operand roles accumulates in the same k order
     swapped = B.dot(bd.t(), ad.t(), out_dtype=bf16, check=True).cpu()
     assert torch.equal(bits(swapped.t().contiguous()), bits(got))
-    # pair / single / stream-K agree within tolerance (stream-K sums partial tiles in a different order)
-    for kw in (dict(cta_pair=2, schedule=1), dict(cta_pair=2, schedule=2)):
+    # pair / single / stream-K / one K atom per stage / the wide tile agree within tolerance (partial sums are formed
+    # in a different order)
+    for kw in (dict(cta_pair=2, schedule=1), dict(cta_pair=2, schedule=2), dict(atoms=1), dict(block_n=512, cta_pair=1)):
         other = B.dot(ad, bd, out_dtype=bf16, config=B.make_config(**kw), check=True).cpu()
         ok, err = tolerance_ok(other, got, 1e-2, 1e-2)
         assert ok, (kw, err)
@@ -169,13 +171,40 @@ def test_cfg3_decode_skinny(B, dot_lib):
     assert torch.equal(bits(again), bits(got)), "two runs of one plan must agree bit for bit"
 
 
+def check_whole_matrix(case, a, b, rs, cs, got):
+    """The kernel's whole C against an fp32 matmul of the same, already quantised operands upcast to fp32, in row panels
+    on the GPU (a checker: torch's fp32 GEMM with TF32 off). The oracle sample above pins the arithmetic on a few tiles;
+    this pass covers every element, so a tile written to the wrong place anywhere in the raster cannot hide."""
+    dev = torch.device("cuda:0")
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        b32 = b.to(dev).float()
+        cs_d = cs.to(dev) if cs is not None else None
+        worst = 0.0
+        for r0 in range(0, case.m, 2048):
+            r1 = min(r0 + 2048, case.m)
+            ref = a[r0:r1].to(dev).float() @ b32 * case.alpha
+            if rs is not None:
+                ref = ref * rs[r0:r1].to(dev)[:, None] * cs_d[None, :]
+            diff = (got[r0:r1].to(dev).float() - ref).abs()
+            bad = diff > case.atol + case.rtol * ref.abs()
+            assert not bool(bad.any()), f"rows {r0}..{r1}: {int(bad.sum())} elements off, max diff {float(diff.max())}"
+            worst = max(worst, float(diff.max()))
+        return worst
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 def test_cfg4_fp8_scaled(B, dot_lib):
-    check_full_size(B, dot_lib, CFG4, 6, 1)
+    a, b, rs, cs, got = check_full_size(B, dot_lib, CFG4, 6, 1)
+    check_whole_matrix(CFG4, a, b, rs, cs, got)
 
 
 def test_cfg5_big_bf16_and_n_shards(B, dot_lib):
     from triton_ext_b200.parallel import split_range
     a, b, rs, cs, got = check_full_size(B, dot_lib, CFG5, 4, 1)
+    check_whole_matrix(CFG5, a, b, rs, cs, got)
     dev = torch.device("cuda:0")
     ad, bd = a.to(dev), b.to(dev)
     # an N-shard computed alone is bit-identical to the same columns of the unsharded result

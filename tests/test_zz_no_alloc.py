@@ -110,3 +110,32 @@ def test_oversized_scratch_is_refused(B):
     b = torch.zeros(k, n, dtype=bf16, device=dev)
     run_static(B, pr, cfg, a, b, out)
     assert bool((out == 0).all())
+
+
+def test_static_entry_reports_a_wait_that_runs_out_and_recovers(B, monkeypatch):
+    """The status word of the static entry point lives inside the fixed array: a wait that runs out (the producer is
+    stalled from the host, no GPU fault is involved) must be reported by tx_dot_static_scratch_check, cleared, and a
+    healthy call on the same array straight afterwards must give the exact result."""
+    dev = torch.device("cuda:0")
+    lib = B.load_library()
+    m, n, k = 256, 512, 1024
+    g = torch.Generator().manual_seed(9)
+    a = torch.randn(m, k, generator=g).to(bf16).to(dev)
+    b = torch.randn(k, n, generator=g).to(bf16).to(dev)
+    out = torch.empty(m, n, dtype=bf16, device=dev)
+    pr = B.make_problem(m, n, k, bf16, bf16)
+    cfg = B.make_config(block_n=64, max_ctas=24)
+    s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    monkeypatch.setenv("TXD_INJECT_STALL", "1")    # read by every launch of this entry point
+    monkeypatch.setenv("TXD_WAIT_LIMIT_MS", "50")
+    rc = lib.tx_dot_run_static_scratch(ctypes.byref(pr), ctypes.byref(cfg), a.data_ptr(), b.data_ptr(), out.data_ptr(), None, None, s)
+    assert rc == B.TXD_OK
+    assert lib.tx_dot_static_scratch_check(s) == B.TXD_ERR_DEVICE_TIMEOUT
+    assert "wait ran out" in lib.tx_dot_static_scratch_last_error().decode()
+    monkeypatch.delenv("TXD_INJECT_STALL")
+    monkeypatch.delenv("TXD_WAIT_LIMIT_MS")
+    assert lib.tx_dot_static_scratch_check(s) == B.TXD_OK          # the status word was cleared by the report
+    want = B.dot(a, b, out_dtype=bf16, config=B.make_config(schedule=B.TXD_SCHED_STREAM_K, cta_pair=2, block_n=64, max_ctas=24), check=True)
+    out.fill_(float("nan"))
+    run_static(B, pr, cfg, a, b, out)
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))

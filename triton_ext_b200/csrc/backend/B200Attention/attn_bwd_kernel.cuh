@@ -48,6 +48,7 @@ struct AttnBwdParams {
   unsigned long long wait_limit_ns;
   float qk_scale, sm_scale;
   int32_t n_ctx, heads_total, kv_blocks;
+  int32_t head_dim;     // columns of q, k, v, do, dk, dv in memory (16 or 32 on the 64-wide kernel: the rest is zero fill)
   int32_t causal;
   uint32_t idesc_st;    // 128 x 128, A and B K-major          (S^T, dP^T)
   uint32_t idesc_acc;   // 128 x 64, A K-major, B MN-major      (dV, dK)
@@ -427,7 +428,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       // every MMA has completed (the last dq_full was committed after them): dV and dK of this KV block, this
       // thread's 32 columns. The TMEM loads are warp-wide; rows past n_ctx take part in them and store nothing.
       tc_fence_after();
-      const long long g = (static_cast<long long>(head) * p.n_ctx + kv_row) * kD + half * (kD / 2);
+      const int col0 = half * (kD / 2);  // first of this thread's columns
+      const long long g = (static_cast<long long>(head) * p.n_ctx + kv_row) * p.head_dim + col0;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const float scale = which == 0 ? 1.0f : p.sm_scale;
@@ -440,6 +442,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
           if (kv_row < p.n_ctx) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
+              if (col0 + c * 32 + q * 8 >= p.head_dim) continue;  // zero-fill columns of a narrow head: not in memory
               uint4 w;
               w.x = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 0]) * scale, __uint_as_float(v[q * 8 + 1]) * scale);
               w.y = pack_pair<kBf16>(__uint_as_float(v[q * 8 + 2]) * scale, __uint_as_float(v[q * 8 + 3]) * scale);

@@ -71,6 +71,12 @@ int encode_head_map(CUtensorMap *map, const void *ptr, bool bf16, long long head
   return TXD_OK;
 }
 
+// Head dimension the kernels are instantiated for. 16 and 32 run on the 64-wide kernels: the tensor maps describe
+// the real tensors, every TMA box is 64 columns wide, and the columns past head_dim arrive as zeros (out-of-bounds
+// fill) and are clipped from TMA stores. Zero columns of Q and K add nothing to Q K^T, zero columns of V and dO give
+// zero columns of O, dQ, dK and dV that are never written.
+int kernel_head_dim(int head_dim) { return head_dim <= 64 ? 64 : 128; }
+
 uint32_t attn_idesc(bool bf16, bool b_mn_major, int n) {
   const uint32_t fmt = bf16 ? 1u : 0u;
   uint32_t d = 0;
@@ -145,8 +151,8 @@ int device_state(DeviceState **out) {
 int validate(const tx_attn_problem *pr) {
   if (!pr) return afail(TXD_ERR_INVALID, "null problem");
   if (pr->batch < 1 || pr->heads < 1 || pr->n_ctx < 1) return afail(TXD_ERR_INVALID, "batch, heads and n_ctx must be >= 1");
-  if (pr->head_dim != 64 && pr->head_dim != 128)
-    return afail(TXD_ERR_UNSUPPORTED, "head_dim %d: 64 and 128 are built", pr->head_dim);
+  if (pr->head_dim != 16 && pr->head_dim != 32 && pr->head_dim != 64 && pr->head_dim != 128)
+    return afail(TXD_ERR_UNSUPPORTED, "head_dim %d: 16, 32, 64 and 128 are built (the reference also lists 256)", pr->head_dim);
   if (pr->dtype != TXD_F16 && pr->dtype != TXD_BF16) return afail(TXD_ERR_UNSUPPORTED, "dtype must be f16 or bf16");
   if (!(pr->sm_scale > 0.f)) return afail(TXD_ERR_INVALID, "sm_scale must be positive");
   if (static_cast<long long>(pr->batch) * pr->heads > 0x7fffffffLL / ((pr->n_ctx + 255) / 256))
@@ -266,10 +272,15 @@ int attn_bwd_typed(const tx_attn_problem *pr, DeviceState *st, const T *q, const
 
 // dq = cast(sm_scale * dq_acc)
 template <typename T>
-__global__ void attn_bwd_dq_convert_kernel(const float *acc, T *dq, long long count, float sm_scale) {
+__global__ void attn_bwd_dq_convert_kernel(const float *acc, T *dq, long long rows, int head_dim, float sm_scale) {
+  // acc is [rows, 64] fp32, dq [rows, head_dim] (head_dim <= 64: the accumulator's other columns are zero fill)
+  const long long count = rows * head_dim;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < count;
-       i += static_cast<long long>(gridDim.x) * blockDim.x)
-    dq[i] = from_f32<T>(acc[i] * sm_scale);
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / head_dim;
+    const int c = static_cast<int>(i - r * head_dim);
+    dq[i] = from_f32<T>(acc[r * 64 + c] * sm_scale);
+  }
 }
 
 // The fused backward (attn_bwd_kernel.cuh) between the delta pre-pass and, at head_dim 64, the dq conversion;
@@ -278,12 +289,13 @@ template <typename T>
 int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const T *k, const T *v, const T *o, const T *d_o,
                    const float *m, T *dq, T *dk, T *dv, cudaStream_t stream) {
   const bool bf16 = pr->dtype == TXD_BF16;
-  const int d = pr->head_dim;
+  const int hd = pr->head_dim;            // columns of the tensors
+  const int d = kernel_head_dim(hd);      // columns the kernels work on (the rest is zero fill)
   const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
   const long long rows = heads_total * pr->n_ctx;
   float *delta = static_cast<float *>(st->bwd_ws);
   float *dq_acc = delta + ((rows + 63) / 64) * 64;
-  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * (d / 8) + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, d);
+  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows * (hd / 8) + 255) / 256), 256, 0, stream>>>(o, d_o, delta, rows, hd);
   TXA_CUDA(cudaGetLastError());
   if (d == 64) TXA_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(rows) * 64 * sizeof(float), stream));
   unsigned long long wait_limit_ns = 2000ull * 1000 * 1000;
@@ -293,10 +305,10 @@ int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   }
   txa::AttnBwdParams prm = {};
   int rc;
-  if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_do, d_o, bf16, heads_total, pr->n_ctx, d, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, hd, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, hd, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, hd, 128))) return rc;
+  if ((rc = encode_head_map(&prm.tmap_do, d_o, bf16, heads_total, pr->n_ctx, hd, 128))) return rc;
   if (d == 64) {
     // the fp32 dq accumulator as a 3-D tensor {64, n_ctx, heads}: boxes of 32 columns (128 bytes) x 32 rows
     EncodeTiledFn enc = attn_encode_fn();
@@ -321,6 +333,7 @@ int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   prm.qk_scale = pr->sm_scale * 1.44269504f;
   prm.sm_scale = pr->sm_scale;
   prm.n_ctx = pr->n_ctx;
+  prm.head_dim = hd;
   prm.heads_total = static_cast<int32_t>(heads_total);
   prm.kv_blocks = (pr->n_ctx + 127) / 128;
   prm.causal = pr->causal ? 1 : 0;
@@ -336,7 +349,7 @@ int attn_bwd_fused(const tx_attn_problem *pr, DeviceState *st, const T *q, const
     if (bf16) txa::attn_bwd_kernel<true, 64><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
     else txa::attn_bwd_kernel<false, 64><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
     TXA_CUDA(cudaGetLastError());
-    attn_bwd_dq_convert_kernel<T><<<148 * 8, 256, 0, stream>>>(dq_acc, dq, rows * 64, pr->sm_scale);
+    attn_bwd_dq_convert_kernel<T><<<148 * 8, 256, 0, stream>>>(dq_acc, dq, rows, hd, pr->sm_scale);
     TXA_CUDA(cudaGetLastError());
   } else {
     if (bf16) txa::attn_bwd_kernel<true, 128><<<grid, txa::kBwdThreads, smem, stream>>>(prm);
@@ -422,9 +435,10 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   }
   prm.causal = pr->causal ? 1 : 0;
   prm.is_bf16 = bf16 ? 1 : 0;
-  prm.kv_stages = pr->head_dim == 128 ? 3 : 6;  // what the kernel templates use; shared memory is sized from it
+  const int kd = kernel_head_dim(pr->head_dim);
+  prm.kv_stages = kd == 128 ? 3 : 6;  // what the kernel templates use; shared memory is sized from it
   prm.idesc_qk = attn_idesc(bf16, false, 128);
-  prm.idesc_pv = attn_idesc(bf16, true, pr->head_dim);
+  prm.idesc_pv = attn_idesc(bf16, true, kd);
   if (!m) {
     // the kernel always writes M; give it a scratch row vector when the caller does not want it
     std::lock_guard<std::mutex> lock(g_state_mutex);
@@ -438,13 +452,13 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
     }
     prm.m_out = st->m;
   }
-  const size_t tile_bytes = static_cast<size_t>(128) * pr->head_dim * 2;
+  const size_t tile_bytes = static_cast<size_t>(128) * kd * 2;
   const size_t smem = 2 * tile_bytes + 2 * txa::kPBytes + prm.kv_stages * tile_bytes + sizeof(txa::AttnCtl) + 1024;
   const unsigned grid = static_cast<unsigned>(heads_total * prm.q_tiles);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (bf16 && pr->head_dim == 64) txa::attn_fwd_kernel<true, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  if (bf16 && kd == 64) txa::attn_fwd_kernel<true, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
   else if (bf16) txa::attn_fwd_kernel<true, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
-  else if (pr->head_dim == 64) txa::attn_fwd_kernel<false, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else if (kd == 64) txa::attn_fwd_kernel<false, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
   else txa::attn_fwd_kernel<false, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
   TXA_CUDA(cudaGetLastError());
   g_attn_launches.fetch_add(1);
@@ -566,7 +580,7 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   const char *force_unfused = getenv("TXA_BWD_UNFUSED");
   if (!(force_unfused && atoi(force_unfused) != 0)) {
     const size_t rows = static_cast<size_t>(pr->batch) * pr->heads * n;
-    const size_t need = ((rows + 63) / 64) * 64 * sizeof(float) + (d == 64 ? rows * 64 * sizeof(float) : 0) + 256;
+    const size_t need = ((rows + 63) / 64) * 64 * sizeof(float) + (d <= 64 ? rows * 64 * sizeof(float) : 0) + 256;
     {
       std::lock_guard<std::mutex> lock(g_state_mutex);
       if (st->bwd_ws_bytes < need) {
