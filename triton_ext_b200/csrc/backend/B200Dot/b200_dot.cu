@@ -404,24 +404,31 @@ int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
       prm.tmap_remote[r] = mk.map;
     }
   }
-  if (tc.cta_pair) {
+  {
+    // Programmatic stream serialization: this launch may be scheduled while the kernel before it in the stream is
+    // still running (as SMs become free); the kernel waits for that predecessor before it touches global memory.
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(tc.grid);
     lc.blockDim = dim3(txd::kNumThreads);
     lc.dynamicSmemBytes = tc.smem_bytes;
     lc.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+    if (tc.cta_pair) {
+      attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+      attr[n_attr].val.clusterDim.x = 2;
+      attr[n_attr].val.clusterDim.y = 1;
+      attr[n_attr].val.clusterDim.z = 1;
+      ++n_attr;
+    }
     lc.attrs = attr;
-    lc.numAttrs = 1;
-    TXD_CUDA(cudaLaunchKernelEx(&lc, prm.kind_f8 ? txd::dot_umma_pair_f8_kernel : txd::dot_umma_pair_kernel, prm));
-  } else if (prm.kind_f8) {
-    txd::dot_umma_f8_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
-  } else {
-    txd::dot_umma_kernel<<<tc.grid, txd::kNumThreads, tc.smem_bytes, stream>>>(prm);
+    lc.numAttrs = n_attr;
+    auto kernel = tc.cta_pair ? (prm.kind_f8 ? txd::dot_umma_pair_f8_kernel : txd::dot_umma_pair_kernel)
+                              : (prm.kind_f8 ? txd::dot_umma_f8_kernel : txd::dot_umma_kernel);
+    TXD_CUDA(cudaLaunchKernelEx(&lc, kernel, prm));
   }
   TXD_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
@@ -613,7 +620,7 @@ int tx_dot_run_host(tx_dot_plan *pl, const void *a_host, const void *b_host, voi
 __attribute__((visibility("default"))) int tx_dot_debug_stamps(tx_dot_plan *pl, unsigned long long *out4) {
   if (!pl || !out4) return TXD_ERR_INVALID;
   TXD_CUDA(cudaDeviceSynchronize());
-  TXD_CUDA(cudaMemcpy(out4, reinterpret_cast<char *>(pl->status) + 64, 32, cudaMemcpyDeviceToHost));
+  TXD_CUDA(cudaMemcpy(out4, reinterpret_cast<char *>(pl->status) + 64, 48, cudaMemcpyDeviceToHost));  // 6 words
   return TXD_OK;
 }
 #endif

@@ -178,7 +178,21 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
         if (cfg.cta_pair == 2 && pair) continue;
         // 512 columns = the wide pair tile: two 256-column MMA halves per K block sharing one P stage.
         if (bn == 512 && !pair) continue;
-        if (bn == 512 && cfg.block_n != 512) continue;  // TEMP: explicit only until calibrated
+        // Unasked, the wide tile is taken only where it was measured to win: tensor-bound problems that it tiles
+        // without padding and in no more machine time than 256-column tiles do (one wave of wide tiles lasts two
+        // waves of narrow ones). There it runs 2.4 % faster (4096 x 4096 x 4160, 8192^3); half a narrow wave of extra
+        // quantisation (the column panels of a sharded GEMM) costs it that gain.
+        bool wide_auto = false;
+        if (bn == 512 && cfg.block_n != 512) {
+          if (cfg.atoms > 1 || (cfg.schedule && cfg.schedule != TXD_SCHED_DATA_PARALLEL)) continue;
+          if (out.hbm_bound || q_extent % 512 != 0 || p_extent % 256 != 0) continue;
+          const int pairs = max_grid / 2;
+          if (pairs < 1) continue;
+          const int tiles_w = (p_extent / 256) * (q_extent / 512), tiles_n = 2 * tiles_w;
+          const int waves_w = cdiv(tiles_w, std::min(pairs, tiles_w)), waves_n = cdiv(tiles_n, std::min(pairs, tiles_n));
+          if (2 * waves_w > waves_n) continue;
+          wide_auto = true;
+        }
         const int mma_n = bn == 512 ? 256 : bn;
         if (pair) {
           // Each CTA of a pair holds half of the Q tile, in whole 128-byte-wide boxes when Q is
@@ -195,7 +209,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
           // Two atoms per stage halve the per-block handshakes but also the ring depth: keep >= 3 stages.
           const int q_rows_cta = pair ? bn / 2 : bn;
           const int stage = atoms * (128 * 128 + round_up((q_mn ? round_up(q_rows_cta, bk) : q_rows_cta) * 128, 1024));
-          const int staging = (!swap && bn >= 64) ? 4 * 2 * 32 * 128 : 0;
+          const int staging = (!swap && bn >= 64) ? 4 * 2 * 32 * 128 /* two 4 KiB staging slabs per epilogue warp */ : 0;
           if (atoms >= 2 && (mm.smem_budget - staging) / stage < 3) continue;
           if (atoms >= 2 && pr.k < 4 * atoms * bk) continue;
         }
@@ -215,6 +229,8 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
             if (tiles < workers || tail == 0 || (long long)tail * k_blocks < workers) continue;
           }
           double t = model_seconds(mm, es, p_extent, q_extent, pr.k, bn, p_mn_c, q_mn, pair != 0, atoms, sched, workers, algo);
+          if (wide_auto)  // priced from the measurement: the two-atom 256-column tile's time, less 2.4 %
+            t = model_seconds(mm, es, p_extent, q_extent, pr.k, 256, p_mn_c, q_mn, true, 2, sched, std::min(max_workers, 2 * tiles), algo) * 0.93 * 0.976;
           // Prefer the simpler schedule on near-ties, and the role assignment that pads less: zero
           // rows still cost shared-memory fill and tensor cycles even when HBM time hides them.
           // Pure stream-K also spreads concurrently running tiles over the whole matrix (worse L2 reuse).
@@ -285,7 +301,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
   // C goes out through a shared-memory slab + TMA store when its rows are 16-byte aligned.
   const int os = elem_bytes(pr.out_dtype);
   out.tma_store = (!out.swap_ab && out.block_n >= 64 && (pr.ldc * os) % 16 == 0) ? 1 : 0;  // whole 128-byte slabs
-  const int staging = out.tma_store ? 4 * 2 * 32 * 128 : 0;
+  const int staging = out.tma_store ? 4 * 2 * 32 * 128 /* two 4 KiB staging slabs per epilogue warp */ : 0;
   int stages = cfg.stages ? cfg.stages : std::min(12, (mm.smem_budget - staging) / stage_bytes);
   if (stages < 2 || stages > 12 || stages * stage_bytes + staging > mm.smem_budget) {
     if (why) *why = "stages out of range for this tile (2..12, ring must fit shared memory)";

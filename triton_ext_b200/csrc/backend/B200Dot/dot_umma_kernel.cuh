@@ -6,7 +6,8 @@
 //                        over a hundred nanoseconds; two issuing warps halve the time to fill a stage)
 //   warp 1 (one lane)  : tcgen05.mma issuer — accumulates in TMEM (fp32), two accumulators so the
 //                        epilogue of segment i overlaps the main loop of segment i+1
-//   warps 3..6         : epilogue — tcgen05.ld TMEM -> registers, fused scale + cast, global store
+//   warps 3..6         : epilogue — tcgen05.ld TMEM -> registers, fused scale + cast, global store; a warp may read
+//                        the 32 TMEM lanes of its quarter (warp index mod 4)
 //
 // The K loop is executed the way the LoopSplit pass leaves it (reference:
 // pass/LoopSplit/LoopSplit.cpp:179-193): an unpredicated main loop over [0, k_main_blocks) and a
@@ -58,10 +59,14 @@ constexpr int kStageRowBytes = 128;   // one K atom = 128 bytes of K per row (on
                                       // a stage (K block) holds 1 or 2 atoms
 constexpr int kMmasPerAtom = 4;       // 128 B / 32 B per tcgen05.mma
 constexpr int kMaxStages = 12;
-constexpr int kNumThreads = 224;
-constexpr int kEpilogueThreads = 128;
+// One epilogue warp per TMEM lane quarter. Eight (two per quarter, columns split) were measured: the epilogue got
+// shorter, but the MMA warp shares its scheduler with the quarter-1 epilogue warps and its issue loop slowed from 525
+// to 562 cycles per K block, a net loss on every shape.
+constexpr int kEpilogueWarps = 4;
+constexpr int kNumThreads = 96 + kEpilogueWarps * 32;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kStoreSlabBytes = 32 * 128;  // one epilogue warp's staging slab: 32 rows x 128 bytes
-constexpr int kStoreStagingBytes = 4 * 2 * kStoreSlabBytes;  // 4 warps, double-buffered
+constexpr int kStoreStagingBytes = kEpilogueWarps * 2 * kStoreSlabBytes;  // double-buffered
 
 enum DeviceStatus : uint32_t {
   kDevOk = 0,
@@ -332,6 +337,8 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
                                               uint32_t staging, int warp, int lane, int worker, int workers,
                                               uint32_t cta_rank) {
   const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+  constexpr int kGroups = kEpilogueWarps / 4;   // warps per TMEM lane quarter; they take alternate column slabs
+  const int group = (warp - 3) >> 2;
   const int row_in_tile = quarter * 32 + lane;  // accumulator row held by this thread
   const int epi_tid = (warp - 3) * 32 + lane;
   const uint32_t tmem_base = ctl->tmem_base;
@@ -339,9 +346,10 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
   const long long total_units = static_cast<long long>(p.tiles_p * p.tiles_q - sk_tile0) * p.k_blocks;
   const int ranks = kPair ? 2 : 1;  // each CTA of a pair parks and combines its own 128 rows
   const int rows_per_tile = kPair ? 2 * kBlockM : kBlockM;
-  const uint32_t my_slabs = staging + static_cast<uint32_t>(quarter) * 2u * kStoreSlabBytes;
-  const int slab_cols = p.out_dtype == 3 ? 32 : 64;  // 128 bytes of output per slab row
+  const uint32_t my_slabs = staging + static_cast<uint32_t>(warp - 3) * 2u * kStoreSlabBytes;
   uint32_t stores = 0;                               // TMA stores issued by this warp (slab parity)
+  const int slab_cols = p.out_dtype == 3 ? 32 : 64;  // 128 bytes of output per slab row
+  const bool scaled = p.scale_row != nullptr || p.scale_col != nullptr || p.alpha != 1.0f;
   // A wide tile is drained as two 256-column halves, one per TMEM accumulator: to this role they are
   // two consecutive segments, so accumulator index and barrier phase follow the same arithmetic.
   const int halves = (kPair && p.wide) ? 2 : 1;
@@ -386,22 +394,27 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
     };
     const bool whole = (s.kb1 - s.kb0) == p.k_blocks;
     if (whole && p.tma_store && kChunk == 32) {
-      // TMEM -> registers -> swizzled slab -> TMA store; each warp owns 32 rows and two slabs.
-      for (int c0 = 0; c0 < p.block_n; c0 += slab_cols) {
+      // TMEM -> registers -> swizzled slab -> TMA store; a warp owns 32 rows and two staging slabs. Both 32-column
+      // loads of a slab are in flight before one wait, and the values are scaled before the wait for the store that
+      // last read the slab, so that wait overlaps the register work.
+      for (int c0 = group * slab_cols; c0 < p.block_n; c0 += kGroups * slab_cols) {
         const uint32_t slab = my_slabs + (stores & 1u) * kStoreSlabBytes;
+        uint32_t v[2][32];
+        tmem_ld_32x32(taddr + c0, v[0]);
+        if (slab_cols == 64) tmem_ld_32x32(taddr + c0 + 32, v[1]);
+        tmem_ld_wait();
+        float f[2][32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (h == 1 && slab_cols != 64) break;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[h][j] = __uint_as_float(v[h][j]);
+          if (scaled) scale_chunk<32>(p, f[h], prow, qcol_tile + c0 + 32 * h);
+        }
         if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this slab has drained
         __syncwarp();
-        for (int h = 0; h < slab_cols; h += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c0 + h, v);
-          tmem_ld_wait();
-          float f[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          scale_chunk<32>(p, f, prow, qcol_tile + c0 + h);
-          stage_chunk(slab, lane, h * (p.out_dtype == 3 ? 4 : 2), f, p.out_dtype);
-        }
-        if (c0 + slab_cols >= p.block_n) release_accumulator();
+        stage_chunk(slab, lane, 0, f[0], p.out_dtype);
+        if (slab_cols == 64) stage_chunk(slab, lane, 64, f[1], p.out_dtype);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0 && !TXD_DBG(p, 4)) {
@@ -416,15 +429,16 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
         }
         ++stores;
       }
+      release_accumulator();
     } else if (whole) {
-      for (int c0 = 0; c0 < p.block_n; c0 += kChunk) {
+      for (int c0 = group * kChunk; c0 < p.block_n; c0 += kGroups * kChunk) {
         uint32_t v[32];
         if (kChunk == 32) tmem_ld_32x32(taddr + c0, v); else tmem_ld_32x16(taddr + c0, v);
         tmem_ld_wait();
         float f[32];
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) f[j] = __uint_as_float(v[j]);
-        scale_chunk<kChunk>(p, f, prow, qcol_tile + c0);
+        if (scaled) scale_chunk<kChunk>(p, f, prow, qcol_tile + c0);
         store_chunk_direct<kChunk>(p, f, prow, qcol_tile + c0);
       }
       release_accumulator();
@@ -435,7 +449,7 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
       const int my_first_tile = sk_tile0 + static_cast<int>((total_units * worker / workers) / p.k_blocks);
       const int slot = (worker * 2 + (s.tile == my_first_tile ? 0 : 1)) * ranks + static_cast<int>(cta_rank);
       float *mine = p.partials + static_cast<long long>(slot) * p.block_n * kBlockM;
-      for (int c0 = 0; c0 < p.block_n; c0 += kChunk) {
+      for (int c0 = group * kChunk; c0 < p.block_n; c0 += kGroups * kChunk) {
         uint32_t v[32];
         if (kChunk == 32) tmem_ld_32x32(taddr + c0, v); else tmem_ld_32x16(taddr + c0, v);
         tmem_ld_wait();
@@ -462,7 +476,7 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
       epilogue_bar_sync();  // fixup_last may be rewritten by the next partial segment
       if (last) {
         __threadfence();
-        for (int c0 = 0; c0 < p.block_n; c0 += kChunk) {
+        for (int c0 = group * kChunk; c0 < p.block_n; c0 += kGroups * kChunk) {
           float f[32];
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) f[j] = 0.0f;
@@ -490,6 +504,15 @@ __device__ __forceinline__ void epilogue_role(const DotParams &p, SharedCtl *ctl
 
 template <bool kPair, bool kF8>
 __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
+#ifdef TXD_MEASURE
+  // Measurement builds: SM cycles and wall time of CTA 0 from kernel entry to exit, so that cycles per K block and
+  // the effective SM clock of a launch can be told apart (and the set-up cost read off).
+  unsigned long long stamp_c0 = 0, stamp_n0 = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    stamp_c0 = clock64();
+    stamp_n0 = global_timer_ns();
+  }
+#endif
   extern __shared__ uint8_t smem_raw[];
   // Stage buffers need 1024-byte alignment (SWIZZLE_128B atoms); the launch asks for 1 KiB of slack.
   // The pad is the same in every CTA of the grid, so both CTAs of a pair use the same offsets.
@@ -529,7 +552,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&ctl->tmem_empty_bar[a]), kPair ? 8 : 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&ctl->tmem_empty_bar[a]), (kPair ? 2 : 1) * kEpilogueWarps);  // one arrival per epilogue warp
     }
     mbar_init(smem_u32(&ctl->drain_bar), 1);
     ctl->abort_flag = 0;
@@ -548,13 +571,16 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
   if (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+  // Everything above touched only this CTA's shared and tensor memory and the kernel's parameters. From here on
+  // global memory is read and written, so a launch that was allowed to start before its predecessor in the stream
+  // had finished (programmatic dependent launch) waits for it here; and the launch behind this one may start its
+  // own set-up now. Back-to-back launches of short GEMMs then pay their launch and set-up latency once.
+  grid_dep_launch();
+  grid_dep_wait();
 #ifdef TXD_MEASURE
-  // Measurement builds: SM cycles and wall time of CTA 0, so that cycles per K block and the effective SM
-  // clock of a launch can be told apart.
-  unsigned long long stamp_c0 = 0, stamp_n0 = 0;
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    stamp_c0 = clock64();
-    stamp_n0 = global_timer_ns();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {   // set-up (barriers, TMEM, cluster sync) is over
+    reinterpret_cast<unsigned long long *>(p.status)[12] = clock64();
+    reinterpret_cast<unsigned long long *>(p.status)[13] = global_timer_ns();
   }
 #endif
 

@@ -149,9 +149,16 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&v)[32])
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void epilogue_bar_sync() {
+__device__ __forceinline__ void epilogue_bar_sync() {  // the four epilogue warps of the tt.dot kernel
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
+
+// Programmatic dependent launch. `grid_dep_launch` lets a grid that was launched behind this one with the
+// programmatic-serialization attribute be scheduled (its CTAs take SMs as they become free and run their set-up);
+// `grid_dep_wait` blocks until every grid this one depends on has completed and its memory is visible. Both are
+// no-ops for launches without the attribute.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // One lane of a converged warp (the rest of the warp executes the same control flow, so addresses and
 // descriptors stay warp-uniform and can live in uniform registers).
