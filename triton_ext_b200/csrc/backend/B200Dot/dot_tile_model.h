@@ -185,6 +185,7 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
         bool wide_auto = false;
         if (bn == 512 && cfg.block_n != 512) {
           if (cfg.atoms > 1 || (cfg.schedule && cfg.schedule != TXD_SCHED_DATA_PARALLEL)) continue;
+          if (es != 2) continue;  // 8-bit operands: measured slower than 256-column tiles with two atoms per stage (8192^3 e4m3)
           if (out.hbm_bound || q_extent % 512 != 0 || p_extent % 256 != 0) continue;
           const int pairs = max_grid / 2;
           if (pairs < 1) continue;
