@@ -188,6 +188,67 @@ def test_loop_split_text_entry_point(built_libs):
         assert k == 0 and same == variant
 
 
+def test_loop_split_text_scopes_names_per_function_and_balances_while_regions(built_libs):
+    """SSA names repeat from one tt.func to the next: the step constant (and, for the mask form, every definition) of a
+    loop must be looked up in the function that holds the loop. And `} do {` of an scf.while closes one region and opens
+    the next, like `} else {`: a loop behind a while must still be found, and its end must be the right brace."""
+    lib = P.load_plugin(P.plugin_path("loop_split"))
+    lib.tx_loop_split_text.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                       ctypes.POINTER(ctypes.c_int32)]
+    lib.tx_loop_split_free.argtypes = [ctypes.c_void_p]
+
+    def run(text: str, mode: int = 1):
+        o, k = ctypes.c_void_p(), ctypes.c_int32(-1)
+        assert lib.tx_loop_split_text(text.encode(), mode, ctypes.byref(o), ctypes.byref(k)) == 0
+        try:
+            return ctypes.string_at(o).decode(), k.value
+        finally:
+            lib.tx_loop_split_free(o)
+
+    def func(name, step):
+        return (f"  tt.func public @{name}(%lo: i32, %hi: i32, %mid: i32, %z: i32) {{\n"
+                f"    %c = arith.constant {step} : i32\n"
+                "    %r = scf.for %i = %lo to %hi step %c iter_args(%acc = %z) -> (i32)  : i32 {\n"
+                "      %p = arith.cmpi sge, %i, %mid : i32\n"
+                "      %s = arith.select %p, %i, %acc : i32\n"
+                "      scf.yield %s : i32\n"
+                "    }\n"
+                "    tt.return\n"
+                "  }\n")
+    # as-written mode writes the step into the text (-step for sge): each function must get its own %c
+    text, k = run("module {\n" + func("f", 4) + func("g", 16) + "}\n")
+    assert k == 2
+    first, second = text.split("tt.func public @g")
+    assert "arith.constant -4 : i32" in first and "arith.constant -16 : i32" not in first
+    assert "arith.constant -16 : i32" in second and "arith.constant -4 : i32" not in second
+    # a loop in a function whose step is only defined in ANOTHER function is not split (no constant step in scope)
+    stray = func("f", 4) + func("g", 16).replace("    %c = arith.constant 16 : i32\n", "").replace("(%lo: i32,", "(%c: i32, %lo: i32,")
+    text, k = run("module {\n" + stray + "}\n")
+    assert k == 1 and text.count("scf.for") == 3
+    # scf.while before the loop: `} do {` must not unbalance the region count
+    while_loop = ("  %w = scf.while (%a = %z) : (i32) -> i32 {\n"
+                  "    %cond = arith.cmpi slt, %a, %hi : i32\n"
+                  "    scf.condition(%cond) %a : i32\n"
+                  "  } do {\n"
+                  "  ^bb0(%b: i32):\n"
+                  "    %n = arith.addi %b, %b : i32\n"
+                  "    scf.yield %n : i32\n"
+                  "  }\n")
+    loop = ("  %c4 = arith.constant 4 : i32\n"
+            "  %r = scf.for %i = %lo to %hi step %c4 iter_args(%acc = %w) -> (i32)  : i32 {\n"
+            "    %p = arith.cmpi slt, %i, %mid : i32\n"
+            "    %s = arith.select %p, %i, %acc : i32\n"
+            "    scf.yield %s : i32\n"
+            "  }\n")
+    text, k = run(while_loop + loop, 0)
+    assert k == 1 and text.count("scf.for") == 2 and text.count("scf.while") == 1
+    # a loop INSIDE the while's body is found as well, and the while's closing brace stays where it was
+    nested = while_loop.replace("    %n = arith.addi %b, %b : i32\n", loop.replace("\n  ", "\n    ").replace("  %c4", "    %c4", 1)
+                                .replace("%acc = %w", "%acc = %b") + "    %n = arith.addi %r, %b : i32\n")
+    text, k = run(nested, 0)
+    assert k == 1 and text.count("scf.for") == 2 and text.rstrip().endswith("}")
+
+
 def test_loop_split_text_peels_masked_remainder(built_libs):
     """The mask form through the C-ABI: tensor compares of (splat iv + range) with a splat bound."""
     lib = P.load_plugin(P.plugin_path("loop_split"))

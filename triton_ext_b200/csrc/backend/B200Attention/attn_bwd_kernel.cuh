@@ -240,21 +240,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
     };
     auto issue_st = [&](int it) {  // S^T = K Q^T
       const uint32_t q_addr = stage_q(it);
+      if (issuer) {
 #pragma unroll
-      for (int i = 0; i < kD / 16; ++i)
-        if (issuer)
+        for (int i = 0; i < kD / 16; ++i)
           umma_f16(tmem_base + kColSt, desc64(desc_hi, (lo_of(k_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(q_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
+      }
       if (issuer) tc_commit(smem_u32(&ctl->s_full));
       __syncwarp();
     };
     auto issue_dp = [&](int it) {  // dP^T = V dO^T
       const uint32_t do_addr = stage_q(it) + kBwdTileBytes;
+      if (issuer) {
 #pragma unroll
-      for (int i = 0; i < kD / 16; ++i)
-        if (issuer)
+        for (int i = 0; i < kD / 16; ++i)
           umma_f16(tmem_base + kColDp, desc64(desc_hi, (lo_of(v_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(do_addr) | lbo_unused) + kmajor_step(i)), p.idesc_st, i > 0 ? 1u : 0u);
+      }
       if (issuer) tc_commit(smem_u32(&ctl->dp_full));
       __syncwarp();
     };
@@ -271,11 +273,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       // dV += P^T dO, then the next block's scores (the compute warps hold S^T(it) in registers by now)
       if (!warp_mbar_poll(smem_u32(&ctl->pt_full), ph, ac, kAttnTimeoutMmaP, lane)) break;
       tc_fence_after();
+      if (issuer) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (issuer)
+        for (int i = 0; i < 8; ++i)
           umma_f16(tmem_base + kColDv, desc64(desc_hi, (lo_of(pt_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(do_addr) | lbo_atom) + mn_step(i)), p.idesc_acc, (it > 0 || i > 0) ? 1u : 0u);
+      }
       __syncwarp();
       if (kStagesT > 1 && it + 1 < n_it) {
         if (!wait_stage(it + 1)) break;
@@ -285,16 +288,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attn_bwd_kernel(const __grid_c
       if (!warp_mbar_poll(smem_u32(&ctl->ds_full), ph, ac, kAttnTimeoutMmaP, lane)) break;
       if (kWithDq && it > 0 && !warp_mbar_poll(smem_u32(&ctl->dq_free), ph ^ 1u, ac, kAttnTimeoutMmaP, lane)) break;
       tc_fence_after();
+      if (issuer) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (issuer)
+        for (int i = 0; i < 8; ++i)
           umma_f16(tmem_base + kColDk, desc64(desc_hi, (lo_of(ds_addr) | lbo_unused) + kmajor_step(i)),
                    desc64(desc_hi, (lo_of(q_addr) | lbo_atom) + mn_step(i)), p.idesc_acc, (it > 0 || i > 0) ? 1u : 0u);
+      }
+      if (issuer) {
 #pragma unroll
-      for (int i = 0; i < (kWithDq ? 8 : 0); ++i)
-        if (issuer)
+        for (int i = 0; i < (kWithDq ? 8 : 0); ++i)
           umma_f16(tmem_base + kColDq, desc64(desc_hi, (lo_of(ds_addr) | lbo_atom) + mn_step(i)),
                    desc64(desc_hi, (lo_of(k_addr) | lbo_atom) + mn_step(i)), p.idesc_dq, i > 0 ? 1u : 0u);
+      }
       if (issuer) {
         tc_commit(smem_u32(&ctl->dq_full));
         tc_commit(smem_u32(&ctl->empty[slot]));

@@ -314,27 +314,33 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const uint32_t qa = lo_of(q_addr0 + t * tile_bytes) | kmajor_lbo;
         const uint32_t ka = lo_of(kv_addr0 + k_slot * tile_bytes) | kmajor_lbo;
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(t) * 128u;
+        // One divergent region for the whole batch: the issuing lane's instruction stream is what paces the tensor
+        // pipe (about 43 cycles per MMA when lean, 60 with a branch and a reconvergence around every MMA).
+        if (issuer) {
 #pragma unroll
-        for (int i = 0; i < D / 16; ++i) {
-          const uint32_t step = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
-          if (issuer) umma_f16(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk, i > 0 ? 1u : 0u);
+          for (int i = 0; i < D / 16; ++i) {
+            const uint32_t step = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
+            if (i == 0) umma<false, false>(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk, 0u);
+            else umma_acc<false, false>(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk);
+          }
+          tc_commit(smem_u32(&ctl->s_full[t]));
         }
-        if (issuer) tc_commit(smem_u32(&ctl->s_full[t]));
         __syncwarp();
       };
       auto issue_pv = [&](int t, uint32_t v_slot, bool accumulate) {  // O_t += P_t V : 8 MMAs of 128 x head_dim x 16
         const uint32_t pa = lo_of(p_addr0 + t * kPBytes) | kmajor_lbo;
         const uint32_t va = lo_of(kv_addr0 + v_slot * tile_bytes) | v_lbo;
         const uint32_t d_tmem = tmem_base + 256u + static_cast<uint32_t>(t) * 128u;
+        if (issuer) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint32_t pstep = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
-          const uint32_t vstep = static_cast<uint32_t>(i) * (16u * 128u >> 4);  // 16 KV rows of 128 bytes
-          if (issuer)
-            umma_f16(d_tmem, desc64(desc_hi, pa + pstep), desc64(desc_hi, va + vstep), idesc_pv,
-                     (accumulate || i > 0) ? 1u : 0u);
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t pstep = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
+            const uint32_t vstep = static_cast<uint32_t>(i) * (16u * 128u >> 4);  // 16 KV rows of 128 bytes
+            if (i == 0) umma<false, false>(d_tmem, desc64(desc_hi, pa + pstep), desc64(desc_hi, va + vstep), idesc_pv, accumulate ? 1u : 0u);
+            else umma_acc<false, false>(d_tmem, desc64(desc_hi, pa + pstep), desc64(desc_hi, va + vstep), idesc_pv);
+          }
+          tc_commit(smem_u32(&ctl->o_done[t]));
         }
-        if (issuer) tc_commit(smem_u32(&ctl->o_done[t]));
         __syncwarp();
       };
       auto release = [&](uint32_t slot) {
