@@ -11,7 +11,8 @@
  * Accepted loops are the reference's (LoopSplit.cpp:107-144): a positive constant step; an arith.cmpi with
  * predicate slt / sle / sgt / sge or the unsigned forms on the induction variable; the other operand defined
  * outside the loop; the first such compare in the body decides the split. Loops nested in a loop that is not
- * split are looked at too.
+ * split are looked at too. Constants and definitions are resolved among the lines of the tt.func that holds the loop
+ * (SSA names repeat from function to function).
  *
  * Beyond the reference (its LoopSplit.cpp:105 leaves "mask logic" as a TODO), in TXLS_INTENT mode only: a loop with
  * no such scalar compare but with tensor compares of the form
@@ -37,7 +38,12 @@ extern "C" {
 typedef enum tx_loop_split_mode {
   /* mid = min(lo + ceildiv(max(T - lo, 0), step) * step, max(hi, lo)), T = comparand (slt, sge) or comparand + 1
    * (sle, sgt); a compare with the induction variable on the right is read with the swapped predicate. Keeps the
-   * meaning of the loop for every bound. */
+   * meaning of the loop for every bound whose distance from lo (plus one, plus a step) stays inside the induction type.
+   * Unsigned predicates (ult, ule, ugt, uge) are monotone in the induction variable only while that is non-negative:
+   * such a compare is split only when the loop's lower bound is a constant >= 0, and the emitted mid point is
+   * guarded at run time: a comparand with its sign bit set (an unsigned value above every non-negative induction
+   * value) gives mid = hi, so the whole range stays in the first copy, where the compare has its one value.
+   * With any other lower bound an unsigned compare is left alone (the loop may still be split on a later compare). */
   TXLS_INTENT = 0,
   /* Exactly the operations the reference emits (LoopSplit.cpp:147-190): the comparand as mid point, +step / -step
    * for sle / sge, `mid_diff += step - mid_diff % step` when the step is not 1, no clamping, the inverted

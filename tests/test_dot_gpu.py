@@ -229,11 +229,13 @@ def test_run_host_matches_device_path(B):
 
 
 @pytest.mark.parametrize("m,n,a_col_major,b_col_major", [(2048, 4096, False, False), (3000, 4096, False, True),
+                                                         (4096, 2048, False, False), (4096, 3000, False, True),
                                                          (2048, 4096, True, False), (2048, 3000, True, False),
                                                          (2048, 4096, True, True)])
 def test_run_host_pipelined_panels(B, m, n, a_col_major, b_col_major):
     """Above 32 MB the host-buffer entry point cuts one operand and C into panels (rows of A and C when A is
-    row-major, else columns of B and C) and overlaps copy-in, kernel and copy-out on three streams. Same schedule forced on both paths: the panels must reproduce the one-launch
+    row-major and not the smaller operand, else columns of B and C: the smaller operand travels whole, first) and
+    overlaps copy-in, kernel and copy-out on three streams. Same schedule forced on both paths: the panels must reproduce the one-launch
     result bit for bit (every output element sums the same K blocks in the same order)."""
     k = 4096            # every case moves more than 32 MB
     g = torch.Generator().manual_seed(77)

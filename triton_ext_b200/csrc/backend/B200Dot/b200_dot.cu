@@ -463,9 +463,14 @@ constexpr int kMaxHostPanels = 8;
 
 // The host-buffer path is dominated by its copies (PCIe), so above 32 MB they are overlapped with the kernels:
 // one operand goes to the device whole, the other one and C are cut into panels; panel j+1 travels to the device
-// while panel j is multiplied and panel j-1 travels back. Panels are rows of A and C when A is row-major (both
-// panels are then contiguous in host memory, which the copy engines move fastest), else columns of B and C.
-bool host_panels_by_rows(const tx_dot_problem &pr) { return pr.a_layout == TXD_ROW_MAJOR; }
+// while panel j is multiplied and panel j-1 travels back.
+// The operand that travels whole comes first and delays the first kernel, so it should be the smaller one: rows of A
+// and C are the panels when A is row-major (contiguous panels) and B is not the bigger operand; otherwise columns of B and
+// C (contiguous for a column-major B, strided 2-D copies for a row-major one).
+bool host_panels_by_rows(const tx_dot_problem &pr) {
+  const long long a_elems = static_cast<long long>(pr.m) * pr.k, b_elems = static_cast<long long>(pr.k) * pr.n;
+  return pr.a_layout == TXD_ROW_MAJOR && b_elems <= a_elems;
+}
 
 int host_panels(const tx_dot_problem &pr) {
   const long long es = txd::elem_bytes(pr.ab_dtype), os = txd::elem_bytes(pr.out_dtype);
