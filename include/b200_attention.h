@@ -25,7 +25,9 @@ extern "C" {
 typedef struct tx_attn_problem {
   int32_t batch, heads; /* Z, H of the reference launch                                             */
   int32_t n_ctx;        /* sequence length; any value >= 1 (the reference asks for multiples of BLOCK_M) */
-  int32_t head_dim;     /* 64 or 128 (reference: {16, 32, 64, 128, 256}, :589)                       */
+  int32_t head_dim;     /* 16, 32, 64, 128 or 256 (the reference's list, :589). 64 and 128: fused     */
+                        /* kernels; 16 and 32: the 64-wide kernels, zero-filled; 256: a composition of */
+                        /* the tt.dot GEMM kernels around a row softmax (slow)                         */
   int32_t dtype;        /* TXD_F16 or TXD_BF16 for q, k, v and out                                   */
   int32_t causal;       /* 0 / 1                                                                     */
   float sm_scale;       /* > 0; scores are scaled by sm_scale * log2(e) and exponentiated in base 2   */

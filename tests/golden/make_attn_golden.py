@@ -30,13 +30,15 @@ CASES = {
     "full_d128": (2, 1, 128, 128, False, 64, 64),
     # the narrow heads of the reference's domain (HEAD_DIM in {16, 32, 64, 128, 256}, :589)
     "causal_d32": (1, 2, 256, 32, True, 64, 32),
-    "full_d16": (1, 2, 256, 16, False, 64, 16),         # the kernel asserts BLOCK_N <= HEAD_DIM (:175)
+    "full_d16": (1, 2, 256, 16, False, 64, 16),      # the kernel asserts BLOCK_N <= HEAD_DIM (:175)
+    "causal_d256": (1, 1, 256, 256, True, 64, 64),
 }
 SM_SCALE = 0.5
 # name: (Z, H, N_CTX, HEAD_DIM, causal); the reference's backward asserts N_CTX % 128 == 0 and is causal-only
 BWD_CASES = {
     "bwd_causal_d64": (1, 2, 256, 64, True),
     "bwd_causal_d128": (1, 1, 256, 128, True),
+    "bwd_causal_d256": (1, 1, 128, 256, True),
     "bwd_causal_d32": (1, 2, 256, 32, True),   # HEAD_DIM 16 has no forward configuration with BLOCK_N <= HEAD_DIM in the
                                                # reference's autotuning list, so its autograd function cannot run there
 }

@@ -62,6 +62,8 @@ SHAPES = [
     (2, 2, 333, 128),
     (1, 2, 512, 32),      # narrow heads of the reference's domain: run on the 64-wide kernel, zero-filled by TMA
     (2, 1, 300, 16),
+    (1, 2, 384, 256),     # the widest head of the reference's list: a composition of tt.dot GEMMs around a row softmax
+    (1, 1, 200, 256),
 ]
 
 
@@ -154,7 +156,7 @@ def test_host_buffers_in_groups(A):
 
 def test_rejected_arguments(A):
     from triton_ext_b200 import backend as B
-    for bad_d in (256, 48):   # 256 is in the reference's list but not built here; 48 is in neither
+    for bad_d in (512, 48):   # neither is in the reference's list {16, 32, 64, 128, 256}
         q = torch.zeros((1, 1, 128, bad_d), dtype=f16, device="cuda")
         with pytest.raises(B.DotError) as e:
             A.attention_forward(q, q, q, True, 0.5)
@@ -206,7 +208,8 @@ def test_backward_matches_reference_kernel_outputs(A, name):
 @pytest.mark.parametrize("dtype", [f16, bf16])
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("z,h,n,d", [(1, 2, 1024, 64), (2, 2, 384, 128), (1, 2, 200, 64), (1, 1, 128, 128),
-                                     (1, 2, 333, 128), (1, 1, 4224, 64), (1, 2, 640, 32), (2, 1, 200, 16)])
+                                     (1, 2, 333, 128), (1, 1, 4224, 64), (1, 2, 640, 32), (2, 1, 200, 16),
+                                     (1, 2, 256, 256)])
 def test_autograd_function_against_oracle(A, z, h, n, d, causal, dtype):
     """`attention(q, k, v, causal, sm_scale)` as the reference exposes it (`_attention.apply`): forward and backward
     through autograd, against fp32 autograd of the eager formula, atol 1e-2 as in the reference's test_op."""

@@ -110,6 +110,9 @@ struct DeviceState {
   cudaEvent_t bwd_fork = nullptr, bwd_join[4] = {};
   int bwd_n = 0, bwd_d = 0, bwd_dtype = -1;
   float bwd_scale = 0.f;
+  // forward as a composition of tt.dot GEMMs (head_dim 256): per lane Q K^T (fp32) and P V with the 1 / l row scale
+  tx_dot_plan *fwd_plan[2 * 4] = {};
+  int fwd_n = 0, fwd_d = 0, fwd_dtype = -1;
 };
 std::mutex g_state_mutex;
 DeviceState g_state[64];
@@ -151,8 +154,8 @@ int device_state(DeviceState **out) {
 int validate(const tx_attn_problem *pr) {
   if (!pr) return afail(TXD_ERR_INVALID, "null problem");
   if (pr->batch < 1 || pr->heads < 1 || pr->n_ctx < 1) return afail(TXD_ERR_INVALID, "batch, heads and n_ctx must be >= 1");
-  if (pr->head_dim != 16 && pr->head_dim != 32 && pr->head_dim != 64 && pr->head_dim != 128)
-    return afail(TXD_ERR_UNSUPPORTED, "head_dim %d: 16, 32, 64 and 128 are built (the reference also lists 256)", pr->head_dim);
+  if (pr->head_dim != 16 && pr->head_dim != 32 && pr->head_dim != 64 && pr->head_dim != 128 && pr->head_dim != 256)
+    return afail(TXD_ERR_UNSUPPORTED, "head_dim %d: the reference's 16, 32, 64, 128 and 256 are built", pr->head_dim);
   if (pr->dtype != TXD_F16 && pr->dtype != TXD_BF16) return afail(TXD_ERR_UNSUPPORTED, "dtype must be f16 or bf16");
   if (!(pr->sm_scale > 0.f)) return afail(TXD_ERR_INVALID, "sm_scale must be positive");
   if (static_cast<long long>(pr->batch) * pr->heads > 0x7fffffffLL / ((pr->n_ctx + 255) / 256))
@@ -269,6 +272,120 @@ int attn_bwd_typed(const tx_attn_problem *pr, DeviceState *st, const T *q, const
   return TXD_OK;
 }
 
+
+// The lanes of the GEMM compositions: kBwdLanes heads in flight, each on a stream of its own.
+int ensure_lanes(DeviceState *st) {
+  if (st->bwd_fork) return TXD_OK;
+  TXA_CUDA(cudaEventCreateWithFlags(&st->bwd_fork, cudaEventDisableTiming));
+  for (int l = 0; l < kBwdLanes; ++l) {
+    TXA_CUDA(cudaStreamCreateWithFlags(&st->bwd_stream[l], cudaStreamNonBlocking));
+    TXA_CUDA(cudaEventCreateWithFlags(&st->bwd_join[l], cudaEventDisableTiming));
+  }
+  return TXD_OK;
+}
+
+// One row of base-2 softmax over fp32 scores, as the reference's forward defines it (06-fused-attention.py:59-89,
+// 236-240): m = max_c s[c] * qk_scale over the visible columns, p[c] = exp2(s[c] * qk_scale - m) rounded to the input
+// type for the second dot, l = sum of the unrounded p, M = m + log2(l); the division by l is left to the P V GEMM's
+// row scale. One block per row.
+template <typename T>
+__global__ void attn_fwd_softmax_rows_kernel(const float *s, T *p, float *m_out, float *inv_l, int n, long long ld,
+                                             float qk_scale, int causal) {
+  const int r = blockIdx.x;
+  const int visible = causal ? r + 1 : n;
+  const float *row = s + static_cast<long long>(r) * ld;
+  __shared__ float red[32];
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < visible; c += blockDim.x) mx = fmaxf(mx, row[c] * qk_scale);
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  float sum = 0.f;
+  T *prow = p + static_cast<long long>(r) * ld;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float e = c < visible ? exp2f(fmaf(row[c], qk_scale, -mx)) : 0.f;
+    sum += e;
+    prow[c] = from_f32<T>(e);
+  }
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float l = 0.f;
+    for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) l += red[w];
+    m_out[r] = mx + log2f(l);
+    inv_l[r] = 1.0f / l;
+  }
+}
+
+// Forward for head dimensions the fused kernel has no tensor-memory plan for (256: two 256-column O accumulators and
+// two S tiles do not fit 512 TMEM columns): per head S = Q K^T by the tt.dot kernel (fp32), the row softmax above, and
+// O = (P V) / l by the tt.dot kernel with its fused row scale. Scores travel through global memory, so this is the slow
+// form; it exists so that the reference's whole HEAD_DIM list runs.
+template <typename T>
+int attn_fwd_composed(const tx_attn_problem *pr, DeviceState *st, const T *q, const T *k, const T *v, T *out, float *m_out,
+                      cudaStream_t stream) {
+  const int n = pr->n_ctx, d = pr->head_dim;
+  const long long ld = (n + 7) / 8 * 8;
+  const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
+  const size_t lane_bytes = static_cast<size_t>(n) * ld * (4 + sizeof(T)) + static_cast<size_t>(n) * sizeof(float) + 256;
+  int rc;
+  {
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    const size_t need = kBwdLanes * lane_bytes + 256;
+    if (st->bwd_ws_bytes < need) {
+      if (st->bwd_ws) cudaFree(st->bwd_ws);
+      st->bwd_ws = nullptr;
+      st->bwd_ws_bytes = 0;
+      TXA_CUDA(cudaMalloc(&st->bwd_ws, need));
+      st->bwd_ws_bytes = need;
+    }
+    if ((rc = ensure_lanes(st))) return rc;
+    if (st->fwd_n != n || st->fwd_d != d || st->fwd_dtype != pr->dtype) {
+      for (tx_dot_plan *&p : st->fwd_plan) {
+        if (p) tx_dot_plan_destroy(p);
+        p = nullptr;
+      }
+      for (int l = 0; l < kBwdLanes; ++l) {
+        tx_dot_problem g = {};
+        // scores [n, n] = Q [n, d] x K^T (K is a row-major [n, d] tensor read transposed), fp32
+        g.m = n; g.n = n; g.k = d; g.ab_dtype = pr->dtype; g.out_dtype = TXD_F32;
+        g.a_layout = TXD_ROW_MAJOR; g.b_layout = TXD_COL_MAJOR; g.lda = d; g.ldb = d; g.ldc = ld; g.alpha = 1.0f;
+        if ((rc = tx_dot_plan_create(&g, nullptr, &st->fwd_plan[2 * l]))) return afail(rc, "forward plan 0: %s", tx_dot_last_error());
+        // O [n, d] = (P [n, n] x V [n, d]) * (1 / l)[row]
+        g.m = n; g.n = d; g.k = n; g.out_dtype = pr->dtype; g.b_layout = TXD_ROW_MAJOR; g.lda = ld; g.ldb = d; g.ldc = d;
+        g.has_row_scale = 1;
+        if ((rc = tx_dot_plan_create(&g, nullptr, &st->fwd_plan[2 * l + 1]))) return afail(rc, "forward plan 1: %s", tx_dot_last_error());
+      }
+      st->fwd_n = n; st->fwd_d = d; st->fwd_dtype = pr->dtype;
+    }
+  }
+  char *ws = static_cast<char *>(st->bwd_ws);
+  const float qk_scale = pr->sm_scale * 1.44269504f;
+  TXA_CUDA(cudaEventRecord(st->bwd_fork, stream));
+  for (int l = 0; l < kBwdLanes; ++l) TXA_CUDA(cudaStreamWaitEvent(st->bwd_stream[l], st->bwd_fork, 0));
+  for (long long h = 0; h < heads_total; ++h) {
+    const int l = static_cast<int>(h % kBwdLanes);
+    cudaStream_t ls = st->bwd_stream[l];
+    float *s_buf = reinterpret_cast<float *>(ws + l * lane_bytes);
+    T *p_buf = reinterpret_cast<T *>(s_buf + static_cast<size_t>(n) * ld);
+    float *inv_l = reinterpret_cast<float *>(p_buf + static_cast<size_t>(n) * ld);
+    const size_t off = static_cast<size_t>(h) * n * d;
+    if ((rc = tx_dot_run(st->fwd_plan[2 * l], q + off, k + off, s_buf, nullptr, nullptr, ls))) return afail(rc, "%s", tx_dot_last_error());
+    attn_fwd_softmax_rows_kernel<T><<<n, 256, 0, ls>>>(s_buf, p_buf, m_out + h * n, inv_l, n, ld, qk_scale, pr->causal ? 1 : 0);
+    if ((rc = tx_dot_run(st->fwd_plan[2 * l + 1], p_buf, v + off, out + off, inv_l, nullptr, ls))) return afail(rc, "%s", tx_dot_last_error());
+  }
+  for (int l = 0; l < kBwdLanes; ++l) {
+    TXA_CUDA(cudaEventRecord(st->bwd_join[l], st->bwd_stream[l]));
+    TXA_CUDA(cudaStreamWaitEvent(stream, st->bwd_join[l], 0));
+  }
+  TXA_CUDA(cudaGetLastError());
+  g_attn_launches.fetch_add(static_cast<uint64_t>(3 * heads_total));
+  return TXD_OK;
+}
 
 // dq = cast(sm_scale * dq_acc)
 template <typename T>
@@ -452,6 +569,14 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
     }
     prm.m_out = st->m;
   }
+  if (pr->head_dim == 256) {
+    cudaStream_t cs = static_cast<cudaStream_t>(stream_v);
+    if (bf16)
+      return attn_fwd_composed<__nv_bfloat16>(pr, st, static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
+                                              static_cast<const __nv_bfloat16 *>(v), static_cast<__nv_bfloat16 *>(out), prm.m_out, cs);
+    return attn_fwd_composed<__half>(pr, st, static_cast<const __half *>(q), static_cast<const __half *>(k),
+                                     static_cast<const __half *>(v), static_cast<__half *>(out), prm.m_out, cs);
+  }
   const size_t tile_bytes = static_cast<size_t>(128) * kd * 2;
   const size_t smem = 2 * tile_bytes + 2 * txa::kPBytes + prm.kv_stages * tile_bytes + sizeof(txa::AttnCtl) + 1024;
   const unsigned grid = static_cast<unsigned>(heads_total * prm.q_tiles);
@@ -578,7 +703,8 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   const int n = pr->n_ctx, d = pr->head_dim;
   const long long ld = (n + 7) / 8 * 8;
   const char *force_unfused = getenv("TXA_BWD_UNFUSED");
-  if (!(force_unfused && atoi(force_unfused) != 0)) {
+  // head_dim 256 has no fused kernel (tensor-memory plan): it takes the composition of tt.dot GEMMs below
+  if (d != 256 && !(force_unfused && atoi(force_unfused) != 0)) {
     const size_t rows = static_cast<size_t>(pr->batch) * pr->heads * n;
     const size_t need = ((rows + 63) / 64) * 64 * sizeof(float) + (d <= 64 ? rows * 64 * sizeof(float) : 0) + 256;
     {
@@ -612,13 +738,7 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
       TXA_CUDA(cudaMalloc(&st->bwd_ws, need));
       st->bwd_ws_bytes = need;
     }
-    if (!st->bwd_fork) {
-      TXA_CUDA(cudaEventCreateWithFlags(&st->bwd_fork, cudaEventDisableTiming));
-      for (int l = 0; l < kBwdLanes; ++l) {
-        TXA_CUDA(cudaStreamCreateWithFlags(&st->bwd_stream[l], cudaStreamNonBlocking));
-        TXA_CUDA(cudaEventCreateWithFlags(&st->bwd_join[l], cudaEventDisableTiming));
-      }
-    }
+    if ((rc = ensure_lanes(st))) return rc;
     if (st->bwd_n != n || st->bwd_d != d || st->bwd_dtype != pr->dtype || st->bwd_scale != pr->sm_scale) {
       for (tx_dot_plan *&p : st->bwd_plan) {
         if (p) tx_dot_plan_destroy(p);
