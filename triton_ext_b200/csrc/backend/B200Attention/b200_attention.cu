@@ -331,7 +331,8 @@ int attn_fwd_composed(const tx_attn_problem *pr, DeviceState *st, const T *q, co
   const int n = pr->n_ctx, d = pr->head_dim;
   const long long ld = (n + 7) / 8 * 8;
   const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
-  const size_t lane_bytes = static_cast<size_t>(n) * ld * (4 + sizeof(T)) + static_cast<size_t>(n) * sizeof(float) + 256;
+  // scores (fp32), probabilities (input type), 1 / l per row; every lane starts on a 256-byte boundary
+  const size_t lane_bytes = (static_cast<size_t>(n) * ld * (4 + sizeof(T)) + static_cast<size_t>(n) * sizeof(float) + 255) / 256 * 256;
   int rc;
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);

@@ -698,7 +698,7 @@ __device__ __forceinline__ void dot_umma_body(const DotParams &p) {
     // This loop is one thread's instruction stream, and that stream, not the tensor pipe, is what bounds the
     // kernel when it is long: a K block of four 256x256x16 MMAs occupies the pipe for 512 cycles, and every
     // instruction the issuing thread executes per block (several cycles each, nothing to overlap them with in a
-    // one-warp dependency chain) comes out of that budget. Measured on this part: a loop of about 80 instructions
+    // one-warp dependency chain) comes out of those 512 cycles. Measured on this part: a loop of about 80 instructions
     // per block ran at 780 cycles per block whatever the MMA's N, a loop of about 30 runs at the pipe's 512, and a
     // tcgen05.commit per block costs nothing by itself. So the main loop below is branch-free apart from its trip
     // count, its descriptors are two multiply-adds per block, the operand kind is a template parameter, and
