@@ -387,9 +387,10 @@ int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
     prm.remote_world = remote->world;
     prm.remote_rank = remote->rank;
     prm.rows_per_rank = pr.m / remote->world;
-    // Rank r starts on the tile rows owned by rank r+1 and ends on its own, so that at any moment every owner
-    // receives from about one peer instead of all peers storing to the same owner.
-    prm.tp_rotate = ((remote->rank + 1) % remote->world) * (prm.rows_per_rank / (tc.cta_pair ? 256 : 128));
+    // Consecutive tile rows of the raster go to consecutive owners (rank + 1, rank + 2, ..., rank): every wave of tiles
+    // stores to all owners at once, so each NVLink pair carries an even share all the time and the tiles whose rows this
+    // rank owns (no NVLink bytes) are spread over the run instead of forming a phase of their own.
+    prm.tp_interleave = remote->world;
     if (pl->remote_cached_world != remote->world) {
       for (auto &mk : pl->remote_cache) mk.ptr = nullptr;
       pl->remote_cached_world = remote->world;

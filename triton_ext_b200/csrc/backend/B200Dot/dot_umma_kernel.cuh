@@ -125,7 +125,8 @@ struct alignas(64) DotParams {
   int32_t remote_world;              // 0 = store to `out` as usual
   int32_t remote_rank;
   int32_t rows_per_rank;             // m / remote_world, a multiple of the tile height
-  int32_t tp_rotate;                 // tile rows are visited starting here (mod tiles_p): ranks start on different owners
+  int32_t tp_interleave;             // > 1: consecutive tile rows of the raster belong to consecutive owners (this many
+                                     // ranks), starting with the rank after this one
   int32_t debug_flags;               // 128 = producer stops after its first K block (host-side fault
                                      // injection: exercises the bounded waits). Builds with -DTXD_MEASURE
                                      // also honour 1 = do not refill stages (tensor-pipe-only timing),
@@ -195,9 +196,11 @@ __device__ __forceinline__ void tile_coords(const DotParams &p, int tile, int &t
   const int r = tile - g * per_group;
   tp = first + r % gsize;
   tq = r / gsize;
-  if (p.tp_rotate) {
-    tp += p.tp_rotate;
-    if (tp >= p.tiles_p) tp -= p.tiles_p;
+  if (p.tp_interleave > 1) {
+    const int w = p.tp_interleave;
+    int owner = tp % w + p.remote_rank + 1;
+    if (owner >= w) owner -= w;
+    tp = owner * (p.tiles_p / w) + tp / w;
   }
 }
 
