@@ -48,6 +48,7 @@ L2_BYTES = 126 * 1024 * 1024
 # beside each figure gives the command); None where no capture exists. These are citations of a profile, not
 # measurements of the run that prints them.
 NCU_TRAFFIC = {
+    "cfg5": (7.99e9, "profiles/dot_umma_pair_kernel_cfg5_bf16_16384x28672x8192_dram_traffic.md"),
     "cfg2": (107.9e6, "profiles/dot_umma_pair_kernel_cfg2_bf16_4096x4096x4160.md"),
     "cfg3": (122.0e6, "profiles/dot_umma_kernel_cfg3_bf16_16x14336x4096.md"),
     "cfg4": (459.1e6, "profiles/dot_umma_pair_f8_kernel_cfg4_fp8_8192x8192x8192.md"),
@@ -571,7 +572,8 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
     per_gpu_flops = info["flops"]
     algo_bytes = info["algorithmic_bytes"]
     launch_s = ms_per_step * 1e-3  # one GEMM launch of this library per step
-    traffic, traffic_src = NCU_TRAFFIC.get(name, (None, None))
+    # the captures are of the unsharded problem: a shard's launch has no figure
+    traffic, traffic_src = NCU_TRAFFIC.get(name, (None, None)) if ctx.world == 1 else (None, None)
     if name == "cfg3":
         achieved = algo_bytes / launch_s / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
