@@ -573,7 +573,8 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
     algo_bytes = info["algorithmic_bytes"]
     launch_s = ms_per_step * 1e-3  # one GEMM launch of this library per step
     # the captures are of the unsharded problem: a shard's launch has no figure
-    traffic, traffic_src = NCU_TRAFFIC.get(name, (None, None)) if ctx.world == 1 else (None, None)
+    whole = (m, n, k) == (w["m"], w["n"], w["k"])
+    traffic, traffic_src = NCU_TRAFFIC.get(name, (None, None)) if whole else (None, None)
     if name == "cfg3":
         achieved = algo_bytes / launch_s / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
