@@ -476,7 +476,8 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
     fused_op = None
     plan = None
     if fused:
-        fused_op = par.FusedKShardedDot(m, n, k, in_dt, out_dt, partial_dtype=slot_dt, device=dev, config_kw=plan_config_kw(w))
+        fused_op = par.FusedKShardedDot(m, n, k, in_dt, out_dt, partial_dtype=slot_dt, device=dev, config_kw=plan_config_kw(w),
+                                        parts=args.exchange_pieces)
         info = fused_op.plan.info
     else:
         kw = plan_config_kw(w)
@@ -821,7 +822,10 @@ def exchange_phases(ctx: Ctx, fused_op, sets, n_sets, slot_dt, m, n) -> dict:
     copy_ms = ctx.max_over_ranks(e0.elapsed_time(e1) / 3)
     copy_gbs = src.numel() * es / copy_ms / 1e6
     gemm_ms = med[1]
-    return {"phase_ms": {"barrier_before": med[0], "gemm_with_remote_stores": med[1], "barrier_after": med[2], "slot_reduction": med[3]},
+    return {"pieces": fused_op.parts,
+            "note": "phases timed with the exchange in one piece, one after the other; the timed steps run it in `pieces` "
+                    "pieces with each piece's slot reduction on a second stream under the next piece's GEMM",
+            "phase_ms": {"barrier_before": med[0], "gemm_with_remote_stores": med[1], "barrier_after": med[2], "slot_reduction": med[3]},
             "bytes_sent_per_rank": int(sent), "nvlink_gbs_during_gemm": sent / gemm_ms / 1e6,
             "peer_copy_gbs_same_run": copy_gbs, "frac_of_peer_copy": (sent / gemm_ms / 1e6) / copy_gbs}
 
@@ -1054,6 +1058,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="time the named workload only")
+    ap.add_argument("--exchange-pieces", type=int, default=None,
+                    help="pieces of the fused K-shard exchange (default: chosen by the library from the problem size)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second back-to-back window")
     ap.add_argument("--kernel-only", action="store_true",
                     help="for profilers: warm-up and the one timed window of the named workload, nothing else "

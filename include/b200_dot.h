@@ -179,6 +179,20 @@ TXD_API int tx_dot_reduce_slots(const void *slots, int32_t world, int32_t rows, 
                                 void *out, int32_t out_dtype, int64_t ldc, const float *row_scale,
                                 const float *col_scale, float alpha, void *stream);
 
+/*
+ * The same exchange in `parts` pieces, so that the sum of a finished piece can run (on another stream, after the ranks'
+ * barrier for that piece) while the next piece's GEMM is still storing. The tile rows are dealt to the owners in turn,
+ * so piece `part` fills rows [part, part + 1) * (m / world / parts) of this rank's slot in every owner's buffer, and
+ * tx_dot_reduce_slots_part sums exactly those rows: rows [row0, row0 + rows) of each of the `world` slots (each
+ * rows_per_rank x n) into rows [row0, row0 + rows) of `out`; `out` and `row_scale` are the whole result's. Needs
+ * (m / world / block_m) % parts == 0. With parts = 1 and row0 = 0, rows = rows_per_rank these are the two calls above.
+ */
+TXD_API int tx_dot_run_to_slots_part(tx_dot_plan *plan, const void *a, const void *b, void *const *slot_bases,
+                                     int32_t world, int32_t rank, int32_t part, int32_t parts, void *stream);
+TXD_API int tx_dot_reduce_slots_part(const void *slots, int32_t world, int32_t rows_per_rank, int32_t row0, int32_t rows,
+                                     int32_t n, int32_t slot_dtype, void *out, int32_t out_dtype, int64_t ldc,
+                                     const float *row_scale, const float *col_scale, float alpha, void *stream);
+
 TXD_API int tx_dot_plan_destroy(tx_dot_plan *plan);
 
 /*

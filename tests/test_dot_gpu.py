@@ -378,3 +378,48 @@ def test_slot_stores_and_reduction_single_gpu(B, dot_lib, partial_dtype):
     with pytest.raises(B.DotError):
         plan.run_to_slots(ad[:, :kshard], bd[:kshard], ptrs, 0)
     plan.close()
+
+
+def test_slot_exchange_in_pieces_single_gpu(B):
+    """The exchange cut into pieces: piece j of every rank fills rows [j, j + 1) * rows / parts of its slot in every
+    owner's buffer and nothing else, all pieces together give the slots of the one-piece form bit for bit, and the
+    piecewise sums give the one-piece result bit for bit."""
+    dev = torch.device("cuda:0")
+    world, parts = 2, 2
+    case = Case("kshard_pieces", 1024, 384, 1152, bf16, bf16, seed=62, scales=True, block=(64, 64, 64))
+    a, b, rs, cs = make_inputs(case)
+    ad, bd, rsd, csd = a.to(dev), b.to(dev), rs.to(dev), cs.to(dev)
+    rows, kshard = case.m // world, case.k // world
+    cfg = dict(schedule=B.TXD_SCHED_DATA_PARALLEL, swap_ab=2, cta_pair=1, block_n=128)
+    plans = [B.DotPlan(B.make_problem(case.m, case.n, kshard, bf16, f32, lda=case.k), B.make_config(**cfg)) for _ in range(world)]
+    shards = [(ad[:, r * kshard:(r + 1) * kshard], bd[r * kshard:(r + 1) * kshard, :]) for r in range(world)]
+    whole = [torch.zeros(world, rows, case.n, dtype=f32, device=dev) for _ in range(world)]
+    for r in range(world):
+        plans[r].run_to_slots(*shards[r], [t.data_ptr() for t in whole], r)
+    pieces = [torch.full((world, rows, case.n), float("nan"), dtype=f32, device=dev) for _ in range(world)]
+    ptrs = [t.data_ptr() for t in pieces]
+    outs = [torch.zeros(rows, case.n, dtype=bf16, device=dev) for _ in range(world)]
+    per = rows // parts
+    for j in range(parts):
+        for r in range(world):
+            plans[r].run_to_slots(*shards[r], ptrs, r, part=j, parts=parts)
+        torch.cuda.synchronize()
+        for owner in range(world):
+            written = ~torch.isnan(pieces[owner])
+            assert bool(written[:, :(j + 1) * per].all()) and not bool(written[:, (j + 1) * per:].any()), (j, owner)
+            B.reduce_slots(pieces[owner], outs[owner], row_scale=rsd[owner * rows:(owner + 1) * rows], col_scale=csd,
+                           row0=j * per, rows=per)
+    torch.cuda.synchronize()
+    for r in range(world):
+        plans[r].check()
+    for owner in range(world):
+        assert torch.equal(pieces[owner], whole[owner])
+        ref = torch.empty(rows, case.n, dtype=bf16, device=dev)
+        B.reduce_slots(whole[owner], ref, row_scale=rsd[owner * rows:(owner + 1) * rows], col_scale=csd)
+        assert torch.equal(outs[owner], ref)
+    with pytest.raises(B.DotError):
+        plans[0].run_to_slots(*shards[0], ptrs, 0, part=0, parts=3)   # 2 tile rows per rank do not divide into 3
+    with pytest.raises(B.DotError):
+        B.reduce_slots(pieces[0], outs[0], row0=rows - 8, rows=16)
+    for pl in plans:
+        pl.close()

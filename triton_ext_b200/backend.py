@@ -110,9 +110,12 @@ def load_library() -> ctypes.CDLL:
     lib.tx_dot_plan_destroy.argtypes = [vp]
     lib.tx_dot_run_to_slots.argtypes = [vp, vp, vp, ctypes.POINTER(vp), i32, i32, vp]
     lib.tx_dot_reduce_slots.argtypes = [vp, i32, i32, i32, i32, vp, i32, ctypes.c_int64, f32p, f32p, ctypes.c_float, vp]
+    lib.tx_dot_run_to_slots_part.argtypes = [vp, vp, vp, ctypes.POINTER(vp), i32, i32, i32, i32, vp]
+    lib.tx_dot_reduce_slots_part.argtypes = [vp, i32, i32, i32, i32, i32, i32, vp, i32, ctypes.c_int64, f32p, f32p,
+                                             ctypes.c_float, vp]
     for name in ("tx_dot_plan_create", "tx_dot_plan_preview", "tx_dot_plan_query", "tx_dot_run",
                  "tx_dot_plan_check", "tx_dot_run_host", "tx_dot_plan_destroy", "tx_dot_run_to_slots",
-                 "tx_dot_reduce_slots"):
+                 "tx_dot_reduce_slots", "tx_dot_run_to_slots_part", "tx_dot_reduce_slots_part"):
         getattr(lib, name).restype = ctypes.c_int
     _lib = lib
     return lib
@@ -246,14 +249,16 @@ class DotPlan:
         _check_scale(col_scale, pr.n, dev, "col_scale")
 
     def run_to_slots(self, a: torch.Tensor, b: torch.Tensor, slot_ptrs: list, rank: int,
-                     stream: Optional[torch.cuda.Stream] = None) -> None:
+                     stream: Optional[torch.cuda.Stream] = None, part: int = 0, parts: int = 1) -> None:
         """K-sharded form: store every tile into slot `rank` of the buffer of the rank owning its rows.
-        `slot_ptrs[o]` is the device address of rank o's [world, m/world, n] slot buffer (peer-mapped)."""
+        `slot_ptrs[o]` is the device address of rank o's [world, m/world, n] slot buffer (peer-mapped).
+        With parts > 1 only piece `part` of the tile rows is computed: rows [part, part + 1) * (m/world/parts) of
+        every owner's slot."""
         s = stream if stream is not None else torch.cuda.current_stream(a.device)
         world = len(slot_ptrs)
         arr = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(p)) for p in slot_ptrs])
-        _check(self._lib.tx_dot_run_to_slots(self._h, a.data_ptr(), b.data_ptr(), arr, world, rank,
-                                             ctypes.c_void_p(s.cuda_stream)))
+        _check(self._lib.tx_dot_run_to_slots_part(self._h, a.data_ptr(), b.data_ptr(), arr, world, rank, part, parts,
+                                                  ctypes.c_void_p(s.cuda_stream)))
 
     def check(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream()
@@ -284,15 +289,24 @@ class DotPlan:
 
 def reduce_slots(slots: torch.Tensor, out: torch.Tensor, *, row_scale: Optional[torch.Tensor] = None,
                  col_scale: Optional[torch.Tensor] = None, alpha: float = 1.0,
-                 stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
-    """out[r, c] = cast(alpha * rs[r] * cs[c] * sum_s slots[s, r, c]); slots is [world, rows, n], f32 or bf16."""
-    world, rows, n = slots.shape
+                 stream: Optional[torch.cuda.Stream] = None, row0: int = 0, rows: Optional[int] = None) -> torch.Tensor:
+    """out[r, c] = cast(alpha * rs[r] * cs[c] * sum_s slots[s, r, c]); slots is [world, rows, n], f32 or bf16.
+    `row0`, `rows` restrict the call to rows [row0, row0 + rows) of every slot and of `out` (one piece of the exchange)."""
+    world, rows_per_rank, n = slots.shape
     if not slots.is_contiguous() or out.stride(1) != 1:
         raise ValueError("slots must be contiguous and out row-major")
+    if tuple(out.shape) != (rows_per_rank, n):
+        raise ValueError(f"out has shape {tuple(out.shape)}, a slot is {(rows_per_rank, n)}")
+    if row_scale is not None and (row_scale.dtype != torch.float32 or row_scale.numel() != rows_per_rank or not row_scale.is_contiguous()):
+        raise ValueError(f"row_scale must be {rows_per_rank} contiguous float32 values")
+    if col_scale is not None and (col_scale.dtype != torch.float32 or col_scale.numel() != n or not col_scale.is_contiguous()):
+        raise ValueError(f"col_scale must be {n} contiguous float32 values")
+    if rows is None:
+        rows = rows_per_rank - row0
     s = stream if stream is not None else torch.cuda.current_stream(slots.device)
-    _check(load_library().tx_dot_reduce_slots(
-        slots.data_ptr(), world, rows, n, _DTYPES[slots.dtype], out.data_ptr(), _DTYPES[out.dtype], out.stride(0),
-        row_scale.data_ptr() if row_scale is not None else None,
+    _check(load_library().tx_dot_reduce_slots_part(
+        slots.data_ptr(), world, rows_per_rank, row0, rows, n, _DTYPES[slots.dtype], out.data_ptr(), _DTYPES[out.dtype],
+        out.stride(0), row_scale.data_ptr() if row_scale is not None else None,
         col_scale.data_ptr() if col_scale is not None else None, ctypes.c_float(alpha), ctypes.c_void_p(s.cuda_stream)))
     return out
 

@@ -230,17 +230,17 @@ namespace {
 struct RemoteTarget {
   void *const *slot_bases = nullptr;
   int world = 0, rank = 0;
+  int part = 0, parts = 1;  // this launch computes tile rows [part, part + 1) * tiles_p / parts of the interleaved order
 };
 int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const float *row_scale, const float *col_scale,
                void *stream_v, const RemoteTarget *remote);
 
-__global__ void reduce_slots_kernel(const void *slots, int world, long long rows, long long n, int slot_f32, void *out,
-                                    int out_dtype, long long ldc, const float *row_scale, const float *col_scale,
-                                    float alpha) {
-  // One thread per 4 consecutive columns; slots are summed in slot order in fp32.
+__global__ void reduce_slots_kernel(const void *slots, int world, long long slot_elems, long long rows, long long n,
+                                    int slot_f32, void *out, int out_dtype, long long ldc, const float *row_scale,
+                                    const float *col_scale, float alpha) {
+  // One thread per 4 consecutive columns; slots (slot_elems apart) are summed in slot order in fp32.
   const long long groups = (n + 3) / 4;
   const long long total = rows * groups;
-  const long long slot_elems = rows * n;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = i / groups, c0 = (i - r * groups) * 4;
@@ -287,12 +287,13 @@ int tx_dot_run(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
   return launch_dot(pl, a, b, c, row_scale, col_scale, stream_v, nullptr);
 }
 
-int tx_dot_run_to_slots(tx_dot_plan *pl, const void *a, const void *b, void *const *slot_bases, int32_t world,
-                        int32_t rank, void *stream_v) {
+int tx_dot_run_to_slots_part(tx_dot_plan *pl, const void *a, const void *b, void *const *slot_bases, int32_t world,
+                             int32_t rank, int32_t part, int32_t parts, void *stream_v) {
   if (!pl || !slot_bases) return fail(TXD_ERR_INVALID, "null argument");
   const tx_dot_problem &pr = pl->problem;
   const txd::TileChoice &tc = pl->tc;
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(TXD_ERR_INVALID, "world must be 1..8 and rank inside it");
+  if (parts < 1 || part < 0 || part >= parts) return fail(TXD_ERR_INVALID, "part must lie in [0, parts)");
   if (pr.m == 0 || pr.n == 0 || pr.k == 0) return fail(TXD_ERR_UNSUPPORTED, "empty problems have no slot form");
   if (pr.has_row_scale || pr.has_col_scale || pr.alpha != 1.0f)
     return fail(TXD_ERR_INVALID, "partials are exchanged unscaled: create the plan without scales; tx_dot_reduce_slots applies them");
@@ -302,6 +303,8 @@ int tx_dot_run_to_slots(tx_dot_plan *pl, const void *a, const void *b, void *con
                                      "(create the plan with schedule = TXD_SCHED_DATA_PARALLEL, swap_ab = 2)");
   if (pr.m % world != 0 || (pr.m / world) % tc.block_m != 0)
     return fail(TXD_ERR_UNSUPPORTED, "m / world = %d must be a multiple of the tile height %d", pr.m / world, tc.block_m);
+  if ((pr.m / world / tc.block_m) % parts != 0)
+    return fail(TXD_ERR_UNSUPPORTED, "the %d tile rows of a rank do not divide into %d parts", pr.m / world / tc.block_m, parts);
   for (int r = 0; r < world; ++r)
     if (!slot_bases[r] || (reinterpret_cast<uintptr_t>(slot_bases[r]) & 15))
       return fail(TXD_ERR_INVALID, "slot base %d is null or not 16-byte aligned", r);
@@ -309,24 +312,45 @@ int tx_dot_run_to_slots(tx_dot_plan *pl, const void *a, const void *b, void *con
   rt.slot_bases = slot_bases;
   rt.world = world;
   rt.rank = rank;
+  rt.part = part;
+  rt.parts = parts;
   return launch_dot(pl, a, b, nullptr, nullptr, nullptr, stream_v, &rt);
 }
 
-int tx_dot_reduce_slots(const void *slots, int32_t world, int32_t rows, int32_t n, int32_t slot_dtype, void *out,
-                        int32_t out_dtype, int64_t ldc, const float *row_scale, const float *col_scale, float alpha,
-                        void *stream_v) {
-  if (!slots || !out || world < 1 || rows < 0 || n < 0 || ldc < n) return fail(TXD_ERR_INVALID, "bad argument");
+int tx_dot_run_to_slots(tx_dot_plan *pl, const void *a, const void *b, void *const *slot_bases, int32_t world,
+                        int32_t rank, void *stream_v) {
+  return tx_dot_run_to_slots_part(pl, a, b, slot_bases, world, rank, 0, 1, stream_v);
+}
+
+int tx_dot_reduce_slots_part(const void *slots, int32_t world, int32_t rows_per_rank, int32_t row0, int32_t rows, int32_t n,
+                             int32_t slot_dtype, void *out, int32_t out_dtype, int64_t ldc, const float *row_scale,
+                             const float *col_scale, float alpha, void *stream_v) {
+  if (!slots || !out || world < 1 || rows_per_rank < 0 || n < 0 || ldc < n) return fail(TXD_ERR_INVALID, "bad argument");
+  if (row0 < 0 || rows < 0 || row0 + static_cast<long long>(rows) > rows_per_rank)
+    return fail(TXD_ERR_INVALID, "rows [%d, %d + %d) are not inside a slot of %d rows", row0, row0, rows, rows_per_rank);
   if (slot_dtype != TXD_F32 && slot_dtype != TXD_BF16) return fail(TXD_ERR_UNSUPPORTED, "slots are f32 or bf16");
   if (out_dtype != TXD_F32 && out_dtype != TXD_BF16 && out_dtype != TXD_F16) return fail(TXD_ERR_UNSUPPORTED, "output dtype must be f16, bf16 or f32");
   if (rows == 0 || n == 0) return TXD_OK;
   const long long total = static_cast<long long>(rows) * ((n + 3) / 4);
   const int threads = 256;
   const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148LL * 16));
+  const size_t slot_es = slot_dtype == TXD_F32 ? 4 : 2;
+  const size_t out_es = out_dtype == TXD_F32 ? 4 : 2;
   reduce_slots_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
-      slots, world, rows, n, slot_dtype == TXD_F32 ? 1 : 0, out, out_dtype, ldc, row_scale, col_scale, alpha);
+      static_cast<const char *>(slots) + static_cast<size_t>(row0) * n * slot_es, world,
+      static_cast<long long>(rows_per_rank) * n, rows, n, slot_dtype == TXD_F32 ? 1 : 0,
+      static_cast<char *>(out) + static_cast<size_t>(row0) * ldc * out_es, out_dtype, ldc,
+      row_scale ? row_scale + row0 : nullptr, col_scale, alpha);
   TXD_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return TXD_OK;
+}
+
+int tx_dot_reduce_slots(const void *slots, int32_t world, int32_t rows, int32_t n, int32_t slot_dtype, void *out,
+                        int32_t out_dtype, int64_t ldc, const float *row_scale, const float *col_scale, float alpha,
+                        void *stream_v) {
+  return tx_dot_reduce_slots_part(slots, world, rows, 0, rows, n, slot_dtype, out, out_dtype, ldc, row_scale, col_scale,
+                                  alpha, stream_v);
 }
 
 }  // extern "C"
@@ -391,6 +415,9 @@ int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const flo
     // stores to all owners at once, so each NVLink pair carries an even share all the time and the tiles whose rows this
     // rank owns (no NVLink bytes) are spread over the run instead of forming a phase of their own.
     prm.tp_interleave = remote->world;
+    prm.tiles_p_all = tc.tiles_p;
+    prm.tiles_p = tc.tiles_p / remote->parts;
+    prm.tp_begin = remote->part * prm.tiles_p;
     if (pl->remote_cached_world != remote->world) {
       for (auto &mk : pl->remote_cache) mk.ptr = nullptr;
       pl->remote_cached_world = remote->world;

@@ -127,6 +127,8 @@ struct alignas(64) DotParams {
   int32_t rows_per_rank;             // m / remote_world, a multiple of the tile height
   int32_t tp_interleave;             // > 1: consecutive tile rows of the raster belong to consecutive owners (this many
                                      // ranks), starting with the rank after this one
+  int32_t tp_begin, tiles_p_all;     // with tp_interleave: this launch covers tile rows [tp_begin, tp_begin + tiles_p)
+                                     // of the interleaved order, out of tiles_p_all (a part of the exchange)
   int32_t debug_flags;               // 128 = producer stops after its first K block (host-side fault
                                      // injection: exercises the bounded waits). Builds with -DTXD_MEASURE
                                      // also honour 1 = do not refill stages (tensor-pipe-only timing),
@@ -198,9 +200,10 @@ __device__ __forceinline__ void tile_coords(const DotParams &p, int tile, int &t
   tq = r / gsize;
   if (p.tp_interleave > 1) {
     const int w = p.tp_interleave;
+    tp += p.tp_begin;
     int owner = tp % w + p.remote_rank + 1;
     if (owner >= w) owner -= w;
-    tp = owner * (p.tiles_p / w) + tp / w;
+    tp = owner * (p.tiles_p_all / w) + tp / w;
   }
 }
 
