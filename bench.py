@@ -17,7 +17,7 @@ Workloads (BASELINE.json `configs`):
     cfg2_jit     cfg2 launched as a @triton.jit kernel through the package's Triton backend.
     cfg3         bf16 16x14336x4096 decode shape; HBM-bound, roofline in GB/s.
     cfg4         fp8 e4m3 8192^3 with per-row / per-column fp32 scales -> bf16.
-    attn_d64[_causal], attn_d128[_causal], attn_d64_16k_causal, attn_bwd_d64_causal
+    attn_d64[_causal], attn_d128[_causal], attn_d64_16k_causal, attn_bwd_d64_causal, attn_d64_fp8, attn_d128_fp8[_causal]
                  the next row after the GEMM: fused attention (two chained tt.dot + online softmax)
                  on the reference benchmark's shapes (batch 4, 32 heads, fp16).
 
@@ -85,6 +85,10 @@ WORKLOADS = {
     "attn_d128_causal": dict(attn=True, z=4, h=32, n_ctx=4096, d=128, causal=True, dtype="f16", seed=6),
     "attn_d64_16k_causal": dict(attn=True, z=4, h=32, n_ctx=16384, d=64, causal=True, dtype="f16", seed=6),
     # backward of the same (the reference benchmarks it causal only, :742-744); FLOPs = 2.5 x forward (:799-800)
+    # the reference benchmark's fp8 forward (q, k, v, out float8_e5m2, V with n_ctx contiguous; 06-fused-attention.py:774-779)
+    "attn_d64_fp8": dict(attn=True, z=4, h=32, n_ctx=4096, d=64, causal=False, dtype="fp8e5m2", seed=6),
+    "attn_d128_fp8": dict(attn=True, z=4, h=32, n_ctx=4096, d=128, causal=False, dtype="fp8e5m2", seed=6),
+    "attn_d128_fp8_causal": dict(attn=True, z=4, h=32, n_ctx=4096, d=128, causal=True, dtype="fp8e5m2", seed=6),
     "attn_bwd_d64_causal": dict(attn=True, bwd=True, z=4, h=32, n_ctx=4096, d=64, causal=True, dtype="f16", seed=6),
 }
 DEFAULT_WORKLOAD = "cfg5"
@@ -870,7 +874,11 @@ def attn_flops(w: dict, z: int) -> float:
 def attn_host_inputs(w: dict, rank: int):
     import torch
     g = torch.Generator().manual_seed(w["seed"] + 1000 * rank)
-    return [torch.randn((w["z"], w["h"], w["n_ctx"], w["d"]), generator=g).to(torch.float16) for _ in range(3)]
+    q, k, v = (torch.randn((w["z"], w["h"], w["n_ctx"], w["d"]), generator=g).to(torch.float16) for _ in range(3))
+    if w["dtype"] == "fp8e5m2":   # as the reference's benchmark casts them; V keeps n_ctx contiguous
+        q, k = q.to(torch.float8_e5m2), k.to(torch.float8_e5m2)
+        v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2).to(torch.float8_e5m2)
+    return [q, k, v]
 
 
 def attn_cpu_sample(w: dict, budget_s: float = 10.0) -> dict:
@@ -957,7 +965,8 @@ def run_attention_gpu_arm(ctx: Ctx, args, name: str, w: dict) -> dict | None:
     o_h = torch.empty_like(q_h).pin_memory()
     q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
     out = torch.empty_like(q)
-    set_bytes = 4 * q.numel() * 2
+    es = q.element_size()
+    set_bytes = 4 * q.numel() * es
     if set_bytes <= L2_BYTES:
         raise RuntimeError("attention workload smaller than L2: add rotating buffers before timing it")
 
@@ -1010,7 +1019,7 @@ def run_attention_gpu_arm(ctx: Ctx, args, name: str, w: dict) -> dict | None:
     else:
         def e2e_step():
             A.attention_forward_host(q_h, k_h, v_h, w["causal"], ATTN_SM_SCALE, out=o_h)
-        h2d_bytes, d2h_bytes = 3 * q.numel() * 2, q.numel() * 2
+        h2d_bytes, d2h_bytes = 3 * q.numel() * es, q.numel() * es
     if args.kernel_only:
         e2e_steps = 0
     else:
@@ -1028,7 +1037,7 @@ def run_attention_gpu_arm(ctx: Ctx, args, name: str, w: dict) -> dict | None:
     achieved = per_gpu_flops / (ms_per_step * 1e-3) / 1e12
     sm_mhz = clocks.get("sm_mhz") or 1965
     sfu_bound = 4.0 * w["d"] * 16 * 148 * sm_mhz * 1e6 / 1e12   # one exp2 per score, 16 per clock per SM
-    algo_bytes = 4 * q.numel() * 2 + q.numel() // w["d"] * 4
+    algo_bytes = 4 * q.numel() * es + q.numel() // w["d"] * 4
     traffic, traffic_src = NCU_TRAFFIC.get(name, (None, None))
     line = {
         "metric": "attention bwd TFLOP/s" if bwd else "attention fwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,

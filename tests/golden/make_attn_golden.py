@@ -8,7 +8,8 @@ with constants in memory, and the module is executed from that text. Nothing of 
 
 Run in a container that has the reference checked out:
     python tests/golden/make_attn_golden.py /path/to/reference
-The inputs follow the reference's test (`test_op`, :690-695): seed 20, normal(0, 0.5), fp16, sm_scale 0.5.
+The inputs follow the reference's test (`test_op`, :690-695): seed 20, normal(0, 0.5), fp16, sm_scale 0.5; the fp8
+cases cast them to float8_e5m2 the way the reference's benchmark does (:774-779).
 """
 import linecache
 import os
@@ -32,6 +33,11 @@ CASES = {
     "causal_d32": (1, 2, 256, 32, True, 64, 32),
     "full_d16": (1, 2, 256, 16, False, 64, 16),      # the kernel asserts BLOCK_N <= HEAD_DIM (:175)
     "causal_d256": (1, 1, 256, 256, True, 64, 64),
+}
+# the fp8 forward (q, k, v, out float8_e5m2, V laid out with N_CTX contiguous, P rounded to e5m2; :81-82, :191, :774-779)
+FP8_CASES = {
+    "fp8_causal_d64": (1, 2, 256, 64, True, 64, 32),
+    "fp8_full_d128": (1, 1, 256, 128, False, 64, 64),
 }
 SM_SCALE = 0.5
 # name: (Z, H, N_CTX, HEAD_DIM, causal); the reference's backward asserts N_CTX % 128 == 0 and is causal-only
@@ -77,6 +83,21 @@ def main():
                      HEAD_DIM=d, BLOCK_M=bm, BLOCK_N=bn, CAUSAL=causal)
         for key, t in (("q", q), ("k", k), ("v", v), ("o", o)):
             out[f"{name}.{key}"] = t.numpy().view(np.uint16)  # fp16 bit patterns
+        out[f"{name}.m"] = m.numpy()
+        out[f"{name}.meta"] = np.array([z, h, n, d, int(causal), bm, bn], dtype=np.int32)
+        print(name, "done", flush=True)
+    for name, (z, h, n, d, causal, bm, bn) in FP8_CASES.items():
+        torch.manual_seed(20)
+        q, k, v = (torch.empty((z, h, n, d), dtype=torch.float16).normal_(mean=0.0, std=0.5) for _ in range(3))
+        q, k = q.to(torch.float8_e5m2), k.to(torch.float8_e5m2)
+        v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2).to(torch.float8_e5m2)  # as the reference's benchmark does
+        o = torch.empty_like(q)
+        m = torch.empty((z, h, n), dtype=torch.float32)
+        grid = (triton.cdiv(n, bm), z * h, 1)
+        kernel[grid](q, k, v, SM_SCALE, m, o, *q.stride(), *k.stride(), *v.stride(), *o.stride(), z, h, N_CTX=n,
+                     HEAD_DIM=d, BLOCK_M=bm, BLOCK_N=bn, CAUSAL=causal)
+        for key, t in (("q", q), ("k", k), ("v", v), ("o", o)):
+            out[f"{name}.{key}"] = t.contiguous().view(torch.uint8).numpy()  # e5m2 bytes, logical [Z, H, N_CTX, HEAD_DIM] order
         out[f"{name}.m"] = m.numpy()
         out[f"{name}.meta"] = np.array([z, h, n, d, int(causal), bm, bn], dtype=np.int32)
         print(name, "done", flush=True)

@@ -32,7 +32,7 @@ def draw(z, h, n, d, dtype, seed=20, std=0.5):
 
 def golden_names():
     npz = np.load(GOLDEN)
-    return sorted({key.split(".")[0] for key in npz.files if "." in key and not key.startswith("bwd_")})
+    return sorted({key.split(".")[0] for key in npz.files if "." in key and not key.startswith(("bwd_", "fp8_"))})
 
 
 # ---- 1. the reference kernel's own outputs -----------------------------------------------------------------
@@ -152,6 +152,93 @@ def test_host_buffers_in_groups(A):
         A.attention_forward_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), True, 0.5, out=out, m=m)
         assert torch.equal(out, want.cpu())
         assert torch.equal(m, want_m.cpu())
+
+
+# ---- the fp8 forward (q, k, v, out float8_e5m2; reference 06-fused-attention.py:81-82, :191, :774-779) ----------------
+f8e5 = torch.float8_e5m2
+
+
+def e5m2_step(x: torch.Tensor) -> torch.Tensor:
+    a = x.float().abs().clamp_min(2.0 ** -14)
+    return torch.exp2(torch.floor(torch.log2(a)) - 2)
+
+
+def check_fp8(A, q, k, v, causal, sm_scale):
+    """Kernel against the nearest-even restatement and against exact attention of the same e5m2 inputs."""
+    from oracle import attn_oracle as AO
+    z, h, n, d = q.shape
+    out, m = A.attention_forward(q.cuda(), k.cuda(), A.fp8_v_layout(v.cuda()), causal, sm_scale, return_m=True, check=True)
+    assert out.dtype == f8e5 and tuple(out.shape) == (z, h, n, d)
+    got = out.cpu().float()
+    assert bool(torch.isfinite(got).all())
+    lse = AO.logsumexp2(q, k, causal, sm_scale)
+    assert float((m.cpu() - lse).abs().max()) <= 2e-3
+    exact = AO.attention_eager(q, k, v, causal, sm_scale, round_p=False)
+    # every P moves by at most 2^-3 of itself when rounded to e5m2, so the sum moves by at most 2^-3 * (P @ |V|); the
+    # output's own rounding adds half a step
+    mag = AO.attention_eager(q, k, v.float().abs(), causal, sm_scale, round_p=False)
+    bound = 0.125 * mag + 0.5 * e5m2_step(exact.abs() + 0.125 * mag) * 1.001 + 1e-3
+    err = (got - exact).abs()
+    assert bool((err <= bound).all()), float((err - bound).max())
+    if n % 128 == 0:
+        want, _ = AO.attention_blockwise(q, k, v, causal, sm_scale, 128, 128, skip_above_diagonal=True)
+        diff = (got - want.float()).abs()
+        # The kernel takes its exponentials against a reference point that lags the running maximum by up to 2^8, so its
+        # P values are the restatement's times a power of two that is not a whole one, and round differently: the two
+        # sums differ by up to twice the P bound, and the outputs by one more step.
+        assert bool((diff <= 0.25 * mag + torch.maximum(e5m2_step(got), e5m2_step(want)) * 1.001).all())
+
+
+def fp8_golden_names():
+    npz = np.load(GOLDEN)
+    return sorted({key.split(".")[0] for key in npz.files if key.startswith("fp8_")})
+
+
+@pytest.mark.parametrize("name", fp8_golden_names())
+def test_fp8_on_the_reference_fixture_inputs(A, name):
+    """The inputs of the reference's fp8 fixtures. Their outputs come from the interpreter's defective e5m2 conversion
+    (pinned by the CPU tests), so the kernel is held to the nearest-even restatement and to exact attention; M, which
+    no conversion touches, is compared with the fixture itself."""
+    npz = np.load(GOLDEN)
+    z, h, n, d, causal, _, _ = (int(x) for x in npz[f"{name}.meta"])
+    q, k, v = (torch.from_numpy(npz[f"{name}.{key}"].copy()).view(f8e5) for key in ("q", "k", "v"))
+    check_fp8(A, q, k, v, bool(causal), float(npz["sm_scale"]))
+    _, m = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), bool(causal), float(npz["sm_scale"]), return_m=True, check=True)
+    assert float((m.cpu() - torch.from_numpy(npz[f"{name}.m"].copy())).abs().max()) <= 1e-3
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("z,h,n,d", [(1, 2, 1024, 64), (2, 2, 384, 128), (1, 2, 208, 64), (1, 1, 128, 128), (1, 2, 512, 32),
+                                     (2, 1, 304, 16), (1, 1, 16, 64)])
+def test_fp8_against_oracle(A, z, h, n, d, causal):
+    q, k, v = draw(z, h, n, d, f8e5)
+    check_fp8(A, q, k, v, causal, 0.5)
+
+
+def test_fp8_benchmark_scale_and_rejections(A):
+    from triton_ext_b200 import backend as B
+    q, k, v = draw(1, 2, 512, 128, f8e5, seed=7, std=1.0)
+    check_fp8(A, q, k, v, True, 1.3)          # the benchmark's sm_scale
+    qd = q.cuda()
+    with pytest.raises(B.DotError) as e:      # rows of the transposed V are TMA strides
+        A.attention_forward(qd[:, :, :200], qd[:, :, :200], qd[:, :, :200], True, 0.5)
+    assert e.value.status == B.TXD_ERR_UNSUPPORTED and "multiple of 16" in str(e.value)
+    q256 = torch.zeros((1, 1, 128, 256), dtype=f8e5, device="cuda")
+    with pytest.raises(B.DotError) as e:
+        A.attention_forward(q256, q256, q256, True, 0.5)
+    assert e.value.status == B.TXD_ERR_UNSUPPORTED
+    o = torch.zeros((1, 2, 512, 128), dtype=f8e5, device="cuda")
+    mm = torch.zeros((1, 2, 512), dtype=torch.float32, device="cuda")
+    with pytest.raises(B.DotError) as e:      # the reference's backward has no fp8 form
+        A.attention_backward(qd, qd, qd, o, mm, o, True, 0.5)
+    assert e.value.status == B.TXD_ERR_UNSUPPORTED
+
+
+def test_fp8_host_buffers(A):
+    q, k, v = draw(2, 2, 256, 64, f8e5, seed=9)
+    dev = A.attention_forward(q.cuda(), k.cuda(), v.cuda(), True, 0.5, check=True).cpu()
+    host = A.attention_forward_host(q, k, v, True, 0.5)
+    assert torch.equal(host.view(torch.uint8), dev.view(torch.uint8))
 
 
 def test_rejected_arguments(A):

@@ -57,8 +57,8 @@ def _raise(lib, rc: int):
 
 def make_problem(z: int, h: int, n_ctx: int, head_dim: int, dtype: torch.dtype, causal: bool,
                  sm_scale: float) -> AttnProblem:
-    if dtype not in (torch.float16, torch.bfloat16):
-        raise B.DotError(B.TXD_ERR_UNSUPPORTED, f"attention dtype {dtype}: f16 and bf16 are built")
+    if dtype not in (torch.float16, torch.bfloat16, torch.float8_e5m2):
+        raise B.DotError(B.TXD_ERR_UNSUPPORTED, f"attention dtype {dtype}: f16, bf16 and (forward only) float8_e5m2 are built")
     return AttnProblem(batch=z, heads=h, n_ctx=n_ctx, head_dim=head_dim, dtype=B._DTYPES[dtype],
                        causal=1 if causal else 0, sm_scale=float(sm_scale))
 
@@ -76,6 +76,24 @@ def kv_loop_split(n_ctx: int, q_start: int, causal: bool, block: int = 128) -> t
     return n, n - 1 if last_masked else n
 
 
+def fp8_v_layout(v: torch.Tensor) -> torch.Tensor:
+    """V as the fp8 forward takes it: shape [Z, H, N_CTX, HEAD_DIM] with the N_CTX index contiguous in memory
+    ([Z, H, HEAD_DIM, N_CTX] storage), which is how the reference lays V out for float8_e5m2
+    (`v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)`, 06-fused-attention.py:777-778); the fp8 second dot
+    takes its B operand K-major. Returns `v` itself when it already is, else a copy."""
+    z, h, n, d = v.shape
+    if v.stride() == (h * n * d, n * d, 1, n):
+        return v
+    return v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+
+
+def _operands(q, k, v):
+    """Contiguous q, k and v in the layout the kernels read (fp8: V with N_CTX contiguous)."""
+    q, k = q.contiguous(), k.contiguous()
+    v = fp8_v_layout(v) if v.dtype == torch.float8_e5m2 else v.contiguous()
+    return q, k, v
+
+
 def flops(problem: AttnProblem) -> float:
     return float(_lib().tx_attn_flops(ctypes.byref(problem)))
 
@@ -86,13 +104,15 @@ def kernel_launches() -> int:
 
 def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, sm_scale: float, *,
                       out: Optional[torch.Tensor] = None, return_m: bool = False, check: bool = False):
-    """softmax(q k^T * sm_scale [+ causal mask]) v on the current CUDA stream (asynchronous unless `check`)."""
+    """softmax(q k^T * sm_scale [+ causal mask]) v on the current CUDA stream (asynchronous unless `check`).
+    With float8_e5m2 tensors this is the reference's fp8 forward (:81-82, :191): P is rounded to e5m2 before the second
+    dot, the output is e5m2, and V is read with N_CTX contiguous (`fp8_v_layout`; any other V is copied into it)."""
     lib = _lib()
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise B.DotError(B.TXD_ERR_NO_DEVICE, "attention_forward takes CUDA tensors; use attention_forward_host for host tensors")
     if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape or not (q.dtype == k.dtype == v.dtype):
         raise B.DotError(B.TXD_ERR_INVALID, "q, k, v must be [Z, H, N_CTX, HEAD_DIM] tensors of one shape and type")
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q, k, v = _operands(q, k, v)
     z, h, n, d = q.shape
     pr = make_problem(z, h, n, d, q.dtype, causal, sm_scale)
     if out is None:
@@ -127,7 +147,7 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ca
     lib = _lib()
     if q.is_cuda or k.is_cuda or v.is_cuda:
         raise B.DotError(B.TXD_ERR_INVALID, "attention_forward_host takes host tensors")
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q, k, v = _operands(q, k, v)
     z, h, n, d = q.shape
     pr = make_problem(z, h, n, d, q.dtype, causal, sm_scale)
     if out is None:

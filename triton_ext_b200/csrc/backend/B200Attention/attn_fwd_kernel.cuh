@@ -27,6 +27,12 @@
 // 128). Blocks above the diagonal, which the reference visits with every element masked (each contributes
 // p == 0 and alpha == 1 exactly), are not visited.
 //
+// The fp8 form (kElt == 2: q, k, v and out in e5m2, the reference's `fp8_v` path, 06-fused-attention.py:81-82,191,586)
+// is the same pipeline in bytes: a Q or K row of up to 128 e5m2 values is one 128-byte swizzle span (zero-filled by
+// TMA past head_dim), V arrives transposed ([head_dim, n_ctx] per head, as the reference lays it out for fp8) and
+// is the K-major B operand of the second dot, P is rounded to e5m2 (one span per row), both dots are
+// kind::f8f6f4 MMAs of 32 bytes of K, and O is cast to e5m2 and stored straight from registers.
+//
 // Every wait on an mbarrier is bounded in time; a wait that runs out raises the abort flag, all roles
 // leave their loops, copies in flight are drained, TMEM is released and the CTA returns.
 #pragma once
@@ -59,7 +65,8 @@ enum AttnDeviceStatus : uint32_t {
 
 struct AttnParams {
   CUtensorMap tmap_q, tmap_k, tmap_v;  // 3-D {head_dim, n_ctx, batch*heads}, box {64, 128, 1}, SWIZZLE_128B
-  CUtensorMap tmap_o;                  // same tensor shape, box {64, 32, 1}
+  CUtensorMap tmap_o;                  // same tensor shape, box {64, 32, 1}; unused by the fp8 form
+  void *out;                           // fp8 form: [batch*heads, n_ctx, head_dim] e5m2, stored from registers
   float *m_out;                        // [batch*heads, n_ctx]: m + log2(l), as the reference stores it
   uint32_t *status;
   unsigned long long wait_limit_ns;
@@ -81,9 +88,17 @@ struct AttnCtl {
   volatile uint32_t abort_flag;
 };
 
-template <bool kBf16>
+// Four floats to four e5m2 bytes, element 0 in the lowest byte (round to nearest even, saturating).
+__device__ __forceinline__ uint32_t pack_e5m2x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+template <int kElt>  // 0 f16, 1 bf16
 __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
-  if (kBf16) {
+  if (kElt == 1) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&h);
   }
@@ -133,7 +148,7 @@ __device__ __forceinline__ void exp_group(const uint32_t (&s)[128], int g, float
   }
 }
 
-template <bool kMasked, bool kBf16>
+template <bool kMasked, int kElt>
 __device__ __forceinline__ float row_block_exp_store(const uint32_t (&s)[128], float qk_scale, float neg_m, int col0,
                                                      int lim, uint32_t p_row, int row_xor) {
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
@@ -146,26 +161,34 @@ __device__ __forceinline__ float row_block_exp_store(const uint32_t (&s)[128], f
     s1 += cur[2] + cur[3];
     s2 += cur[4] + cur[5];
     s3 += cur[6] + cur[7];
-    st_shared_v4(p_row + (g >> 3) * kAtomBytes + (((g & 7) ^ row_xor) << 4), pack_pair<kBf16>(cur[0], cur[1]),
-                 pack_pair<kBf16>(cur[2], cur[3]), pack_pair<kBf16>(cur[4], cur[5]), pack_pair<kBf16>(cur[6], cur[7]));
+    if (kElt == 2)  // 8 columns = 8 bytes: half of a 16-byte chunk of the row's one span
+      st_shared_v2(p_row + ((((g >> 1) & 7) ^ row_xor) << 4) + (g & 1) * 8, pack_e5m2x4(cur[0], cur[1], cur[2], cur[3]),
+                   pack_e5m2x4(cur[4], cur[5], cur[6], cur[7]));
+    else
+      st_shared_v4(p_row + (g >> 3) * kAtomBytes + (((g & 7) ^ row_xor) << 4), pack_pair<kElt>(cur[0], cur[1]),
+                   pack_pair<kElt>(cur[2], cur[3]), pack_pair<kElt>(cur[4], cur[5]), pack_pair<kElt>(cur[6], cur[7]));
 #pragma unroll
     for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
   }
   return (s0 + s1) + (s2 + s3);
 }
 
-template <bool kBf16, int kD>
+template <int kElt, int kD>  // kElt: 0 f16, 1 bf16, 2 e5m2
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t attn_smem_raw[];
   const uint32_t raw = smem_u32(attn_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   constexpr int D = kD;
-  const uint32_t tile_bytes = static_cast<uint32_t>(kTileRows * D * 2);  // one Q / K / V tile
-  constexpr int d_atoms = D / 64;
-  constexpr uint32_t kStages = kD == 128 ? 3u : 6u;  // ring slots of one K or V tile each
+  constexpr bool kF8 = kElt == 2;
+  // One Q / K tile = one ring slot: 128 rows of D 16-bit values, or of one 128-byte span of e5m2 values.
+  constexpr uint32_t tile_bytes = kF8 ? static_cast<uint32_t>(kAtomBytes) : static_cast<uint32_t>(kTileRows * D * 2);
+  constexpr uint32_t v_bytes = kF8 ? static_cast<uint32_t>(D * 128) : tile_bytes;  // fp8: V^T, D rows of 128 KV bytes
+  constexpr uint32_t p_bytes = kF8 ? static_cast<uint32_t>(kAtomBytes) : static_cast<uint32_t>(kPBytes);
+  constexpr int d_atoms = kF8 ? 1 : D / 64;
+  constexpr uint32_t kStages = (!kF8 && kD == 128) ? 3u : 6u;  // ring slots of one K or V tile each
   const uint32_t q_addr0 = base;
   const uint32_t p_addr0 = base + 2 * tile_bytes;
-  const uint32_t kv_addr0 = p_addr0 + 2 * kPBytes;
+  const uint32_t kv_addr0 = p_addr0 + 2 * p_bytes;
   AttnCtl *ctl = reinterpret_cast<AttnCtl *>(attn_smem_raw + (kv_addr0 - raw) + kStages * tile_bytes);
 
   const int warp = threadIdx.x >> 5;
@@ -250,7 +273,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
                           smem_u32(&ctl->q_full));
       }
       __syncwarp();
-      auto load_tile = [&](const CUtensorMap *map, int kv_block) {
+      auto load_tile = [&](const CUtensorMap *map, int kv_block, bool is_v) {
         const uint32_t slot = issued % kStages;
         const uint32_t phase = (issued / kStages) & 1u;
         if (!warp_mbar_poll(smem_u32(&ctl->kv_empty[slot]), phase ^ 1u, ac, kAttnTimeoutProducer, lane)) {
@@ -259,18 +282,23 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
         if (issuer) {
           const uint32_t bar = smem_u32(&ctl->kv_full[slot]);
-          mbar_arrive_expect_tx(bar, tile_bytes);
-          for (int a = 0; a < d_atoms; ++a)
-            tma_load_3d(kv_addr0 + slot * tile_bytes + a * kAtomBytes, map, a * 64, kv_block * kTileRows, head, bar);
+          if (kF8 && is_v) {  // V^T: the KV index is the contiguous one
+            mbar_arrive_expect_tx(bar, v_bytes);
+            tma_load_3d(kv_addr0 + slot * tile_bytes, map, kv_block * kTileRows, 0, head, bar);
+          } else {
+            mbar_arrive_expect_tx(bar, tile_bytes);
+            for (int a = 0; a < d_atoms; ++a)
+              tma_load_3d(kv_addr0 + slot * tile_bytes + a * kAtomBytes, map, a * 64, kv_block * kTileRows, head, bar);
+          }
         }
         __syncwarp();
         ++issued;
       };
       if (!p.inject_stall) {
-        load_tile(&p.tmap_k, 0);
+        load_tile(&p.tmap_k, 0, false);
         for (int j = 0; ok && j < nmax; ++j) {
-          if (j + 1 < nmax) load_tile(&p.tmap_k, j + 1);
-          if (ok) load_tile(&p.tmap_v, j);
+          if (j + 1 < nmax) load_tile(&p.tmap_k, j + 1, false);
+          if (ok) load_tile(&p.tmap_v, j, true);
         }
       }
       // Copies still in flight must land before the CTA's shared memory goes away. On the normal path the
@@ -318,20 +346,29 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         // pipe (about 43 cycles per MMA when lean, 60 with a branch and a reconvergence around every MMA).
         if (issuer) {
 #pragma unroll
-          for (int i = 0; i < D / 16; ++i) {
+          for (int i = 0; i < (kF8 ? D / 32 : D / 16); ++i) {  // 32 bytes of the head dimension per MMA
             const uint32_t step = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
-            if (i == 0) umma<false, false>(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk, 0u);
-            else umma_acc<false, false>(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk);
+            if (i == 0) umma<false, kF8>(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk, 0u);
+            else umma_acc<false, kF8>(d_tmem, desc64(desc_hi, qa + step), desc64(desc_hi, ka + step), idesc_qk);
           }
           tc_commit(smem_u32(&ctl->s_full[t]));
         }
         __syncwarp();
       };
       auto issue_pv = [&](int t, uint32_t v_slot, bool accumulate) {  // O_t += P_t V : 8 MMAs of 128 x head_dim x 16
-        const uint32_t pa = lo_of(p_addr0 + t * kPBytes) | kmajor_lbo;
-        const uint32_t va = lo_of(kv_addr0 + v_slot * tile_bytes) | v_lbo;
+        const uint32_t pa = lo_of(p_addr0 + t * p_bytes) | kmajor_lbo;
+        const uint32_t va = lo_of(kv_addr0 + v_slot * tile_bytes) | (kF8 ? kmajor_lbo : v_lbo);
         const uint32_t d_tmem = tmem_base + 256u + static_cast<uint32_t>(t) * 128u;
-        if (issuer) {
+        if (issuer && kF8) {
+          // P (128 rows x 128 KV bytes) and V^T (D rows x 128 KV bytes) are both K-major: 4 MMAs of 32 KV bytes
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t step = static_cast<uint32_t>(i) * 2u;
+            if (i == 0) umma<false, true>(d_tmem, desc64(desc_hi, pa + step), desc64(desc_hi, va + step), idesc_pv, accumulate ? 1u : 0u);
+            else umma_acc<false, true>(d_tmem, desc64(desc_hi, pa + step), desc64(desc_hi, va + step), idesc_pv);
+          }
+          tc_commit(smem_u32(&ctl->o_done[t]));
+        } else if (issuer) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const uint32_t pstep = static_cast<uint32_t>(i >> 2) * (kAtomBytes >> 4) + static_cast<uint32_t>(i & 3) * 2u;
@@ -414,7 +451,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t s_tmem = lane_base + static_cast<uint32_t>(t) * 128u;
     const uint32_t o_tmem = lane_base + 256u + static_cast<uint32_t>(t) * 128u;
-    const uint32_t p_tile = p_addr0 + t * kPBytes;
+    const uint32_t p_tile = p_addr0 + t * p_bytes;
     const uint32_t p_row = p_tile + static_cast<uint32_t>((row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128);
     const int row_xor = row_in_tile & 7;
     const int lim = p.causal ? min(row, p.n_ctx - 1) : p.n_ctx - 1;  // last column this row may attend to
@@ -467,8 +504,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           tmem_st_wait();
         }
       }
-      const float sum = masked ? row_block_exp_store<true, kBf16>(s, p.qk_scale, -m_new, col0, lim, p_row, row_xor)
-                               : row_block_exp_store<false, kBf16>(s, p.qk_scale, -m_new, col0, lim, p_row, row_xor);
+      const float sum = masked ? row_block_exp_store<true, kElt>(s, p.qk_scale, -m_new, col0, lim, p_row, row_xor)
+                               : row_block_exp_store<false, kElt>(s, p.qk_scale, -m_new, col0, lim, p_row, row_xor);
       l_i = l_i * alpha + sum;
       m_i = m_new;
       fence_proxy_async();  // P is read by the tensor core through the async proxy
@@ -481,6 +518,25 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       if (ok) {
         tc_fence_after();
         const float inv_l = 1.0f / l_i;
+        if (kF8) {
+          // O / l as e5m2, 32 columns = 32 bytes at a time, straight from this thread's registers to its row
+          uint8_t *o_row = static_cast<uint8_t *>(p.out) + (static_cast<long long>(head) * p.n_ctx + row) * p.head_dim;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_tmem + c * 32, o);
+            tmem_ld_wait();
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              w[i] = pack_e5m2x4(__uint_as_float(o[4 * i]) * inv_l, __uint_as_float(o[4 * i + 1]) * inv_l,
+                                 __uint_as_float(o[4 * i + 2]) * inv_l, __uint_as_float(o[4 * i + 3]) * inv_l);
+            if (row < p.n_ctx) {
+              if (c * 32 < p.head_dim) *reinterpret_cast<uint4 *>(o_row + c * 32) = make_uint4(w[0], w[1], w[2], w[3]);
+              if (c * 32 + 16 < p.head_dim) *reinterpret_cast<uint4 *>(o_row + c * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+          }
+        } else {
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
@@ -492,7 +548,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              w[i] = pack_pair<kBf16>(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l);
+              w[i] = pack_pair<kElt>(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l);
             st_shared_v4(p_tile + (c >> 1) * kAtomBytes + swz_off(row_in_tile, (c & 1) * 4 + q), w[0], w[1], w[2], w[3]);
           }
         }
@@ -506,6 +562,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           bulk_wait_group_all();
         }
         __syncwarp();
+        }
         if (row < p.n_ctx) p.m_out[static_cast<long long>(head) * p.n_ctx + row] = m_i + log2f(l_i);
       }
     }

@@ -71,14 +71,31 @@ int encode_head_map(CUtensorMap *map, const void *ptr, bool bf16, long long head
   return TXD_OK;
 }
 
+// The fp8 form's operands as byte tensors. Q and K: [batch*heads, n_ctx, head_dim] e5m2, a box is one 128-byte span
+// x 128 rows (columns past head_dim are out of bounds and arrive as zeros). V: [batch*heads, head_dim, n_ctx]
+// (transposed, as the reference lays V out for fp8), a box is 128 KV bytes x box_rows head-dimension rows.
+int encode_byte_map(CUtensorMap *map, const void *ptr, long long heads_total, long long rows, long long cols, int box_rows) {
+  EncodeTiledFn enc = attn_encode_fn();
+  if (!enc) return afail(TXD_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads_total)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows) * cols};
+  cuuint32_t box[3] = {128, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return afail(TXD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+  return TXD_OK;
+}
+
 // Head dimension the kernels are instantiated for. 16 and 32 run on the 64-wide kernels: the tensor maps describe
 // the real tensors, every TMA box is 64 columns wide, and the columns past head_dim arrive as zeros (out-of-bounds
 // fill) and are clipped from TMA stores. Zero columns of Q and K add nothing to Q K^T, zero columns of V and dO give
 // zero columns of O, dQ, dK and dV that are never written.
 int kernel_head_dim(int head_dim) { return head_dim <= 64 ? 64 : 128; }
 
-uint32_t attn_idesc(bool bf16, bool b_mn_major, int n) {
-  const uint32_t fmt = bf16 ? 1u : 0u;
+// `fmt`: kind::f16 0 = f16, 1 = bf16; kind::f8f6f4 1 = e5m2
+uint32_t attn_idesc(uint32_t fmt, bool b_mn_major, int n) {
   uint32_t d = 0;
   d |= 1u << 4;    // fp32 accumulator
   d |= fmt << 7;   // A type
@@ -135,10 +152,12 @@ int device_state(DeviceState **out) {
     TXA_CUDA(cudaMemset(st.status, 0, sizeof(uint32_t)));
   }
   if (!st.attr_set) {
-    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<0, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<0, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<1, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<1, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<2, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TXA_CUDA(cudaFuncSetAttribute(txa::attn_fwd_kernel<2, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TXA_CUDA(cudaFuncSetAttribute(txa::attn_bwd_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -156,7 +175,13 @@ int validate(const tx_attn_problem *pr) {
   if (pr->batch < 1 || pr->heads < 1 || pr->n_ctx < 1) return afail(TXD_ERR_INVALID, "batch, heads and n_ctx must be >= 1");
   if (pr->head_dim != 16 && pr->head_dim != 32 && pr->head_dim != 64 && pr->head_dim != 128 && pr->head_dim != 256)
     return afail(TXD_ERR_UNSUPPORTED, "head_dim %d: the reference's 16, 32, 64, 128 and 256 are built", pr->head_dim);
-  if (pr->dtype != TXD_F16 && pr->dtype != TXD_BF16) return afail(TXD_ERR_UNSUPPORTED, "dtype must be f16 or bf16");
+  if (pr->dtype != TXD_F16 && pr->dtype != TXD_BF16 && pr->dtype != TXD_F8E5M2)
+    return afail(TXD_ERR_UNSUPPORTED, "dtype must be f16, bf16 or (forward only) f8e5m2");
+  if (pr->dtype == TXD_F8E5M2) {
+    if (pr->head_dim == 256) return afail(TXD_ERR_UNSUPPORTED, "head_dim 256 is built for f16 and bf16 only");
+    if (pr->n_ctx % 16 != 0)
+      return afail(TXD_ERR_UNSUPPORTED, "f8e5m2: n_ctx %d must be a multiple of 16 (rows of the transposed V are TMA strides)", pr->n_ctx);
+  }
   if (!(pr->sm_scale > 0.f)) return afail(TXD_ERR_INVALID, "sm_scale must be positive");
   if (static_cast<long long>(pr->batch) * pr->heads > 0x7fffffffLL / ((pr->n_ctx + 255) / 256))
     return afail(TXD_ERR_UNSUPPORTED, "too many (head, query tile) pairs for one grid");
@@ -522,12 +547,21 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   rc = device_state(&st);
   if (rc) return rc;
   const bool bf16 = pr->dtype == TXD_BF16;
+  const bool f8 = pr->dtype == TXD_F8E5M2;
   const long long heads_total = static_cast<long long>(pr->batch) * pr->heads;
+  const int kd = kernel_head_dim(pr->head_dim);
   txa::AttnParams prm = {};
-  if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
-  if ((rc = encode_head_map(&prm.tmap_o, out, bf16, heads_total, pr->n_ctx, pr->head_dim, 32))) return rc;
+  if (f8) {
+    if ((rc = encode_byte_map(&prm.tmap_q, q, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+    if ((rc = encode_byte_map(&prm.tmap_k, k, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+    if ((rc = encode_byte_map(&prm.tmap_v, v, heads_total, pr->head_dim, pr->n_ctx, kd))) return rc;
+    prm.out = out;
+  } else {
+    if ((rc = encode_head_map(&prm.tmap_q, q, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+    if ((rc = encode_head_map(&prm.tmap_k, k, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+    if ((rc = encode_head_map(&prm.tmap_v, v, bf16, heads_total, pr->n_ctx, pr->head_dim, 128))) return rc;
+    if ((rc = encode_head_map(&prm.tmap_o, out, bf16, heads_total, pr->n_ctx, pr->head_dim, 32))) return rc;
+  }
   prm.m_out = m;
   prm.status = st->status;
   prm.wait_limit_ns = 2000ull * 1000 * 1000;
@@ -543,7 +577,7 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   prm.q_tiles = (pr->n_ctx + 255) / 256;
   {
     // heads whose K and V (2 tensors x n_ctx x head_dim x 2 bytes each) fit in 48 MB of the 126 MB L2 together
-    const long long kv_bytes = 4LL * pr->n_ctx * pr->head_dim;
+    const long long kv_bytes = (f8 ? 2LL : 4LL) * pr->n_ctx * pr->head_dim;
     long long grp = (48LL << 20) / (kv_bytes > 0 ? kv_bytes : 1);
     if (grp < 1) grp = 1;
     if (grp > heads_total) grp = heads_total;
@@ -553,10 +587,9 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
   }
   prm.causal = pr->causal ? 1 : 0;
   prm.is_bf16 = bf16 ? 1 : 0;
-  const int kd = kernel_head_dim(pr->head_dim);
-  prm.kv_stages = kd == 128 ? 3 : 6;  // what the kernel templates use; shared memory is sized from it
-  prm.idesc_qk = attn_idesc(bf16, false, 128);
-  prm.idesc_pv = attn_idesc(bf16, true, kd);
+  prm.kv_stages = (kd == 128 && !f8) ? 3 : 6;  // what the kernel templates use; shared memory is sized from it
+  prm.idesc_qk = attn_idesc(f8 || bf16 ? 1u : 0u, false, 128);
+  prm.idesc_pv = attn_idesc(f8 || bf16 ? 1u : 0u, !f8, kd);  // fp8: V arrives transposed, K-major
   if (!m) {
     // the kernel always writes M; give it a scratch row vector when the caller does not want it
     std::lock_guard<std::mutex> lock(g_state_mutex);
@@ -578,14 +611,17 @@ int tx_attn_fwd(const tx_attn_problem *pr, const void *q, const void *k, const v
     return attn_fwd_composed<__half>(pr, st, static_cast<const __half *>(q), static_cast<const __half *>(k),
                                      static_cast<const __half *>(v), static_cast<__half *>(out), prm.m_out, cs);
   }
-  const size_t tile_bytes = static_cast<size_t>(128) * kd * 2;
-  const size_t smem = 2 * tile_bytes + 2 * txa::kPBytes + prm.kv_stages * tile_bytes + sizeof(txa::AttnCtl) + 1024;
+  const size_t tile_bytes = f8 ? static_cast<size_t>(txa::kAtomBytes) : static_cast<size_t>(128) * kd * 2;
+  const size_t p_bytes = f8 ? static_cast<size_t>(txa::kAtomBytes) : static_cast<size_t>(txa::kPBytes);
+  const size_t smem = 2 * tile_bytes + 2 * p_bytes + prm.kv_stages * tile_bytes + sizeof(txa::AttnCtl) + 1024;
   const unsigned grid = static_cast<unsigned>(heads_total * prm.q_tiles);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (bf16 && kd == 64) txa::attn_fwd_kernel<true, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
-  else if (bf16) txa::attn_fwd_kernel<true, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
-  else if (kd == 64) txa::attn_fwd_kernel<false, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
-  else txa::attn_fwd_kernel<false, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  if (f8 && kd == 64) txa::attn_fwd_kernel<2, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else if (f8) txa::attn_fwd_kernel<2, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else if (bf16 && kd == 64) txa::attn_fwd_kernel<1, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else if (bf16) txa::attn_fwd_kernel<1, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else if (kd == 64) txa::attn_fwd_kernel<0, 64><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
+  else txa::attn_fwd_kernel<0, 128><<<grid, txa::kAttnThreads, smem, stream>>>(prm);
   TXA_CUDA(cudaGetLastError());
   g_attn_launches.fetch_add(1);
   return TXD_OK;
@@ -615,7 +651,8 @@ int tx_attn_fwd_host(const tx_attn_problem *pr, const void *q, const void *k, co
   rc = device_state(&st);
   if (rc) return rc;
   const size_t heads_total = static_cast<size_t>(pr->batch) * pr->heads;
-  const size_t bytes = heads_total * pr->n_ctx * pr->head_dim * 2;
+  const size_t es = pr->dtype == TXD_F8E5M2 ? 1 : 2;
+  const size_t bytes = heads_total * pr->n_ctx * pr->head_dim * es;
   const size_t m_bytes = heads_total * pr->n_ctx * sizeof(float);
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);
@@ -664,7 +701,7 @@ int tx_attn_fwd_host(const tx_attn_problem *pr, const void *q, const void *k, co
       st->events_made = true;
     }
   }
-  const size_t head_bytes = static_cast<size_t>(pr->n_ctx) * pr->head_dim * 2;
+  const size_t head_bytes = static_cast<size_t>(pr->n_ctx) * pr->head_dim * es;
   const size_t head_m_bytes = static_cast<size_t>(pr->n_ctx) * sizeof(float);
   for (size_t g = 0; g < groups; ++g) {
     const size_t h0 = heads_total * g / groups, h1 = heads_total * (g + 1) / groups;
@@ -697,6 +734,8 @@ int tx_attn_bwd(const tx_attn_problem *pr, const void *q, const void *k, const v
                 const float *m, void *dq, void *dk, void *dv, void *stream_v) {
   int rc = validate(pr);
   if (rc) return rc;
+  if (pr->dtype == TXD_F8E5M2)
+    return afail(TXD_ERR_UNSUPPORTED, "the backward takes f16 or bf16 (the reference's backward has no fp8 form)");
   if (!q || !k || !v || !o || !d_o || !m || !dq || !dk || !dv) return afail(TXD_ERR_INVALID, "null tensor pointer");
   DeviceState *st = nullptr;
   rc = device_state(&st);
