@@ -4,7 +4,7 @@
  * reference's demo kernel: `_attn_fwd[grid](q, k, v, sm_scale, M, o, strides..., Z, H, N_CTX, HEAD_DIM,
  * BLOCK_M, BLOCK_N, CAUSAL)` in pass/LoopSplit/06-fused-attention.py:626-637 (kernel :164-240, inner loop
  * :43-90). Same operands and results: q, k, v, out are contiguous [batch, heads, n_ctx, head_dim] tensors
- * of one 16-bit type; `m` receives, per query row, running max + log2(sum) in base 2 (:236,:239), which
+ * of one 16-bit type (or float8_e5m2, see `dtype` below); `m` receives, per query row, running max + log2(sum) in base 2 (:236,:239), which
  * the reference keeps for its backward pass.
  *
  * Plain pointers and sizes only; every function returns a tx_dot_status code (b200_dot.h) and
@@ -28,7 +28,11 @@ typedef struct tx_attn_problem {
   int32_t head_dim;     /* 16, 32, 64, 128 or 256 (the reference's list, :589). 64 and 128: fused     */
                         /* kernels; 16 and 32: the 64-wide kernels, zero-filled; 256: a composition of */
                         /* the tt.dot GEMM kernels around a row softmax (slow)                         */
-  int32_t dtype;        /* TXD_F16 or TXD_BF16 for q, k, v and out                                   */
+  int32_t dtype;        /* TXD_F16 or TXD_BF16 for q, k, v and out; TXD_F8E5M2 for the forward only    */
+                        /* (the reference's fp8 path, :81-82, :191, :774-779): q, k, out as above in    */
+                        /* e5m2, v stored [batch, heads, head_dim, n_ctx] (n_ctx contiguous, as the      */
+                        /* reference lays it out for fp8), P and out rounded to e5m2 (nearest even);     */
+                        /* head_dim 16, 32, 64 or 128, n_ctx a multiple of 16                            */
   int32_t causal;       /* 0 / 1                                                                     */
   float sm_scale;       /* > 0; scores are scaled by sm_scale * log2(e) and exponentiated in base 2   */
   int32_t reserved[5];  /* zero                                                                      */
