@@ -827,8 +827,9 @@ def exchange_phases(ctx: Ctx, fused_op, sets, n_sets, slot_dt, m, n) -> dict:
     copy_gbs = src.numel() * es / copy_ms / 1e6
     gemm_ms = med[1]
     return {"pieces": fused_op.parts,
-            "note": "phases timed with the exchange in one piece, one after the other; the timed steps run it in `pieces` "
-                    "pieces with each piece's slot reduction on a second stream under the next piece's GEMM",
+            "note": ("phases timed with the exchange in one piece, one after the other"
+                     + ("; the timed steps run it in `pieces` pieces with each piece's slot reduction on a second stream "
+                        "under the next piece's GEMM" if fused_op.parts > 1 else "")),
             "phase_ms": {"barrier_before": med[0], "gemm_with_remote_stores": med[1], "barrier_after": med[2], "slot_reduction": med[3]},
             "bytes_sent_per_rank": int(sent), "nvlink_gbs_during_gemm": sent / gemm_ms / 1e6,
             "peer_copy_gbs_same_run": copy_gbs, "frac_of_peer_copy": (sent / gemm_ms / 1e6) / copy_gbs}
