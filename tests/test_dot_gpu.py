@@ -380,6 +380,32 @@ def test_slot_stores_and_reduction_single_gpu(B, dot_lib, partial_dtype):
     plan.close()
 
 
+@pytest.mark.parametrize("world,rows,n", [(3, 37, 1001), (2, 5, 7), (4, 64, 1004), (8, 33, 520), (8, 256, 4096)])
+@pytest.mark.parametrize("slot_dtype", [f32, bf16])
+def test_slot_reduction_shapes(B, world, rows, n, slot_dtype):
+    """The slot sum on its own: any slot count, ragged and vector-width row lengths, every output type, a padded
+    output; summed in slot order in fp32 (bit-exact against the same sum written with torch for fp32 output)."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(world * 1000 + n)
+    slots = torch.randn(world, rows, n, generator=g).to(slot_dtype).to(dev)
+    rs = (torch.rand(rows, generator=g) + 0.5).to(dev)
+    cs = (torch.rand(n, generator=g) + 0.5).to(dev)
+    acc = torch.zeros(rows, n, device=dev)
+    for s in range(world):
+        acc = acc + slots[s].float()
+    for out_dtype in (f32, bf16, f16):
+        padded = torch.full((rows, n + 3), 7.0, device=dev, dtype=out_dtype)
+        out = padded[:, :n]
+        B.reduce_slots(slots, out, row_scale=rs, col_scale=cs, alpha=0.5)
+        torch.cuda.synchronize()
+        want = (acc * (rs * 0.5)[:, None] * cs[None, :])
+        if out_dtype == f32:
+            assert torch.equal(out, want)
+        else:
+            assert torch.equal(out, want.to(out_dtype))
+        assert bool((padded[:, n:] == 7.0).all())
+
+
 def test_slot_exchange_in_pieces_single_gpu(B):
     """The exchange cut into pieces: piece j of every rank fills rows [j, j + 1) * rows / parts of its slot in every
     owner's buffer and nothing else, all pieces together give the slots of the one-piece form bit for bit, and the

@@ -235,47 +235,92 @@ struct RemoteTarget {
 int launch_dot(tx_dot_plan *pl, const void *a, const void *b, void *c, const float *row_scale, const float *col_scale,
                void *stream_v, const RemoteTarget *remote);
 
-__global__ void reduce_slots_kernel(const void *slots, int world, long long slot_elems, long long rows, long long n,
-                                    int slot_f32, void *out, int out_dtype, long long ldc, const float *row_scale,
-                                    const float *col_scale, float alpha) {
-  // One thread per 4 consecutive columns; slots (slot_elems apart) are summed in slot order in fp32.
-  const long long groups = (n + 3) / 4;
+// One thread per 16 bytes of a slot row (4 fp32 or 8 bf16 columns); slots (slot_elems apart) are summed in slot order in
+// fp32. kWorld > 0: the slot count is a compile-time constant, so that all `world` loads of a thread are in flight before
+// the first add (the sum is HBM-bound: bytes in flight per SM are what sets its rate); kWorld == 0: any count.
+template <int kWorld, bool kF32Slots>
+__global__ void __launch_bounds__(256) reduce_slots_kernel(const void *slots, int world_rt, long long slot_elems, long long rows,
+                                                           long long n, void *out, int out_dtype, long long ldc,
+                                                           const float *row_scale, const float *col_scale, float alpha) {
+  constexpr int kCols = kF32Slots ? 4 : 8;
+  constexpr int kMaxWorld = kWorld > 0 ? kWorld : 1;
+  const int world = kWorld > 0 ? kWorld : world_rt;
+  const long long groups = (n + kCols - 1) / kCols;
   const long long total = rows * groups;
+  const bool rows_vec = n % kCols == 0;  // every group is whole and 16-byte aligned inside its slot
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / groups, c0 = (i - r * groups) * 4;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool vec = (c0 + 4 <= n) && (n % 4 == 0);
-    for (int s = 0; s < world; ++s) {
-      const long long off = s * slot_elems + r * n + c0;
-      if (slot_f32) {
-        const float *src = static_cast<const float *>(slots) + off;
-        if (vec) {
-          const float4 v = __ldcs(reinterpret_cast<const float4 *>(src));
-          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
-        } else {
-          for (int j = 0; j < 4 && c0 + j < n; ++j) acc[j] += src[j];
-        }
+    const long long r = i / groups, c0 = (i - r * groups) * kCols;
+    float acc[kCols];
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+    auto add = [&](const uint4 &v) {
+      if (kF32Slots) {
+        acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
+        acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
       } else {
-        const __nv_bfloat16 *src = static_cast<const __nv_bfloat16 *>(slots) + off;
-        if (vec) {
-          const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(src));
-          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&v.x);
-          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&v.y);
-          acc[0] += __low2float(lo); acc[1] += __high2float(lo); acc[2] += __low2float(hi); acc[3] += __high2float(hi);
-        } else {
-          for (int j = 0; j < 4 && c0 + j < n; ++j) acc[j] += __bfloat162float(src[j]);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&w[q]);
+          acc[(2 * q) % kCols] += __low2float(h);
+          acc[(2 * q + 1) % kCols] += __high2float(h);
         }
       }
+    };
+    const size_t es = kF32Slots ? 4 : 2;
+    const char *base = static_cast<const char *>(slots) + static_cast<size_t>(r * n + c0) * es;
+    if (rows_vec && kWorld > 0) {
+      uint4 v[kMaxWorld];
+#pragma unroll
+      for (int s = 0; s < kMaxWorld; ++s)
+        v[s] = __ldcs(reinterpret_cast<const uint4 *>(base + static_cast<size_t>(s) * slot_elems * es));
+#pragma unroll
+      for (int s = 0; s < kMaxWorld; ++s) add(v[s]);
+    } else if (rows_vec) {
+      for (int s = 0; s < world; ++s) add(__ldcs(reinterpret_cast<const uint4 *>(base + static_cast<size_t>(s) * slot_elems * es)));
+    } else {
+      for (int s = 0; s < world; ++s)
+        for (int j = 0; j < kCols && c0 + j < n; ++j) {
+          const char *e = base + (static_cast<size_t>(s) * slot_elems + j) * es;
+          acc[j] += kF32Slots ? *reinterpret_cast<const float *>(e) : __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(e));
+        }
     }
     const float rs = (row_scale ? row_scale[r] : 1.0f) * alpha;
-    for (int j = 0; j < 4 && c0 + j < n; ++j) {
-      const float v = acc[j] * rs * (col_scale ? col_scale[c0 + j] : 1.0f);
-      const long long o = r * ldc + c0 + j;
-      if (out_dtype == TXD_F32) static_cast<float *>(out)[o] = v;
-      else if (out_dtype == TXD_BF16) static_cast<__nv_bfloat16 *>(out)[o] = __float2bfloat16_rn(v);
-      else static_cast<__half *>(out)[o] = __float2half_rn(v);
+    float o[kCols];
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) o[j] = acc[j] * rs * ((col_scale && c0 + j < n) ? col_scale[c0 + j] : 1.0f);
+    if (rows_vec && out_dtype == TXD_BF16) {
+      __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(out) + r * ldc + c0;
+      if ((reinterpret_cast<uintptr_t>(dst) & (kCols * 2 - 1)) == 0) {
+        uint32_t w[kCols / 2];
+#pragma unroll
+        for (int q = 0; q < kCols / 2; ++q) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
+          w[q] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        if (kCols == 8) *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2 % (kCols / 2)], w[3 % (kCols / 2)]);
+        else *reinterpret_cast<uint2 *>(dst) = make_uint2(w[0], w[1]);
+        continue;
+      }
     }
+    for (int j = 0; j < kCols && c0 + j < n; ++j) {
+      const long long at = r * ldc + c0 + j;
+      if (out_dtype == TXD_F32) static_cast<float *>(out)[at] = o[j];
+      else if (out_dtype == TXD_BF16) static_cast<__nv_bfloat16 *>(out)[at] = __float2bfloat16_rn(o[j]);
+      else static_cast<__half *>(out)[at] = __float2half_rn(o[j]);
+    }
+  }
+}
+
+template <bool kF32Slots>
+void (*pick_reduce_kernel(int world))(const void *, int, long long, long long, long long, void *, int, long long, const float *,
+                                      const float *, float) {
+  switch (world) {
+    case 2: return reduce_slots_kernel<2, kF32Slots>;
+    case 4: return reduce_slots_kernel<4, kF32Slots>;
+    case 8: return reduce_slots_kernel<8, kF32Slots>;
+    default: return reduce_slots_kernel<0, kF32Slots>;
   }
 }
 }  // namespace
@@ -331,16 +376,18 @@ int tx_dot_reduce_slots_part(const void *slots, int32_t world, int32_t rows_per_
   if (slot_dtype != TXD_F32 && slot_dtype != TXD_BF16) return fail(TXD_ERR_UNSUPPORTED, "slots are f32 or bf16");
   if (out_dtype != TXD_F32 && out_dtype != TXD_BF16 && out_dtype != TXD_F16) return fail(TXD_ERR_UNSUPPORTED, "output dtype must be f16, bf16 or f32");
   if (rows == 0 || n == 0) return TXD_OK;
-  const long long total = static_cast<long long>(rows) * ((n + 3) / 4);
+  const bool f32_slots = slot_dtype == TXD_F32;
+  const int cols = f32_slots ? 4 : 8;
+  const long long total = static_cast<long long>(rows) * ((n + cols - 1) / cols);
   const int threads = 256;
   const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148LL * 16));
-  const size_t slot_es = slot_dtype == TXD_F32 ? 4 : 2;
+  const size_t slot_es = f32_slots ? 4 : 2;
   const size_t out_es = out_dtype == TXD_F32 ? 4 : 2;
-  reduce_slots_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
+  auto kernel = f32_slots ? pick_reduce_kernel<true>(world) : pick_reduce_kernel<false>(world);
+  kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
       static_cast<const char *>(slots) + static_cast<size_t>(row0) * n * slot_es, world,
-      static_cast<long long>(rows_per_rank) * n, rows, n, slot_dtype == TXD_F32 ? 1 : 0,
-      static_cast<char *>(out) + static_cast<size_t>(row0) * ldc * out_es, out_dtype, ldc,
-      row_scale ? row_scale + row0 : nullptr, col_scale, alpha);
+      static_cast<long long>(rows_per_rank) * n, rows, n, static_cast<char *>(out) + static_cast<size_t>(row0) * ldc * out_es,
+      out_dtype, ldc, row_scale ? row_scale + row0 : nullptr, col_scale, alpha);
   TXD_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return TXD_OK;
