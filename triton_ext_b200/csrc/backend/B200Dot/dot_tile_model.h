@@ -304,6 +304,11 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
   out.tma_store = (!out.swap_ab && out.block_n >= 64 && (pr.ldc * os) % 16 == 0) ? 1 : 0;  // whole 128-byte slabs
   const int staging = out.tma_store ? 4 * 2 * 32 * 128 /* two 4 KiB staging slabs per epilogue warp */ : 0;
   int stages = cfg.stages ? cfg.stages : std::min(12, (mm.smem_budget - staging) / stage_bytes);
+  // A ring above 200 KiB was measured slower than one stage less (bf16 16 x 14336 x 4096, 36 KiB stages: six stages
+  // 23.1 us, five and four 22.1 us; 16 x 4096 x 14336: 30.5 against 30.2 us), while rings of 192-200 KiB are the best of
+  // their shapes (five 40 KiB stages at m = 32 and m = 64, three 64 KiB stages for the tensor-bound pairs).
+  if (!cfg.stages)
+    while (stages > 3 && stages * stage_bytes > 200 * 1024) --stages;
   if (stages < 2 || stages > 12 || stages * stage_bytes + staging > mm.smem_budget) {
     if (why) *why = "stages out of range for this tile (2..12, ring must fit shared memory)";
     return -1;
