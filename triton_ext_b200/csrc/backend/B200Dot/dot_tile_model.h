@@ -223,7 +223,13 @@ inline int select_tiles(const tx_dot_problem &pr, const tx_dot_config *cfg_in, c
           if (units < 1) units = 1;
           const int max_workers = pair ? max_grid / 2 : max_grid;
           if (max_workers < 1) continue;
-          const int workers = (int)std::min<long long>(max_workers, units);
+          int workers = (int)std::min<long long>(max_workers, units);
+          // HBM-bound whole tiles: as many workers as give every one the same number of tiles. A worker streams at its
+          // own SM's rate, so a last round in which half of them have no tile left runs at half the bandwidth
+          // (bf16 16 x 28672 x 8192, 224 tiles: 148 workers 77.8 us, 112 workers 71.8 us). Tensor-bound shapes measured
+          // no better with the smaller grid (4096 x 4096 x 4160: 110 against 99.5 us), so they keep every SM.
+          if (out.hbm_bound && sched == TXD_SCHED_DATA_PARALLEL && tiles > workers)
+            workers = cdiv(tiles, cdiv(tiles, workers));
           if (sched == TXD_SCHED_HYBRID) {
             // Needs at least one full wave, a partial last wave, and a K block for every worker in it.
             const int tail = tiles % workers;
