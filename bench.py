@@ -595,7 +595,7 @@ def run_dot_workload(ctx: Ctx, args, name: str, w: dict, headline: bool) -> dict
         if w["dtype"] == "fp8":
             f8 = None if args.kernel_only else fp8_peak(ctx)
             if f8:
-                peak, peak_src = f8["burst_tflops"], "torch._scaled_mm e4m3 8192^3 (tensor-wide scales) measured in this run, best of 10"
+                peak, peak_src = f8["burst_tflops"], "torch._scaled_mm e4m3 8192^3 (tensor-wide scales) measured in this run: best of 10 single launches and a 20-launch window after an idle second"
                 speak, speak_src = f8["sustained_tflops"], "torch._scaled_mm e4m3 8192^3 measured in this run, 2 s back to back"
             else:
                 peak, peak_src = 2 * peak, peak_src + " x2 for fp8 (torch._scaled_mm unavailable)"
@@ -752,8 +752,10 @@ _FP8_PEAK = {}
 
 
 def fp8_peak(ctx: Ctx):
-    """Dense e4m3 throughput of the library GEMM on this GPU: torch._scaled_mm 8192^3 with tensor-wide unit scales,
-    best of 10 single launches (burst) and two seconds back to back (sustained)."""
+    """Dense e4m3 throughput of the library GEMM on this GPU: torch._scaled_mm 8192^3 with tensor-wide unit scales.
+    Burst: the better of 10 single launches and of a 20-launch window after an idle second and five warm-up launches
+    (the regime of this bench's own first window: on a box that has just run the sustained loops, single launches
+    with a synchronise after each were measured 15 % below that window). Sustained: two seconds back to back."""
     if "v" in _FP8_PEAK:
         return _FP8_PEAK["v"]
     torch = ctx.torch
@@ -777,6 +779,16 @@ def fp8_peak(ctx: Ctx):
             e1.record()
             torch.cuda.synchronize(ctx.dev)
             best = min(best, e0.elapsed_time(e1))
+        time.sleep(1.0)
+        for _ in range(5):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            run()
+        e1.record()
+        torch.cuda.synchronize(ctx.dev)
+        best = min(best, e0.elapsed_time(e1) / 20)
         iters = int(math.ceil(2000.0 / best))
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for _ in range(iters // 2):
