@@ -336,14 +336,14 @@ def test_bounded_wait_reports_timeout(B, monkeypatch):
 
 
 # ---- 8. K-sharded GEMM with the exchange in its epilogue, emulated on one GPU ----------------------------------
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("partial_dtype", [f32, bf16])
-def test_slot_stores_and_reduction_single_gpu(B, dot_lib, partial_dtype):
-    """Two "ranks" share one GPU: each runs its K shard and stores tiles into its slot of the owner's buffer
-    (both buffers are local here, on a real job they are peer-mapped); the slot reduction then gives each
+def test_slot_stores_and_reduction_single_gpu(B, dot_lib, partial_dtype, world):
+    """`world` "ranks" share one GPU: each runs its K shard and stores tiles into its slot of the owner's buffer
+    (all buffers are local here, on a real job they are peer-mapped); the slot reduction then gives each
     owner its rows of C. The kernels run one after the other, never waiting on one another."""
     dev = torch.device("cuda:0")
-    world = 2
-    case = Case("kshard", 512, 384, 1152, bf16, bf16, seed=61, scales=True, block=(64, 64, 64))
+    case = Case("kshard", 256 * world, 384, 1152, bf16, bf16, seed=61, scales=True, block=(64, 64, 64))
     a, b, rs, cs = make_inputs(case)
     ad, bd, rsd, csd = a.to(dev), b.to(dev), rs.to(dev), cs.to(dev)
     rows = case.m // world
