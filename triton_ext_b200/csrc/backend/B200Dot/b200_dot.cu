@@ -255,16 +255,16 @@ __global__ void __launch_bounds__(256) reduce_slots_kernel(const void *slots, in
 #pragma unroll
     for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
     auto add = [&](const uint4 &v) {
-      if (kF32Slots) {
-        acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
-        acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      if constexpr (kF32Slots) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += __uint_as_float(w[q]);
       } else {
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&w[q]);
-          acc[(2 * q) % kCols] += __low2float(h);
-          acc[(2 * q + 1) % kCols] += __high2float(h);
+          acc[2 * q] += __low2float(h);
+          acc[2 * q + 1] += __high2float(h);
         }
       }
     };
@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(256) reduce_slots_kernel(const void *slots, in
           __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
           w[q] = *reinterpret_cast<uint32_t *>(&h);
         }
-        if (kCols == 8) *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2 % (kCols / 2)], w[3 % (kCols / 2)]);
+        if constexpr (kCols == 8) *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
         else *reinterpret_cast<uint2 *>(dst) = make_uint2(w[0], w[1]);
         continue;
       }
