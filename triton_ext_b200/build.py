@@ -101,6 +101,12 @@ def build_all(force: bool = False, verbose: bool = False, ptxas_verbose: bool = 
                 cmd = ["g++", *CXXFLAGS, "-shared", *defs, *incs, *srcs, *link, "-Wl,-rpath,$ORIGIN", "-o", out]
             _run(cmd, verbose or ptxas_verbose)
         built.append(out)
+    # The calibration probe of the tile model (a stand-alone program, not a library: nothing loads it).
+    probe_src = os.path.join(CSRC, "backend", "B200Dot", "calibrate", "tcgen05_issue_probe.cu")
+    probe = os.path.join(LIB, "tcgen05_issue_probe")
+    if os.path.exists(probe_src) and (force or _stale(probe, [probe_src])):
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        _run([nvcc, *NVCC_ARCH, "-O3", "-std=c++17", probe_src, "-o", probe], verbose)
     return built
 
 
