@@ -50,6 +50,22 @@ def test_decode_shape_is_swapped(built_libs):
     assert forced["grid"] == 148 and forced["scratch_bytes"] > 0
 
 
+def test_measured_rules_of_the_tile_model(built_libs):
+    """Three choices that come from measurements, not from the model's arithmetic: an operand ring of at most 200 KiB,
+    raster groups twice as tall where their P panels then still fit 32 MiB of L2, and an evenly dividing grid for
+    HBM-bound whole-tile schedules."""
+    cfg3 = B.preview(B.make_problem(16, 14336, 4096, bf16, bf16))
+    assert cfg3["stages"] == 5 and cfg3["stages"] * 36 * 1024 <= 200 * 1024 < 6 * 36 * 1024
+    assert B.preview(B.make_problem(16, 14336, 4096, bf16, bf16), B.make_config(stages=6))["stages"] == 6   # a request is honoured
+    cfg4 = B.preview(B.make_problem(8192, 8192, 8192, f8, bf16))
+    assert cfg4["group_m"] == 16          # 16 x 256 rows x 8192 bytes = 32 MiB
+    cfg5 = B.preview(B.make_problem(16384, 28672, 8192, bf16, bf16))
+    assert cfg5["group_m"] == 8 and cfg5["grid"] == 148      # 8 rows already hold 32 MiB; tensor-bound keeps every SM
+    skinny = B.preview(B.make_problem(16, 28672, 8192, bf16, bf16))
+    assert skinny["schedule"] == B.TXD_SCHED_DATA_PARALLEL and skinny["grid"] == 112      # 224 tiles = 2 x 112
+    assert B.preview(B.make_problem(16, 28672, 8192, bf16, bf16), B.make_config(group_m=4))["group_m"] == 4
+
+
 def test_split_point_fields(built_libs):
     info = B.preview(B.make_problem(4096, 4096, 4160, bf16, bf16), B.make_config(atoms=1))
     assert (info["k_main_iters"], info["k_tail_iters"], info["k_tail_mmas"]) == (65, 0, 4)
