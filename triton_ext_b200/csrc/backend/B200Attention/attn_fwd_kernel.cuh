@@ -13,10 +13,11 @@
 //                     (tcgen05.ld / tcgen05.st) only when the running max moved by more than 2^8, final
 //                     O / l and TMA store
 //   warp 8          : TMA producer (Q once; K0, K1, V0, K2, V1, ... through the ring)
-//   warp 9          : tcgen05.mma issuer. Per KV block j: S_t(j+1) = Q_t K_{j+1}^T for both sub-tiles as soon
-//                     as their S_t(j) has been read, K_{j+1} released; then O_t += P_t(j) V_j as each P_t(j)
-//                     is complete, V_j released. The tensor pipe works on one sub-tile while the other one
-//                     is in its softmax.
+//   warp 9          : tcgen05.mma issuer. Per KV block j and sub-tile t in turn: S_t(j+1) = Q_t K_{j+1}^T as soon
+//                     as S_t(j) has been read, then O_t += P_t(j) V_j as soon as P_t(j) is complete; K_{j+1} is
+//                     released after the second S, V_j after the second O update. Serving the sub-tiles in turn
+//                     holds their softmax warpgroups half a block apart, so that one is in its exponentials
+//                     while the tensor pipe and the other warpgroup's loads and row maxima run.
 //
 // Barriers wait by polling mbarrier.test_wait (mbarrier.try_wait was measured to return hundreds of cycles
 // late even for phases completed long before, and every hop of this pipeline is on the critical path).
@@ -394,16 +395,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           if (n_blk[t] > 0) issue_qk(t, k_slot);
         release(k_slot);
       }
-      // Order of a block's four batches of MMAs. Taking turns (kTakeTurns): per sub-tile the next S (as soon as its
-      // softmax warps hold S(j) in registers), then O_t += P_t(j) V_j (once P_t(j) is in shared memory and O_t is
-      // rescaled); sub-tile 1's next S is then issued only after sub-tile 0 has finished its block, which keeps the
-      // two softmax warpgroups half a block apart: one is in its exponentials while the other waits, loads and takes
-      // its row maxima. With both next-S dots first the warpgroups run in step, in their exponentials at the same time
-      // and idle at the same time. Measured, batch 4 x 32 heads, N_CTX 4096: HEAD_DIM 64 0.916 -> 0.820 ms, causal
-      // 0.528 -> 0.498 ms, fp8 HEAD_DIM 128 1.078 -> 1.017 ms; 16-bit HEAD_DIM 128, whose dots are twice as long and
-      // whose ring has three slots, is 3 % slower that way (1.064 -> 1.094 ms) and keeps both next-S dots first, with
-      // K_{j+1} handed back before the second dots.
-      constexpr bool kTakeTurns = kF8 || kD == 64;
+      // Order of a block's four batches of MMAs: per sub-tile the next S (as soon as its softmax warps hold S(j) in
+      // registers), then O_t += P_t(j) V_j (once P_t(j) is in shared memory and O_t is rescaled); K_{j+1} goes back to
+      // the producer as soon as both next-S dots are issued. Sub-tile 1's next S is then issued only after sub-tile 0
+      // has finished its block, which keeps the two softmax warpgroups half a block apart: one is in its exponentials
+      // while the other waits, loads and takes its row maxima. With both next-S dots first, [S0, S1, O0, O1], the
+      // warpgroups ran in step, in their exponentials at the same time and idle at the same time. Measured, batch
+      // 4 x 32 heads, N_CTX 4096: HEAD_DIM 64 0.916 -> 0.812 ms, causal 0.528 -> 0.496 ms, HEAD_DIM 128 1.064 -> 1.011 ms,
+      // causal 0.607 -> 0.587 ms, fp8 HEAD_DIM 128 1.078 -> 1.011 ms.
       for (int j = 0; ok && j < nmax; ++j) {
         const bool have_next = j + 1 < nmax;
         uint32_t kn_slot = 0;
@@ -431,20 +430,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           tc_fence_after();
           issue_pv(t, v_slot, j > 0);
         };
-        if (kTakeTurns) {
-          for (int t = 0; ok && t < 2; ++t) {
-            next_s(t);
-            if (ok) update_o(t);
-          }
-          if (!ok) break;
-          if (have_next) release(kn_slot);
-        } else {
-          for (int t = 0; ok && t < 2; ++t) next_s(t);
-          if (!ok) break;
-          if (have_next) release(kn_slot);
-          for (int t = 0; ok && t < 2; ++t) update_o(t);
-          if (!ok) break;
-        }
+        next_s(0);
+        if (ok) update_o(0);
+        if (ok) next_s(1);
+        if (!ok) break;
+        if (have_next) release(kn_slot);
+        update_o(1);
+        if (!ok) break;
         release(v_slot);
       }
       // every MMA issued above has completed before TMEM and shared memory are given back
