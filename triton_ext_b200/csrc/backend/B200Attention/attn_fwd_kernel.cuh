@@ -403,13 +403,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       // warpgroups ran in step, in their exponentials at the same time and idle at the same time. Measured, batch
       // 4 x 32 heads, N_CTX 4096: HEAD_DIM 64 0.916 -> 0.812 ms, causal 0.528 -> 0.496 ms, HEAD_DIM 128 1.064 -> 1.011 ms,
       // causal 0.607 -> 0.587 ms, fp8 HEAD_DIM 128 1.078 -> 1.011 ms.
+      // K_{j+1} is taken off the ring one block early, while the warp would otherwise wait for P_1 (a take costs this
+      // warp about 250 cycles even when the tile arrived long ago, and this warp's program paces the block).
+      uint32_t k_ahead = 0;
+      if (ok && nmax > 1) k_ahead = take();
       for (int j = 0; ok && j < nmax; ++j) {
         const bool have_next = j + 1 < nmax;
-        uint32_t kn_slot = 0;
-        if (have_next) {
-          kn_slot = take();
-          if (!ok) break;
-        }
+        const uint32_t kn_slot = k_ahead;
         const uint32_t v_slot = take();
         if (!ok) break;
         auto next_s = [&](int t) {
@@ -435,6 +435,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         if (ok) next_s(1);
         if (!ok) break;
         if (have_next) release(kn_slot);
+        if (j + 2 < nmax) {
+          k_ahead = take();
+          if (!ok) break;
+        }
         update_o(1);
         if (!ok) break;
         release(v_slot);
