@@ -405,12 +405,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       // causal 0.607 -> 0.587 ms, fp8 HEAD_DIM 128 1.078 -> 1.011 ms.
       // K_{j+1} is taken off the ring one block early, while the warp would otherwise wait for P_1 (a take costs this
       // warp about 250 cycles even when the tile arrived long ago, and this warp's program paces the block).
-      uint32_t k_ahead = 0;
+      // With six ring slots V_{j+1} is in shared memory by then as well and is taken early too; with three its copy
+      // only starts when K_{j+1} has just been handed back.
+      constexpr bool kVAhead = kStages >= 6;
+      uint32_t k_ahead = 0, v_ahead = 0;
       if (ok && nmax > 1) k_ahead = take();
+      if (ok && kVAhead) v_ahead = take();
       for (int j = 0; ok && j < nmax; ++j) {
         const bool have_next = j + 1 < nmax;
         const uint32_t kn_slot = k_ahead;
-        const uint32_t v_slot = take();
+        const uint32_t v_slot = kVAhead ? v_ahead : take();
         if (!ok) break;
         auto next_s = [&](int t) {
           if (!(have_next && j + 1 < n_blk[t])) return;
@@ -437,6 +441,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         if (have_next) release(kn_slot);
         if (j + 2 < nmax) {
           k_ahead = take();
+          if (!ok) break;
+        }
+        if (kVAhead && have_next) {
+          v_ahead = take();
           if (!ok) break;
         }
         update_o(1);
