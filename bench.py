@@ -52,7 +52,7 @@ NCU_TRAFFIC = {
     "cfg2": (107.9e6, "profiles/dot_umma_pair_kernel_cfg2_bf16_4096x4096x4160.md"),
     "cfg3": (122.0e6, "profiles/dot_umma_kernel_cfg3_bf16_16x14336x4096.md"),
     "cfg4": (365.9e6, "profiles/dot_umma_pair_f8_kernel_cfg4_fp8_8192x8192x8192.md"),
-    "attn_d64": (376.8e6, "profiles/attn_fwd_kernel_f16_batch4_heads32_nctx4096_d64.md"),
+    "attn_d64": (386.4e6, "profiles/attn_fwd_kernel_f16_batch4_heads32_nctx4096_d64.md"),
 }
 
 
