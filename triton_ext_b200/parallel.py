@@ -144,7 +144,7 @@ class FusedKShardedDot:
             raise ValueError(f"M / world = {self.rows} must be a multiple of the tile height {block_m}")
         # Pieces of the exchange: with parts > 1 the sum of piece j runs on a second stream while piece j + 1's GEMM is
         # storing. Measured on B200s (bf16 16384 x 28672 x 8192): no gain at 2 ranks (3.27 against 3.24 ms; the GEMM is
-        # power-bound there and the sum's energy comes out of the same budget) and none worth having at 4 (fp32 slots 2.61
+        # power-bound there and the sum draws on the same power limit) and none worth having at 4 (fp32 slots 2.61
         # against 2.66 ms, bf16 slots 1.73 against 1.67 ms: every piece is a launch of its own with a partial last wave
         # and a barrier) or 8 (2.79 against 2.80 ms, 1.51 against 1.49 ms), so the default is one piece.
         tile_rows = self.rows // block_m
