@@ -1016,6 +1016,27 @@ def run_attention_gpu_arm(ctx: Ctx, args, name: str, w: dict) -> dict | None:
     per_gpu_flops = attn_flops(w, w["z"])
     value = per_gpu_flops * world / (ms_per_step * 1e-3) / 1e12
 
+    # torch's fused attention (a library kernel) on the same tensors, same warm-up and window: context, never part of
+    # a timed step of this library
+    sdpa_ms = None
+    if not args.kernel_only and w["dtype"] != "fp8e5m2":
+        try:
+            import torch.nn.functional as F
+            if bwd:
+                qg, kg, vg = (t.detach().clone().requires_grad_() for t in (q, k, v))
+                o_lib = F.scaled_dot_product_attention(qg, kg, vg, is_causal=w["causal"], scale=ATTN_SM_SCALE)
+
+                def lib(i):
+                    torch.autograd.grad(o_lib, (qg, kg, vg), d_o, retain_graph=True)
+            else:
+                def lib(i):
+                    F.scaled_dot_product_attention(q, k, v, is_causal=w["causal"], scale=ATTN_SM_SCALE)
+            for i in range(args.warmup):
+                lib(i)
+            sdpa_ms = timed_window(ctx, lib, args.steps, stream) / args.steps
+        except Exception:
+            sdpa_ms = None
+
     e2e_steps = max(1, min(args.steps, 10))
     if bwd:
         oh, mh = o_fwd.cpu().pin_memory(), m_fwd.cpu().pin_memory()
@@ -1067,6 +1088,7 @@ def run_attention_gpu_arm(ctx: Ctx, args, name: str, w: dict) -> dict | None:
         "gpu_launches": int(launches),
         "clocks": clocks,
         "windows": {"n": len(sw), "median_ms_per_step": sw[len(sw) // 2], "min_ms_per_step": sw[0], "max_ms_per_step": sw[-1]},
+        "sdpa_ms": sdpa_ms,
     }
     return line if rank == 0 else None
 
